@@ -1,0 +1,123 @@
+// Shared device helpers for the sm_100a kernels of quicknn_b200.
+//
+// Conventions of every launcher in this directory:
+//   * plain C entry points, raw device pointers, an explicit cudaStream_t;
+//   * dtype codes: 0 = float32, 1 = bfloat16;
+//   * the return value is a cudaError_t cast to int (0 = launched);
+//   * sizes that a kernel cannot take are refused on the host side of the launcher
+//     with QNN_ERR_UNSUPPORTED, never computed wrongly.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+#define QNN_ERR_UNSUPPORTED 10001
+#define QNN_ERR_ARGUMENT 10002
+
+#define QNN_DT_F32 0
+#define QNN_DT_BF16 1
+
+#define QNN_API extern "C" __attribute__((visibility("default")))
+
+typedef __nv_bfloat16 bf16;
+
+namespace qnn {
+
+__device__ __forceinline__ float to_f(float v) { return v; }
+__device__ __forceinline__ float to_f(bf16 v) { return __bfloat162float(v); }
+template <typename T> __device__ __forceinline__ T from_f(float v);
+template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 from_f<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+// A value of runtime dtype read as float.
+__device__ __forceinline__ float load_as_f(const void* p, int dtype, size_t i) {
+    return dtype == QNN_DT_BF16 ? __bfloat162float(((const bf16*)p)[i]) : ((const float*)p)[i];
+}
+__device__ __forceinline__ void store_from_f(void* p, int dtype, size_t i, float v) {
+    if (dtype == QNN_DT_BF16) ((bf16*)p)[i] = __float2bfloat16_rn(v);
+    else ((float*)p)[i] = v;
+}
+
+// 16-byte vectors: 4 floats or 8 bf16.
+template <typename T> struct Vec16;
+template <> struct Vec16<float> {
+    static constexpr int N = 4;
+    float4 raw;
+    __device__ __forceinline__ void load(const float* p) { raw = *reinterpret_cast<const float4*>(p); }
+    __device__ __forceinline__ void unpack(float* o) const { o[0] = raw.x; o[1] = raw.y; o[2] = raw.z; o[3] = raw.w; }
+    __device__ __forceinline__ static void store(float* p, const float* v) {
+        *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    }
+};
+template <> struct Vec16<bf16> {
+    static constexpr int N = 8;
+    uint4 raw;
+    __device__ __forceinline__ void load(const bf16* p) { raw = *reinterpret_cast<const uint4*>(p); }
+    __device__ __forceinline__ void unpack(float* o) const {
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            o[2 * i] = __uint_as_float(w[i] << 16);
+            o[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        }
+    }
+    __device__ __forceinline__ static void store(bf16* p, const float* v) {
+        uint4 r;
+        uint32_t* w = reinterpret_cast<uint32_t*>(&r);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+            w[i] = *reinterpret_cast<uint32_t*>(&h);
+        }
+        *reinterpret_cast<uint4*>(p) = r;
+    }
+};
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result.  The order of
+// additions depends only on blockDim, so a row gives the same sum in any batch.
+__device__ __forceinline__ float block_sum(float v, float* smem32) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) smem32[warp] = v;
+    __syncthreads();
+    float r = (lane < nwarp) ? smem32[lane] : 0.f;
+    r = warp_sum(r);
+    return r;
+}
+
+// cap * tanh(clamp(x / cap, -20, 20)); cap <= 0 switches it off.
+__device__ __forceinline__ float softcap(float x, float cap) {
+    if (cap > 0.f) {
+        float t = fminf(fmaxf(x / cap, -20.f), 20.f);
+        return cap * tanhf(t);
+    }
+    return x;
+}
+
+__device__ __forceinline__ float gelu_tanh(float x) {
+    return 0.5f * x * (1.f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+}
+__device__ __forceinline__ float silu(float x) { return x / (1.f + expf(-x)); }
+
+// activation codes of the gated feed-forward
+#define QNN_ACT_GELU_TANH 0
+#define QNN_ACT_SILU 1
+__device__ __forceinline__ float activate(float x, int act) {
+    return act == QNN_ACT_SILU ? silu(x) : gelu_tanh(x);
+}
+
+}  // namespace qnn
+
+#define QNN_LAUNCH_CHECK() return (int)cudaGetLastError()

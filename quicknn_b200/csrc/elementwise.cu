@@ -1,0 +1,205 @@
+// Embedding, norms, gated activation, softcap and small helpers.
+//
+// Reference formulas (HemulGM/QuickNN, src/backends/vulkan/shaders/tensor.comp):
+//   embedding gather, id >= vocab -> 0 ........ :237-242 (op 15), scale :309 (op 43)
+//   RMSNorm: inv = rsqrt(sum(x^2)/dim + eps) ... :63-72 (op 2), "+1" weight bit :70
+//   residual add .............................. :221 (op 4)
+//   gelu_tanh(gate) * up ...................... :23, :228 (op 75)
+//   final softcap ............................. :308 (op 76)
+//   finite check into an error word ........... :235 (op 13)
+// The reference runs each as its own dispatch; here the post-sublayer norm, the
+// residual add and the next pre-norm are one kernel, and sums are always float32.
+#include "common.cuh"
+
+using namespace qnn;
+
+// ---------------------------------------------------------------------------------
+// out[t, :] = table[token_t, :] * scale   (float32 residual stream)
+// ---------------------------------------------------------------------------------
+template <typename W>
+__global__ void embed_kernel(const int* __restrict__ tokens, const W* __restrict__ table, float scale,
+                             float* __restrict__ out, int H, int V) {
+    const int t = blockIdx.x;
+    const int tok = tokens[t];
+    float* o = out + (size_t)t * H;
+    if (tok < 0 || tok >= V) {
+        for (int j = threadIdx.x; j < H; j += blockDim.x) o[j] = 0.f;
+        return;
+    }
+    const W* row = table + (size_t)tok * H;
+    for (int j = threadIdx.x; j < H; j += blockDim.x) o[j] = to_f(row[j]) * scale;
+}
+
+QNN_API int qnn_embed(const int* tokens, const void* table, int table_dtype, float scale, float* out,
+                      int T, int H, int V, cudaStream_t st) {
+    if (T <= 0) return 0;
+    const int threads = H >= 1024 ? 256 : 128;
+    if (table_dtype == QNN_DT_BF16)
+        embed_kernel<bf16><<<T, threads, 0, st>>>(tokens, (const bf16*)table, scale, out, H, V);
+    else
+        embed_kernel<float><<<T, threads, 0, st>>>(tokens, (const float*)table, scale, out, H, V);
+    QNN_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------------------------
+// RMSNorm of one row per block.
+// ---------------------------------------------------------------------------------
+__global__ void rmsnorm_kernel(const void* __restrict__ x, int x_dt, const void* __restrict__ w, int w_dt,
+                               float eps, float offset, void* __restrict__ out, int out_dt, int H) {
+    __shared__ float red[32];
+    const size_t base = (size_t)blockIdx.x * H;
+    float ss = 0.f;
+    for (int j = threadIdx.x; j < H; j += blockDim.x) {
+        float v = load_as_f(x, x_dt, base + j);
+        ss += v * v;
+    }
+    ss = block_sum(ss, red);
+    const float inv = rsqrtf(ss / (float)H + eps);
+    for (int j = threadIdx.x; j < H; j += blockDim.x) {
+        float v = load_as_f(x, x_dt, base + j);
+        float g = load_as_f(w, w_dt, j) + offset;
+        store_from_f(out, out_dt, base + j, v * inv * g);
+    }
+}
+
+static inline int norm_threads(int H) { return H >= 2048 ? 512 : (H >= 512 ? 256 : 128); }
+
+QNN_API int qnn_rmsnorm(const void* x, int x_dt, const void* w, int w_dt, float eps, int unit_offset,
+                        void* out, int out_dt, int T, int H, cudaStream_t st) {
+    if (T <= 0) return 0;
+    rmsnorm_kernel<<<T, norm_threads(H), 0, st>>>(x, x_dt, w, w_dt, eps, unit_offset ? 1.f : 0.f, out, out_dt, H);
+    QNN_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------------------------
+// resid += rmsnorm(y; w_post);  optionally  out_next = rmsnorm(resid; w_next).
+// Three passes over a row by the same thread -> element mapping, so a thread re-reads
+// only what it wrote itself.
+// ---------------------------------------------------------------------------------
+__global__ void add_rmsnorm_kernel(float* __restrict__ resid, const void* __restrict__ y, int y_dt,
+                                   const void* __restrict__ w_post, int w_post_dt, float eps_post, float off_post,
+                                   const void* __restrict__ w_next, int w_next_dt, float eps_next, float off_next,
+                                   void* __restrict__ out_next, int out_dt, int H) {
+    __shared__ float red[32];
+    const size_t base = (size_t)blockIdx.x * H;
+    float ss = 0.f;
+    for (int j = threadIdx.x; j < H; j += blockDim.x) {
+        float v = load_as_f(y, y_dt, base + j);
+        ss += v * v;
+    }
+    ss = block_sum(ss, red);
+    const float inv = rsqrtf(ss / (float)H + eps_post);
+    float ss2 = 0.f;
+    for (int j = threadIdx.x; j < H; j += blockDim.x) {
+        float v = load_as_f(y, y_dt, base + j);
+        float g = load_as_f(w_post, w_post_dt, j) + off_post;
+        float r = resid[base + j] + v * inv * g;
+        resid[base + j] = r;
+        ss2 += r * r;
+    }
+    if (w_next == nullptr) return;
+    ss2 = block_sum(ss2, red);
+    const float inv2 = rsqrtf(ss2 / (float)H + eps_next);
+    for (int j = threadIdx.x; j < H; j += blockDim.x) {
+        float r = resid[base + j];
+        float g = load_as_f(w_next, w_next_dt, j) + off_next;
+        store_from_f(out_next, out_dt, base + j, r * inv2 * g);
+    }
+}
+
+QNN_API int qnn_add_rmsnorm(float* resid, const void* y, int y_dt, const void* w_post, int w_post_dt,
+                            float eps_post, int unit_post, const void* w_next, int w_next_dt, float eps_next,
+                            int unit_next, void* out_next, int out_dt, int T, int H, cudaStream_t st) {
+    if (T <= 0) return 0;
+    add_rmsnorm_kernel<<<T, norm_threads(H), 0, st>>>(resid, y, y_dt, w_post, w_post_dt, eps_post,
+                                                      unit_post ? 1.f : 0.f, w_next, w_next_dt, eps_next,
+                                                      unit_next ? 1.f : 0.f, out_next, out_dt, H);
+    QNN_LAUNCH_CHECK();
+}
+
+// resid[i] += y[i]   (generic residual add for blocks that do not fuse)
+__global__ void add_kernel(float* __restrict__ resid, const void* __restrict__ y, int y_dt, size_t n) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) resid[i] += load_as_f(y, y_dt, i);
+}
+QNN_API int qnn_add(float* resid, const void* y, int y_dt, long long n, cudaStream_t st) {
+    if (n <= 0) return 0;
+    add_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(resid, y, y_dt, (size_t)n);
+    QNN_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------------------------
+// out[t, i] = act(gu[t, i]) * gu[t, I + i]
+// ---------------------------------------------------------------------------------
+template <typename T>
+__global__ void gated_act_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, int act, size_t n) {
+    size_t id = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (id >= n) return;
+    size_t t = id / I;
+    int i = (int)(id % I);
+    float g = to_f(gu[t * 2 * I + i]), u = to_f(gu[t * 2 * I + I + i]);
+    out[id] = from_f<T>(activate(g, act) * u);
+}
+QNN_API int qnn_gated_act(const void* gu, void* out, int dtype, int T, int I, int act, cudaStream_t st) {
+    size_t n = (size_t)T * I;
+    if (n == 0) return 0;
+    unsigned blocks = (unsigned)((n + 255) / 256);
+    if (dtype == QNN_DT_BF16)
+        gated_act_kernel<bf16><<<blocks, 256, 0, st>>>((const bf16*)gu, (bf16*)out, I, act, n);
+    else
+        gated_act_kernel<float><<<blocks, 256, 0, st>>>((const float*)gu, (float*)out, I, act, n);
+    QNN_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------------------------
+// out[i] = softcap(x[i])  -> float32 (the logits)
+// ---------------------------------------------------------------------------------
+__global__ void softcap_kernel(const void* __restrict__ x, int x_dt, float* __restrict__ out, float cap, size_t n) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = softcap(load_as_f(x, x_dt, i), cap);
+}
+QNN_API int qnn_softcap(const void* x, int x_dt, float* out, float cap, long long n, cudaStream_t st) {
+    if (n <= 0) return 0;
+    softcap_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(x, x_dt, out, cap, (size_t)n);
+    QNN_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------------------------
+// dst[r, :] = src[rows[r], :]  with dtype conversion (gather the rows whose logits are wanted)
+// ---------------------------------------------------------------------------------
+__global__ void gather_rows_kernel(const void* __restrict__ src, int src_dt, const int* __restrict__ rows,
+                                   void* __restrict__ dst, int dst_dt, int H) {
+    const size_t s = (size_t)rows[blockIdx.x] * H, d = (size_t)blockIdx.x * H;
+    for (int j = threadIdx.x; j < H; j += blockDim.x) store_from_f(dst, dst_dt, d + j, load_as_f(src, src_dt, s + j));
+}
+QNN_API int qnn_gather_rows(const void* src, int src_dt, const int* rows, void* dst, int dst_dt, int R, int H,
+                            cudaStream_t st) {
+    if (R <= 0) return 0;
+    gather_rows_kernel<<<R, 256, 0, st>>>(src, src_dt, rows, dst, dst_dt, H);
+    QNN_LAUNCH_CHECK();
+}
+
+// dst = convert(src)
+__global__ void cast_kernel(const void* __restrict__ src, int src_dt, void* __restrict__ dst, int dst_dt, size_t n) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) store_from_f(dst, dst_dt, i, load_as_f(src, src_dt, i));
+}
+QNN_API int qnn_cast(const void* src, int src_dt, void* dst, int dst_dt, long long n, cudaStream_t st) {
+    if (n <= 0) return 0;
+    cast_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(src, src_dt, dst, dst_dt, (size_t)n);
+    QNN_LAUNCH_CHECK();
+}
+
+// flag |= 1 when any value is NaN or Inf
+__global__ void finite_kernel(const float* __restrict__ x, size_t n, int* __restrict__ flag) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) {
+        float v = x[i];
+        if (isnan(v) || isinf(v)) atomicOr(flag, 1);
+    }
+}
+QNN_API int qnn_check_finite(const float* x, long long n, int* flag, cudaStream_t st) {
+    if (n <= 0) return 0;
+    finite_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(x, (size_t)n, flag);
+    QNN_LAUNCH_CHECK();
+}

@@ -1,0 +1,96 @@
+// Rotary position encoding of Q and K in place, fused with the append of K and V to
+// the paged cache.
+//
+// Reference: two GO_LLM_ROPE dispatches and one GO_LLM_CACHE_WRITE per layer
+// (src/models/QuickNN.Models.Gemma2.pas:170-175; shaders/tensor.comp:318-327 and :312-317).
+// The rotation is the half-split one over the rotated width:
+//   x' = x_j cos(a) - x_{j+r/2} sin(a),  y' = x_j sin(a) + x_{j+r/2} cos(a),
+//   a = float(position) * inv_freq[j],  inv_freq[j] = theta^(-2j/r) rounded to float32 on the host.
+// The reference computes inv_freq in the shader and reduces the angle by hand before
+// native sin/cos; here sincosf() does the full-range reduction.
+//
+// Cache layout of one line: K and V pools [page][kv_head][slot_in_page][head_dim]; the
+// page of position p of a sequence is page_table[slot][ (p mod ring) / page_size ] where
+// ring = 0 means "no ring" (every position kept).
+#include "common.cuh"
+
+using namespace qnn;
+
+template <typename T>
+__global__ void rope_cache_kernel(T* __restrict__ qkv, int nq, int nkv, int hd, int rot,
+                                  const float* __restrict__ inv_freq, const int* __restrict__ tok_pos,
+                                  const int* __restrict__ tok_slot, T* __restrict__ k_pool, T* __restrict__ v_pool,
+                                  const int* __restrict__ page_table, int max_pages, int page_size, int ring,
+                                  const int* __restrict__ slot_len, int write_cache) {
+    const int t = blockIdx.x;
+    const int pos = tok_pos[t];
+    const int slot = tok_slot[t];
+    const int half = hd / 2, rh = rot / 2;
+    const size_t row = (size_t)t * (nq + 2 * nkv) * hd;
+    T* q = qkv + row;
+    T* k = q + (size_t)nq * hd;
+    T* v = k + (size_t)nkv * hd;
+
+    size_t cache_base = 0;
+    bool wr = write_cache && slot >= 0;
+    // A prompt longer than the ring would write one cell from several positions in this
+    // launch; only the last `ring` positions of the sequence (its length after this step
+    // is slot_len[slot]) are kept.
+    if (wr && ring > 0 && pos + ring < slot_len[slot]) wr = false;
+    if (wr) {
+        const int r = ring > 0 ? pos % ring : pos;
+        const int page = page_table[(size_t)slot * max_pages + r / page_size];
+        cache_base = ((size_t)page * nkv * page_size + (r % page_size)) * hd;  // + h * page_size * hd
+    }
+    const size_t head_stride = (size_t)page_size * hd;
+
+    const int nwork = (nq + nkv) * half;
+    for (int w = threadIdx.x; w < nwork; w += blockDim.x) {
+        const int h = w / half, idx = w % half;
+        const bool is_k = h >= nq;
+        T* x = is_k ? k + (size_t)(h - nq) * hd : q + (size_t)h * hd;
+        if (idx < rh) {
+            float s, c;
+            sincosf((float)pos * inv_freq[idx], &s, &c);
+            const float a = to_f(x[idx]), b = to_f(x[idx + rh]);
+            const T ra = from_f<T>(a * c - b * s), rb = from_f<T>(a * s + b * c);
+            x[idx] = ra;
+            x[idx + rh] = rb;
+            if (is_k && wr) {
+                T* dst = k_pool + cache_base + (size_t)(h - nq) * head_stride;
+                dst[idx] = ra;
+                dst[idx + rh] = rb;
+            }
+        } else if (is_k && wr) {
+            const int d = rot + 2 * (idx - rh);
+            T* dst = k_pool + cache_base + (size_t)(h - nq) * head_stride;
+            dst[d] = x[d];
+            dst[d + 1] = x[d + 1];
+        }
+    }
+    if (wr) {
+        for (int w = threadIdx.x; w < nkv * hd; w += blockDim.x) {
+            const int h = w / hd, d = w % hd;
+            v_pool[cache_base + (size_t)h * head_stride + d] = v[w];
+        }
+    }
+}
+
+QNN_API int qnn_rope_cache_write(void* qkv, int dtype, int T, int nq, int nkv, int hd, int rot,
+                                 const float* inv_freq, const int* tok_pos, const int* tok_slot, void* k_pool,
+                                 void* v_pool, const int* page_table, int max_pages, int page_size, int ring,
+                                 const int* slot_len, int write_cache, cudaStream_t st) {
+    if (T <= 0) return 0;
+    if (hd % 2 || rot % 2 || rot > hd || rot < 0) return QNN_ERR_UNSUPPORTED;
+    const int work = (nq + nkv) * hd / 2;
+    const int threads = work >= 1024 ? 256 : (work >= 256 ? 128 : 64);
+    if (dtype == QNN_DT_BF16)
+        rope_cache_kernel<bf16><<<T, threads, 0, st>>>((bf16*)qkv, nq, nkv, hd, rot, inv_freq, tok_pos, tok_slot,
+                                                       (bf16*)k_pool, (bf16*)v_pool, page_table, max_pages,
+                                                       page_size, ring, slot_len, write_cache);
+    else
+        rope_cache_kernel<float><<<T, threads, 0, st>>>((float*)qkv, nq, nkv, hd, rot, inv_freq, tok_pos, tok_slot,
+                                                        (float*)k_pool, (float*)v_pool, page_table, max_pages,
+                                                        page_size, ring, slot_len, write_cache);
+    QNN_LAUNCH_CHECK();
+}

@@ -1,0 +1,187 @@
+// Token selection on the device: greedy, and temperature sampling with top-k, nucleus cut
+// and repetition penalty.  Only the chosen ids (and an error word) cross to the host.
+//
+// Reference (src/backends/vulkan/shaders/tensor.comp):
+//   op 50 :121-155  exact top-k of each 512-token tile; k = 1 is an arg-max; repetition
+//                   penalty s<0 ? s*pen : s/pen on seen ids; ties go to the lowest id
+//   op 51/46 :156-199  merge to the global top-k (k <= 64), p_j = exp((s_j - s_0)/T), keep the
+//                   shortest prefix with mass >= top_p * total, draw target = u * retained,
+//                   first j whose running sum exceeds it, else the last kept
+//   op 48 :328      mark ids in the "seen" table
+//   op 13 :235      NaN/Inf -> error word
+// Host side of the reference: xorshift32 per token, u = min(0.99999994, (x + 0.5) / 2^32)
+// (src/models/QuickNN.Models.LLM.pas:625-628); temperature 0 forces k = 1
+// (QuickNN.Vulkan.Context.Implementation.inc:1169-1170).  Here the generator state lives on
+// the device, one per row, and tiles are 1024 wide.
+#include "common.cuh"
+#include <float.h>
+
+using namespace qnn;
+
+#define SAMPLE_TILE 1024
+#define SAMPLE_THREADS 256
+#define SAMPLE_MAX_K 64
+#define NO_ID 0xffffffffu
+
+__device__ __forceinline__ bool better(float a, unsigned ia, float b, unsigned ib) {
+    return a > b || (a == b && ia < ib);
+}
+
+// Block-wide arg-max with lowest-id ties; every thread gets the winner.
+__device__ __forceinline__ void block_argmax(float& v, unsigned& id, float* sv, unsigned* si) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+        const unsigned oi = __shfl_xor_sync(0xffffffffu, id, o);
+        if (better(ov, oi, v, id)) { v = ov; id = oi; }
+    }
+    __syncthreads();
+    if (lane == 0) { sv[warp] = v; si[warp] = id; }
+    __syncthreads();
+    float rv = lane < nwarp ? sv[lane] : -FLT_MAX;
+    unsigned ri = lane < nwarp ? si[lane] : NO_ID;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, rv, o);
+        const unsigned oi = __shfl_xor_sync(0xffffffffu, ri, o);
+        if (better(ov, oi, rv, ri)) { rv = ov; ri = oi; }
+    }
+    v = rv;
+    id = ri;
+}
+
+// cand[(r * tiles + tile) * k + j] = j-th best (value, id) of the tile
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+sample_tile_kernel(const float* __restrict__ logits, int V, int k, float penalty, const unsigned char* __restrict__ seen,
+                   const int* __restrict__ seen_rows, float2* __restrict__ cand, int* __restrict__ error_flag) {
+    __shared__ float sv[32];
+    __shared__ unsigned si[32];
+    const int tile = blockIdx.x, r = blockIdx.y, tiles = gridDim.x;
+    const float* row = logits + (size_t)r * V;
+    const unsigned char* srow = nullptr;
+    if (seen != nullptr && seen_rows != nullptr && seen_rows[r] >= 0) srow = seen + (size_t)seen_rows[r] * V;
+    constexpr int PER = SAMPLE_TILE / SAMPLE_THREADS;
+    float val[PER];
+    unsigned ids[PER];
+    bool bad = false;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+        const int tok = tile * SAMPLE_TILE + i * SAMPLE_THREADS + threadIdx.x;
+        val[i] = -FLT_MAX;
+        ids[i] = NO_ID;
+        if (tok < V) {
+            float s = row[tok];
+            if (isnan(s) || isinf(s)) { bad = true; s = -FLT_MAX; }
+            else if (srow != nullptr && srow[tok]) s = s < 0.f ? s * penalty : s / penalty;
+            val[i] = s;
+            ids[i] = (unsigned)tok;
+        }
+    }
+    if (bad && error_flag != nullptr) atomicOr(error_flag, 1);
+    for (int j = 0; j < k; ++j) {
+        float bv = -FLT_MAX;
+        unsigned bi = NO_ID;
+#pragma unroll
+        for (int i = 0; i < PER; ++i)
+            if (better(val[i], ids[i], bv, bi)) { bv = val[i]; bi = ids[i]; }
+        block_argmax(bv, bi, sv, si);
+        if (threadIdx.x == 0) cand[((size_t)r * tiles + tile) * k + j] = make_float2(bv, __uint_as_float(bi));
+#pragma unroll
+        for (int i = 0; i < PER; ++i)
+            if (ids[i] == bi && bi != NO_ID) { val[i] = -FLT_MAX; ids[i] = NO_ID; }
+    }
+}
+
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+sample_merge_kernel(float2* __restrict__ cand, int ncand, int k, float temperature, float top_p,
+                    unsigned* __restrict__ rng_state, int* __restrict__ out_tokens, unsigned char* __restrict__ seen,
+                    const int* __restrict__ seen_rows, int V) {
+    __shared__ float sv[32];
+    __shared__ unsigned si[32];
+    __shared__ float top_v[SAMPLE_MAX_K];
+    __shared__ unsigned top_i[SAMPLE_MAX_K];
+    const int r = blockIdx.x;
+    float2* c = cand + (size_t)r * ncand;
+    for (int j = 0; j < k; ++j) {
+        float bv = -FLT_MAX;
+        unsigned bi = NO_ID;
+        for (int i = threadIdx.x; i < ncand; i += blockDim.x) {
+            const float2 e = c[i];
+            const unsigned id = __float_as_uint(e.y);
+            if (better(e.x, id, bv, bi)) { bv = e.x; bi = id; }
+        }
+        block_argmax(bv, bi, sv, si);
+        if (threadIdx.x == 0) { top_v[j] = bv; top_i[j] = bi; }
+        if (bi != NO_ID)
+            for (int i = threadIdx.x; i < ncand; i += blockDim.x)
+                if (__float_as_uint(c[i].y) == bi) c[i] = make_float2(-FLT_MAX, __uint_as_float(NO_ID));
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        unsigned selected = top_i[0];
+        if (temperature > 0.f && k > 1) {
+            unsigned x = rng_state[r];
+            x ^= x << 13; x ^= x >> 17; x ^= x << 5;
+            rng_state[r] = x;
+            const float u = fminf(0.99999994f, (float)(((double)x + 0.5) / 4294967296.0));
+            int kk = k;
+            while (kk > 1 && top_i[kk - 1] == NO_ID) --kk;  // fewer valid ids than k
+            float total = 0.f;
+            const float mx = top_v[0];
+            for (int j = 0; j < kk; ++j) { top_v[j] = expf((top_v[j] - mx) / temperature); total += top_v[j]; }
+            float retained = 0.f;
+            int count = 0;
+            do { retained += top_v[count]; ++count; } while (count < kk && retained < top_p * total);
+            const float target = u * retained;
+            float acc = 0.f;
+            selected = top_i[count - 1];
+            for (int j = 0; j < count; ++j) { acc += top_v[j]; if (target < acc) { selected = top_i[j]; break; } }
+        }
+        out_tokens[r] = (selected == NO_ID) ? -1 : (int)selected;
+        if (seen != nullptr && seen_rows != nullptr && seen_rows[r] >= 0 && selected != NO_ID)
+            seen[(size_t)seen_rows[r] * V + selected] = 1;
+    }
+}
+
+// Scratch `cand`: R * ceil(V/1024) * k float2.
+QNN_API int qnn_sample(const float* logits, int R, int V, int top_k, float temperature, float top_p, float penalty,
+                       unsigned* rng_state, unsigned char* seen, const int* seen_rows, void* cand, int* out_tokens,
+                       int* error_flag, cudaStream_t st) {
+    if (R <= 0) return 0;
+    if (V <= 0 || top_k < 1 || !(temperature >= 0.f) || !(top_p > 0.f && top_p <= 1.f) || !(penalty > 0.f))
+        return QNN_ERR_ARGUMENT;
+    int k = top_k > SAMPLE_MAX_K ? SAMPLE_MAX_K : top_k;
+    if (k > V) k = V;
+    if (temperature <= 0.f) k = 1;
+    const int tiles = (V + SAMPLE_TILE - 1) / SAMPLE_TILE;
+    if (R > 65535) return QNN_ERR_UNSUPPORTED;
+    sample_tile_kernel<<<dim3(tiles, R), SAMPLE_THREADS, 0, st>>>(logits, V, k, penalty, penalty != 1.f ? seen : nullptr,
+                                                                 seen_rows, (float2*)cand, error_flag);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return (int)e;
+    sample_merge_kernel<<<R, SAMPLE_THREADS, 0, st>>>((float2*)cand, tiles * k, k, temperature, top_p, rng_state,
+                                                      out_tokens, seen, seen_rows, V);
+    QNN_LAUNCH_CHECK();
+}
+
+QNN_API int qnn_sample_scratch_bytes(int R, int V, int top_k) {
+    int k = top_k > SAMPLE_MAX_K ? SAMPLE_MAX_K : (top_k < 1 ? 1 : top_k);
+    const long long tiles = (V + SAMPLE_TILE - 1) / SAMPLE_TILE;
+    long long b = (long long)R * tiles * k * 8;
+    return b > 0x7fffffff ? -1 : (int)b;
+}
+
+// seen[rows[t]][tokens[t]] = 1   (prompt tokens; rows[t] < 0 is skipped)
+__global__ void mark_seen_kernel(const int* __restrict__ tokens, const int* __restrict__ rows,
+                                 unsigned char* __restrict__ seen, int V, int T) {
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= T) return;
+    const int tok = tokens[t], r = rows[t];
+    if (r >= 0 && tok >= 0 && tok < V) seen[(size_t)r * V + tok] = 1;
+}
+QNN_API int qnn_mark_seen(const int* tokens, const int* rows, unsigned char* seen, int V, int T, cudaStream_t st) {
+    if (T <= 0) return 0;
+    mark_seen_kernel<<<(T + 255) / 256, 256, 0, st>>>(tokens, rows, seen, V, T);
+    QNN_LAUNCH_CHECK();
+}

@@ -1,0 +1,34 @@
+"""What one step brings: the tokens of a batch and where they stand."""
+from __future__ import annotations
+
+import dataclasses
+from typing import Optional
+
+import torch
+
+
+@dataclasses.dataclass
+class StepBatch:
+    """Device-side description of one step.
+
+    ``mode`` is "prefill" when every sequence starts at its first token (the whole
+    prompts, packed one after another) and "decode" when every sequence goes on by
+    one token.  Row t of the packed batch belongs to the sequence in slot
+    ``tok_slot[t]`` (a negative slot marks a padding row: nothing is written for it
+    and it attends to nothing) at position ``tok_pos[t]``; its sequence's first row is
+    ``tok_row0[t]``.
+    """
+
+    mode: str
+    n_tokens: int
+    n_seqs: int
+    tokens: torch.Tensor            # [T] int32
+    tok_pos: torch.Tensor           # [T] int32
+    tok_slot: torch.Tensor          # [T] int32
+    tok_row0: torch.Tensor          # [T] int32
+    slots: torch.Tensor             # [B] int32
+    want_rows: torch.Tensor         # [R] int32: rows whose logits are returned
+    act_dtype: torch.dtype
+    decode_splits: int = 1
+    part_o: Optional[torch.Tensor] = None
+    part_ml: Optional[torch.Tensor] = None

@@ -1,0 +1,143 @@
+"""The step function: a batch of sequences that start together, from the cache.
+
+One ``Engine`` owns a model, its cache and the scratch of the kernels.  ``step``
+runs exactly the tokens it is given as one batch and returns the logits at the
+wanted places.  The reference's counterpart is ``ForwardRows`` for one sequence in
+128-row chunks, returning the last row's logits
+(src/models/QuickNN.Models.LLM.pas:459-493); here a step takes several sequences of
+unequal length, whole prompts at once, then one token each.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence, Tuple, Union
+
+import numpy as np
+import torch
+
+from ..cache import PAGE, CacheFull, KVCache
+from .batch import StepBatch
+from .model import Model
+
+
+class StepError(ValueError):
+    pass
+
+
+class Engine:
+    def __init__(self, model: Model, max_tokens: int, max_slots: Optional[int] = None,
+                 max_seq: Optional[int] = None, decode_splits: Optional[int] = None):
+        self.model = model
+        self.device = model.device
+        if self.device.type != "cuda":
+            raise RuntimeError("quicknn_b200 runs on a CUDA device only; there is no CPU path")
+        max_tokens = (int(max_tokens) + PAGE - 1) // PAGE * PAGE
+        if max_seq is None:
+            max_seq = min(max_tokens, model.spec.max_positions)
+        if max_seq > model.spec.max_positions:
+            raise ValueError(f"max_seq {max_seq} exceeds the model's max positions {model.spec.max_positions}")
+        if max_slots is None:
+            max_slots = max(1, min(max_tokens // PAGE, 256))
+        needs, states = model.cache_needs()
+        self.cache = KVCache(needs, states, max_tokens, max_slots, max_seq, model.dtype, self.device)
+        self.max_seq, self.max_slots = max_seq, max_slots
+        self.decode_splits = int(decode_splits) if decode_splits else min(32, max(1, max_seq // 128))
+        self._scratch: Dict[int, Tuple[torch.Tensor, torch.Tensor]] = {}
+        self.error_flag = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.steps_run = 0
+
+    # ---- sequences -------------------------------------------------------------------
+    def new_sequence(self) -> int:
+        return self.cache.allocate()
+
+    def release(self, slot: int) -> None:
+        self.cache.free(slot)
+
+    def length(self, slot: int) -> int:
+        return self.cache.length(slot)
+
+    # ---- the step ----------------------------------------------------------------------
+    def _scratch_for(self, batch: int) -> Tuple[torch.Tensor, torch.Tensor]:
+        key = 1
+        while key < batch:
+            key *= 2
+        if key not in self._scratch:
+            po, pm = self.model.decode_scratch(key, self.decode_splits)
+            self._scratch[key] = (torch.empty(max(po, 1), dtype=torch.float32, device=self.device),
+                                  torch.empty(max(pm, 1), dtype=torch.float32, device=self.device))
+        return self._scratch[key]
+
+    def plan(self, entries: Sequence[Tuple[int, Sequence[int]]],
+             want: Union[str, Sequence[Sequence[int]]] = "last"):
+        """Host-side half of a step: checks, cache growth, packed metadata (numpy)."""
+        if not entries:
+            raise StepError("a step needs at least one sequence")
+        slots = [int(s) for s, _ in entries]
+        if len(set(slots)) != len(slots):
+            raise StepError("a sequence appears twice in one step")
+        lens = [len(t) for _, t in entries]
+        if min(lens) < 1:
+            raise StepError("every sequence of a step brings at least one token")
+        starts = [self.cache.length(s) for s in slots]
+        if all(p == 0 for p in starts):
+            mode = "prefill"
+        elif all(n == 1 for n in lens):
+            mode = "decode"
+        else:
+            raise StepError("the sequences of a step either all start at their first token or all go on "
+                            "by one token")
+        V = self.model.spec.embedding.vocab_size
+        for _, toks in entries:
+            for t in toks:
+                if not (0 <= int(t) < V):
+                    raise StepError(f"token id {t} is outside the vocabulary of {V}")
+        if want == "last":
+            want = [[n - 1] for n in lens]
+        elif want == "all":
+            want = [list(range(n)) for n in lens]
+        if len(want) != len(entries):
+            raise StepError("`want` needs one list per sequence")
+        T, B = sum(lens), len(entries)
+        tokens = np.empty(T, np.int32)
+        tok_pos = np.empty(T, np.int32)
+        tok_slot = np.empty(T, np.int32)
+        tok_row0 = np.empty(T, np.int32)
+        rows: List[int] = []
+        r = 0
+        for (s, toks), p0, n, w in zip(entries, starts, lens, want):
+            tokens[r:r + n] = np.asarray(toks, dtype=np.int64)
+            tok_pos[r:r + n] = np.arange(p0, p0 + n)
+            tok_slot[r:r + n] = s
+            tok_row0[r:r + n] = r
+            for i in w:
+                if not (0 <= int(i) < n):
+                    raise StepError(f"wanted place {i} is outside the {n} tokens the sequence brings")
+                rows.append(r + int(i))
+            r += n
+        # only now, with everything checked, does the cache change
+        self.cache.extend([(s, p + n) for s, p, n in zip(slots, starts, lens)])
+        return mode, T, B, tokens, tok_pos, tok_slot, tok_row0, np.asarray(slots, np.int32), np.asarray(rows, np.int32)
+
+    def step(self, entries: Sequence[Tuple[int, Sequence[int]]],
+             want: Union[str, Sequence[Sequence[int]]] = "last") -> torch.Tensor:
+        """Run the given tokens as one batch; return float32 logits ``[wanted, vocab]`` in the
+        order of the entries and of their wanted places."""
+        mode, T, B, tokens, tok_pos, tok_slot, tok_row0, slots, rows = self.plan(entries, want)
+        self.cache.sync()
+        packed = np.concatenate([tokens, tok_pos, tok_slot, tok_row0, slots, rows])
+        dev = torch.from_numpy(packed).to(self.device)
+        o = 0
+        views = []
+        for n in (T, T, T, T, B, len(rows)):
+            views.append(dev[o:o + n])
+            o += n
+        part_o, part_ml = self._scratch_for(B) if mode == "decode" else (None, None)
+        step = StepBatch(mode, T, B, views[0], views[1], views[2], views[3], views[4], views[5],
+                         self.model.dtype, self.decode_splits, part_o, part_ml)
+        logits = self.model.forward(step, self.cache)
+        self.steps_run += 1
+        return logits
+
+    def stats(self) -> Dict[str, int]:
+        return {"weight_bytes": self.model.weight_bytes(), "cache_bytes": self.cache.bytes(),
+                "tokens_held": self.cache.tokens_held(), "max_tokens": self.cache.max_tokens,
+                "live_sequences": len(self.cache.slots.live()), "steps": self.steps_run}

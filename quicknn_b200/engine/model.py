@@ -1,0 +1,141 @@
+"""A model: embedding, the layers in the order of the schedule, final norm and head.
+
+Built from a ``ModelSpec`` only; which architecture wrote the spec is not known here.
+Forward order as in the reference (src/models/QuickNN.Models.Gemma2.pas:158-196):
+gather and scale the embedding rows; the layers; then, for the rows whose logits are
+wanted only (the reference: the last row), final norm, the tied head and the softcap.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Mapping, Optional, Sequence, Tuple
+
+import torch
+
+from ..config.base import Architecture, ModelConfig, load_config
+from ..kernels import ops
+from ..parts.base import BLOCKS, NORMS, CacheNeed, StateNeed
+from ..parts.layout import expected_tensors
+from ..parts.linear import project
+from ..parts.spec import ModelSpec
+from ..weights.loader import check_state_dict, load_named_tensors, place
+from .batch import StepBatch
+
+DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
+
+
+def as_dtype(d) -> torch.dtype:
+    if isinstance(d, torch.dtype):
+        if d not in (torch.bfloat16, torch.float32):
+            raise ValueError(f"compute dtype must be bfloat16 or float32, got {d}")
+        return d
+    try:
+        return DTYPES[str(d)]
+    except KeyError:
+        raise ValueError(f"compute dtype must be one of {sorted(DTYPES)}, got {d!r}") from None
+
+
+class Model:
+    def __init__(self, arch: Architecture, config: ModelConfig, tensors: Mapping[str, torch.Tensor],
+                 dtype, device):
+        self.arch, self.config = arch, config
+        self.spec: ModelSpec = arch.build_spec(config)
+        self.dtype = as_dtype(dtype)
+        self.device = torch.device(device)
+        spec = self.spec
+        self.blocks = []
+        for layer in spec.layers:
+            blk = BLOCKS.get(layer.block.kind)(layer)
+            local = {ln: tensors[cn] for ln, cn in layer.tensors.items()}
+            blk.load(local, self.dtype, self.device)
+            self.blocks.append(blk)
+        self.embedding = tensors[spec.embedding.tensor].contiguous()
+        self.final_norm = NORMS.get(spec.head.norm.kind)(spec.head.norm)
+        self.final_norm.load({"weight": tensors[spec.head.norm_tensor]}, self.dtype, self.device)
+        self.head = self.embedding if spec.head.tied else tensors[spec.head.tensor].contiguous()
+        self._check_schedule()
+
+    # ---- construction --------------------------------------------------------------
+    @classmethod
+    def from_folder(cls, model_dir: str, dtype="bfloat16", device="cuda:0") -> "Model":
+        arch, cfg = load_config(model_dir)
+        spec = arch.build_spec(cfg)
+        want = {n: s for n, (s, _) in expected_tensors(spec).items()}
+        tensors = load_named_tensors(model_dir, want, as_dtype(dtype), device)
+        return cls(arch, cfg, tensors, dtype, device)
+
+    @classmethod
+    def from_tensors(cls, arch: Architecture, cfg: ModelConfig, tensors: Mapping[str, torch.Tensor],
+                     dtype="bfloat16", device="cuda:0") -> "Model":
+        spec = arch.build_spec(cfg)
+        check_state_dict({n: s for n, (s, _) in expected_tensors(spec).items()}, tensors)
+        placed = {n: place(t, as_dtype(dtype), device) for n, t in tensors.items()}
+        return cls(arch, cfg, placed, dtype, device)
+
+    # ---- what the cache has to provide ------------------------------------------------
+    def _check_schedule(self) -> None:
+        spec = self.spec
+        writers: Dict[int, int] = {}
+        for e in spec.schedule:
+            if not (0 <= e.layer < len(self.blocks)):
+                raise ValueError(f"schedule names layer {e.layer}, the model has {len(self.blocks)}")
+            if e.writes_cache:
+                if e.cache in writers:
+                    raise ValueError(f"cache line {e.cache} is written by two schedule entries")
+                writers[e.cache] = e.layer
+        for e in spec.schedule:
+            if not e.writes_cache:
+                if e.cache not in writers:
+                    raise ValueError(f"schedule entry of layer {e.layer} reads cache line {e.cache} that nobody writes")
+                a = self.blocks[e.layer].mixer.cache_need()
+                b = self.blocks[writers[e.cache]].mixer.cache_need()
+                if a is None or b is None or (a.n_kv_heads, a.head_dim) != (b.n_kv_heads, b.head_dim):
+                    raise ValueError(f"layer {e.layer} cannot read cache line {e.cache}: its keys have another shape")
+
+    def cache_needs(self) -> Tuple[List[Optional[CacheNeed]], List[Optional[StateNeed]]]:
+        n = self.spec.n_cache_lines()
+        needs: List[Optional[CacheNeed]] = [None] * n
+        states: List[Optional[StateNeed]] = [None] * n
+        for e in self.spec.schedule:
+            if e.writes_cache:
+                needs[e.cache] = self.blocks[e.layer].mixer.cache_need()
+                states[e.cache] = self.blocks[e.layer].mixer.state_need()
+        return needs, states
+
+    def decode_scratch(self, batch: int, splits: int) -> Tuple[int, int]:
+        po = pm = 0
+        for b in self.blocks:
+            m = b.mixer
+            nq, hd = getattr(m, "n_heads", 0), getattr(m, "head_dim", 0)
+            po = max(po, batch * nq * splits * hd)
+            pm = max(pm, batch * nq * splits * 2)
+        return po, pm
+
+    def weight_bytes(self) -> int:
+        n = self.embedding.numel() * self.embedding.element_size()
+        if self.head is not self.embedding:
+            n += self.head.numel() * self.head.element_size()
+        return n + self.final_norm.weight_bytes() + sum(b.weight_bytes() for b in self.blocks)
+
+    def step_weight_bytes(self) -> int:
+        """Bytes of weights that one decode step reads: every scheduled layer's matrices and
+        norms once, the head once (the embedding rows it gathers are negligible)."""
+        n = self.head.numel() * self.head.element_size() + self.final_norm.weight_bytes()
+        return n + sum(self.blocks[e.layer].weight_bytes() for e in self.spec.schedule)
+
+    # ---- forward ----------------------------------------------------------------------
+    def forward(self, step: StepBatch, cache) -> torch.Tensor:
+        """Logits (float32, [wanted rows, vocab]) of the rows in ``step.want_rows``."""
+        spec = self.spec
+        x = ops.embed(step.tokens, self.embedding, spec.embedding.scale)
+        for e in spec.schedule:
+            line = cache.line(e.cache, writes=e.writes_cache)
+            x = self.blocks[e.layer].forward(x, step, line)
+        return self.logits_of_rows(x, step.want_rows, step.act_dtype)
+
+    def logits_of_rows(self, x: torch.Tensor, rows: torch.Tensor, act_dtype: torch.dtype) -> torch.Tensor:
+        if rows.numel() == 0:
+            return torch.empty((0, self.spec.head.vocab_size), dtype=torch.float32, device=x.device)
+        picked = ops.gather_rows(x, rows, torch.float32)
+        n = self.final_norm(picked, act_dtype)
+        cap = self.spec.head.softcap
+        return project(n, self.head, epilogue=ops.EPI_SOFTCAP, cap=cap, out_dtype=torch.float32)

@@ -1,0 +1,139 @@
+"""Interfaces of the parts and the registries that name them.
+
+A model is put together from five kinds of part.  Each is chosen by a
+``PartSpec`` (kind + parameters) that the architecture wrote into the model's
+layout, layer by layer; no part knows which model it is in.
+
+=============  ==============================================================
+kind of part   interface
+=============  ==============================================================
+Norm           ``param_shapes(spec)``; ``load(tensors)``; ``__call__(x, out_dtype)``
+Positions      ``param_shapes`` (usually none); ``prepare(device)``;
+               ``tables()`` gives what the mixer's kernels need
+Mixer          ``param_shapes``; ``load``; ``cache_need()`` (growing keys/values,
+               possibly windowed), ``state_need()`` (fixed-size per-sequence
+               state); ``forward(x, step, cache_line)``
+FeedForward    ``param_shapes``; ``load``; ``forward(x, step)``
+Block          arrangement of the four above around the residual stream:
+               ``forward(resid, step, cache_line)``
+=============  ==============================================================
+
+``param_shapes`` is a classmethod over the spec so that the expected tensor list
+(and random weights) can be produced without a GPU.
+"""
+from __future__ import annotations
+
+import dataclasses
+from typing import Any, Callable, Dict, Mapping, Optional, Tuple, Type
+
+from .spec import PartSpec
+
+
+class PartRegistry:
+    def __init__(self, what: str):
+        self.what = what
+        self._kinds: Dict[str, type] = {}
+
+    def register(self, kind: str, cls: Optional[type] = None, *, replace: bool = False):
+        def deco(c):
+            if kind in self._kinds and not replace and self._kinds[kind] is not c:
+                raise KeyError(f"{self.what} kind '{kind}' is already registered")
+            self._kinds[kind] = c
+            return c
+        return deco(cls) if cls is not None else deco
+
+    def unregister(self, kind: str) -> None:
+        self._kinds.pop(kind, None)
+
+    def get(self, kind: str) -> type:
+        try:
+            return self._kinds[kind]
+        except KeyError:
+            raise KeyError(f"unknown {self.what} kind '{kind}'; registered: {sorted(self._kinds)}") from None
+
+    def kinds(self):
+        return sorted(self._kinds)
+
+
+NORMS = PartRegistry("norm")
+POSITIONS = PartRegistry("position encoding")
+MIXERS = PartRegistry("mixer")
+FEED_FORWARDS = PartRegistry("feed-forward")
+BLOCKS = PartRegistry("block")
+
+
+# ---- what a mixer asks of the cache ------------------------------------------------
+
+@dataclasses.dataclass(frozen=True)
+class CacheNeed:
+    """Keys and values that grow with the sequence.  ``window`` = None keeps every
+    position; an integer keeps the last ``window`` positions (a ring)."""
+
+    n_kv_heads: int
+    head_dim: int
+    window: Optional[int] = None
+
+    def group_key(self) -> Tuple:
+        return (self.n_kv_heads, self.head_dim, self.window)
+
+
+@dataclasses.dataclass(frozen=True)
+class StateNeed:
+    """Fixed-size per-sequence state: ``shape`` elements of ``dtype`` ("float32",
+    "bfloat16" or "compute"), zeroed when a slot is handed out, never rewound."""
+
+    shape: Tuple[int, ...]
+    dtype: str = "float32"
+
+
+class Part:
+    """Common base: parameters by local name."""
+
+    PARAM_ROLE_MATRIX = "matrix"
+    PARAM_ROLE_NORM = "norm"
+
+    def __init__(self, spec: PartSpec):
+        self.spec = spec
+
+    @classmethod
+    def param_shapes(cls, spec: PartSpec) -> Dict[str, Tuple[Tuple[int, ...], str]]:
+        """local name -> (shape, role).  The role picks the standard deviation that the
+        random-weights mode draws with."""
+        return {}
+
+    def load(self, tensors: Mapping[str, Any], compute_dtype, device) -> None:
+        """Take the tensors named in ``param_shapes`` (already on the device)."""
+
+    def weight_bytes(self) -> int:
+        return 0
+
+
+class Norm(Part):
+    def __call__(self, x, out_dtype=None):  # pragma: no cover - interface
+        raise NotImplementedError
+
+
+class Positions(Part):
+    def prepare(self, device) -> None:
+        pass
+
+
+class Mixer(Part):
+    def cache_need(self) -> Optional[CacheNeed]:
+        return None
+
+    def state_need(self) -> Optional[StateNeed]:
+        return None
+
+    def forward(self, x, step, line):  # pragma: no cover - interface
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, x, step):  # pragma: no cover - interface
+        raise NotImplementedError
+
+
+class Block(Part):
+    def forward(self, resid, step, line):  # pragma: no cover - interface
+        raise NotImplementedError
