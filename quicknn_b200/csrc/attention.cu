@@ -286,12 +286,17 @@ __global__ void attn_combine_kernel(const float* __restrict__ part_o, const floa
 
 constexpr int PRE_WARPS = 4;
 
-template <typename T, int CPL, int GT>
+// One warp per (token, kv head, head tile).  PAGED = false: keys are rows of this step's
+// packed projections (k, v, row_stride, tok_row0).  PAGED = true: keys come from the paged
+// cache of the token's sequence (k = K pool, v = V pool, tok_row0 = slot per token); used
+// by a layer that reads a cache line which another layer wrote.
+template <typename T, int CPL, int GT, bool PAGED>
 __global__ void __launch_bounds__(PRE_WARPS * 32)
-attn_prefill_generic_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, size_t row_stride,
-                            T* __restrict__ out, size_t out_stride, const int* __restrict__ tok_pos,
+attn_prefill_generic_kernel(const T* __restrict__ q, size_t q_stride, const T* __restrict__ k, const T* __restrict__ v,
+                            size_t row_stride, T* __restrict__ out, size_t out_stride, const int* __restrict__ tok_pos,
                             const int* __restrict__ tok_row0, int n_tokens, int nq, int nkv, int hd, int LPT,
-                            float scale, float cap, int window) {
+                            float scale, float cap, int window, const int* __restrict__ page_table, int max_pages,
+                            int page_size, int ring) {
     constexpr int VEC = Vec16<T>::N;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x * PRE_WARPS + warp;
@@ -317,9 +322,14 @@ attn_prefill_generic_kernel(const T* __restrict__ q, const T* __restrict__ k, co
         const int end = p + 1;
         const int begin = (window > 0 && end > window) ? end - window : 0;
         float qr[GT][CPL][VEC];
-        load_query<T, CPL, GT>(q + (size_t)t * row_stride + (size_t)kh * G * hd, hd, G, gt0, LPT, chunks, scale, qr);
-        PackedKV<T> kv{k + (size_t)kh * hd, v + (size_t)kh * hd, row_stride, row0};
-        attend_range<T, CPL, GT>(qr, kv, begin, end, 0, TPW, LPT, chunks, cap, m, l, o);
+        load_query<T, CPL, GT>(q + (size_t)t * q_stride + (size_t)kh * G * hd, hd, G, gt0, LPT, chunks, scale, qr);
+        if (PAGED) {
+            PagedKV<T> kv{k, v, page_table + (size_t)row0 * max_pages, page_size, nkv, hd, ring, kh};
+            attend_range<T, CPL, GT>(qr, kv, begin, end, 0, TPW, LPT, chunks, cap, m, l, o);
+        } else {
+            PackedKV<T> kv{k + (size_t)kh * hd, v + (size_t)kh * hd, row_stride, row0};
+            attend_range<T, CPL, GT>(qr, kv, begin, end, 0, TPW, LPT, chunks, cap, m, l, o);
+        }
     }
     merge_groups<CPL, GT, VEC>(LPT, m, l, o);
     if (ti == 0) {
@@ -422,21 +432,29 @@ QNN_API int qnn_attn_decode(const void* q, long long q_stride, int dtype, const 
 }
 
 template <typename T>
-static int prefill_launch(const void* q, const void* k, const void* v, long long row_stride, void* out,
-                          long long out_stride, const int* tok_pos, const int* tok_row0, int n_tokens, int nq, int nkv,
-                          int hd, float scale, float cap, int window, cudaStream_t st) {
+static int prefill_launch(const void* q, long long q_stride, const void* k, const void* v, long long row_stride,
+                          void* out, long long out_stride, const int* tok_pos, const int* tok_row0, int n_tokens,
+                          int nq, int nkv, int hd, float scale, float cap, int window, const int* page_table,
+                          int max_pages, int page_size, int ring, bool paged, cudaStream_t st) {
     if (nkv <= 0 || nq % nkv) return QNN_ERR_ARGUMENT;
     const Geometry geo = geometry<T>(hd, nq / nkv);
     if (!geo.ok) return QNN_ERR_UNSUPPORTED;
-    if ((row_stride * sizeof(T)) % 16 || (out_stride * sizeof(T)) % 16 ||
+    if ((q_stride * sizeof(T)) % 16 || (row_stride * sizeof(T)) % 16 || (out_stride * sizeof(T)) % 16 ||
         (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)out) & 15))
         return QNN_ERR_ARGUMENT;
     const int gtiles = (nq / nkv + geo.gt - 1) / geo.gt;
     dim3 grid((n_tokens + PRE_WARPS - 1) / PRE_WARPS, nkv * gtiles);
     QNN_DISPATCH_ALL({
-        attn_prefill_generic_kernel<T, CPL, GT><<<grid, PRE_WARPS * 32, 0, st>>>(
-            (const T*)q, (const T*)k, (const T*)v, (size_t)row_stride, (T*)out, (size_t)out_stride, tok_pos, tok_row0,
-            n_tokens, nq, nkv, hd, geo.lpt, scale, cap, window);
+        if (paged)
+            attn_prefill_generic_kernel<T, CPL, GT, true><<<grid, PRE_WARPS * 32, 0, st>>>(
+                (const T*)q, (size_t)q_stride, (const T*)k, (const T*)v, (size_t)row_stride, (T*)out,
+                (size_t)out_stride, tok_pos, tok_row0, n_tokens, nq, nkv, hd, geo.lpt, scale, cap, window, page_table,
+                max_pages, page_size, ring);
+        else
+            attn_prefill_generic_kernel<T, CPL, GT, false><<<grid, PRE_WARPS * 32, 0, st>>>(
+                (const T*)q, (size_t)q_stride, (const T*)k, (const T*)v, (size_t)row_stride, (T*)out,
+                (size_t)out_stride, tok_pos, tok_row0, n_tokens, nq, nkv, hd, geo.lpt, scale, cap, window, page_table,
+                max_pages, page_size, ring);
     })
     QNN_LAUNCH_CHECK();
 }
@@ -449,8 +467,23 @@ QNN_API int qnn_attn_prefill_generic(const void* q, const void* k, const void* v
                                      cudaStream_t st) {
     if (n_tokens <= 0) return 0;
     if (dtype == QNN_DT_BF16)
-        return prefill_launch<bf16>(q, k, v, row_stride, out, out_stride, tok_pos, tok_row0, n_tokens, nq, nkv, hd,
-                                    scale, cap, window, st);
-    return prefill_launch<float>(q, k, v, row_stride, out, out_stride, tok_pos, tok_row0, n_tokens, nq, nkv, hd, scale,
-                                 cap, window, st);
+        return prefill_launch<bf16>(q, row_stride, k, v, row_stride, out, out_stride, tok_pos, tok_row0, n_tokens, nq,
+                                    nkv, hd, scale, cap, window, nullptr, 0, 1, 0, false, st);
+    return prefill_launch<float>(q, row_stride, k, v, row_stride, out, out_stride, tok_pos, tok_row0, n_tokens, nq, nkv,
+                                 hd, scale, cap, window, nullptr, 0, 1, 0, false, st);
+}
+
+// Several query rows per sequence against the paged cache: token t of the sequence in slot
+// tok_slot[t] at position tok_pos[t] sees the cached positions up to its own.  With a ring
+// the caller must make sure that no needed position has been overwritten.
+QNN_API int qnn_attn_prefill_paged(const void* q, long long q_stride, int dtype, const void* k_pool, const void* v_pool,
+                                   const int* page_table, int max_pages, int page_size, int ring, void* out,
+                                   long long out_stride, const int* tok_pos, const int* tok_slot, int n_tokens, int nq,
+                                   int nkv, int hd, float scale, float cap, int window, cudaStream_t st) {
+    if (n_tokens <= 0) return 0;
+    if (dtype == QNN_DT_BF16)
+        return prefill_launch<bf16>(q, q_stride, k_pool, v_pool, 0, out, out_stride, tok_pos, tok_slot, n_tokens, nq,
+                                    nkv, hd, scale, cap, window, page_table, max_pages, page_size, ring, true, st);
+    return prefill_launch<float>(q, q_stride, k_pool, v_pool, 0, out, out_stride, tok_pos, tok_slot, n_tokens, nq, nkv,
+                                 hd, scale, cap, window, page_table, max_pages, page_size, ring, true, st);
 }

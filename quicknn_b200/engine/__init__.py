@@ -1,6 +1,9 @@
 """Model, step function, generation loop and the Python entry point."""
 from .batch import StepBatch
 from .engine import Engine, StepError
+from .generate import GenerationBackend, GenerationResult, PromptError, generate, plan_batches
+from .llm import LLM
 from .model import Model, as_dtype
 
-__all__ = ["StepBatch", "Engine", "StepError", "Model", "as_dtype"]
+__all__ = ["StepBatch", "Engine", "StepError", "GenerationBackend", "GenerationResult", "PromptError",
+           "generate", "plan_batches", "LLM", "Model", "as_dtype"]

@@ -32,3 +32,4 @@ class StepBatch:
     decode_splits: int = 1
     part_o: Optional[torch.Tensor] = None
     part_ml: Optional[torch.Tensor] = None
+    max_q_len: int = 1              # longest run of tokens that one sequence brings

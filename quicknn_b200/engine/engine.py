@@ -42,6 +42,8 @@ class Engine:
         self.max_seq, self.max_slots = max_seq, max_slots
         self.decode_splits = int(decode_splits) if decode_splits else min(32, max(1, max_seq // 128))
         self._scratch: Dict[int, Tuple[torch.Tensor, torch.Tensor]] = {}
+        self._decode_state: Dict[int, dict] = {}
+        self.use_graphs = True
         self.error_flag = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.steps_run = 0
 
@@ -132,10 +134,58 @@ class Engine:
             o += n
         part_o, part_ml = self._scratch_for(B) if mode == "decode" else (None, None)
         step = StepBatch(mode, T, B, views[0], views[1], views[2], views[3], views[4], views[5],
-                         self.model.dtype, self.decode_splits, part_o, part_ml)
+                         self.model.dtype, self.decode_splits, part_o, part_ml, max_q_len=max(len(t) for _, t in entries))
         logits = self.model.forward(step, self.cache)
         self.steps_run += 1
         return logits
+
+    # ---- decode with ids that are already on the device -------------------------------
+    def decode(self, slots: Sequence[int], tokens_dev: torch.Tensor, use_graph: Optional[bool] = None) -> torch.Tensor:
+        """One token for each sequence in ``slots``; ``tokens_dev`` ([B] int32) stays on the
+        device (the reference feeds the sampled id from device memory too,
+        src/models/QuickNN.Models.LLM.pas:802-807).  Returns the logits of every row.
+
+        The launch sequence of a batch size is captured in a CUDA graph the first time it
+        runs and replayed afterwards; lengths, page tables and ids are read from device
+        memory by the kernels, so one graph serves every step of that batch size."""
+        B = len(slots)
+        if B < 1:
+            raise StepError("a step needs at least one sequence")
+        if len(set(slots)) != B:
+            raise StepError("a sequence appears twice in one step")
+        starts = [self.cache.length(s) for s in slots]
+        if min(starts) < 1:
+            raise StepError("decode continues sequences that have at least one token")
+        if tokens_dev.dtype != torch.int32 or tokens_dev.numel() != B or not tokens_dev.is_cuda:
+            raise StepError("decode needs one int32 id per sequence on the device")
+        self.cache.extend([(s, p + 1) for s, p in zip(slots, starts)])
+        self.cache.sync()
+        use_graph = self.use_graphs if use_graph is None else use_graph
+        st = self._decode_state.get(B)
+        if st is None:
+            meta = torch.zeros(2 * B, dtype=torch.int32, device=self.device)
+            ar = torch.arange(B, dtype=torch.int32, device=self.device)
+            part_o, part_ml = self._scratch_for(B)
+            tokens = torch.zeros(B, dtype=torch.int32, device=self.device)
+            step = StepBatch("decode", B, B, tokens, meta[:B], meta[B:], ar, meta[B:], ar, self.model.dtype,
+                             self.decode_splits, part_o, part_ml)
+            st = {"meta": meta, "step": step, "graph": None, "logits": None}
+            self._decode_state[B] = st
+        st["meta"].copy_(torch.from_numpy(np.concatenate([np.asarray(starts, np.int32), np.asarray(slots, np.int32)])))
+        st["step"].tokens.copy_(tokens_dev.reshape(-1))
+        self.steps_run += 1
+        if not use_graph:
+            return self.model.forward(st["step"], self.cache)
+        if st["graph"] is None:
+            logits = self.model.forward(st["step"], self.cache)      # eager: also warms everything up
+            torch.cuda.synchronize(self.device)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                st["logits"] = self.model.forward(st["step"], self.cache)
+            st["graph"] = g
+            return logits
+        st["graph"].replay()
+        return st["logits"]
 
     def stats(self) -> Dict[str, int]:
         return {"weight_bytes": self.model.weight_bytes(), "cache_bytes": self.cache.bytes(),

@@ -1,0 +1,140 @@
+"""The Python entry point, in the manner of the reference's ``TQNNLLM``
+(src/models/QuickNN.Models.LLM.pas:55-77): ``Create(ModelDir, ..., MaxContext)``,
+``Generate(..., Options, OnToken)``, ``EvaluateTokens(Ids)``, ``ResetContext``,
+``MemoryStatus``.  The interface is token ids; there is no tokenizer.
+"""
+from __future__ import annotations
+
+from typing import Callable, Dict, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..config.base import Architecture, ModelConfig, find_architecture
+from ..sampling import GenerationOptions, Sampler
+from ..weights.random_init import random_tensors
+from .engine import Engine
+from .generate import GenerationBackend, GenerationResult, generate
+from .model import Model, as_dtype
+
+PAGE = 64
+
+
+class _Backend(GenerationBackend):
+    def __init__(self, engine: Engine, sampler: Sampler, max_batch: int):
+        self.engine, self.sampler = engine, sampler
+        self.max_batch = max_batch
+        self.max_tokens = engine.cache.max_tokens
+        self.max_seq = engine.max_seq
+        self.vocab_size = engine.model.spec.embedding.vocab_size
+        self.slots: List[int] = []
+        self.last: Optional[torch.Tensor] = None
+
+    def begin(self, first_index: int, prompts: Sequence[Sequence[int]]) -> np.ndarray:
+        eng = self.engine
+        self.slots = [eng.new_sequence() for _ in prompts]
+        self.sampler.start(first_index, len(prompts))
+        if self.sampler.penalised:
+            toks = torch.tensor([t for p in prompts for t in p], dtype=torch.int32, device=eng.device)
+            rows = torch.tensor([r for r, p in enumerate(prompts) for _ in p], dtype=torch.int32, device=eng.device)
+            self.sampler.mark_prompt(toks, rows)
+        logits = eng.step(list(zip(self.slots, prompts)), "last")
+        self.last = self.sampler(logits)
+        return self.sampler.read(self.last)
+
+    def advance(self, keep_rows: Sequence[int]) -> np.ndarray:
+        eng = self.engine
+        keep = list(keep_rows)
+        if len(keep) != len(self.slots):
+            for r, s in enumerate(self.slots):
+                if r not in keep:
+                    eng.release(s)
+            self.slots = [self.slots[r] for r in keep]
+            idx = torch.tensor(keep, dtype=torch.long, device=eng.device)
+            tokens = self.last[idx].contiguous()
+            self.sampler.compact(keep)
+        else:
+            tokens = self.last
+        logits = eng.decode(self.slots, tokens)
+        self.last = self.sampler(logits)
+        return self.sampler.read(self.last)
+
+    def finish(self) -> None:
+        for s in self.slots:
+            self.engine.release(s)
+        self.slots = []
+        self.last = None
+
+
+class LLM:
+    """A loaded model with its cache, ready to generate.
+
+    ``LLM(model_dir, max_context=...)`` loads a folder with ``config.json`` and
+    ``model.safetensors``; ``LLM.random(config, seed)`` builds random weights on the
+    device.  ``max_context`` is the reference's ``MaxContext``: the longest sequence
+    (prompt plus generated) a request may reach."""
+
+    def __init__(self, model_dir: Optional[str] = None, *, max_context: int = 2048, max_batch: int = 8,
+                 max_tokens: Optional[int] = None, dtype="bfloat16", device="cuda:0", model: Optional[Model] = None,
+                 decode_splits: Optional[int] = None):
+        if model is None:
+            if model_dir is None:
+                raise ValueError("give a model folder or a Model")
+            model = Model.from_folder(model_dir, dtype, device)
+        self.model = model
+        if max_context > model.spec.max_positions:
+            raise ValueError(f"max_context {max_context} exceeds max_position_embeddings {model.spec.max_positions}")
+        if max_tokens is None:
+            max_tokens = max_batch * ((max_context + PAGE - 1) // PAGE * PAGE)
+        self.max_batch = max_batch
+        self.engine = Engine(model, max_tokens=max_tokens, max_slots=max(max_batch, 1), max_seq=max_context,
+                             decode_splits=decode_splits)
+        self._samplers: Dict[tuple, Sampler] = {}
+
+    @classmethod
+    def random(cls, config: Dict, seed: int = 0, *, dtype="bfloat16", device="cuda:0", norm_std: Optional[float] = None,
+               **kw) -> "LLM":
+        arch = find_architecture(config)
+        cfg = arch.config_cls.from_dict(config)
+        cd = as_dtype(dtype)
+        tensors = dict(random_tensors(arch, cfg, seed, cd, norm_std, device=device))
+        model = Model(arch, cfg, tensors, cd, device)
+        return cls(model=model, dtype=dtype, device=device, **kw)
+
+    @property
+    def stop_ids(self) -> List[int]:
+        """Stop ids from the configuration's ``eos_token_id`` (LLM.pas:166)."""
+        return list(self.model.spec.stop_ids)
+
+    def _sampler(self, options: GenerationOptions) -> Sampler:
+        key = (options.top_k, options.temperature, options.top_p, options.repetition_penalty, options.seed)
+        s = self._samplers.get(key)
+        if s is None:
+            if len(self._samplers) > 4:
+                self._samplers.clear()
+            s = Sampler(self.model.spec.embedding.vocab_size, self.max_batch, options, self.engine.device)
+            self._samplers[key] = s
+        return s
+
+    def generate(self, prompts: Sequence[Sequence[int]], options: Optional[GenerationOptions] = None,
+                 on_token: Optional[Callable[[int, int], Optional[bool]]] = None,
+                 stop_ids: Optional[Sequence[int]] = None,
+                 should_cancel: Optional[Callable[[], bool]] = None) -> List[GenerationResult]:
+        """Generate for a list of prompts (lists of token ids).  Requests are run in batches of
+        up to ``max_batch``, one batch after another."""
+        options = options or GenerationOptions()
+        options.validate()
+        backend = _Backend(self.engine, self._sampler(options), self.max_batch)
+        stops = self.stop_ids if stop_ids is None else list(stop_ids)
+        return generate(backend, prompts, options, stops, on_token, should_cancel)
+
+    def evaluate_tokens(self, ids: Sequence[int]) -> np.ndarray:
+        """Logits after the last of ``ids`` as a host array (``EvaluateTokens``, LLM.pas:1064-1088)."""
+        slot = self.engine.new_sequence()
+        try:
+            return self.engine.step([(slot, list(ids))], "last")[0].cpu().numpy()
+        finally:
+            self.engine.release(slot)
+
+    def memory_status(self) -> Dict[str, int]:
+        return self.engine.stats()

@@ -248,6 +248,25 @@ def attn_prefill(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, tok_
     return out
 
 
+def attn_prefill_paged(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, k_pool: torch.Tensor,
+                       v_pool: torch.Tensor, page_table: torch.Tensor, page_size: int, ring: int,
+                       tok_pos: torch.Tensor, tok_slot: torch.Tensor, scale: float, cap: Optional[float],
+                       window: Optional[int]):
+    """Several query rows per sequence against the paged cache (keys written earlier in the
+    same step by the layer that owns the line).  q = the first nq*hd columns of qkv."""
+    _req(qkv, "qkv", None, 2)
+    _req(k_pool, "k_pool", qkv.dtype, 4)
+    _req(v_pool, "v_pool", qkv.dtype, 4)
+    T = qkv.shape[0]
+    out = torch.empty((T, n_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
+    L = _lib.load()
+    _lib.check(L.qnn_attn_prefill_paged(
+        _p(qkv), qkv.shape[1], dt_code(qkv), _p(k_pool), _p(v_pool), _p(page_table), page_table.shape[1],
+        page_size, ring, _p(out), out.shape[1], _p(tok_pos), _p(tok_slot), T, n_heads, n_kv, head_dim,
+        float(scale), float(cap or 0.0), int(window or 0), _stream()), "attn_prefill_paged")
+    return out
+
+
 def attn_decode(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, k_pool: torch.Tensor,
                 v_pool: torch.Tensor, page_table: torch.Tensor, page_size: int, ring: int,
                 slots: torch.Tensor, slot_len: torch.Tensor, scale: float, cap: Optional[float],

@@ -66,7 +66,15 @@ class AttentionMixer(Mixer):
         ops.rope_cache_write(qkv, self.n_heads, self.n_kv, self.head_dim, self.position.rotary_dim,
                              self.position.inv_freq, step.tok_pos, step.tok_slot, line.k, line.v,
                              line.page_table, line.page_size, line.ring, line.slot_len, line.writes)
-        if step.mode == "prefill":
+        if step.mode == "prefill" and not line.writes:
+            # the keys of this line were written by another layer earlier in this step
+            if line.ring and step.max_q_len > line.ring:
+                raise ValueError(f"a prompt of {step.max_q_len} tokens has overrun the ring of {line.ring} "
+                                 f"positions that this layer reads from another layer's cache line")
+            a = ops.attn_prefill_paged(qkv, self.n_heads, self.n_kv, self.head_dim, line.k, line.v,
+                                       line.page_table, line.page_size, line.ring, step.tok_pos, step.tok_slot,
+                                       self.scale, self.softcap, self.window)
+        elif step.mode == "prefill":
             a = ops.attn_prefill(qkv, self.n_heads, self.n_kv, self.head_dim, step.tok_pos, step.tok_row0,
                                  self.scale, self.softcap, self.window)
         else:

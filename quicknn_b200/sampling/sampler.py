@@ -1,0 +1,74 @@
+"""Device-side token selection for a batch of rows (see csrc/sampling.cu)."""
+from __future__ import annotations
+
+from typing import Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..kernels import ops
+from .options import GenerationOptions, seed_state
+
+
+class NonFiniteLogits(RuntimeError):
+    """NaN or Inf in the logits (the reference raises "non-finite values" at the next
+    readback, QuickNN.Vulkan.Context.Implementation.inc:732-756)."""
+
+
+class Sampler:
+    """Greedy when ``temperature`` is 0 (k forced to 1), else top-k / temperature /
+    nucleus sampling with an optional repetition penalty.  One generator state per row."""
+
+    def __init__(self, vocab_size: int, max_rows: int, options: GenerationOptions, device):
+        options.validate()
+        self.vocab, self.max_rows, self.options, self.device = vocab_size, max_rows, options, device
+        self.rng = torch.zeros(max_rows, dtype=torch.int32, device=device)
+        self.out = torch.zeros(max_rows, dtype=torch.int32, device=device)
+        self.flag = torch.zeros(1, dtype=torch.int32, device=device)
+        nbytes = ops.sample_scratch_bytes(max_rows, vocab_size, options.top_k)
+        if nbytes < 0:
+            raise ValueError("sampling scratch would exceed 2 GiB; lower the batch")
+        self.scratch = torch.empty(max(nbytes, 8), dtype=torch.uint8, device=device)
+        self.penalised = options.repetition_penalty != 1.0
+        self.seen: Optional[torch.Tensor] = None
+        if self.penalised:
+            self.seen = torch.zeros((max_rows, vocab_size), dtype=torch.uint8, device=device)
+
+    def start(self, first_index: int, n_rows: int) -> None:
+        """Seed rows 0..n_rows-1 for the requests first_index, first_index+1, ..."""
+        states = np.array([seed_state(self.options.seed, first_index + i) for i in range(n_rows)], dtype=np.uint32)
+        self.rng[:n_rows].copy_(torch.from_numpy(states.view(np.int32)))
+        if self.seen is not None:
+            self.seen[:n_rows].zero_()
+
+    def mark_prompt(self, tokens: torch.Tensor, rows: torch.Tensor) -> None:
+        """Prompt ids count as seen (src/models/QuickNN.Models.LLM.pas:735-742)."""
+        if self.seen is not None:
+            ops.mark_seen(tokens, rows, self.seen)
+
+    def compact(self, keep_rows: Sequence[int]) -> None:
+        """Rows that stay alive move to the front, in order."""
+        idx = torch.tensor(list(keep_rows), dtype=torch.long, device=self.device)
+        n = len(keep_rows)
+        self.rng[:n] = self.rng[idx]
+        if self.seen is not None:
+            self.seen[:n] = self.seen[idx]
+
+    def __call__(self, logits: torch.Tensor) -> torch.Tensor:
+        """logits [R, V] float32 -> chosen ids [R] int32 (device)."""
+        R = logits.shape[0]
+        o = self.options
+        seen_rows = None
+        if self.seen is not None:
+            seen_rows = torch.arange(R, dtype=torch.int32, device=self.device)
+        ops.sample(logits, o.top_k, o.temperature, o.top_p, o.repetition_penalty, self.rng, self.seen,
+                   seen_rows, self.scratch, self.out, self.flag)
+        return self.out[:R]
+
+    def read(self, tokens: torch.Tensor) -> np.ndarray:
+        """Chosen ids and the error word in one device-to-host read."""
+        both = torch.cat([tokens, self.flag]).cpu().numpy()
+        if both[-1] != 0:
+            self.flag.zero_()
+            raise NonFiniteLogits("the model produced non-finite logits")
+        return both[:-1]

@@ -17,6 +17,7 @@ import json
 import mmap
 import os
 import struct
+import warnings
 from typing import Dict, Iterable, List, Mapping, Optional, Tuple
 
 import torch
@@ -141,7 +142,10 @@ class SafetensorsFile:
             count *= d
         if count == 0:
             return torch.empty(e.shape, dtype=e.dtype)
-        t = torch.frombuffer(self._mm, dtype=e.dtype, count=count, offset=self.data_start + e.begin)
+        with warnings.catch_warnings():
+            # the map is read-only on purpose; nothing here writes through the tensor
+            warnings.filterwarnings("ignore", message="The given buffer is not writable")
+            t = torch.frombuffer(self._mm, dtype=e.dtype, count=count, offset=self.data_start + e.begin)
         return t.view(e.shape)
 
     def close(self) -> None:

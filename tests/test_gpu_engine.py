@@ -1,0 +1,197 @@
+"""The engine in process: long decoding, the first tokens of a sequence, padding, captured
+decode steps, greedy and sampled generation through the Python entry point."""
+import numpy as np
+import pytest
+import torch
+
+from plain import gemma2_plain as P
+from conftest import TINY, close, prompts_for
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _need_gpu():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+
+
+def build(folder, dtype, **kw):
+    from quicknn_b200.engine import Engine, Model
+    return Engine(Model.from_folder(folder, dtype, DEV), **kw)
+
+
+@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("B", "bfloat16")])
+def test_long_decoding_matches_whole_sequences(folders, plain_models, name, dtype):
+    """400 tokens decoded one by one (pages fill and new ones are taken, the window slides over
+    the ring several times), eager and through the captured graph, against one plain pass."""
+    eng = build(folders(name, dtype), dtype, max_tokens=1024, decode_splits=3)
+    seqs = prompts_for(name, [420, 401])
+    ref = [plain_models(name, dtype).logits(s) for s in seqs]
+    slots = [eng.new_sequence(), eng.new_sequence()]
+    starts = [20, 1]
+    got = eng.step([(s, q[:n]) for s, q, n in zip(slots, seqs, starts)], "last").cpu().numpy()
+    for r in range(2):
+        ok, err, tol = close(got[r], ref[r][starts[r] - 1], dtype)
+        assert ok, ("prompt", r, err, tol)
+    worst = 0.0
+    for step in range(400):
+        toks = torch.tensor([seqs[r][starts[r] + step] for r in range(2)], dtype=torch.int32, device=DEV)
+        got = eng.decode(slots, toks, use_graph=(step % 2 == 0)).cpu().numpy()
+        for r in range(2):
+            ok, err, tol = close(got[r], ref[r][starts[r] + step], dtype)
+            worst = max(worst, err)
+            assert ok, (f"step {step} row {r}", err, tol)
+    for s in slots:
+        eng.release(s)
+    eng.cache.audit()
+    print(f"long decoding tiny {name} {dtype}: largest error {worst:.3g}")
+
+
+@pytest.mark.parametrize("name,dtype", [("A", "bfloat16"), ("B", "float32")])
+def test_first_tokens_of_a_sequence(folders, plain_models, name, dtype):
+    """Prompts of one, two and three tokens, then the first decoded tokens: the places where a
+    sequence has fewer keys than a window, a page or a split."""
+    eng = build(folders(name, dtype), dtype, max_tokens=512, decode_splits=4)
+    plain = plain_models(name, dtype)
+    seqs = prompts_for(name, [12, 12, 12], seed=5)
+    slots = [eng.new_sequence() for _ in seqs]
+    got = eng.step([(s, q[:n]) for s, q, n in zip(slots, seqs, (1, 2, 3))], "all").cpu().numpy()
+    ref = [plain.logits(q) for q in seqs]
+    want = np.concatenate([ref[0][:1], ref[1][:2], ref[2][:3]])
+    ok, err, tol = close(got, want, dtype)
+    assert ok, (err, tol)
+    pos = [1, 2, 3]
+    for _ in range(8):
+        got = eng.step([(s, [q[p]]) for s, q, p in zip(slots, seqs, pos)]).cpu().numpy()
+        for r in range(3):
+            ok, err, tol = close(got[r], ref[r][pos[r]], dtype)
+            assert ok, (r, pos[r], err, tol)
+            pos[r] += 1
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_padding_rows_change_no_result(folders, dtype):
+    """The same decode step with and without padding rows (negative slot) in the batch."""
+    from quicknn_b200.engine.batch import StepBatch
+    eng = build(folders("B", dtype), dtype, max_tokens=512, decode_splits=2)
+    seqs = prompts_for("B", [30, 9])
+    slots = [eng.new_sequence(), eng.new_sequence()]
+    eng.step(list(zip(slots, seqs)))
+    nxt = [11, 12]
+    base = eng.step([(s, [t]) for s, t in zip(slots, nxt)]).cpu().numpy()
+    # run the same step again by hand, with padding rows around the real ones: the cache already
+    # holds these positions, the rewrite stores identical values
+    i32 = lambda a: torch.tensor(a, dtype=torch.int32, device=DEV)  # noqa: E731
+    po, pm = eng._scratch_for(5)
+    step = StepBatch("decode", 5, 5, i32([3, nxt[0], 4, nxt[1], 5]), i32([0, 30, 0, 9, 0]),
+                     i32([-1, slots[0], -1, slots[1], -1]), i32([0, 1, 2, 3, 4]),
+                     i32([-1, slots[0], -1, slots[1], -1]), i32([1, 3]), eng.model.dtype, eng.decode_splits, po, pm)
+    again = eng.model.forward(step, eng.cache).cpu().numpy()
+    assert np.array_equal(again, base)
+
+
+@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("B", "float32"), ("A", "bfloat16")])
+def test_greedy_generation_through_the_entry_point(folders, plain_models, name, dtype):
+    from quicknn_b200.engine import LLM
+    from quicknn_b200.sampling import GenerationOptions
+    plain = plain_models(name, dtype)
+    llm = LLM(folders(name, dtype), max_context=128, max_batch=3, dtype=dtype)
+    lens = [5, 11, 17] if name == "A" else [1, 6, 13, 29]
+    prompts = prompts_for(name, lens)
+    steps = 8 if name == "A" else 12
+    streamed = {}
+    res = llm.generate(prompts, GenerationOptions.greedy(steps), stop_ids=[],
+                       on_token=lambda i, t: streamed.setdefault(i, []).append(t))
+    for r, p in zip(res, prompts):
+        assert r.finish_reason == "max_tokens" and r.generated_tokens == steps
+        assert streamed[r.index] == r.tokens
+        if dtype == "float32":
+            assert r.tokens == plain.greedy(p, steps), f"request {r.index}"
+        else:
+            # bfloat16 may break a near-tie differently; every chosen token must be the plain model's
+            # best or within the tolerance of it, given the same history
+            seq = list(p)
+            for t in r.tokens:
+                row = plain.logits(seq)[-1]
+                assert row[t] >= row.max() - 0.06 * max(1.0, np.abs(row).max()), (r.index, len(seq))
+                seq.append(t)
+    # stop tokens: the token that the plain model generates third ends request 0 after two tokens
+    ref0 = plain.greedy(prompts[0], steps)
+    if dtype == "float32" and ref0[2] not in ref0[:2]:
+        res = llm.generate(prompts[:2], GenerationOptions.greedy(steps), stop_ids=[ref0[2]])
+        assert res[0].tokens == ref0[:2] and res[0].finish_reason == "eos"
+        ref1 = plain.greedy(prompts[1], steps, stop_ids=[ref0[2]])
+        assert res[1].tokens == ref1
+    assert llm.engine.cache.slots.live() == []
+    llm.engine.cache.audit()
+    assert np.abs(llm.evaluate_tokens(prompts[1]) - plain.logits(prompts[1])[-1]).max() < (1e-4 if dtype == "float32" else 0.1)
+
+
+def test_more_requests_than_slots_reuse_them(folders, plain_models):
+    from quicknn_b200.engine import LLM
+    from quicknn_b200.sampling import GenerationOptions
+    plain = plain_models("B", "float32")
+    llm = LLM(folders("B", "float32"), max_context=64, max_batch=2, dtype="float32")
+    prompts = prompts_for("B", [3, 20, 7, 1, 15], seed=9)
+    res = llm.generate(prompts, GenerationOptions.greedy(6), stop_ids=[])
+    for r, p in zip(res, prompts):
+        assert r.tokens == plain.greedy(p, 6)
+    assert llm.memory_status()["live_sequences"] == 0
+
+
+def test_temperature_sampling_is_seeded_and_follows_the_plain_sampler(folders, plain_models):
+    from quicknn_b200.engine import LLM
+    from quicknn_b200.sampling import GenerationOptions
+    llm = LLM(folders("B", "float32"), max_context=64, max_batch=4, dtype="float32")
+    prompts = prompts_for("B", [1, 6, 13, 29])
+    opt = GenerationOptions(max_new_tokens=12, temperature=0.8, seed=1234)
+    a = llm.generate(prompts, opt, stop_ids=[])
+    b = llm.generate(prompts, opt, stop_ids=[])
+    assert [r.tokens for r in a] == [r.tokens for r in b]
+    c = llm.generate(prompts, GenerationOptions(max_new_tokens=12, temperature=0.8, seed=99), stop_ids=[])
+    assert [r.tokens for r in a] != [r.tokens for r in c]
+    # the same draws with the plain model and the plain sampler: request i uses seed + i
+    plain = plain_models("B", "float32")
+    for i, (r, p) in enumerate(zip(a, prompts)):
+        st = P.seed_state(1234 + i)
+        seq = list(p)
+        for t in r.tokens:
+            st, u = P.xorshift32(st)
+            row = plain.logits(seq)[-1]
+            ref = P.sample(row.astype(np.float32), 0.8, 20, 0.95, 1.0, None, u)
+            if ref != t:
+                # the engine's float32 logits differ from the float64 ones by rounding; a draw that
+                # falls within that distance of a boundary may land on the neighbour
+                order = np.argsort(-row)[:20]
+                assert t in order, (i, len(seq))
+            seq.append(t)
+    # repetition penalty and top-k 1 run and stay reproducible
+    o2 = GenerationOptions(max_new_tokens=8, temperature=1.0, top_k=5, repetition_penalty=1.5, seed=3)
+    d1 = llm.generate(prompts[:2], o2, stop_ids=[])
+    d2 = llm.generate(prompts[:2], o2, stop_ids=[])
+    assert [r.tokens for r in d1] == [r.tokens for r in d2]
+
+
+def test_step_rules_and_loud_failures(folders):
+    from quicknn_b200.cache import CacheFull
+    from quicknn_b200.engine import StepError
+    eng = build(folders("A", "float32"), "float32", max_tokens=128)
+    a, b = eng.new_sequence(), eng.new_sequence()
+    eng.step([(a, [5, 6, 7])])
+    with pytest.raises(StepError):
+        eng.step([(a, [8]), (b, [5, 6])])          # one goes on, one starts
+    with pytest.raises(StepError):
+        eng.step([(a, [8, 9])])                     # more than one token onto a started sequence
+    with pytest.raises(StepError):
+        eng.step([(b, [600])])                      # outside the vocabulary
+    with pytest.raises(StepError):
+        eng.step([(b, [5])], want=[[1]])            # a wanted place that the step does not bring
+    with pytest.raises(CacheFull):
+        eng.step([(b, list(range(1, 100)))])        # 64 (held by a) + 128 > 128 tokens
+    assert eng.length(a) == 3 and eng.length(b) == 0
+    eng.cache.audit()
+    with pytest.raises(Exception):
+        from quicknn_b200.engine import Model
+        Model.from_folder(folders("A", "float32"), "float32", "cpu").forward(None, None)

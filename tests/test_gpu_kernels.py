@@ -1,0 +1,441 @@
+"""Each CUDA kernel alone against its plain reference, at sizes other than the engine's:
+widths and vocabularies that are no power of two, head sizes in steps of 8 and 16, any
+number of heads and groups, float32 and bfloat16."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from plain import gemma2_plain as P
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def ops():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from quicknn_b200.kernels import ops as o
+    return o
+
+
+def T(a, dtype):
+    return torch.from_numpy(np.asarray(a)).to(DEV).to(dtype).contiguous()
+
+
+def N(t):
+    return t.detach().float().cpu().numpy().astype(np.float64)
+
+
+def bf16_round(a):
+    return torch.from_numpy(np.asarray(a, dtype=np.float32)).to(torch.bfloat16).float().numpy().astype(np.float64)
+
+
+TOL = {torch.float32: 2e-6, torch.bfloat16: 1.0 / 128}
+
+
+def assert_close(got, ref, dtype, what="", mult=1.0):
+    ref = np.asarray(ref, dtype=np.float64)
+    scale = max(1e-30, float(np.abs(ref).max()))
+    g = N(got) if isinstance(got, torch.Tensor) else np.asarray(got, dtype=np.float64)
+    err = float(np.abs(g - ref).max())
+    assert err <= TOL[dtype] * mult * scale, f"{what}: error {err:.3g} > {TOL[dtype] * mult * scale:.3g}"
+
+
+# ---- embedding, norms, elementwise --------------------------------------------------
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embed(ops, dtype):
+    rng = np.random.default_rng(0)
+    table = bf16_round(rng.normal(size=(37, 100)))
+    ids = np.array([0, 36, 5, 37, -1, 12], dtype=np.int32)
+    out = ops.embed(T(ids, torch.int32), T(table, dtype), math.sqrt(100))
+    ref = P.embed(table, ids.tolist(), 100, np.float64)
+    assert out.dtype == torch.float32
+    assert_close(out, ref, torch.float32, "embed")
+    assert float(out[3].abs().sum()) == 0.0 and float(out[4].abs().sum()) == 0.0   # ids outside the table
+
+
+@pytest.mark.parametrize("H", [8, 100, 2304])
+@pytest.mark.parametrize("act,wdt", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16),
+                                     (torch.bfloat16, torch.float32)])
+def test_rmsnorm_and_fused_residual(ops, H, act, wdt):
+    rng = np.random.default_rng(H)
+    x = rng.normal(size=(5, H)) * 3
+    y = bf16_round(rng.normal(size=(5, H)))
+    w1, w2 = bf16_round(rng.normal(size=H) * 0.2), bf16_round(rng.normal(size=H) * 0.2)
+    out = ops.rmsnorm(T(x, torch.float32), T(w1, wdt), 1e-5, True, act)
+    assert_close(out, P.rmsnorm(x.astype(np.float32).astype(np.float64), w1, 1e-5), act, "rmsnorm(1+w)")
+    out = ops.rmsnorm(T(y, act), T(w1, wdt), 1e-6, False, act)
+    assert_close(out, P.rmsnorm(y, w1 - 1.0, 1e-6), act, "rmsnorm(w)")
+    resid = T(x, torch.float32)
+    x32 = N(resid)
+    nxt = ops.add_rmsnorm(resid, T(y, act), T(w1, wdt), 1e-5, True, T(w2, wdt), 1e-6, True, act)
+    r_ref = x32 + P.rmsnorm(y, w1, 1e-5)
+    assert_close(resid, r_ref, torch.float32, "residual", mult=4)
+    assert_close(nxt, P.rmsnorm(r_ref, w2, 1e-6), act, "next norm")
+    resid2 = T(x, torch.float32)
+    assert ops.add_rmsnorm(resid2, T(y, act), T(w1, wdt), 1e-5, True) is None
+    assert_close(resid2, r_ref, torch.float32, "residual only", mult=4)
+    ops.add_(resid2, T(y, act))
+    assert_close(resid2, r_ref + y, torch.float32, "add", mult=4)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_gated_activation_softcap_gather_cast(ops, dtype):
+    rng = np.random.default_rng(3)
+    gu = bf16_round(rng.normal(size=(7, 2 * 50)) * 2)
+    out = ops.gated_act(T(gu, dtype), "gelu_tanh")
+    assert_close(out, P.gelu_tanh(gu[:, :50]) * gu[:, 50:], dtype, "geglu")
+    out = ops.gated_act(T(gu, dtype), "silu")
+    g = gu[:, :50]
+    assert_close(out, g / (1 + np.exp(-g)) * gu[:, 50:], dtype, "swiglu")
+    x = bf16_round(rng.normal(size=(3, 33)) * 40)
+    assert_close(ops.softcap(T(x, dtype), 15.0), P.softcap(x, 15.0), torch.float32, "softcap")
+    assert_close(ops.softcap(T(x, dtype), None), x, torch.float32, "softcap off")
+    rows = T(np.array([2, 0, 2], dtype=np.int32), torch.int32)
+    assert_close(ops.gather_rows(T(x, dtype), rows, torch.float32), x[[2, 0, 2]], torch.float32, "gather")
+    assert ops.cast(T(x, torch.float32), torch.bfloat16).dtype == torch.bfloat16
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops.check_finite(T(x, torch.float32), flag)
+    assert int(flag) == 0
+    x[1, 5] = np.inf
+    ops.check_finite(T(x, torch.float32), flag)
+    assert int(flag) == 1
+
+
+# ---- matrix products ------------------------------------------------------------------
+
+@pytest.mark.parametrize("M", [1, 5, 8, 17, 33, 64])
+@pytest.mark.parametrize("N_,K", [(50, 96), (1000, 200), (2304, 2304), (24, 8)])
+def test_skinny_bf16(ops, M, N_, K):
+    rng = np.random.default_rng(M * 1000 + N_)
+    x, w = bf16_round(rng.normal(size=(M, K))), bf16_round(rng.normal(size=(N_, K)) / math.sqrt(K))
+    ref = x @ w.T
+    y = ops.linear(T(x, torch.bfloat16), T(w, torch.bfloat16))
+    assert y.dtype == torch.bfloat16 and tuple(y.shape) == (M, N_)
+    assert_close(y, ref, torch.bfloat16, "skinny")
+    y = ops.linear(T(x, torch.bfloat16), T(w, torch.bfloat16), epilogue=ops.EPI_SOFTCAP, cap=2.0)
+    assert y.dtype == torch.float32
+    assert_close(y, P.softcap(ref, 2.0), torch.float32, "skinny softcap", mult=50)
+    y = ops.linear(T(x, torch.bfloat16), T(w, torch.bfloat16), epilogue=ops.EPI_GATED, activation="gelu_tanh")
+    h = N_ // 2
+    assert tuple(y.shape) == (M, h)
+    assert_close(y, P.gelu_tanh(ref[:, :h]) * ref[:, h:], torch.bfloat16, "skinny geglu")
+
+
+def test_bf16_products_refuse_odd_inner_sizes(ops):
+    from quicknn_b200.kernels.lib import KernelError
+    with pytest.raises(KernelError):
+        ops.linear(torch.zeros(2, 12, dtype=torch.bfloat16, device=DEV), torch.zeros(4, 12, dtype=torch.bfloat16, device=DEV))
+    with pytest.raises(TypeError):
+        ops.linear(torch.zeros(2, 16, dtype=torch.bfloat16, device=DEV), torch.zeros(4, 16, device=DEV))
+
+
+@pytest.mark.parametrize("M", [65, 200])
+def test_bf16_large_m_library_product_with_epilogues(ops, M):
+    rng = np.random.default_rng(M)
+    x, w = bf16_round(rng.normal(size=(M, 96))), bf16_round(rng.normal(size=(40, 96)) / 10)
+    ref = x @ w.T
+    assert_close(ops.linear(T(x, torch.bfloat16), T(w, torch.bfloat16)), ref, torch.bfloat16, "gemm")
+    y = ops.linear(T(x, torch.bfloat16), T(w, torch.bfloat16), epilogue=ops.EPI_GATED)
+    assert_close(y, P.gelu_tanh(bf16_round(ref[:, :20])) * bf16_round(ref[:, 20:]), torch.bfloat16, "gemm geglu", mult=2)
+    y = ops.linear(T(x, torch.bfloat16), T(w, torch.bfloat16), epilogue=ops.EPI_SOFTCAP, cap=3.0)
+    assert y.dtype == torch.float32
+    assert_close(y, P.softcap(bf16_round(ref), 3.0), torch.float32, "gemm softcap", mult=4000)
+
+
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 70, 130])
+@pytest.mark.parametrize("N_,K", [(50, 96), (130, 50), (1000, 200), (7, 3)])
+def test_fp32_products_are_true_fp32(ops, M, N_, K):
+    rng = np.random.default_rng(M + N_)
+    # values with 24 significant bits: a tf32 or bf16 product would be off by 1e-3
+    x = rng.normal(size=(M, K)).astype(np.float32)
+    w = (rng.normal(size=(N_, K)) / math.sqrt(K)).astype(np.float32)
+    ref = x.astype(np.float64) @ w.astype(np.float64).T
+    y = ops.linear(T(x, torch.float32), T(w, torch.float32))
+    assert_close(y, ref, torch.float32, "fp32 product", mult=2)
+    y = ops.linear(T(x, torch.float32), T(w, torch.float32), epilogue=ops.EPI_SOFTCAP, cap=1.5)
+    assert_close(y, P.softcap(ref, 1.5), torch.float32, "fp32 softcap", mult=2)
+    if N_ % 2 == 0:
+        y = ops.linear(T(x, torch.float32), T(w, torch.float32), epilogue=ops.EPI_GATED)
+        h = N_ // 2
+        assert_close(y, P.gelu_tanh(ref[:, :h]) * ref[:, h:], torch.float32, "fp32 geglu", mult=4)
+
+
+# ---- rotation and the cache write -----------------------------------------------------
+
+def _pools(pages, nkv, hd, dtype):
+    k = torch.zeros((pages, nkv, 64, hd), dtype=dtype, device=DEV)
+    return k, torch.zeros_like(k)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nq,nkv,hd,rot,theta", [(4, 2, 16, 16, 1e4), (6, 1, 24, 24, 1e6), (3, 3, 32, 8, 100.0),
+                                                 (2, 2, 16, 0, 1e4)])
+def test_rope_and_cache_write(ops, dtype, nq, nkv, hd, rot, theta):
+    rng = np.random.default_rng(hd + rot)
+    lens = [70, 3]                                # sequence 0 crosses a page boundary
+    slots = [2, 0]
+    Tn = sum(lens)
+    qkv = bf16_round(rng.normal(size=(Tn, (nq + 2 * nkv) * hd)))
+    pos = np.concatenate([np.arange(n) for n in lens]).astype(np.int32)
+    slot = np.concatenate([np.full(n, s) for n, s in zip(lens, slots)]).astype(np.int32)
+    table = np.zeros((3, 4), dtype=np.int32)
+    table[2, :2] = [5, 3]
+    table[0, :1] = [1]
+    slot_len = np.array([3, 0, 70], dtype=np.int32)
+    k_pool, v_pool = _pools(7, nkv, hd, dtype)
+    inv = torch.exp(-math.log(theta) * 2.0 * torch.arange(rot // 2, dtype=torch.float64) / max(rot, 1)).float().to(DEV)
+    t = T(qkv, dtype)
+    ops.rope_cache_write(t, nq, nkv, hd, rot, inv, T(pos, torch.int32), T(slot, torch.int32), k_pool, v_pool,
+                         T(table, torch.int32), 64, 0, T(slot_len, torch.int32), True)
+    q = qkv[:, :nq * hd].reshape(Tn, nq, hd)
+    k = qkv[:, nq * hd:(nq + nkv) * hd].reshape(Tn, nkv, hd)
+    v = qkv[:, (nq + nkv) * hd:].reshape(Tn, nkv, hd)
+
+    def rot_ref(x):
+        if rot == 0:
+            return x
+        return np.concatenate([P.rope(x[..., :rot], pos, theta), x[..., rot:]], axis=-1)
+    got = N(t)
+    assert_close(got[:, :nq * hd], rot_ref(q).reshape(Tn, -1), dtype, "q", mult=2)
+    assert_close(got[:, nq * hd:(nq + nkv) * hd], rot_ref(k).reshape(Tn, -1), dtype, "k", mult=2)
+    assert np.array_equal(got[:, (nq + nkv) * hd:], v.reshape(Tn, -1))
+    kr = rot_ref(k)
+    kp, vp = N(k_pool), N(v_pool)
+    for r in range(Tn):
+        page = table[slot[r], pos[r] // 64]
+        assert_close(kp[page, :, pos[r] % 64, :], kr[r], dtype, "cached k", mult=2)
+        assert np.array_equal(vp[page, :, pos[r] % 64, :], v[r])
+    assert float(np.abs(kp[0]).sum()) == 0.0 and float(np.abs(kp[2]).sum()) == 0.0   # nobody's pages untouched
+    assert float(np.abs(kp[5, :, 6:, :]).sum()) != 0.0 and float(np.abs(kp[3, :, 6:, :]).sum()) == 0.0
+
+
+def test_cache_write_ring_and_padding(ops):
+    """A prompt longer than the ring leaves its last `ring` positions, each in its place; a
+    row with a negative slot writes nothing."""
+    nq, nkv, hd = 2, 1, 16
+    n = 150
+    qkv = np.zeros((n + 1, (nq + 2 * nkv) * hd), dtype=np.float32)
+    qkv[:, (nq + nkv) * hd] = np.arange(n + 1) + 1.0                     # v[.., 0] = position + 1
+    pos = np.concatenate([np.arange(n), [7]]).astype(np.int32)
+    slot = np.concatenate([np.full(n, 1), [-1]]).astype(np.int32)
+    table = np.array([[0, 0], [4, 2]], dtype=np.int32)
+    k_pool, v_pool = _pools(6, nkv, hd, torch.float32)
+    inv = torch.zeros(0, device=DEV)
+    ops.rope_cache_write(T(qkv, torch.float32), nq, nkv, hd, 0, inv, T(pos, torch.int32), T(slot, torch.int32),
+                         k_pool, v_pool, T(table, torch.int32), 64, 128, T(np.array([0, n], np.int32), torch.int32), True)
+    vp = N(v_pool)[:, 0, :, 0]
+    for p in range(n - 128, n):
+        r = p % 128
+        assert vp[table[1, r // 64], r % 64] == p + 1
+    assert float(np.abs(vp[0]).sum()) == 0.0                               # the padding row wrote nothing
+
+
+# ---- attention --------------------------------------------------------------------------
+
+GEOMS = [(4, 2, 16), (6, 1, 24), (8, 4, 64), (3, 3, 40), (8, 4, 256), (8, 1, 128), (5, 5, 8)]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nq,nkv,hd", GEOMS)
+@pytest.mark.parametrize("window,cap", [(None, 50.0), (5, None), (64, 30.0)])
+def test_attention_prefill(ops, dtype, nq, nkv, hd, window, cap):
+    rng = np.random.default_rng(nq * hd + (window or 0))
+    lens = [1, 37, 70]
+    Tn = sum(lens)
+    qkv = bf16_round(rng.normal(size=(Tn, (nq + 2 * nkv) * hd)))
+    pos = np.concatenate([np.arange(n) for n in lens]).astype(np.int32)
+    row0 = np.concatenate([np.full(n, s) for n, s in zip(lens, np.cumsum([0] + lens[:-1]))]).astype(np.int32)
+    scale = 1.0 / math.sqrt(hd + 3)
+    out = ops.attn_prefill(T(qkv, dtype), nq, nkv, hd, T(pos, torch.int32), T(row0, torch.int32), scale, cap, window)
+    ref = np.zeros((Tn, nq * hd))
+    r = 0
+    for n in lens:
+        blk = qkv[r:r + n]
+        q = blk[:, :nq * hd].reshape(n, nq, hd)
+        k = blk[:, nq * hd:(nq + nkv) * hd].reshape(n, nkv, hd)
+        v = blk[:, (nq + nkv) * hd:].reshape(n, nkv, hd)
+        ref[r:r + n] = P.attention(q, k, v, scale, cap, window).reshape(n, -1)
+        r += n
+    assert_close(out, ref, dtype, "prefill attention", mult=4)
+
+
+def _fill_cache(k, v, tables, dtype, pages, ring=0):
+    """k, v: per sequence [n, nkv, hd]; returns pools with every sequence in its pages."""
+    nkv, hd = k[0].shape[1:]
+    k_pool, v_pool = _pools(pages, nkv, hd, dtype)
+    for s, (ks, vs) in enumerate(zip(k, v)):
+        n = ks.shape[0]
+        for p in range(max(0, n - ring) if ring else 0, n):
+            r = p % ring if ring else p
+            page = tables[s][r // 64]
+            k_pool[page, :, r % 64, :] = T(ks[p], dtype)
+            v_pool[page, :, r % 64, :] = T(vs[p], dtype)
+    return k_pool, v_pool
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nq,nkv,hd", GEOMS)
+@pytest.mark.parametrize("window,cap,splits", [(None, 50.0, 1), (None, None, 5), (40, 30.0, 3), (128, None, 4)])
+def test_attention_decode(ops, dtype, nq, nkv, hd, window, cap, splits):
+    rng = np.random.default_rng(nq + hd + splits)
+    lens = [200, 1, 65, 130]
+    tables = [[7, 2, 9, 11], [4, 0, 0, 0], [1, 6, 0, 0], [3, 8, 10, 0]]      # scattered, out of order
+    slots = [3, 0, 2, 1]                                                       # rows are not in slot order
+    ring = 128 if window == 128 else 0
+    if ring:
+        tables = [t[:2] + [0, 0] for t in tables]
+    k = [bf16_round(rng.normal(size=(n, nkv, hd))) for n in lens]
+    v = [bf16_round(rng.normal(size=(n, nkv, hd))) for n in lens]
+    q = bf16_round(rng.normal(size=(len(lens) + 1, nq, hd)))
+    k_pool, v_pool = _fill_cache(k, v, tables, dtype, 12, ring)
+    table = np.zeros((4, 4), dtype=np.int32)
+    slot_len = np.zeros(4, dtype=np.int32)
+    for s, tb, n in zip(slots, tables, lens):
+        table[s] = tb
+        slot_len[s] = n
+    qkv = np.zeros((len(lens) + 1, (nq + 2 * nkv) * hd))
+    qkv[:, :nq * hd] = q.reshape(len(lens) + 1, -1)
+    scale = 1.0 / math.sqrt(hd)
+    B = len(lens) + 1
+    part_o = torch.empty(B * nq * splits * hd, device=DEV)
+    part_ml = torch.empty(B * nq * splits * 2, device=DEV)
+    out = ops.attn_decode(T(qkv, dtype), nq, nkv, hd, k_pool, v_pool, T(table, torch.int32), 64, ring,
+                          T(np.array(slots + [-1], np.int32), torch.int32), T(slot_len, torch.int32), scale, cap,
+                          window, splits, part_o, part_ml)
+    for b, n in enumerate(lens):
+        qq = np.zeros((n, nq, hd))
+        qq[-1] = q[b]
+        ref = P.attention(qq, k[b], v[b], scale, cap, window)[-1].reshape(-1)
+        assert_close(out[b], ref, dtype, f"decode attention row {b}", mult=4)
+    assert float(out[-1].abs().sum()) == 0.0                                  # the padding row attends to nothing
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_decode_attention_finds_one_far_key_among_hundreds(ops, dtype):
+    """Random keys would hide a skipped key: here one key per test scores far above the rest and
+    carries a value of its own, at every position of a 700-key sequence in turn for the places
+    where faults live (first key, page and split edges, last key)."""
+    nq, nkv, hd, n, splits = 4, 2, 32, 700, 6
+    rng = np.random.default_rng(0)
+    base_k = bf16_round(rng.normal(size=(n, nkv, hd)) * 0.05)
+    v = np.zeros((n, nkv, hd))
+    v[:, :, 0] = (np.arange(n) // 16)[:, None]          # the position in two digits that bfloat16 holds exactly
+    v[:, :, 1] = (np.arange(n) % 16)[:, None]
+    q = np.zeros((1, nq, hd))
+    q[0, :, 3] = 8.0
+    tables = [[5, 1, 9, 2, 11, 3, 7, 4, 10, 6, 8]]
+    table = np.array(tables, dtype=np.int32)
+    part_o = torch.empty(nq * splits * hd, device=DEV)
+    part_ml = torch.empty(nq * splits * 2, device=DEV)
+    qkv = np.zeros((1, (nq + 2 * nkv) * hd))
+    qkv[:, :nq * hd] = q.reshape(1, -1)
+    per = -(-n // splits)
+    places = sorted({0, 1, 63, 64, 65, 127, 128, per - 1, per, per + 1, 2 * per, 5 * per - 1, 5 * per, n - 2, n - 1})
+    for far in places:
+        k = base_k.copy()
+        k[far, :, 3] = 8.0                                    # score 64 * scale against ~0 elsewhere
+        k_pool, v_pool = _fill_cache([k], [v], tables, dtype, 12)
+        out = ops.attn_decode(T(qkv, dtype), nq, nkv, hd, k_pool, v_pool, T(table, torch.int32), 64, 0,
+                              T(np.array([0], np.int32), torch.int32), T(np.array([n], np.int32), torch.int32),
+                              1.0, None, None, splits, part_o, part_ml)
+        got = N(out).reshape(nq, hd)
+        got = np.rint(got[:, 0]) * 16 + np.rint(got[:, 1])
+        assert np.all(got == far), f"key {far} was not found: {got}"
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_window_edge_in_both_attention_kernels(ops, dtype):
+    """The key just inside the window must be seen, the one just outside must not, although the
+    outside one scores highest."""
+    nq, nkv, hd, n, W = 2, 1, 16, 300, 100
+    k = np.zeros((n, nkv, hd))
+    v = np.zeros((n, nkv, hd))
+    v[:, 0, 0] = np.arange(n)
+    k[n - W, 0, 0] = 6.0          # first key inside the window of the last query
+    k[n - W - 1, 0, 0] = 12.0     # just outside: would win if it were seen
+    q = np.zeros((n, nq, hd))
+    q[:, :, 0] = 6.0
+    qkv = np.concatenate([q.reshape(n, -1), k.reshape(n, -1), v.reshape(n, -1)], axis=1)
+    pos = np.arange(n, dtype=np.int32)
+    out = ops.attn_prefill(T(qkv, dtype), nq, nkv, hd, T(pos, torch.int32), T(np.zeros(n, np.int32), torch.int32),
+                           1.0, None, W)
+    last = N(out)[-1].reshape(nq, hd)[:, 0]
+    assert np.all(np.abs(last - (n - W)) < 0.5), last
+    before = N(out)[-2].reshape(nq, hd)[:, 0]                 # the query before still sees the outside key
+    assert np.all(np.abs(before - (n - W - 1)) < 0.5), before
+    for ring in (0, 128):
+        tables = [[3, 1, 4, 2, 5]] if not ring else [[3, 1, 0, 0, 0]]
+        k_pool, v_pool = _fill_cache([k], [v], tables, dtype, 6, ring)
+        part_o = torch.empty(nq * 4 * hd, device=DEV)
+        part_ml = torch.empty(nq * 4 * 2, device=DEV)
+        o = ops.attn_decode(T(qkv[-1:], dtype), nq, nkv, hd, k_pool, v_pool, T(np.array(tables, np.int32), torch.int32),
+                            64, ring, T(np.array([0], np.int32), torch.int32), T(np.array([n], np.int32), torch.int32),
+                            1.0, None, W, 4, part_o, part_ml)
+        got = N(o).reshape(nq, hd)[:, 0]
+        assert np.all(np.abs(got - (n - W)) < 0.5), (ring, got)
+
+
+def test_attention_refuses_sizes_it_cannot_take(ops):
+    from quicknn_b200.kernels.lib import KernelError
+    qkv = torch.zeros((2, (2 + 2) * 12), dtype=torch.bfloat16, device=DEV)     # 12 * 2 bytes is no 16-byte vector
+    z = torch.zeros(2, dtype=torch.int32, device=DEV)
+    with pytest.raises(KernelError):
+        ops.attn_prefill(qkv, 2, 1, 12, z, z, 1.0, None, None)
+
+
+# ---- sampling ---------------------------------------------------------------------------
+
+@pytest.mark.parametrize("V", [100, 1000, 5000])
+def test_sampling_follows_the_plain_sampler(ops, V):
+    rng = np.random.default_rng(V)
+    R = 6
+    logits = rng.normal(size=(R, V)).astype(np.float32) * 3
+    logits[0, 17] = logits[0, 5] = logits[0].max() + 1.0            # a tie: the lowest id wins
+    seen = (rng.random(size=(R, V)) < 0.3).astype(np.uint8)
+    lg = T(logits, torch.float32)
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    for temp, k, p, pen in [(0.0, 20, 0.95, 1.0), (0.8, 20, 0.95, 1.0), (1.5, 64, 0.5, 1.3), (0.7, 3, 1.0, 0.8),
+                            (1.0, 1, 1.0, 1.0)]:
+        states = np.array([P.seed_state(42 + i) for i in range(R)], dtype=np.uint32)
+        rng_state = T(states.view(np.int32), torch.int32)
+        seen_t = T(seen, torch.uint8)
+        scratch = torch.empty(ops.sample_scratch_bytes(R, V, k), dtype=torch.uint8, device=DEV)
+        out = torch.zeros(R, dtype=torch.int32, device=DEV)
+        seen_rows = torch.arange(R, dtype=torch.int32, device=DEV)
+        st = states.copy()
+        for draw in range(4):
+            ops.sample(lg, k, temp, p, pen, rng_state, seen_t, seen_rows, scratch, out, flag)
+            got = out.cpu().numpy()
+            for r in range(R):
+                u = 0.0
+                if temp > 0 and min(k, V) > 1:
+                    s, u = P.xorshift32(int(st[r]))
+                    st[r] = s
+                ref = P.sample(logits[r], temp, k, p, pen, seen[r] if pen != 1.0 else None, u)
+                assert got[r] == ref, (temp, k, p, pen, draw, r, got[r], ref)
+            if pen != 1.0:
+                assert all(int(seen_t[r, got[r]]) == 1 for r in range(R))    # the chosen id is marked seen
+                seen[np.arange(R), got] = 1
+        if temp == 0.0:
+            assert got[0] == 5
+    assert int(flag) == 0
+
+
+def test_sampling_flags_non_finite_logits_and_marks_prompts(ops):
+    V = 300
+    lg = torch.zeros((2, V), device=DEV)
+    lg[1, 7] = float("nan")
+    lg[0, 9] = 1.0
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    out = torch.zeros(2, dtype=torch.int32, device=DEV)
+    scratch = torch.empty(ops.sample_scratch_bytes(2, V, 1), dtype=torch.uint8, device=DEV)
+    ops.sample(lg, 1, 0.0, 1.0, 1.0, torch.ones(2, dtype=torch.int32, device=DEV), None, None, scratch, out, flag)
+    assert int(flag) == 1 and int(out[0]) == 9
+    seen = torch.zeros((3, V), dtype=torch.uint8, device=DEV)
+    ops.mark_seen(T(np.array([5, 6, 299, 5], np.int32), torch.int32), T(np.array([0, 0, 2, -1], np.int32), torch.int32), seen)
+    assert seen.sum().item() == 3 and seen[0, 5] == 1 and seen[2, 299] == 1 and seen[1].sum() == 0
