@@ -1,0 +1,259 @@
+#!/usr/bin/env python3
+"""Decode throughput of the Gemma 2 2B layer sizes on one B200, with prefill, roofline and
+end-to-end figures on the same JSON line.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--layers L]
+
+A "step" is one decode step of a batch of 8 sequences whose cached context reaches the
+benchmark context length (8192) at the last timed step.  Weights are random (seeded,
+generated on the device); the cached history of the device-timed runs is random too
+(``Engine.fill_synthetic``), because a decode step's time does not depend on the values.
+Timing is by CUDA events on the launching stream after W warm-up steps; every step reads all
+weights (5.2 GB) and the live cache, far more than the 126 MB L2, so no L2 flush is needed.
+``e2e`` runs the same batch through the Python entry point (``LLM.generate``): prompts go in
+as host lists, the prompts are really prefilled, and each step reads the sampled ids back.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# BASELINE.json configs[2]: Gemma 2 2B layer sizes
+SIZES = dict(
+    architectures=["Gemma2ForCausalLM"], model_type="gemma2", hidden_size=2304, intermediate_size=9216,
+    num_attention_heads=8, num_key_value_heads=4, head_dim=256, vocab_size=256000, num_hidden_layers=26,
+    max_position_embeddings=8192, rope_theta=10000.0, rms_norm_eps=1e-6, sliding_window=4096,
+    attn_logit_softcapping=50.0, final_logit_softcapping=30.0, query_pre_attn_scalar=256, eos_token_id=1,
+    initializer_range=0.02)
+CONTEXT = 8192
+BATCH = 8
+PREFILL_TOKENS = 2048
+SEED = 2
+FALLBACK_HBM_GBS, FALLBACK_BF16_TFLOPS = 6650.0, 1590.0
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    out = {"hbm_gbs": FALLBACK_HBM_GBS, "bf16_tflops": FALLBACK_BF16_TFLOPS, "source": "fallback"}
+    try:
+        with open(path) as fh:
+            m = json.load(fh)
+        if "hbm_gbs" in m:
+            out["hbm_gbs"] = float(m["hbm_gbs"])
+        if "bf16_tflops" in m:
+            out["bf16_tflops"] = float(m["bf16_tflops"])
+        out["source"] = "measured"
+    except (OSError, ValueError):
+        pass
+    return out
+
+
+class Clocks:
+    """Samples nvidia-smi while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    NAMES = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+
+    def __init__(self):
+        self.rows, self.proc = [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *a):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            try:
+                sm.append(int(float(r[0])))
+                mx.append(int(float(r[1])))
+            except (ValueError, IndexError):
+                continue
+            for name, v in zip(self.NAMES, r[2:]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi gave no samples"]}
+        return {"sm_mhz": int(statistics.median(sm)), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def prefill_flops(cfg, T):
+    """Products 2*T*K*N per matrix and causal attention 4*nq*hd*sum(keys seen), per layer, plus the head
+    for one row."""
+    H, I, nq, nkv, hd, L = (cfg["hidden_size"], cfg["intermediate_size"], cfg["num_attention_heads"],
+                            cfg["num_key_value_heads"], cfg["head_dim"], cfg["num_hidden_layers"])
+    mats = H * (nq + 2 * nkv) * hd + nq * hd * H + 3 * H * I
+    total = 0
+    for i in range(L):
+        W = cfg["sliding_window"] if i % 2 == 0 else None
+        keys = sum(min(p + 1, W) if W else p + 1 for p in range(T))
+        total += 2 * T * mats + 4 * nq * hd * keys
+    return total + 2 * H * cfg["vocab_size"]
+
+
+def timed_decode(engine, batch, steps, warmup, torch, with_clocks=False, context=CONTEXT):
+    """Tokens per second of `steps` decode steps of `batch` sequences ending at `context` tokens."""
+    start_len = context - steps - warmup - 1
+    slots = [engine.new_sequence() for _ in range(batch)]
+    engine.fill_synthetic(slots, [start_len] * batch)
+    tokens = torch.randint(1, SIZES["vocab_size"], (batch,), dtype=torch.int32, device=engine.device)
+    engine.decode(slots, tokens)          # eager pass, captures the graph
+    for _ in range(warmup):
+        engine.decode(slots, tokens)
+    torch.cuda.synchronize()
+    k0 = engine.kernels_launched()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    clocks = Clocks()
+    ctx = clocks if with_clocks else open(os.devnull)
+    with ctx:
+        if with_clocks:
+            time.sleep(0.25)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(steps):
+            engine.decode(slots, tokens)
+        e1.record()
+        torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    launches = engine.kernels_launched() - k0
+    bytes_step = engine.model.step_weight_bytes() + engine.cache.bytes_read_per_step(slots)
+    for s in slots:
+        engine.release(s)
+    return {"tok_s": batch * steps / (ms / 1e3), "ms_per_step": ms / steps, "bytes_per_step": bytes_step,
+            "launches": launches, "clocks": clocks.summary() if with_clocks else None}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=SIZES["num_hidden_layers"],
+                    help="fewer layers than the configuration has (reported in config)")
+    ap.add_argument("--batch", type=int, default=BATCH, help="batch of the timed decode (the record is for 8)")
+    ap.add_argument("--context", type=int, default=CONTEXT, help="context that the timed decode ends at")
+    ap.add_argument("--no-graph", action="store_true", help="launch decode steps eagerly (for profilers)")
+    ap.add_argument("--skip-prefill", action="store_true")
+    ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--skip-points", action="store_true")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "HemulGM/QuickNN is Delphi-only Object Pascal (no setup.py/pyproject, pip cannot install "
+                          "it; no Pascal compiler here) and its Gemma 2 path needs a Vulkan device: unavailable on "
+                          "this box"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py measures one GPU only: this library is single-GPU by design (--gpus {args.gpus} refused)")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import torch
+    from quicknn_b200.engine import LLM
+    from quicknn_b200.sampling import GenerationOptions
+
+    pk = peaks()
+    cfg = dict(SIZES, num_hidden_layers=args.layers)
+    max_b = 64 if not args.skip_points else args.batch
+    llm = LLM.random(cfg, SEED, dtype="bfloat16", max_context=CONTEXT, max_batch=max_b,
+                     max_tokens=max_b * CONTEXT)
+    eng = llm.engine
+    eng.use_graphs = not args.no_graph
+
+    # ---- the headline: decode, batch 8 --------------------------------------------------
+    main_run = timed_decode(eng, args.batch, args.steps, args.warmup, torch, with_clocks=True, context=args.context)
+    achieved = main_run["bytes_per_step"] / (main_run["ms_per_step"] / 1e3) / 1e9
+
+    points = {}
+    if not args.skip_points:
+        for b in (1, 64):
+            points[f"decode_b{b}"] = round(timed_decode(eng, b, min(args.steps, 64), args.warmup, torch)["tok_s"], 1)
+
+    # ---- prefill of 2,048 tokens -----------------------------------------------------------
+    ids = torch.randint(1, cfg["vocab_size"], (PREFILL_TOKENS,)).tolist()
+    times = []
+    for i in range(0 if args.skip_prefill else 4):
+        slot = eng.new_sequence()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        eng.step([(slot, ids)], "last")
+        e1.record()
+        torch.cuda.synchronize()
+        eng.release(slot)
+        if i:
+            times.append(e0.elapsed_time(e1))
+    pre_ms = statistics.median(times) if times else float("nan")
+    flops = prefill_flops(cfg, PREFILL_TOKENS)
+    prefill = None if args.skip_prefill else {"value": round(PREFILL_TOKENS / (pre_ms / 1e3), 1), "tokens": PREFILL_TOKENS, "ms": round(pre_ms, 3),
+               "frac": round(flops / (pre_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
+
+    # ---- end to end through the Python entry point ------------------------------------------
+    e2e = None
+    if not args.skip_e2e:
+        new = min(args.steps, 64)
+        plen = CONTEXT - new - 1
+        prompts = [torch.randint(1, cfg["vocab_size"], (plen,)).tolist() for _ in range(BATCH)]
+        llm.max_batch = BATCH
+        res = llm.generate(prompts, GenerationOptions.greedy(new), stop_ids=[])
+        dec = max(r.decode_seconds for r in res)
+        gen = sum(r.generated_tokens - 1 for r in res)
+        e2e = {"value": round(gen / dec, 1), "unit": "tokens/s", "h2d_bytes_per_step": 2 * BATCH * 4,
+               "d2h_bytes_per_step": BATCH * 4 + 4, "prefill_seconds": round(max(r.time_to_first_token_seconds for r in res), 3)}
+
+    out = {
+        "metric": f"decode tokens/s, Gemma 2 2B layer sizes, batch {args.batch}, context {args.context}", "value": round(main_run["tok_s"], 1),
+        "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(main_run["ms_per_step"], 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
+        "config": {"model": "gemma2-2b-sizes", "global_batch": args.batch, "seq_len": args.context, "parallelism": "none",
+                   "layers": args.layers, "layers_of_config": SIZES["num_hidden_layers"],
+                   "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
+                   "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+                   "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
+                   "window": cfg["sliding_window"], "prefill_tokens": PREFILL_TOKENS, "weights": "random seed 2",
+                   "l2": "each step reads > 5 GB, larger than L2; no flush", "peaks": pk["source"]},
+        "clocks": main_run["clocks"], "gpu_launches": main_run["launches"],
+        "e2e": e2e, "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "points": points,
+    }
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -15,6 +15,7 @@ import numpy as np
 import torch
 
 from ..cache import PAGE, CacheFull, KVCache
+from ..kernels import lib as _klib
 from .batch import StepBatch
 from .model import Model
 
@@ -44,6 +45,7 @@ class Engine:
         self._scratch: Dict[int, Tuple[torch.Tensor, torch.Tensor]] = {}
         self._decode_state: Dict[int, dict] = {}
         self.use_graphs = True
+        self.graph_kernels_replayed = 0
         self.error_flag = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.steps_run = 0
 
@@ -180,12 +182,33 @@ class Engine:
             logits = self.model.forward(st["step"], self.cache)      # eager: also warms everything up
             torch.cuda.synchronize(self.device)
             g = torch.cuda.CUDAGraph()
+            before = _klib.launches
             with torch.cuda.graph(g):
                 st["logits"] = self.model.forward(st["step"], self.cache)
+            st["kernels"] = _klib.launches - before      # our kernels in one replay of this graph
+            _klib.launches = before
             st["graph"] = g
             return logits
         st["graph"].replay()
+        self.graph_kernels_replayed += st["kernels"]
         return st["logits"]
+
+    def kernels_launched(self) -> int:
+        """Kernels of this library launched so far, eagerly or inside replayed graphs."""
+        return _klib.launches + self.graph_kernels_replayed
+
+    def fill_synthetic(self, slots: Sequence[int], lengths: Sequence[int], seed: int = 0) -> None:
+        """Give sequences a history of the given lengths without computing it: pages are taken
+        as a prompt of that length would take them and every cache line is filled with random
+        keys and values.  For timing decode steps at a chosen context; the logits mean nothing."""
+        self.cache.extend(list(zip(slots, lengths)))
+        self.cache.sync()
+        g = torch.Generator(device=self.device)
+        g.manual_seed(seed)
+        for grp in self.cache.groups:
+            for t in (grp.k, grp.v):
+                for li in range(t.shape[0]):
+                    t[li].normal_(0.0, 1.0, generator=g)
 
     def stats(self) -> Dict[str, int]:
         return {"weight_bytes": self.model.weight_bytes(), "cache_bytes": self.cache.bytes(),

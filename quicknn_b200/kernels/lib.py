@@ -85,8 +85,13 @@ def library_file() -> Optional[str]:
     return _path
 
 
-def check(code: int, what: str) -> None:
+launches = 0          # kernels launched through this module since import (a graph replay is not seen here)
+
+
+def check(code: int, what: str, kernels: int = 1) -> None:
+    global launches
     if code == 0:
+        launches += kernels
         return
     if code == ERR_UNSUPPORTED:
         raise KernelError(f"{what}: the kernel does not take these sizes")

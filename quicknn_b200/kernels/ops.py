@@ -287,7 +287,7 @@ def attn_decode(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, k_poo
     _lib.check(L.qnn_attn_decode(
         _p(qkv), qkv.shape[1], dt_code(qkv), _p(k_pool), _p(v_pool), _p(page_table), page_table.shape[1],
         page_size, ring, _p(slots), _p(slot_len), B, n_heads, n_kv, head_dim, float(scale), float(cap or 0.0),
-        int(window or 0), _p(part_o), _p(part_ml), n_splits, _p(out), out.shape[1], _stream()), "attn_decode")
+        int(window or 0), _p(part_o), _p(part_ml), n_splits, _p(out), out.shape[1], _stream()), "attn_decode", 2)
     return out
 
 
@@ -310,7 +310,7 @@ def sample(logits: torch.Tensor, top_k: int, temperature: float, top_p: float, p
     L = _lib.load()
     _lib.check(L.qnn_sample(_p(logits), R, V, int(top_k), float(temperature), float(top_p), float(penalty),
                             _p(rng_state), _p(seen), _p(seen_rows), _p(scratch), _p(out_tokens), _p(error_flag),
-                            _stream()), "sample")
+                            _stream()), "sample", 2)
     return out_tokens
 
 

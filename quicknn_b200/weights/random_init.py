@@ -44,6 +44,8 @@ def write_model_folder(path: str, arch: Architecture, cfg: ModelConfig, seed: in
     """Write ``config.json`` and ``model.safetensors`` for a random model."""
     os.makedirs(path, exist_ok=True)
     raw = cfg.to_dict()
+    if not raw.get("architectures"):
+        raw["architectures"] = [arch.name]        # the registry finds the model class by this name
     raw["torch_dtype"] = "bfloat16" if dtype == torch.bfloat16 else "float32"
     with open(os.path.join(path, "config.json"), "w", encoding="utf-8") as fh:
         json.dump(raw, fh, indent=1)
