@@ -34,6 +34,19 @@ template <typename T> __device__ __forceinline__ float fexp(float x);
 template <> __device__ __forceinline__ float fexp<float>(float x) { return expf(x); }
 template <> __device__ __forceinline__ float fexp<bf16>(float x) { return __expf(x); }
 
+// softcap with the exact tanhf in the float32 path and the hardware tanh where the data are
+// bfloat16 (its error, about 2^-11, is below bfloat16's own rounding)
+template <typename T> __device__ __forceinline__ float softcap_t(float x, float cap);
+template <> __device__ __forceinline__ float softcap_t<float>(float x, float cap) { return softcap(x, cap); }
+template <> __device__ __forceinline__ float softcap_t<bf16>(float x, float cap) {
+    if (cap > 0.f) {
+        float t = fminf(fmaxf(__fdividef(x, cap), -20.f), 20.f), r;
+        asm("tanh.approx.f32 %0, %1;" : "=f"(r) : "f"(t));
+        return cap * r;
+    }
+    return x;
+}
+
 template <typename T>
 struct PagedKV {
     const T* k_pool;
@@ -174,49 +187,15 @@ __device__ __forceinline__ void load_query(const T* qrow0, int hd, int G, int gt
 
 constexpr int DEC_WARPS = 4;
 
-template <typename T, int CPL, int GT>
-__global__ void __launch_bounds__(DEC_WARPS * 32)
-attn_decode_kernel(const T* __restrict__ q, size_t q_stride, const T* __restrict__ k_pool, const T* __restrict__ v_pool,
-                   const int* __restrict__ page_table, int max_pages, int page_size, int ring,
-                   const int* __restrict__ slots, const int* __restrict__ slot_len, int nq, int nkv, int hd, int LPT,
-                   float scale, float cap, int window, float* __restrict__ part_o, float* __restrict__ part_ml,
-                   int n_splits) {
-    constexpr int VEC = Vec16<T>::N;
-    extern __shared__ float smem[];  // [DEC_WARPS][GT][hd + 2]
-    const int split = blockIdx.x, b = blockIdx.z;
-    const int G = nq / nkv, gtiles = (G + GT - 1) / GT;
-    const int kh = blockIdx.y / gtiles, gt0 = (blockIdx.y % gtiles) * GT;
+// The warps of a CTA hand their states to shared memory; the threads that own a dimension
+// merge them in warp order and write the CTA's partial (max, sum, O) for its split.
+template <int CPL, int GT, int VEC>
+__device__ __forceinline__ void write_partials(float* smem, const float (&m)[GT], const float (&l)[GT],
+                                               const float (&o)[GT][CPL][VEC], int hd, int LPT, int chunks, int G,
+                                               int gt0, int kh, int nq, int b, int split, int n_splits,
+                                               float* __restrict__ part_o, float* __restrict__ part_ml) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int chunks = hd / VEC;
-    const int sl = lane % LPT, ti = lane / LPT, TPW = 32 / LPT;
-    const int slot = slots[b];
-
-    float m[GT], l[GT], o[GT][CPL][VEC];
-#pragma unroll
-    for (int g = 0; g < GT; ++g) {
-        m[g] = -CUDART_INF_F;
-        l[g] = 0.f;
-#pragma unroll
-        for (int i = 0; i < CPL; ++i)
-#pragma unroll
-            for (int e = 0; e < VEC; ++e) o[g][i][e] = 0.f;
-    }
-    if (slot >= 0) {
-        const int n = slot_len[slot];
-        const int kbeg = (window > 0 && n > window) ? n - window : 0;
-        const int count = n - kbeg;
-        const int per = (count + n_splits - 1) / n_splits;
-        const int begin = kbeg + split * per;
-        const int end = min(begin + per, n);
-        if (begin < end) {
-            float qr[GT][CPL][VEC];
-            load_query<T, CPL, GT>(q + (size_t)b * q_stride + (size_t)kh * G * hd, hd, G, gt0, LPT, chunks, scale, qr);
-            PagedKV<T> kv{k_pool, v_pool, page_table + (size_t)slot * max_pages, page_size, nkv, hd, ring, kh};
-            attend_range<T, CPL, GT>(qr, kv, begin, end, warp * TPW, DEC_WARPS * TPW, LPT, chunks, cap, m, l, o);
-        }
-    }
-    merge_groups<CPL, GT, VEC>(LPT, m, l, o);
-    // warps -> shared memory -> merged in warp order by the threads that own a dimension
+    const int sl = lane % LPT, ti = lane / LPT;
     const int row = hd + 2;
     if (ti == 0) {
 #pragma unroll
@@ -260,26 +239,291 @@ attn_decode_kernel(const T* __restrict__ q, size_t q_stride, const T* __restrict
     }
 }
 
+
+template <typename T, int CPL, int GT>
+__global__ void __launch_bounds__(DEC_WARPS * 32)
+attn_decode_kernel(const T* __restrict__ q, size_t q_stride, const T* __restrict__ k_pool, const T* __restrict__ v_pool,
+                   const int* __restrict__ page_table, int max_pages, int page_size, int ring,
+                   const int* __restrict__ slots, const int* __restrict__ slot_len, int nq, int nkv, int hd, int LPT,
+                   float scale, float cap, int window, float* __restrict__ part_o, float* __restrict__ part_ml,
+                   int n_splits) {
+    constexpr int VEC = Vec16<T>::N;
+    extern __shared__ float smem[];  // [DEC_WARPS][GT][hd + 2]
+    const int split = blockIdx.x, b = blockIdx.z;
+    const int G = nq / nkv, gtiles = (G + GT - 1) / GT;
+    const int kh = blockIdx.y / gtiles, gt0 = (blockIdx.y % gtiles) * GT;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int chunks = hd / VEC;
+    const int sl = lane % LPT, ti = lane / LPT, TPW = 32 / LPT;
+    const int slot = slots[b];
+
+    float m[GT], l[GT], o[GT][CPL][VEC];
+#pragma unroll
+    for (int g = 0; g < GT; ++g) {
+        m[g] = -CUDART_INF_F;
+        l[g] = 0.f;
+#pragma unroll
+        for (int i = 0; i < CPL; ++i)
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) o[g][i][e] = 0.f;
+    }
+    if (slot >= 0) {
+        const int n = slot_len[slot];
+        const int kbeg = (window > 0 && n > window) ? n - window : 0;
+        const int count = n - kbeg;
+        const int per = (count + n_splits - 1) / n_splits;
+        const int begin = kbeg + split * per;
+        const int end = min(begin + per, n);
+        if (begin < end) {
+            float qr[GT][CPL][VEC];
+            load_query<T, CPL, GT>(q + (size_t)b * q_stride + (size_t)kh * G * hd, hd, G, gt0, LPT, chunks, scale, qr);
+            PagedKV<T> kv{k_pool, v_pool, page_table + (size_t)slot * max_pages, page_size, nkv, hd, ring, kh};
+            attend_range<T, CPL, GT>(qr, kv, begin, end, warp * TPW, DEC_WARPS * TPW, LPT, chunks, cap, m, l, o);
+        }
+    }
+    merge_groups<CPL, GT, VEC>(LPT, m, l, o);
+    write_partials<CPL, GT, VEC>(smem, m, l, o, hd, LPT, chunks, G, gt0, kh, nq, b, split, n_splits, part_o, part_ml);
+}
+
+// The tiled, pipelined decode kernel.  Same grid, same scratch and same results (up to
+// rounding) as attn_decode_kernel, but
+//   * a lane group takes TT keys per step instead of one, and the keys and values of the next
+//     steps are already on their way: every warp owns DEC_STAGES buffers in shared memory that it
+//     fills with cp.async (16 bytes per lane, zero-filled beyond the end of its range), so about
+//     two tiles per warp are in flight while the third is being worked on;
+//   * the GT*TT partial dot products of a lane are summed over the group by a transposed
+//     reduction (each exchange halves what a lane still carries: GT*TT - 1 shuffles instead of
+//     GT*TT*log2(LPT)), after which every score lives on one lane (replicated LPT/(GT*TT) times),
+//     so softcap and exp are evaluated once per score, not once per lane;
+//   * the running maximum is updated once per tile, so O is rescaled once per TT keys.
+// Needs GT*TT <= LPT and a page size that is a power of two.
+constexpr int DEC_STAGES = 3;
+
+__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gmem_src, bool valid) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
+    const int bytes = valid ? 16 : 0;   // 0 source bytes: the 16 destination bytes are zero-filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(gmem_src), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+template <typename T, int CPL, int GT, int TT>
+__global__ void __launch_bounds__(DEC_WARPS * 32)
+attn_decode_tiled_kernel(const T* __restrict__ q, size_t q_stride, const T* __restrict__ k_pool,
+                         const T* __restrict__ v_pool, const int* __restrict__ page_table, int max_pages,
+                         int page_size, int ring, const int* __restrict__ slots, const int* __restrict__ slot_len,
+                         int nq, int nkv, int hd, int LPT, float scale, float cap, int window,
+                         float* __restrict__ part_o, float* __restrict__ part_ml, int n_splits) {
+    constexpr int VEC = Vec16<T>::N;
+    constexpr int NV = GT * TT;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int split = blockIdx.x, b = blockIdx.z;
+    const int G = nq / nkv, gtiles = (G + GT - 1) / GT;
+    const int kh = blockIdx.y / gtiles, gt0 = (blockIdx.y % gtiles) * GT;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int chunks = hd / VEC;
+    const int sl = lane % LPT, grp = lane / LPT, TPW = 32 / LPT;
+    const int group_base = grp * LPT;
+    const int R = LPT / NV;                    // lanes that hold the same score after the reduction
+    const int my_idx = sl / R, my_g = my_idx / TT, my_tt = my_idx % TT;
+    const int slot = slots[b];
+    const int tile = TT * TPW;                 // keys per warp step
+    const size_t tile_elems = (size_t)tile * hd;
+    // this warp's buffers: [stage][K | V][key of the tile][hd]
+    T* wbuf = reinterpret_cast<T*>(smem_raw) + (size_t)warp * DEC_STAGES * 2 * tile_elems;
+    int* pages_s = reinterpret_cast<int*>(reinterpret_cast<T*>(smem_raw) + (size_t)DEC_WARPS * DEC_STAGES * 2 * tile_elems);
+
+    float m[GT], l[GT], o[GT][CPL][VEC];
+#pragma unroll
+    for (int g = 0; g < GT; ++g) {
+        m[g] = -CUDART_INF_F;
+        l[g] = 0.f;
+#pragma unroll
+        for (int i = 0; i < CPL; ++i)
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) o[g][i][e] = 0.f;
+    }
+    if (slot >= 0) {
+        const int n = slot_len[slot];
+        const int kbeg = (window > 0 && n > window) ? n - window : 0;
+        const int count = n - kbeg;
+        const int per = (count + n_splits - 1) / n_splits;
+        const int begin = kbeg + split * per;
+        const int end = min(begin + per, n);
+        if (begin < end) {
+            float qr[GT][CPL][VEC];
+            load_query<T, CPL, GT>(q + (size_t)b * q_stride + (size_t)kh * G * hd, hd, G, gt0, LPT, chunks, scale, qr);
+            // The page ids of this CTA's key range go to shared memory once, so that the fetches
+            // below do not wait on a lookup in global memory.  Entry u is the page of the u-th
+            // page-sized stretch counted from the range's first key (unwrapped over a ring).
+            const int page_shift = 31 - __clz(page_size), page_mask = page_size - 1;
+            const int* page_row = page_table + (size_t)slot * max_pages;
+            const int rb0 = ring > 0 ? begin % ring : begin;
+            const int first_pg = rb0 >> page_shift;
+            const int npg = ((rb0 + (end - begin) - 1) >> page_shift) - first_pg + 1;
+            const int ring_pages = ring > 0 ? ring >> page_shift : 0x7fffffff;
+            for (int u = threadIdx.x; u < npg; u += blockDim.x) {
+                int pi = first_pg + u;
+                if (pi >= ring_pages) pi -= ring_pages;
+                pages_s[u] = page_row[pi];
+            }
+            __syncthreads();
+            const int first = begin + warp * tile, stride = DEC_WARPS * tile;
+            const int my_tiles = first < end ? (end - first + stride - 1) / stride : 0;
+
+            // fetch tile `it` of this warp into stage it % DEC_STAGES
+            auto fetch = [&](int it) {
+                if (it < my_tiles) {
+                    const int base = first + it * stride;
+                    T* kst = wbuf + (size_t)(it % DEC_STAGES) * 2 * tile_elems;
+                    T* vst = kst + tile_elems;
+                    const int rbase = rb0 + (base - begin);            // unwrapped place in the ring
+#pragma unroll
+                    for (int tt = 0; tt < TT; ++tt) {
+                        const int j = tt * TPW + grp;
+                        const bool valid = base + j < end;
+                        const int r = rbase + j;
+                        const int page = valid ? pages_s[(r >> page_shift) - first_pg] : 0;
+                        const size_t off = ((size_t)(page * nkv + kh) * page_size + (r & page_mask)) * hd;
+#pragma unroll
+                        for (int i = 0; i < CPL; ++i) {
+                            const int c = sl + i * LPT;
+                            if (c < chunks) {
+                                cp_async_16(kst + (size_t)j * hd + c * VEC, k_pool + off + c * VEC, valid);
+                                cp_async_16(vst + (size_t)j * hd + c * VEC, v_pool + off + c * VEC, valid);
+                            }
+                        }
+                    }
+                }
+                cp_async_commit();   // an empty group keeps the count of outstanding groups uniform
+            };
+#pragma unroll
+            for (int it = 0; it < DEC_STAGES - 1; ++it) fetch(it);
+
+            for (int it = 0; it < my_tiles; ++it) {
+                fetch(it + DEC_STAGES - 1);
+                cp_async_wait<DEC_STAGES - 1>();
+                __syncwarp();
+                const int base = first + it * stride;
+                const T* kst = wbuf + (size_t)(it % DEC_STAGES) * 2 * tile_elems;
+                const T* vst = kst + tile_elems;
+                float s[NV];
+#pragma unroll
+                for (int j = 0; j < NV; ++j) s[j] = 0.f;
+#pragma unroll
+                for (int tt = 0; tt < TT; ++tt)
+#pragma unroll
+                    for (int i = 0; i < CPL; ++i) {
+                        const int c = sl + i * LPT;
+                        if (c < chunks) {
+                            Vec16<T> kv_;
+                            kv_.load(kst + (size_t)(tt * TPW + grp) * hd + c * VEC);
+                            float kk[VEC];
+                            kv_.unpack(kk);
+#pragma unroll
+                            for (int g = 0; g < GT; ++g)
+#pragma unroll
+                                for (int e = 0; e < VEC; ++e) s[g * TT + tt] = fmaf(qr[g][i][e], kk[e], s[g * TT + tt]);
+                        }
+                    }
+                // transposed reduction over the LPT lanes of the group
+                int d = LPT >> 1;
+#pragma unroll
+                for (int h = NV / 2; h >= 1; h >>= 1) {
+                    const bool upper = (sl & d) != 0;
+#pragma unroll
+                    for (int j = 0; j < h; ++j) {
+                        const float keep = upper ? s[j + h] : s[j];
+                        const float send = upper ? s[j] : s[j + h];
+                        s[j] = keep + __shfl_xor_sync(0xffffffffu, send, d);
+                    }
+                    d >>= 1;
+                }
+                float sc = s[0];
+                for (; d >= 1; d >>= 1) sc += __shfl_xor_sync(0xffffffffu, sc, d);
+                // this lane now owns the score of (head my_g, key my_tt of the tile)
+                const bool mine = (base + my_tt * TPW + grp) < end;
+                sc = mine ? softcap_t<T>(sc, cap) : -CUDART_INF_F;
+                float tmax = sc;
+                for (int off = R; off < R * TT; off <<= 1) tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, off));
+                float m_old = m[0];
+#pragma unroll
+                for (int g = 1; g < GT; ++g) m_old = (my_g == g) ? m[g] : m_old;
+                const float m_new = fmaxf(m_old, tmax);
+                float pw = (m_new == -CUDART_INF_F) ? 0.f : fexp<T>(sc - m_new);
+                float tsum = pw;
+                for (int off = R; off < R * TT; off <<= 1) tsum += __shfl_xor_sync(0xffffffffu, tsum, off);
+#pragma unroll
+                for (int g = 0; g < GT; ++g) {
+                    const int src = group_base + (g * TT) * R;
+                    const float mg = __shfl_sync(0xffffffffu, m_new, src);
+                    const float ls = __shfl_sync(0xffffffffu, tsum, src);
+                    const float corr = (mg == -CUDART_INF_F) ? 1.f : fexp<T>(m[g] - mg);
+                    l[g] = l[g] * corr + ls;
+                    m[g] = mg;
+#pragma unroll
+                    for (int i = 0; i < CPL; ++i)
+#pragma unroll
+                        for (int e = 0; e < VEC; ++e) o[g][i][e] *= corr;
+                }
+#pragma unroll
+                for (int tt = 0; tt < TT; ++tt) {
+                    float pg[GT];
+#pragma unroll
+                    for (int g = 0; g < GT; ++g) pg[g] = __shfl_sync(0xffffffffu, pw, group_base + (g * TT + tt) * R);
+#pragma unroll
+                    for (int i = 0; i < CPL; ++i) {
+                        const int c = sl + i * LPT;
+                        if (c < chunks) {
+                            Vec16<T> vv_;
+                            vv_.load(vst + (size_t)(tt * TPW + grp) * hd + c * VEC);
+                            float vv[VEC];
+                            vv_.unpack(vv);
+#pragma unroll
+                            for (int g = 0; g < GT; ++g)
+#pragma unroll
+                                for (int e = 0; e < VEC; ++e) o[g][i][e] = fmaf(pg[g], vv[e], o[g][i][e]);
+                        }
+                    }
+                }
+                __syncwarp();   // everybody is done with this stage before a later fetch refills it
+            }
+            cp_async_wait<0>();
+        }
+    }
+    merge_groups<CPL, GT, VEC>(LPT, m, l, o);
+    __syncthreads();            // the stage buffers are free now: reuse them for the merge of the warps
+    write_partials<CPL, GT, VEC>(reinterpret_cast<float*>(smem_raw), m, l, o, hd, LPT, chunks, G, gt0, kh, nq, b, split,
+                                 n_splits, part_o, part_ml);
+}
+
 // out[b, h, :] = sum_s e^{m_s - M} O_s / sum_s e^{m_s - M} l_s, splits in ascending order.
 template <typename T>
 __global__ void attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                     T* __restrict__ out, size_t out_stride, int nq, int hd, int n_splits) {
+    extern __shared__ float coef[];  // [n_splits] weights of the splits, then 1/sum
     const int b = blockIdx.x / nq, h = blockIdx.x % nq;
     const size_t pbase = ((size_t)b * nq + h) * n_splits;
-    float mm = -CUDART_INF_F;
-    for (int s = 0; s < n_splits; ++s) mm = fmaxf(mm, part_ml[(pbase + s) * 2]);
-    float ll = 0.f;
-    for (int s = 0; s < n_splits; ++s) {
-        const float ms = part_ml[(pbase + s) * 2];
-        if (ms != -CUDART_INF_F) ll += expf(ms - mm) * part_ml[(pbase + s) * 2 + 1];
+    if (threadIdx.x < 32) {
+        float mm = -CUDART_INF_F;
+        for (int s = threadIdx.x; s < n_splits; s += 32) mm = fmaxf(mm, part_ml[(pbase + s) * 2]);
+        mm = warp_max(mm);
+        for (int s = threadIdx.x; s < n_splits; s += 32) {
+            const float ms = part_ml[(pbase + s) * 2];
+            coef[s] = (ms == -CUDART_INF_F) ? 0.f : expf(ms - mm);
+        }
+        __syncwarp();
+        if (threadIdx.x == 0) {
+            float ll = 0.f;
+            for (int s = 0; s < n_splits; ++s) ll += coef[s] * part_ml[(pbase + s) * 2 + 1];   // ascending order
+            coef[n_splits] = ll > 0.f ? 1.f / ll : 0.f;
+        }
     }
-    const float inv = ll > 0.f ? 1.f / ll : 0.f;
+    __syncthreads();
+    const float inv = coef[n_splits];
     for (int d = threadIdx.x; d < hd; d += blockDim.x) {
         float acc = 0.f;
-        for (int s = 0; s < n_splits; ++s) {
-            const float ms = part_ml[(pbase + s) * 2];
-            if (ms != -CUDART_INF_F) acc += expf(ms - mm) * part_o[(pbase + s) * hd + d];
-        }
+        for (int s = 0; s < n_splits; ++s) acc += coef[s] * part_o[(pbase + s) * hd + d];
         out[(size_t)b * out_stride + (size_t)h * hd + d] = from_f<T>(acc * inv);
     }
 }
@@ -391,6 +635,12 @@ Geometry geometry(int hd, int G) {
     QNN_DISPATCH_CPL_GT(4, 1, __VA_ARGS__) QNN_DISPATCH_CPL_GT(4, 2, __VA_ARGS__)                    \
     QNN_DISPATCH_CPL_GT(4, 4, __VA_ARGS__)
 
+extern "C" int qnn_attn_decode_mma_split(const void* q, long long q_stride, const void* k_pool, const void* v_pool,
+                                         const int* page_table, int max_pages, int page_size, int ring,
+                                         const int* slots, const int* slot_len, int B, int nq, int nkv, int hd,
+                                         float scale, float cap, int window, float* part_o, float* part_ml,
+                                         int n_splits, cudaStream_t st);
+
 template <typename T>
 static int decode_launch(const void* q, long long q_stride, const void* k_pool, const void* v_pool,
                          const int* page_table, int max_pages, int page_size, int ring, const int* slots,
@@ -405,14 +655,47 @@ static int decode_launch(const void* q, long long q_stride, const void* k_pool, 
     dim3 grid(n_splits, nkv * gtiles, B);
     const size_t smem = (size_t)DEC_WARPS * geo.gt * (hd + 2) * sizeof(float);
     if (smem > 48 * 1024) return QNN_ERR_UNSUPPORTED;
-    QNN_DISPATCH_ALL({
-        attn_decode_kernel<T, CPL, GT><<<grid, DEC_WARPS * 32, smem, st>>>(
-            (const T*)q, (size_t)q_stride, (const T*)k_pool, (const T*)v_pool, page_table, max_pages, page_size, ring,
-            slots, slot_len, nq, nkv, hd, geo.lpt, scale, cap, window, part_o, part_ml, n_splits);
-    })
+#define QNN_DEC_ARGS                                                                                              \
+    (const T*)q, (size_t)q_stride, (const T*)k_pool, (const T*)v_pool, page_table, max_pages, page_size, ring, slots, \
+        slot_len, nq, nkv, hd, geo.lpt, scale, cap, window, part_o, part_ml, n_splits
+    int tt = (geo.cpl == 1 && geo.gt * 8 <= geo.lpt) ? 8 : ((geo.cpl <= 2 && geo.gt * 4 <= geo.lpt) ? 4 : 0);
+    if (page_size <= 0 || (page_size & (page_size - 1)) || (ring > 0 && ring < 8 * 32)) tt = 0;   // the tiled kernel's address arithmetic
+    bool launched = false;
+    if (sizeof(T) == 2) {   // bfloat16: the tensor-core kernel where it takes the sizes
+        const int rc = qnn_attn_decode_mma_split(q, q_stride, k_pool, v_pool, page_table, max_pages, page_size, ring,
+                                                 slots, slot_len, B, nq, nkv, hd, scale, cap, window, part_o, part_ml,
+                                                 n_splits, st);
+        if (rc == 0) launched = true;
+        else if (rc != QNN_ERR_UNSUPPORTED) return rc;
+    }
+    const size_t tile_bytes = (size_t)tt * (32 / geo.lpt) * hd * sizeof(T) * 2;
+    size_t smem_tiled = (size_t)DEC_WARPS * DEC_STAGES * tile_bytes;
+    if (smem_tiled < smem) smem_tiled = smem;      // the merge of the warps reuses the stage buffers
+    smem_tiled += ((size_t)max_pages + 2) * sizeof(int);   // page ids of the CTA's key range
+    if (smem_tiled > 100 * 1024) tt = 0;
+#define QNN_TILED(CPLV, GTV, TTV)                                                                          \
+    if (!launched && geo.cpl == CPLV && geo.gt == GTV && tt == TTV) {                                        \
+        auto kern = attn_decode_tiled_kernel<T, CPLV, GTV, TTV>;                                            \
+        static bool configured = false;                                                                     \
+        if (!configured) {                                                                                  \
+            cudaError_t ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024); \
+            if (ce != cudaSuccess) return (int)ce;                                                          \
+            configured = true;                                                                              \
+        }                                                                                                   \
+        kern<<<grid, DEC_WARPS * 32, smem_tiled, st>>>(QNN_DEC_ARGS);                                       \
+        launched = true;                                                                                    \
+    }
+    QNN_TILED(1, 1, 8) QNN_TILED(1, 2, 8) QNN_TILED(1, 4, 8)
+    QNN_TILED(1, 1, 4) QNN_TILED(1, 2, 4) QNN_TILED(1, 4, 4)
+    QNN_TILED(2, 1, 4) QNN_TILED(2, 2, 4) QNN_TILED(2, 4, 4)
+#undef QNN_TILED
+    if (!launched) {
+        QNN_DISPATCH_ALL({ attn_decode_kernel<T, CPL, GT><<<grid, DEC_WARPS * 32, smem, st>>>(QNN_DEC_ARGS); })
+    }
+#undef QNN_DEC_ARGS
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
-    attn_combine_kernel<T><<<B * nq, 128, 0, st>>>(part_o, part_ml, (T*)out, (size_t)out_stride, nq, hd, n_splits);
+    attn_combine_kernel<T><<<B * nq, hd >= 256 ? 256 : 128, (n_splits + 1) * sizeof(float), st>>>(part_o, part_ml, (T*)out, (size_t)out_stride, nq, hd, n_splits);
     QNN_LAUNCH_CHECK();
 }
 

@@ -1,0 +1,339 @@
+// Decode attention over the paged cache on the tensor cores, bfloat16, for head sizes 64, 128
+// and 256 and up to 8 query heads per kv head (more heads take several CTAs).
+//
+// Formulas: those of attention.cu (reference: src/backends/vulkan/shaders/attention.comp:18-38).
+// What differs is the mapping.  One query row per sequence leaves the matrix shapes lopsided, so
+// the products are taken transposed and the keys, not the queries, fill the 16-row side of
+// mma.m16n8k16:
+//     S^T[16 keys x 8 heads]  = K[16 keys x hd]   * Q^T[hd x 8 heads]        (A = K,   B = Q^T)
+//     O^T[hd x 8 heads]      += V^T[hd x 16 keys] * P^T[16 keys x 8 heads]   (A = V^T, B = P^T)
+// K and V tiles of 16 keys travel global -> shared memory by cp.async in a 3-stage pipeline per
+// warp (rows XOR-swizzled by 16-byte chunk so that ldmatrix does not conflict); K fragments come
+// from ldmatrix, V^T fragments from ldmatrix.trans; Q^T stays in registers for the whole kernel;
+// P^T is rearranged from the accumulator layout of S^T with eight shuffles.  Softmax state
+// (max, sum) is float32, one pair of heads per lane; O^T accumulates in float32.
+//
+// Grid (splits, kv heads x head tiles, sequences), 4 warps per CTA; the warps of a CTA interleave
+// the 16-key tiles of the CTA's key range and are merged through shared memory in warp order; the
+// CTA writes (max, sum, O) of its range to the scratch that qnn_attn_combine reads.
+#include "common.cuh"
+#include <math_constants.h>
+#include <stdlib.h>
+
+using namespace qnn;
+
+namespace {
+
+constexpr int MMA_STAGES = 3;
+constexpr int TILE = 16;   // keys per warp step
+
+__device__ __forceinline__ void cp_async_16(unsigned smem_dst, const void* gmem_src, bool valid) {
+    const int bytes = valid ? 16 : 0;   // 0 source bytes: the destination is zero-filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_dst), "l"(gmem_src), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], unsigned addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], unsigned addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ float tanh_fast(float x) {
+    float r;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+
+template <int HD, int MMA_WARPS>
+__global__ void __launch_bounds__(MMA_WARPS * 32)
+attn_decode_mma_kernel(const bf16* __restrict__ q, size_t q_stride, const bf16* __restrict__ k_pool,
+                       const bf16* __restrict__ v_pool, const int* __restrict__ page_table, int max_pages,
+                       int page_size, int ring, const int* __restrict__ slots, const int* __restrict__ slot_len,
+                       int nq, int nkv, float scale, float cap, int window, float* __restrict__ part_o,
+                       float* __restrict__ part_ml, int n_splits) {
+    constexpr int KSTEPS = HD / 16;              // k16 steps of S^T, and 16-row tiles of O^T
+    constexpr int CH = HD / 8;                   // 16-byte chunks per row
+    constexpr int ROW_BYTES = HD * 2;
+    constexpr int TILE_BYTES = TILE * ROW_BYTES; // one of K or V
+    constexpr int PER_LANE = TILE * CH / 32;     // cp.async per lane for K (and as many for V)
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    const int split = blockIdx.x, b = blockIdx.z;
+    const int G = nq / nkv, htiles = (G + 7) / 8;
+    const int kh = blockIdx.y / htiles, h0 = (blockIdx.y % htiles) * 8;   // first query head of this CTA within the group
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int slot = slots[b];
+    const unsigned wbase = (unsigned)__cvta_generic_to_shared(smem_raw) + warp * MMA_STAGES * 2 * TILE_BYTES;
+    int* pages_s = reinterpret_cast<int*>(smem_raw + (size_t)MMA_WARPS * MMA_STAGES * 2 * TILE_BYTES);
+
+    float o[KSTEPS][4];
+#pragma unroll
+    for (int i = 0; i < KSTEPS; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) o[i][j] = 0.f;
+    float m0 = -CUDART_INF_F, m1 = -CUDART_INF_F, l0 = 0.f, l1 = 0.f;   // heads h0 + 2t and h0 + 2t + 1
+
+    int begin = 0, end = 0;
+    if (slot >= 0) {
+        const int n = slot_len[slot];
+        const int kbeg = (window > 0 && n > window) ? n - window : 0;
+        const int per = (n - kbeg + n_splits - 1) / n_splits;
+        begin = kbeg + split * per;
+        end = min(begin + per, n);
+    }
+    if (begin < end) {
+        // Q^T fragments: b0 = Q[head g][16 ks + 2t, +1], b1 = Q[head g][16 ks + 8 + 2t, +1]
+        uint32_t qf[KSTEPS][2];
+        {
+            const bool have = h0 + g < G;
+            const uint32_t* qrow = reinterpret_cast<const uint32_t*>(q + (size_t)b * q_stride + (size_t)(kh * G + h0 + g) * HD);
+#pragma unroll
+            for (int ks = 0; ks < KSTEPS; ++ks) {
+                qf[ks][0] = have ? qrow[ks * 8 + t] : 0u;
+                qf[ks][1] = have ? qrow[ks * 8 + 4 + t] : 0u;
+            }
+        }
+        const int page_shift = 31 - __clz(page_size), page_mask = page_size - 1;
+        const int* page_row = page_table + (size_t)slot * max_pages;
+        const int rb0 = ring > 0 ? begin % ring : begin;
+        const int first_pg = rb0 >> page_shift;
+        const int npg = ((rb0 + (end - begin) - 1) >> page_shift) - first_pg + 1;
+        const int ring_pages = ring > 0 ? ring >> page_shift : 0x7fffffff;
+        for (int u = threadIdx.x; u < npg; u += blockDim.x) {
+            int pi = first_pg + u;
+            if (pi >= ring_pages) pi -= ring_pages;
+            pages_s[u] = page_row[pi];
+        }
+        __syncthreads();
+        const int first = begin + warp * TILE, stride = MMA_WARPS * TILE;
+        const int my_tiles = first < end ? (end - first + stride - 1) / stride : 0;
+
+        auto fetch = [&](int it) {
+            if (it < my_tiles) {
+                const int base = first + it * stride;
+                const unsigned kst = wbase + (it % MMA_STAGES) * 2 * TILE_BYTES, vst = kst + TILE_BYTES;
+                const int rbase = rb0 + (base - begin);
+#pragma unroll
+                for (int i = 0; i < PER_LANE; ++i) {
+                    const int idx = i * 32 + lane;
+                    const int row = idx / CH, chunk = idx % CH;
+                    const bool valid = base + row < end;
+                    const int r = rbase + row;
+                    const int page = valid ? pages_s[(r >> page_shift) - first_pg] : 0;
+                    const size_t off = ((size_t)(page * nkv + kh) * page_size + (r & page_mask)) * HD + chunk * 8;
+                    const unsigned dst = row * ROW_BYTES + ((chunk ^ (row & 7)) << 4);
+                    cp_async_16(kst + dst, k_pool + off, valid);
+                    cp_async_16(vst + dst, v_pool + off, valid);
+                }
+            }
+            cp_async_commit();
+        };
+#pragma unroll
+        for (int it = 0; it < MMA_STAGES - 1; ++it) fetch(it);
+
+        const float inv_cap = cap > 0.f ? 1.f / cap : 0.f;
+        for (int it = 0; it < my_tiles; ++it) {
+            fetch(it + MMA_STAGES - 1);
+            cp_async_wait<MMA_STAGES - 1>();
+            __syncwarp();
+            const int base = first + it * stride;
+            const unsigned kst = wbase + (it % MMA_STAGES) * 2 * TILE_BYTES, vst = kst + TILE_BYTES;
+
+            // S^T = K Q^T
+            float s[4] = {0.f, 0.f, 0.f, 0.f};
+            {
+                const int row = lane & 15, half = lane >> 4;
+#pragma unroll
+                for (int ks = 0; ks < KSTEPS; ++ks) {
+                    uint32_t a[4];
+                    const int chunk = ks * 2 + half;
+                    ldmatrix_x4(a, kst + row * ROW_BYTES + ((chunk ^ (row & 7)) << 4));
+                    mma_16816(s, a, qf[ks][0], qf[ks][1]);
+                }
+            }
+            // s[0], s[1]: key base+g, heads 2t, 2t+1;  s[2], s[3]: key base+g+8
+            const bool v_lo = base + g < end, v_hi = base + g + 8 < end;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                float x = s[j] * scale;
+                if (cap > 0.f) x = cap * tanh_fast(fminf(fmaxf(x * inv_cap, -20.f), 20.f));
+                s[j] = ((j < 2) ? v_lo : v_hi) ? x : -CUDART_INF_F;
+            }
+            float mx0 = fmaxf(s[0], s[2]), mx1 = fmaxf(s[1], s[3]);
+#pragma unroll
+            for (int off = 4; off < 32; off <<= 1) {
+                mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
+                mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
+            }
+            const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);    // finite: every tile has a valid key
+            const float c0 = __expf(m0 - mn0), c1 = __expf(m1 - mn1);
+            float p[4];
+            p[0] = __expf(s[0] - mn0);
+            p[1] = __expf(s[1] - mn1);
+            p[2] = __expf(s[2] - mn0);
+            p[3] = __expf(s[3] - mn1);
+            float ls0 = p[0] + p[2], ls1 = p[1] + p[3];
+#pragma unroll
+            for (int off = 4; off < 32; off <<= 1) {
+                ls0 += __shfl_xor_sync(0xffffffffu, ls0, off);
+                ls1 += __shfl_xor_sync(0xffffffffu, ls1, off);
+            }
+            l0 = l0 * c0 + ls0;
+            l1 = l1 * c1 + ls1;
+            m0 = mn0;
+            m1 = mn1;
+#pragma unroll
+            for (int i = 0; i < KSTEPS; ++i) {
+                o[i][0] *= c0;
+                o[i][1] *= c1;
+                o[i][2] *= c0;
+                o[i][3] *= c1;
+            }
+            // P^T fragments for B: b0 = P[key 2t, 2t+1][head g], b1 = P[key 2t+8, 2t+9][head g];
+            // P[key a][head g] sits on lane ((a & 7) << 2) | (g >> 1), in p[g & 1] (a < 8) or p[2 + (g & 1)]
+            uint32_t pb0, pb1;
+            {
+                const int srcA = ((2 * t) << 2) | (g >> 1), srcB = ((2 * t + 1) << 2) | (g >> 1);
+                const bool odd = g & 1;
+                const float a0 = __shfl_sync(0xffffffffu, p[0], srcA), a1 = __shfl_sync(0xffffffffu, p[1], srcA);
+                const float b0 = __shfl_sync(0xffffffffu, p[0], srcB), b1 = __shfl_sync(0xffffffffu, p[1], srcB);
+                const float a2 = __shfl_sync(0xffffffffu, p[2], srcA), a3 = __shfl_sync(0xffffffffu, p[3], srcA);
+                const float b2 = __shfl_sync(0xffffffffu, p[2], srcB), b3 = __shfl_sync(0xffffffffu, p[3], srcB);
+                pb0 = pack_bf16(odd ? a1 : a0, odd ? b1 : b0);
+                pb1 = pack_bf16(odd ? a3 : a2, odd ? b3 : b2);
+            }
+            // O^T += V^T P^T
+            {
+                const int row = (lane & 7) + ((lane >> 4) << 3), sub = (lane >> 3) & 1;
+#pragma unroll
+                for (int mt = 0; mt < KSTEPS; ++mt) {
+                    uint32_t a[4];
+                    const int chunk = mt * 2 + sub;
+                    ldmatrix_x4_trans(a, vst + row * ROW_BYTES + ((chunk ^ (row & 7)) << 4));
+                    mma_16816(o[mt], a, pb0, pb1);
+                }
+            }
+            __syncwarp();   // the stage may be refilled by a later fetch
+        }
+        cp_async_wait<0>();
+    }
+    __syncthreads();
+    // The warps' states go to shared memory as [warp][head][HD + 2]; then as in attention.cu.
+    float* ms = reinterpret_cast<float*>(smem_raw);
+    constexpr int ROW = HD + 2;
+#pragma unroll
+    for (int mt = 0; mt < KSTEPS; ++mt) {
+        float* r0 = ms + ((size_t)warp * 8 + 2 * t) * ROW;
+        float* r1 = r0 + ROW;
+        r0[mt * 16 + g] = o[mt][0];
+        r1[mt * 16 + g] = o[mt][1];
+        r0[mt * 16 + g + 8] = o[mt][2];
+        r1[mt * 16 + g + 8] = o[mt][3];
+    }
+    if (g == 0) {
+        float* r0 = ms + ((size_t)warp * 8 + 2 * t) * ROW;
+        r0[HD] = m0;
+        r0[HD + 1] = l0;
+        r0[ROW + HD] = m1;
+        r0[ROW + HD + 1] = l1;
+    }
+    __syncthreads();
+    for (int hh = 0; hh < 8; ++hh) {
+        if (h0 + hh >= G) break;
+        const int h = kh * G + h0 + hh;
+        float mm = -CUDART_INF_F;
+        for (int w = 0; w < MMA_WARPS; ++w) mm = fmaxf(mm, ms[((size_t)w * 8 + hh) * ROW + HD]);
+        float coef[MMA_WARPS], ll = 0.f;
+        for (int w = 0; w < MMA_WARPS; ++w) {
+            const float mw = ms[((size_t)w * 8 + hh) * ROW + HD];
+            coef[w] = (mw == -CUDART_INF_F) ? 0.f : expf(mw - mm);
+            ll += coef[w] * ms[((size_t)w * 8 + hh) * ROW + HD + 1];
+        }
+        const size_t pbase = ((size_t)b * nq + h) * n_splits + split;
+        for (int d = threadIdx.x; d < HD; d += blockDim.x) {
+            float acc = 0.f;
+            for (int w = 0; w < MMA_WARPS; ++w) acc += coef[w] * ms[((size_t)w * 8 + hh) * ROW + d];
+            part_o[pbase * HD + d] = acc;
+        }
+        if (threadIdx.x == 0) {
+            part_ml[pbase * 2] = mm;
+            part_ml[pbase * 2 + 1] = ll;
+        }
+    }
+}
+
+template <int HD, int MMA_WARPS>
+int launch(const void* q, long long q_stride, const void* k_pool, const void* v_pool, const int* page_table,
+           int max_pages, int page_size, int ring, const int* slots, const int* slot_len, int B, int nq, int nkv,
+           float scale, float cap, int window, float* part_o, float* part_ml, int n_splits, cudaStream_t st) {
+    auto kern = attn_decode_mma_kernel<HD, MMA_WARPS>;
+    size_t smem = (size_t)MMA_WARPS * MMA_STAGES * 2 * TILE * HD * 2;
+    const size_t merge = (size_t)MMA_WARPS * 8 * (HD + 2) * sizeof(float);
+    if (smem < merge) smem = merge;
+    smem += ((size_t)max_pages + 2) * sizeof(int);
+    if (smem > 220 * 1024) return QNN_ERR_UNSUPPORTED;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    const int G = nq / nkv;
+    dim3 grid(n_splits, nkv * ((G + 7) / 8), B);
+    kern<<<grid, MMA_WARPS * 32, smem, st>>>((const bf16*)q, (size_t)q_stride, (const bf16*)k_pool, (const bf16*)v_pool,
+                                             page_table, max_pages, page_size, ring, slots, slot_len, nq, nkv, scale,
+                                             cap, window, part_o, part_ml, n_splits);
+    return (int)cudaGetLastError();
+}
+
+}  // namespace
+
+// The split pass of decode attention for bfloat16 on the tensor cores.  Returns
+// QNN_ERR_UNSUPPORTED for sizes it does not take (the caller then uses the generic kernel);
+// on success the caller still has to run the combine pass over part_o / part_ml.
+extern "C" int qnn_attn_decode_mma_split(const void* q, long long q_stride, const void* k_pool, const void* v_pool,
+                                         const int* page_table, int max_pages, int page_size, int ring,
+                                         const int* slots, const int* slot_len, int B, int nq, int nkv, int hd,
+                                         float scale, float cap, int window, float* part_o, float* part_ml,
+                                         int n_splits, cudaStream_t st) {
+    if (nkv <= 0 || nq % nkv) return QNN_ERR_ARGUMENT;
+    if (page_size < TILE || (page_size & (page_size - 1))) return QNN_ERR_UNSUPPORTED;
+    if (ring > 0 && (ring % page_size)) return QNN_ERR_UNSUPPORTED;
+    if ((q_stride * 2) % 4 || ((uintptr_t)q & 3)) return QNN_ERR_UNSUPPORTED;
+#define QNN_MMA_ARGS q, q_stride, k_pool, v_pool, page_table, max_pages, page_size, ring, slots, slot_len, B, nq, nkv, \
+                     scale, cap, window, part_o, part_ml, n_splits, st
+    static int warps = 0;
+    if (warps == 0) {
+        const char* e = getenv("QNN_MMA_WARPS");
+        warps = (e && atoi(e) == 4) ? 4 : 2;
+    }
+    if (warps == 4) {
+        switch (hd) {
+            case 64: return launch<64, 4>(QNN_MMA_ARGS);
+            case 128: return launch<128, 4>(QNN_MMA_ARGS);
+            case 256: return launch<256, 4>(QNN_MMA_ARGS);
+            default: return QNN_ERR_UNSUPPORTED;
+        }
+    }
+    switch (hd) {
+        case 64: return launch<64, 2>(QNN_MMA_ARGS);
+        case 128: return launch<128, 2>(QNN_MMA_ARGS);
+        case 256: return launch<256, 2>(QNN_MMA_ARGS);
+        default: return QNN_ERR_UNSUPPORTED;
+    }
+#undef QNN_MMA_ARGS
+}

@@ -44,6 +44,7 @@ template <> struct Vec16<float> {
     static constexpr int N = 4;
     float4 raw;
     __device__ __forceinline__ void load(const float* p) { raw = *reinterpret_cast<const float4*>(p); }
+    __device__ __forceinline__ void zero() { raw = make_float4(0.f, 0.f, 0.f, 0.f); }
     __device__ __forceinline__ void unpack(float* o) const { o[0] = raw.x; o[1] = raw.y; o[2] = raw.z; o[3] = raw.w; }
     __device__ __forceinline__ static void store(float* p, const float* v) {
         *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
@@ -53,6 +54,7 @@ template <> struct Vec16<bf16> {
     static constexpr int N = 8;
     uint4 raw;
     __device__ __forceinline__ void load(const bf16* p) { raw = *reinterpret_cast<const uint4*>(p); }
+    __device__ __forceinline__ void zero() { raw = make_uint4(0u, 0u, 0u, 0u); }
     __device__ __forceinline__ void unpack(float* o) const {
         const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll

@@ -9,7 +9,7 @@
 //
 //   qnn_skinny_bf16 : M <= 64 rows of bf16 activations against bf16 weights on the tensor
 //                     cores (mma.sync m16n8k16, fp32 accumulate): a CTA owns 16 weight rows,
-//                     its 8 warps split K, weights are read once with 16-byte loads.
+//                     its 8 to 32 warps split K, weights are read once with 16-byte loads.
 //   qnn_gemv_f32    : true fp32, one warp per output column, up to 8 rows at a time.
 //   qnn_sgemm_f32   : true fp32 tiled GEMM (FFMA only) for whole prompts.
 //
@@ -44,12 +44,12 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint3
 
 __device__ __forceinline__ uint4 ldg16(const bf16* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
 
-template <int NT, int EPI>
-__global__ void __launch_bounds__(256) skinny_bf16_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W,
+template <int NT, int EPI, int NW>
+__global__ void __launch_bounds__(NW * 32) skinny_bf16_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W,
                                                           void* __restrict__ out, int out_dt, int M, int N, int K,
                                                           float cap, int act) {
-    constexpr int NW = 8;
     constexpr int COLS = NT * 8;
+    constexpr int THREADS = NW * 32;
     __shared__ float red[NW][16][COLS + 1];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int Nout = (EPI == EPI_GATED) ? N / 2 : N;
@@ -106,7 +106,7 @@ __global__ void __launch_bounds__(256) skinny_bf16_kernel(const bf16* __restrict
     // (row, col) pairs.  Consecutive threads take consecutive weight rows, so a row of `out`
     // is written in runs of 16 and the shared-memory reads (row stride COLS+1, odd) do not
     // conflict.
-    constexpr int SLOTS = (16 * COLS + 255) / 256;
+    constexpr int SLOTS = (16 * COLS + THREADS - 1) / THREADS;
     float gate_sum[SLOTS];
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
@@ -118,7 +118,7 @@ __global__ void __launch_bounds__(256) skinny_bf16_kernel(const bf16* __restrict
     __syncthreads();
 #pragma unroll
     for (int sl = 0; sl < SLOTS; ++sl) {
-        const int e = threadIdx.x + sl * 256;
+        const int e = threadIdx.x + sl * THREADS;
         float s = 0.f;
         if (e < 16 * COLS) {
             const int row = e % 16, col = e / 16;
@@ -140,7 +140,7 @@ __global__ void __launch_bounds__(256) skinny_bf16_kernel(const bf16* __restrict
     }
 #pragma unroll
     for (int sl = 0; sl < SLOTS; ++sl) {
-        const int e = threadIdx.x + sl * 256;
+        const int e = threadIdx.x + sl * THREADS;
         if (e >= 16 * COLS) continue;
         const int row = e % 16, col = e / 16;
         const int n = n0 + row, m = col;
@@ -157,14 +157,26 @@ __global__ void __launch_bounds__(256) skinny_bf16_kernel(const bf16* __restrict
     }
 }
 
+// The K range of a 16-row tile is split over the NW warps of its CTA.  Matrices with few rows
+// (N/16 CTAs do not fill the GPU) get more warps per CTA, as far as K gives every warp at
+// least two 32-wide blocks and the partial tiles fit in shared memory.
 template <int EPI>
 static int launch_skinny(const bf16* x, const bf16* W, void* out, int out_dt, int M, int N, int K, float cap, int act,
                          cudaStream_t st) {
     const int Nout = (EPI == EPI_GATED) ? N / 2 : N;
     const unsigned blocks = (unsigned)((Nout + 15) / 16);
     const int nt = (M + 7) / 8;
-#define QNN_SK(NTV)                                                                                         \
-    skinny_bf16_kernel<NTV, EPI><<<blocks, 256, 0, st>>>(x, W, out, out_dt, M, N, K, cap, act);             \
+    const int kblocks = (K + 31) / 32;
+    int nw = 8;
+    if (nt <= 2 && blocks * 8u < 3000u && kblocks >= 32) nw = 16;
+    if (nt == 1 && blocks * 16u < 3000u && kblocks >= 64) nw = 32;
+#define QNN_SK(NTV)                                                                                            \
+    if (nw == 32 && NTV == 1)                                                                                  \
+        skinny_bf16_kernel<1, EPI, 32><<<blocks, 1024, 0, st>>>(x, W, out, out_dt, M, N, K, cap, act);         \
+    else if (nw >= 16 && NTV <= 2)                                                                             \
+        skinny_bf16_kernel<(NTV <= 2 ? NTV : 1), EPI, 16><<<blocks, 512, 0, st>>>(x, W, out, out_dt, M, N, K, cap, act); \
+    else                                                                                                       \
+        skinny_bf16_kernel<NTV, EPI, 8><<<blocks, 256, 0, st>>>(x, W, out, out_dt, M, N, K, cap, act);         \
     break;
     switch (nt) {
         case 1: QNN_SK(1)

@@ -41,7 +41,13 @@ class Engine:
         needs, states = model.cache_needs()
         self.cache = KVCache(needs, states, max_tokens, max_slots, max_seq, model.dtype, self.device)
         self.max_seq, self.max_slots = max_seq, max_slots
-        self.decode_splits = int(decode_splits) if decode_splits else min(32, max(1, max_seq // 128))
+        # Key ranges per sequence in decode attention.  A fixed number when given; else chosen per
+        # batch size so that one wave of CTAs covers the GPU (results then differ between batch
+        # sizes by rounding only: the ranges are summed in a fixed order either way).
+        self._fixed_splits = int(decode_splits) if decode_splits else None
+        self._max_splits = max(1, min(64, max_seq // 128))
+        self._kv_groups = max([getattr(b.mixer, "n_kv", 1) for b in model.blocks] or [1])
+        self.decode_splits = self._fixed_splits or self._max_splits
         self._scratch: Dict[int, Tuple[torch.Tensor, torch.Tensor]] = {}
         self._decode_state: Dict[int, dict] = {}
         self.use_graphs = True
@@ -60,12 +66,21 @@ class Engine:
         return self.cache.length(slot)
 
     # ---- the step ----------------------------------------------------------------------
+    def splits_for(self, batch: int) -> int:
+        if self._fixed_splits:
+            return self._fixed_splits
+        pairs = batch * self._kv_groups
+        resident = 296                       # 148 SMs x 2 CTAs of the decode attention kernel
+        if pairs >= resident // 2:
+            return min(2, self._max_splits)
+        return max(1, min(self._max_splits, resident // pairs))
+
     def _scratch_for(self, batch: int) -> Tuple[torch.Tensor, torch.Tensor]:
         key = 1
         while key < batch:
             key *= 2
         if key not in self._scratch:
-            po, pm = self.model.decode_scratch(key, self.decode_splits)
+            po, pm = self.model.decode_scratch(key, max(self._max_splits, self.decode_splits))
             self._scratch[key] = (torch.empty(max(po, 1), dtype=torch.float32, device=self.device),
                                   torch.empty(max(pm, 1), dtype=torch.float32, device=self.device))
         return self._scratch[key]
@@ -136,7 +151,7 @@ class Engine:
             o += n
         part_o, part_ml = self._scratch_for(B) if mode == "decode" else (None, None)
         step = StepBatch(mode, T, B, views[0], views[1], views[2], views[3], views[4], views[5],
-                         self.model.dtype, self.decode_splits, part_o, part_ml, max_q_len=max(len(t) for _, t in entries))
+                         self.model.dtype, self.splits_for(B), part_o, part_ml, max_q_len=max(len(t) for _, t in entries))
         logits = self.model.forward(step, self.cache)
         self.steps_run += 1
         return logits
@@ -170,7 +185,7 @@ class Engine:
             part_o, part_ml = self._scratch_for(B)
             tokens = torch.zeros(B, dtype=torch.int32, device=self.device)
             step = StepBatch("decode", B, B, tokens, meta[:B], meta[B:], ar, meta[B:], ar, self.model.dtype,
-                             self.decode_splits, part_o, part_ml)
+                             self.splits_for(B), part_o, part_ml)
             st = {"meta": meta, "step": step, "graph": None, "logits": None}
             self._decode_state[B] = st
         st["meta"].copy_(torch.from_numpy(np.concatenate([np.asarray(starts, np.int32), np.asarray(slots, np.int32)])))

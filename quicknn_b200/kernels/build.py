@@ -131,6 +131,12 @@ def build(name: str = "qnn_kernels", files: Optional[Sequence[str]] = None,
         if r.returncode != 0:
             raise BuildError(f"linking {out} failed:\n{r.stdout}")
         os.replace(tmp, out)
+        for old in os.listdir(bdir):          # libraries of earlier sources
+            if old.startswith(f"lib{name}_") and old.endswith(".so") and os.path.join(bdir, old) != out:
+                try:
+                    os.remove(os.path.join(bdir, old))
+                except OSError:
+                    pass
     finally:
         done.set()
         for o in objs:
