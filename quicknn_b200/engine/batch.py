@@ -33,3 +33,5 @@ class StepBatch:
     part_o: Optional[torch.Tensor] = None
     part_ml: Optional[torch.Tensor] = None
     max_q_len: int = 1              # longest run of tokens that one sequence brings
+    seq_row0: Optional[torch.Tensor] = None   # [B] int32: first row of each sequence in the packed batch
+    seq_len: Optional[torch.Tensor] = None    # [B] int32: tokens that each sequence brings

@@ -142,16 +142,19 @@ class Engine:
         order of the entries and of their wanted places."""
         mode, T, B, tokens, tok_pos, tok_slot, tok_row0, slots, rows = self.plan(entries, want)
         self.cache.sync()
-        packed = np.concatenate([tokens, tok_pos, tok_slot, tok_row0, slots, rows])
+        lens = np.asarray([len(t) for _, t in entries], np.int32)
+        starts = np.concatenate([[0], np.cumsum(lens)[:-1]]).astype(np.int32)
+        packed = np.concatenate([tokens, tok_pos, tok_slot, tok_row0, slots, rows, starts, lens])
         dev = torch.from_numpy(packed).to(self.device)
         o = 0
         views = []
-        for n in (T, T, T, T, B, len(rows)):
+        for n in (T, T, T, T, B, len(rows), B, B):
             views.append(dev[o:o + n])
             o += n
         part_o, part_ml = self._scratch_for(B) if mode == "decode" else (None, None)
         step = StepBatch(mode, T, B, views[0], views[1], views[2], views[3], views[4], views[5],
-                         self.model.dtype, self.splits_for(B), part_o, part_ml, max_q_len=max(len(t) for _, t in entries))
+                         self.model.dtype, self.splits_for(B), part_o, part_ml, max_q_len=int(lens.max()),
+                         seq_row0=views[6], seq_len=views[7])
         logits = self.model.forward(step, self.cache)
         self.steps_run += 1
         return logits

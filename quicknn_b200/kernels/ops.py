@@ -230,9 +230,13 @@ def linear(x: torch.Tensor, w: torch.Tensor, *, epilogue: int = EPI_NONE, cap: O
 
 
 def attn_prefill(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, tok_pos: torch.Tensor,
-                 tok_row0: torch.Tensor, scale: float, cap: Optional[float], window: Optional[int]):
+                 tok_row0: torch.Tensor, scale: float, cap: Optional[float], window: Optional[int],
+                 seq_row0: Optional[torch.Tensor] = None, seq_len: Optional[torch.Tensor] = None,
+                 max_len: int = 0):
     """Causal (optionally windowed) attention of this step's own rows.  qkv: [T, (nq+2nkv)*hd]
-    after rotation; returns [T, nq*hd]."""
+    after rotation; returns [T, nq*hd].  bfloat16 with head sizes 64/128/256 runs on the tensor
+    cores when the per-sequence arrays (first row, length) are given; everything else takes the
+    generic kernel."""
     _req(qkv, "qkv", None, 2)
     T = qkv.shape[0]
     out = torch.empty((T, n_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
@@ -241,6 +245,17 @@ def attn_prefill(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, tok_
     k_ptr = q_ptr + n_heads * head_dim * es
     v_ptr = k_ptr + n_kv * head_dim * es
     L = _lib.load()
+    if (qkv.dtype == torch.bfloat16 and seq_row0 is not None and seq_len is not None and max_len > 0
+            and head_dim in (64, 128, 256)):
+        _req(seq_row0, "seq_row0", torch.int32, 1)
+        _req(seq_len, "seq_len", torch.int32, 1)
+        code = L.qnn_attn_prefill_mma(
+            ctypes.c_void_p(q_ptr), ctypes.c_void_p(k_ptr), ctypes.c_void_p(v_ptr), qkv.shape[1], _p(out),
+            out.shape[1], _p(seq_row0), _p(seq_len), seq_row0.numel(), int(max_len), n_heads, n_kv, head_dim,
+            float(scale), float(cap or 0.0), int(window or 0), _stream())
+        if code != _lib.ERR_UNSUPPORTED:
+            _lib.check(code, "attn_prefill_mma")
+            return out
     _lib.check(L.qnn_attn_prefill_generic(
         ctypes.c_void_p(q_ptr), ctypes.c_void_p(k_ptr), ctypes.c_void_p(v_ptr), qkv.shape[1], dt_code(qkv),
         _p(out), out.shape[1], _p(tok_pos), _p(tok_row0), T, n_heads, n_kv, head_dim, float(scale),

@@ -76,7 +76,7 @@ class AttentionMixer(Mixer):
                                        self.scale, self.softcap, self.window)
         elif step.mode == "prefill":
             a = ops.attn_prefill(qkv, self.n_heads, self.n_kv, self.head_dim, step.tok_pos, step.tok_row0,
-                                 self.scale, self.softcap, self.window)
+                                 self.scale, self.softcap, self.window, step.seq_row0, step.seq_len, step.max_q_len)
         else:
             a = ops.attn_decode(qkv, self.n_heads, self.n_kv, self.head_dim, line.k, line.v, line.page_table,
                                 line.page_size, line.ring, step.slots, line.slot_len, self.scale, self.softcap,

@@ -262,6 +262,56 @@ def test_attention_prefill(ops, dtype, nq, nkv, hd, window, cap):
         ref[r:r + n] = P.attention(q, k, v, scale, cap, window).reshape(n, -1)
         r += n
     assert_close(out, ref, dtype, "prefill attention", mult=4)
+    # with the per-sequence arrays, bfloat16 at head sizes 64/128/256 takes the tensor-core kernel
+    starts = np.cumsum([0] + lens[:-1]).astype(np.int32)
+    out2 = ops.attn_prefill(T(qkv, dtype), nq, nkv, hd, T(pos, torch.int32), T(row0, torch.int32), scale, cap, window,
+                            T(starts, torch.int32), T(np.array(lens, np.int32), torch.int32), max(lens))
+    assert_close(out2, ref, dtype, "prefill attention with sequence arrays", mult=4)
+
+
+@pytest.mark.parametrize("nq,nkv,hd", [(8, 4, 256), (4, 1, 128), (6, 2, 64)])
+@pytest.mark.parametrize("window,cap", [(None, 50.0), (100, None), (64, 30.0)])
+def test_attention_prefill_tensor_core_kernel_long_unequal(ops, nq, nkv, hd, window, cap):
+    """Sequences that span several 64-row tiles, of unequal lengths, against the plain attention."""
+    rng = np.random.default_rng(hd + (window or 0))
+    lens = [200, 1, 65, 130, 64]
+    Tn = sum(lens)
+    qkv = bf16_round(rng.normal(size=(Tn, (nq + 2 * nkv) * hd)))
+    pos = np.concatenate([np.arange(n) for n in lens]).astype(np.int32)
+    starts = np.cumsum([0] + lens[:-1]).astype(np.int32)
+    row0 = np.concatenate([np.full(n, s) for n, s in zip(lens, starts)]).astype(np.int32)
+    scale = 1.0 / math.sqrt(hd)
+    out = ops.attn_prefill(T(qkv, torch.bfloat16), nq, nkv, hd, T(pos, torch.int32), T(row0, torch.int32), scale, cap,
+                           window, T(starts, torch.int32), T(np.array(lens, np.int32), torch.int32), max(lens))
+    r = 0
+    for n in lens:
+        blk = qkv[r:r + n]
+        q = blk[:, :nq * hd].reshape(n, nq, hd)
+        k = blk[:, nq * hd:(nq + nkv) * hd].reshape(n, nkv, hd)
+        v = blk[:, (nq + nkv) * hd:].reshape(n, nkv, hd)
+        ref = P.attention(q, k, v, scale, cap, window).reshape(n, -1)
+        assert_close(out[r:r + n], ref, torch.bfloat16, f"sequence of {n}", mult=4)
+        r += n
+
+
+def test_window_edge_in_the_tensor_core_prefill_kernel(ops):
+    nq, nkv, hd, n, W = 2, 1, 64, 300, 100
+    k = np.zeros((n, nkv, hd))
+    v = np.zeros((n, nkv, hd))
+    v[:, 0, 0] = np.arange(n) // 16
+    v[:, 0, 1] = np.arange(n) % 16
+    k[n - W, 0, 0] = 6.0
+    k[n - W - 1, 0, 0] = 12.0
+    q = np.zeros((n, nq, hd))
+    q[:, :, 0] = 6.0
+    qkv = np.concatenate([q.reshape(n, -1), k.reshape(n, -1), v.reshape(n, -1)], axis=1)
+    i32 = lambda a: T(np.asarray(a, np.int32), torch.int32)  # noqa: E731
+    out = ops.attn_prefill(T(qkv, torch.bfloat16), nq, nkv, hd, i32(np.arange(n)), i32(np.zeros(n)), 1.0, None, W,
+                           i32([0]), i32([n]), n)
+    o = N(out).reshape(n, nq, hd)
+    found = np.rint(o[:, :, 0]) * 16 + np.rint(o[:, :, 1])
+    assert np.all(found[-1] == n - W), found[-1]               # the key just inside the window
+    assert np.all(found[-2] == n - W - 1), found[-2]           # one row earlier the outside key is still inside
 
 
 def _fill_cache(k, v, tables, dtype, pages, ring=0):
