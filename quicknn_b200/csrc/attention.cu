@@ -247,6 +247,8 @@ attn_decode_kernel(const T* __restrict__ q, size_t q_stride, const T* __restrict
                    const int* __restrict__ slots, const int* __restrict__ slot_len, int nq, int nkv, int hd, int LPT,
                    float scale, float cap, int window, float* __restrict__ part_o, float* __restrict__ part_ml,
                    int n_splits) {
+    pdl_launch_dependents();
+    pdl_wait();
     constexpr int VEC = Vec16<T>::N;
     extern __shared__ float smem[];  // [DEC_WARPS][GT][hd + 2]
     const int split = blockIdx.x, b = blockIdx.z;
@@ -314,6 +316,8 @@ attn_decode_tiled_kernel(const T* __restrict__ q, size_t q_stride, const T* __re
                          int page_size, int ring, const int* __restrict__ slots, const int* __restrict__ slot_len,
                          int nq, int nkv, int hd, int LPT, float scale, float cap, int window,
                          float* __restrict__ part_o, float* __restrict__ part_ml, int n_splits) {
+    pdl_launch_dependents();
+    pdl_wait();
     constexpr int VEC = Vec16<T>::N;
     constexpr int NV = GT * TT;
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -501,6 +505,8 @@ attn_decode_tiled_kernel(const T* __restrict__ q, size_t q_stride, const T* __re
 template <typename T>
 __global__ void attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                     T* __restrict__ out, size_t out_stride, int nq, int hd, int n_splits) {
+    pdl_launch_dependents();
+    pdl_wait();
     extern __shared__ float coef[];  // [n_splits] weights of the splits, then 1/sum
     const int b = blockIdx.x / nq, h = blockIdx.x % nq;
     const size_t pbase = ((size_t)b * nq + h) * n_splits;
@@ -541,6 +547,8 @@ attn_prefill_generic_kernel(const T* __restrict__ q, size_t q_stride, const T* _
                             const int* __restrict__ tok_row0, int n_tokens, int nq, int nkv, int hd, int LPT,
                             float scale, float cap, int window, const int* __restrict__ page_table, int max_pages,
                             int page_size, int ring) {
+    pdl_launch_dependents();
+    pdl_wait();
     constexpr int VEC = Vec16<T>::N;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x * PRE_WARPS + warp;
@@ -682,7 +690,7 @@ static int decode_launch(const void* q, long long q_stride, const void* k_pool, 
             if (ce != cudaSuccess) return (int)ce;                                                          \
             configured = true;                                                                              \
         }                                                                                                   \
-        kern<<<grid, DEC_WARPS * 32, smem_tiled, st>>>(QNN_DEC_ARGS);                                       \
+        qnn::launch_pdl(kern, dim3(grid), dim3(DEC_WARPS * 32), smem_tiled, st, QNN_DEC_ARGS);                                       \
         launched = true;                                                                                    \
     }
     QNN_TILED(1, 1, 8) QNN_TILED(1, 2, 8) QNN_TILED(1, 4, 8)
@@ -690,12 +698,12 @@ static int decode_launch(const void* q, long long q_stride, const void* k_pool, 
     QNN_TILED(2, 1, 4) QNN_TILED(2, 2, 4) QNN_TILED(2, 4, 4)
 #undef QNN_TILED
     if (!launched) {
-        QNN_DISPATCH_ALL({ attn_decode_kernel<T, CPL, GT><<<grid, DEC_WARPS * 32, smem, st>>>(QNN_DEC_ARGS); })
+        QNN_DISPATCH_ALL({ qnn::launch_pdl(attn_decode_kernel<T, CPL, GT>, dim3(grid), dim3(DEC_WARPS * 32), smem, st, QNN_DEC_ARGS); })
     }
 #undef QNN_DEC_ARGS
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
-    attn_combine_kernel<T><<<B * nq, hd >= 256 ? 256 : 128, (n_splits + 1) * sizeof(float), st>>>(part_o, part_ml, (T*)out, (size_t)out_stride, nq, hd, n_splits);
+    qnn::launch_pdl(attn_combine_kernel<T>, dim3(B * nq), dim3(hd >= 256 ? 256 : 128), (n_splits + 1) * sizeof(float), st, part_o, part_ml, (T*)out, (size_t)out_stride, nq, hd, n_splits);
     QNN_LAUNCH_CHECK();
 }
 
@@ -729,12 +737,12 @@ static int prefill_launch(const void* q, long long q_stride, const void* k, cons
     dim3 grid((n_tokens + PRE_WARPS - 1) / PRE_WARPS, nkv * gtiles);
     QNN_DISPATCH_ALL({
         if (paged)
-            attn_prefill_generic_kernel<T, CPL, GT, true><<<grid, PRE_WARPS * 32, 0, st>>>(
+            qnn::launch_pdl(attn_prefill_generic_kernel<T, CPL, GT, true>, dim3(grid), dim3(PRE_WARPS * 32), 0, st, 
                 (const T*)q, (size_t)q_stride, (const T*)k, (const T*)v, (size_t)row_stride, (T*)out,
                 (size_t)out_stride, tok_pos, tok_row0, n_tokens, nq, nkv, hd, geo.lpt, scale, cap, window, page_table,
                 max_pages, page_size, ring);
         else
-            attn_prefill_generic_kernel<T, CPL, GT, false><<<grid, PRE_WARPS * 32, 0, st>>>(
+            qnn::launch_pdl(attn_prefill_generic_kernel<T, CPL, GT, false>, dim3(grid), dim3(PRE_WARPS * 32), 0, st, 
                 (const T*)q, (size_t)q_stride, (const T*)k, (const T*)v, (size_t)row_stride, (T*)out,
                 (size_t)out_stride, tok_pos, tok_row0, n_tokens, nq, nkv, hd, geo.lpt, scale, cap, window, page_table,
                 max_pages, page_size, ring);

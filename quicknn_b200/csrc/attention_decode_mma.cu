@@ -65,6 +65,8 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, size_t q_stride, const bf16* 
                        int page_size, int ring, const int* __restrict__ slots, const int* __restrict__ slot_len,
                        int nq, int nkv, float scale, float cap, int window, float* __restrict__ part_o,
                        float* __restrict__ part_ml, int n_splits) {
+    pdl_launch_dependents();
+    pdl_wait();
     constexpr int KSTEPS = HD / 16;              // k16 steps of S^T, and 16-row tiles of O^T
     constexpr int CH = HD / 8;                   // 16-byte chunks per row
     constexpr int ROW_BYTES = HD * 2;
@@ -294,7 +296,7 @@ int launch(const void* q, long long q_stride, const void* k_pool, const void* v_
     }
     const int G = nq / nkv;
     dim3 grid(n_splits, nkv * ((G + 7) / 8), B);
-    kern<<<grid, MMA_WARPS * 32, smem, st>>>((const bf16*)q, (size_t)q_stride, (const bf16*)k_pool, (const bf16*)v_pool,
+    qnn::launch_pdl(kern, dim3(grid), dim3(MMA_WARPS * 32), smem, st, (const bf16*)q, (size_t)q_stride, (const bf16*)k_pool, (const bf16*)v_pool,
                                              page_table, max_pages, page_size, ring, slots, slot_len, nq, nkv, scale,
                                              cap, window, part_o, part_ml, n_splits);
     return (int)cudaGetLastError();

@@ -58,6 +58,8 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, 
                         size_t row_stride, bf16* __restrict__ out, size_t out_stride,
                         const int* __restrict__ seq_row0, const int* __restrict__ seq_len, int nq, int nkv, float scale,
                         float cap, int window) {
+    pdl_launch_dependents();
+    pdl_wait();
     constexpr int KSTEPS = HD / 16, CH = HD / 8, ROWB = HD * 2, NDT = HD / 8;
     constexpr int TILEB = BN * ROWB;
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -235,7 +237,7 @@ int launch(const void* q, const void* k, const void* v, long long row_stride, vo
         configured = true;
     }
     dim3 grid((max_len + BM - 1) / BM, B, nq);
-    kern<<<grid, PF_WARPS * 32, smem, st>>>((const bf16*)q, (const bf16*)k, (const bf16*)v, (size_t)row_stride,
+    qnn::launch_pdl(kern, dim3(grid), dim3(PF_WARPS * 32), smem, st, (const bf16*)q, (const bf16*)k, (const bf16*)v, (size_t)row_stride,
                                             (bf16*)out, (size_t)out_stride, seq_row0, seq_len, nq, nkv, scale, cap,
                                             window);
     return (int)cudaGetLastError();

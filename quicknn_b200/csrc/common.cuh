@@ -10,6 +10,7 @@
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #define QNN_ERR_UNSUPPORTED 10001
 #define QNN_ERR_ARGUMENT 10002
@@ -120,6 +121,43 @@ __device__ __forceinline__ float activate(float x, int act) {
     return act == QNN_ACT_SILU ? silu(x) : gelu_tanh(x);
 }
 
+}  // namespace qnn
+
+// ---- programmatic dependent launch ---------------------------------------------------------
+// Every kernel of this library starts with pdl_launch_dependents(); pdl_wait();  The first lets
+// the kernel that follows in the stream be scheduled while this one still runs; the second
+// blocks until everything before this kernel in the stream has completed and its writes are
+// visible.  So a kernel touches memory only after its predecessors are done (ordering is what it
+// would be without the feature), but its launch latency, and whatever it chooses to do before
+// pdl_wait() (prefetching weights, which no kernel writes), overlap the predecessor.
+namespace qnn {
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+inline bool pdl_enabled() {
+    static int on = -1;
+    if (on < 0) {
+        const char* e = getenv("QNN_PDL");
+        on = (e && e[0] == '0') ? 0 : 1;
+    }
+    return on == 1;
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                              Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 }  // namespace qnn
 
 #define QNN_LAUNCH_CHECK() return (int)cudaGetLastError()

@@ -19,6 +19,8 @@ using namespace qnn;
 template <typename W>
 __global__ void embed_kernel(const int* __restrict__ tokens, const W* __restrict__ table, float scale,
                              float* __restrict__ out, int H, int V) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x;
     const int tok = tokens[t];
     float* o = out + (size_t)t * H;
@@ -35,9 +37,9 @@ QNN_API int qnn_embed(const int* tokens, const void* table, int table_dtype, flo
     if (T <= 0) return 0;
     const int threads = H >= 1024 ? 256 : 128;
     if (table_dtype == QNN_DT_BF16)
-        embed_kernel<bf16><<<T, threads, 0, st>>>(tokens, (const bf16*)table, scale, out, H, V);
+        qnn::launch_pdl(embed_kernel<bf16>, dim3(T), dim3(threads), 0, st, tokens, (const bf16*)table, scale, out, H, V);
     else
-        embed_kernel<float><<<T, threads, 0, st>>>(tokens, (const float*)table, scale, out, H, V);
+        qnn::launch_pdl(embed_kernel<float>, dim3(T), dim3(threads), 0, st, tokens, (const float*)table, scale, out, H, V);
     QNN_LAUNCH_CHECK();
 }
 
@@ -46,6 +48,8 @@ QNN_API int qnn_embed(const int* tokens, const void* table, int table_dtype, flo
 // ---------------------------------------------------------------------------------
 __global__ void rmsnorm_kernel(const void* __restrict__ x, int x_dt, const void* __restrict__ w, int w_dt,
                                float eps, float offset, void* __restrict__ out, int out_dt, int H) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float red[32];
     const size_t base = (size_t)blockIdx.x * H;
     float ss = 0.f;
@@ -67,7 +71,7 @@ static inline int norm_threads(int H) { return H >= 2048 ? 512 : (H >= 512 ? 256
 QNN_API int qnn_rmsnorm(const void* x, int x_dt, const void* w, int w_dt, float eps, int unit_offset,
                         void* out, int out_dt, int T, int H, cudaStream_t st) {
     if (T <= 0) return 0;
-    rmsnorm_kernel<<<T, norm_threads(H), 0, st>>>(x, x_dt, w, w_dt, eps, unit_offset ? 1.f : 0.f, out, out_dt, H);
+    qnn::launch_pdl(rmsnorm_kernel, dim3(T), dim3(norm_threads(H)), 0, st, x, x_dt, w, w_dt, eps, unit_offset ? 1.f : 0.f, out, out_dt, H);
     QNN_LAUNCH_CHECK();
 }
 
@@ -76,12 +80,51 @@ QNN_API int qnn_rmsnorm(const void* x, int x_dt, const void* w, int w_dt, float 
 // Three passes over a row by the same thread -> element mapping, so a thread re-reads
 // only what it wrote itself.
 // ---------------------------------------------------------------------------------
+// PER = elements per thread held in registers (H <= PER * blockDim): every global load of the
+// kernel is issued before the first reduction, so the row costs two block reductions and no
+// dependent reloads.  PER = 0 is the looping form for rows that do not fit.
+template <int PER>
 __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const void* __restrict__ y, int y_dt,
                                    const void* __restrict__ w_post, int w_post_dt, float eps_post, float off_post,
                                    const void* __restrict__ w_next, int w_next_dt, float eps_next, float off_next,
                                    void* __restrict__ out_next, int out_dt, int H) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float red[32];
     const size_t base = (size_t)blockIdx.x * H;
+    if (PER > 0) {
+        float yv[PER > 0 ? PER : 1], rv[PER > 0 ? PER : 1], g1[PER > 0 ? PER : 1], g2[PER > 0 ? PER : 1];
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+            const int j = threadIdx.x + i * blockDim.x;
+            const bool in = j < H;
+            yv[i] = in ? load_as_f(y, y_dt, base + j) : 0.f;
+            rv[i] = in ? resid[base + j] : 0.f;
+            g1[i] = in ? load_as_f(w_post, w_post_dt, j) + off_post : 0.f;
+            g2[i] = (in && w_next != nullptr) ? load_as_f(w_next, w_next_dt, j) + off_next : 0.f;
+            ss += yv[i] * yv[i];
+        }
+        ss = block_sum(ss, red);
+        const float inv = rsqrtf(ss / (float)H + eps_post);
+        float ss2 = 0.f;
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+            const int j = threadIdx.x + i * blockDim.x;
+            rv[i] = rv[i] + yv[i] * inv * g1[i];
+            if (j < H) resid[base + j] = rv[i];
+            ss2 += rv[i] * rv[i];
+        }
+        if (w_next == nullptr) return;
+        ss2 = block_sum(ss2, red);
+        const float inv2 = rsqrtf(ss2 / (float)H + eps_next);
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+            const int j = threadIdx.x + i * blockDim.x;
+            if (j < H) store_from_f(out_next, out_dt, base + j, rv[i] * inv2 * g2[i]);
+        }
+        return;
+    }
     float ss = 0.f;
     for (int j = threadIdx.x; j < H; j += blockDim.x) {
         float v = load_as_f(y, y_dt, base + j);
@@ -111,20 +154,30 @@ QNN_API int qnn_add_rmsnorm(float* resid, const void* y, int y_dt, const void* w
                             float eps_post, int unit_post, const void* w_next, int w_next_dt, float eps_next,
                             int unit_next, void* out_next, int out_dt, int T, int H, cudaStream_t st) {
     if (T <= 0) return 0;
-    add_rmsnorm_kernel<<<T, norm_threads(H), 0, st>>>(resid, y, y_dt, w_post, w_post_dt, eps_post,
-                                                      unit_post ? 1.f : 0.f, w_next, w_next_dt, eps_next,
-                                                      unit_next ? 1.f : 0.f, out_next, out_dt, H);
+    const int threads = norm_threads(H);
+    const float o1 = unit_post ? 1.f : 0.f, o2 = unit_next ? 1.f : 0.f;
+#define QNN_ARN(PERV)                                                                                              \
+    qnn::launch_pdl(add_rmsnorm_kernel<PERV>, dim3(T), dim3(threads), 0, st, resid, y, y_dt, w_post, w_post_dt,     \
+                    eps_post, o1, w_next, w_next_dt, eps_next, o2, out_next, out_dt, H)
+    const int per = (H + threads - 1) / threads;
+    if (per <= 2) QNN_ARN(2);
+    else if (per <= 5) QNN_ARN(5);
+    else if (per <= 8) QNN_ARN(8);
+    else QNN_ARN(0);
+#undef QNN_ARN
     QNN_LAUNCH_CHECK();
 }
 
 // resid[i] += y[i]   (generic residual add for blocks that do not fuse)
 __global__ void add_kernel(float* __restrict__ resid, const void* __restrict__ y, int y_dt, size_t n) {
+    pdl_launch_dependents();
+    pdl_wait();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) resid[i] += load_as_f(y, y_dt, i);
 }
 QNN_API int qnn_add(float* resid, const void* y, int y_dt, long long n, cudaStream_t st) {
     if (n <= 0) return 0;
-    add_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(resid, y, y_dt, (size_t)n);
+    qnn::launch_pdl(add_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, resid, y, y_dt, (size_t)n);
     QNN_LAUNCH_CHECK();
 }
 
@@ -133,6 +186,8 @@ QNN_API int qnn_add(float* resid, const void* y, int y_dt, long long n, cudaStre
 // ---------------------------------------------------------------------------------
 template <typename T>
 __global__ void gated_act_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, int act, size_t n) {
+    pdl_launch_dependents();
+    pdl_wait();
     size_t id = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (id >= n) return;
     size_t t = id / I;
@@ -145,9 +200,9 @@ QNN_API int qnn_gated_act(const void* gu, void* out, int dtype, int T, int I, in
     if (n == 0) return 0;
     unsigned blocks = (unsigned)((n + 255) / 256);
     if (dtype == QNN_DT_BF16)
-        gated_act_kernel<bf16><<<blocks, 256, 0, st>>>((const bf16*)gu, (bf16*)out, I, act, n);
+        qnn::launch_pdl(gated_act_kernel<bf16>, dim3(blocks), dim3(256), 0, st, (const bf16*)gu, (bf16*)out, I, act, n);
     else
-        gated_act_kernel<float><<<blocks, 256, 0, st>>>((const float*)gu, (float*)out, I, act, n);
+        qnn::launch_pdl(gated_act_kernel<float>, dim3(blocks), dim3(256), 0, st, (const float*)gu, (float*)out, I, act, n);
     QNN_LAUNCH_CHECK();
 }
 
@@ -155,12 +210,14 @@ QNN_API int qnn_gated_act(const void* gu, void* out, int dtype, int T, int I, in
 // out[i] = softcap(x[i])  -> float32 (the logits)
 // ---------------------------------------------------------------------------------
 __global__ void softcap_kernel(const void* __restrict__ x, int x_dt, float* __restrict__ out, float cap, size_t n) {
+    pdl_launch_dependents();
+    pdl_wait();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) out[i] = softcap(load_as_f(x, x_dt, i), cap);
 }
 QNN_API int qnn_softcap(const void* x, int x_dt, float* out, float cap, long long n, cudaStream_t st) {
     if (n <= 0) return 0;
-    softcap_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(x, x_dt, out, cap, (size_t)n);
+    qnn::launch_pdl(softcap_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, x, x_dt, out, cap, (size_t)n);
     QNN_LAUNCH_CHECK();
 }
 
@@ -169,29 +226,35 @@ QNN_API int qnn_softcap(const void* x, int x_dt, float* out, float cap, long lon
 // ---------------------------------------------------------------------------------
 __global__ void gather_rows_kernel(const void* __restrict__ src, int src_dt, const int* __restrict__ rows,
                                    void* __restrict__ dst, int dst_dt, int H) {
+    pdl_launch_dependents();
+    pdl_wait();
     const size_t s = (size_t)rows[blockIdx.x] * H, d = (size_t)blockIdx.x * H;
     for (int j = threadIdx.x; j < H; j += blockDim.x) store_from_f(dst, dst_dt, d + j, load_as_f(src, src_dt, s + j));
 }
 QNN_API int qnn_gather_rows(const void* src, int src_dt, const int* rows, void* dst, int dst_dt, int R, int H,
                             cudaStream_t st) {
     if (R <= 0) return 0;
-    gather_rows_kernel<<<R, 256, 0, st>>>(src, src_dt, rows, dst, dst_dt, H);
+    qnn::launch_pdl(gather_rows_kernel, dim3(R), dim3(256), 0, st, src, src_dt, rows, dst, dst_dt, H);
     QNN_LAUNCH_CHECK();
 }
 
 // dst = convert(src)
 __global__ void cast_kernel(const void* __restrict__ src, int src_dt, void* __restrict__ dst, int dst_dt, size_t n) {
+    pdl_launch_dependents();
+    pdl_wait();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) store_from_f(dst, dst_dt, i, load_as_f(src, src_dt, i));
 }
 QNN_API int qnn_cast(const void* src, int src_dt, void* dst, int dst_dt, long long n, cudaStream_t st) {
     if (n <= 0) return 0;
-    cast_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(src, src_dt, dst, dst_dt, (size_t)n);
+    qnn::launch_pdl(cast_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, src, src_dt, dst, dst_dt, (size_t)n);
     QNN_LAUNCH_CHECK();
 }
 
 // flag |= 1 when any value is NaN or Inf
 __global__ void finite_kernel(const float* __restrict__ x, size_t n, int* __restrict__ flag) {
+    pdl_launch_dependents();
+    pdl_wait();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) {
         float v = x[i];
@@ -200,6 +263,6 @@ __global__ void finite_kernel(const float* __restrict__ x, size_t n, int* __rest
 }
 QNN_API int qnn_check_finite(const float* x, long long n, int* flag, cudaStream_t st) {
     if (n <= 0) return 0;
-    finite_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(x, (size_t)n, flag);
+    qnn::launch_pdl(finite_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, x, (size_t)n, flag);
     QNN_LAUNCH_CHECK();
 }

@@ -48,6 +48,7 @@ template <int NT, int EPI, int NW>
 __global__ void __launch_bounds__(NW * 32) skinny_bf16_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W,
                                                           void* __restrict__ out, int out_dt, int M, int N, int K,
                                                           float cap, int act) {
+    pdl_launch_dependents();
     constexpr int COLS = NT * 8;
     constexpr int THREADS = NW * 32;
     __shared__ float red[NW][16][COLS + 1];
@@ -76,6 +77,23 @@ __global__ void __launch_bounds__(NW * 32) skinny_bf16_kernel(const bf16* __rest
     const bf16* w1 = W + (size_t)r1 * K;
     const bf16* u0 = W + (size_t)(Nout + r0) * K;
     const bf16* u1 = W + (size_t)(Nout + r1) * K;
+
+    // The weights do not depend on the kernel before this one: pull this warp's share of them
+    // towards L2 while that kernel is still running, then wait for the activations.
+    if (t == 0) {
+        for (int kb = warp; kb < nkb; kb += NW) {
+            const size_t ko = (size_t)kb * 32;
+            if (ko < (size_t)K) {
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(w0 + ko));
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(w1 + ko));
+                if (EPI == EPI_GATED) {
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(u0 + ko));
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(u1 + ko));
+                }
+            }
+        }
+    }
+    pdl_wait();
 
 #pragma unroll 4
     for (int kb = warp; kb < nkb; kb += NW) {
@@ -172,11 +190,11 @@ static int launch_skinny(const bf16* x, const bf16* W, void* out, int out_dt, in
     if (nt == 1 && blocks * 16u < 3000u && kblocks >= 64) nw = 32;
 #define QNN_SK(NTV)                                                                                            \
     if (nw == 32 && NTV == 1)                                                                                  \
-        skinny_bf16_kernel<1, EPI, 32><<<blocks, 1024, 0, st>>>(x, W, out, out_dt, M, N, K, cap, act);         \
+        qnn::launch_pdl(skinny_bf16_kernel<1, EPI, 32>, dim3(blocks), dim3(1024), 0, st, x, W, out, out_dt, M, N, K, cap, act);         \
     else if (nw >= 16 && NTV <= 2)                                                                             \
-        skinny_bf16_kernel<(NTV <= 2 ? NTV : 1), EPI, 16><<<blocks, 512, 0, st>>>(x, W, out, out_dt, M, N, K, cap, act); \
+        qnn::launch_pdl(skinny_bf16_kernel<(NTV <= 2 ? NTV : 1), EPI, 16>, dim3(blocks), dim3(512), 0, st, x, W, out, out_dt, M, N, K, cap, act); \
     else                                                                                                       \
-        skinny_bf16_kernel<NTV, EPI, 8><<<blocks, 256, 0, st>>>(x, W, out, out_dt, M, N, K, cap, act);         \
+        qnn::launch_pdl(skinny_bf16_kernel<NTV, EPI, 8>, dim3(blocks), dim3(256), 0, st, x, W, out, out_dt, M, N, K, cap, act);         \
     break;
     switch (nt) {
         case 1: QNN_SK(1)
@@ -210,6 +228,8 @@ QNN_API int qnn_skinny_bf16(const void* x, const void* W, void* out, int out_dt,
 template <int MT, int EPI>
 __global__ void gemv_f32_kernel(const float* __restrict__ x, const float* __restrict__ W, float* __restrict__ out,
                                 int M, int N, int K, int m0, float cap, int act) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int Nout = (EPI == EPI_GATED) ? N / 2 : N;
     const int n = blockIdx.x * (blockDim.x >> 5) + warp;
@@ -269,9 +289,9 @@ QNN_API int qnn_gemv_f32(const float* x, const float* W, float* out, int M, int 
     const unsigned blocks = (unsigned)((Nout + warps - 1) / warps);
     for (int m0 = 0; m0 < M; m0 += 4) {
         switch (epi) {
-            case EPI_NONE: gemv_f32_kernel<4, EPI_NONE><<<blocks, warps * 32, 0, st>>>(x, W, out, M, N, K, m0, cap, act); break;
-            case EPI_SOFTCAP: gemv_f32_kernel<4, EPI_SOFTCAP><<<blocks, warps * 32, 0, st>>>(x, W, out, M, N, K, m0, cap, act); break;
-            case EPI_GATED: gemv_f32_kernel<4, EPI_GATED><<<blocks, warps * 32, 0, st>>>(x, W, out, M, N, K, m0, cap, act); break;
+            case EPI_NONE: qnn::launch_pdl(gemv_f32_kernel<4, EPI_NONE>, dim3(blocks), dim3(warps * 32), 0, st, x, W, out, M, N, K, m0, cap, act); break;
+            case EPI_SOFTCAP: qnn::launch_pdl(gemv_f32_kernel<4, EPI_SOFTCAP>, dim3(blocks), dim3(warps * 32), 0, st, x, W, out, M, N, K, m0, cap, act); break;
+            case EPI_GATED: qnn::launch_pdl(gemv_f32_kernel<4, EPI_GATED>, dim3(blocks), dim3(warps * 32), 0, st, x, W, out, M, N, K, m0, cap, act); break;
             default: return QNN_ERR_ARGUMENT;
         }
     }
@@ -285,6 +305,8 @@ QNN_API int qnn_gemv_f32(const float* x, const float* W, float* out, int M, int 
 template <int EPI>
 __global__ void __launch_bounds__(256) sgemm_f32_kernel(const float* __restrict__ A, const float* __restrict__ B,
                                                         float* __restrict__ C, int M, int N, int K, float cap) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float As[16][64 + 4];
     __shared__ float Bs[16][64 + 4];
     const int tid = threadIdx.x;
@@ -351,8 +373,8 @@ QNN_API int qnn_sgemm_f32(const float* A, const float* B, float* C, int M, int N
     if (K <= 0) return QNN_ERR_ARGUMENT;
     dim3 grid((N + 63) / 64, (M + 63) / 64);
     if (grid.y > 65535) return QNN_ERR_UNSUPPORTED;
-    if (epi == EPI_SOFTCAP) sgemm_f32_kernel<EPI_SOFTCAP><<<grid, 256, 0, st>>>(A, B, C, M, N, K, cap);
-    else if (epi == EPI_NONE) sgemm_f32_kernel<EPI_NONE><<<grid, 256, 0, st>>>(A, B, C, M, N, K, cap);
+    if (epi == EPI_SOFTCAP) qnn::launch_pdl(sgemm_f32_kernel<EPI_SOFTCAP>, dim3(grid), dim3(256), 0, st, A, B, C, M, N, K, cap);
+    else if (epi == EPI_NONE) qnn::launch_pdl(sgemm_f32_kernel<EPI_NONE>, dim3(grid), dim3(256), 0, st, A, B, C, M, N, K, cap);
     else return QNN_ERR_ARGUMENT;
     QNN_LAUNCH_CHECK();
 }

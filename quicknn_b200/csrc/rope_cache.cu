@@ -22,6 +22,8 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, int nq, int nkv, int hd, 
                                   const int* __restrict__ tok_slot, T* __restrict__ k_pool, T* __restrict__ v_pool,
                                   const int* __restrict__ page_table, int max_pages, int page_size, int ring,
                                   const int* __restrict__ slot_len, int write_cache) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x;
     const int pos = tok_pos[t];
     const int slot = tok_slot[t];
@@ -85,11 +87,11 @@ QNN_API int qnn_rope_cache_write(void* qkv, int dtype, int T, int nq, int nkv, i
     const int work = (nq + nkv) * hd / 2;
     const int threads = work >= 1024 ? 256 : (work >= 256 ? 128 : 64);
     if (dtype == QNN_DT_BF16)
-        rope_cache_kernel<bf16><<<T, threads, 0, st>>>((bf16*)qkv, nq, nkv, hd, rot, inv_freq, tok_pos, tok_slot,
+        qnn::launch_pdl(rope_cache_kernel<bf16>, dim3(T), dim3(threads), 0, st, (bf16*)qkv, nq, nkv, hd, rot, inv_freq, tok_pos, tok_slot,
                                                        (bf16*)k_pool, (bf16*)v_pool, page_table, max_pages,
                                                        page_size, ring, slot_len, write_cache);
     else
-        rope_cache_kernel<float><<<T, threads, 0, st>>>((float*)qkv, nq, nkv, hd, rot, inv_freq, tok_pos, tok_slot,
+        qnn::launch_pdl(rope_cache_kernel<float>, dim3(T), dim3(threads), 0, st, (float*)qkv, nq, nkv, hd, rot, inv_freq, tok_pos, tok_slot,
                                                         (float*)k_pool, (float*)v_pool, page_table, max_pages,
                                                         page_size, ring, slot_len, write_cache);
     QNN_LAUNCH_CHECK();

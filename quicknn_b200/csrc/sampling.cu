@@ -55,6 +55,8 @@ __device__ __forceinline__ void block_argmax(float& v, unsigned& id, float* sv, 
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_tile_kernel(const float* __restrict__ logits, int V, int k, float penalty, const unsigned char* __restrict__ seen,
                    const int* __restrict__ seen_rows, float2* __restrict__ cand, int* __restrict__ error_flag) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float sv[32];
     __shared__ unsigned si[32];
     const int tile = blockIdx.x, r = blockIdx.y, tiles = gridDim.x;
@@ -97,6 +99,8 @@ __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_merge_kernel(float2* __restrict__ cand, int ncand, int k, float temperature, float top_p,
                     unsigned* __restrict__ rng_state, int* __restrict__ out_tokens, unsigned char* __restrict__ seen,
                     const int* __restrict__ seen_rows, int V) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float sv[32];
     __shared__ unsigned si[32];
     __shared__ float top_v[SAMPLE_MAX_K];
@@ -156,11 +160,11 @@ QNN_API int qnn_sample(const float* logits, int R, int V, int top_k, float tempe
     if (temperature <= 0.f) k = 1;
     const int tiles = (V + SAMPLE_TILE - 1) / SAMPLE_TILE;
     if (R > 65535) return QNN_ERR_UNSUPPORTED;
-    sample_tile_kernel<<<dim3(tiles, R), SAMPLE_THREADS, 0, st>>>(logits, V, k, penalty, penalty != 1.f ? seen : nullptr,
+    qnn::launch_pdl(sample_tile_kernel, dim3(dim3(tiles, R)), dim3(SAMPLE_THREADS), 0, st, logits, V, k, penalty, penalty != 1.f ? seen : nullptr,
                                                                  seen_rows, (float2*)cand, error_flag);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
-    sample_merge_kernel<<<R, SAMPLE_THREADS, 0, st>>>((float2*)cand, tiles * k, k, temperature, top_p, rng_state,
+    qnn::launch_pdl(sample_merge_kernel, dim3(R), dim3(SAMPLE_THREADS), 0, st, (float2*)cand, tiles * k, k, temperature, top_p, rng_state,
                                                       out_tokens, seen, seen_rows, V);
     QNN_LAUNCH_CHECK();
 }
@@ -175,6 +179,8 @@ QNN_API int qnn_sample_scratch_bytes(int R, int V, int top_k) {
 // seen[rows[t]][tokens[t]] = 1   (prompt tokens; rows[t] < 0 is skipped)
 __global__ void mark_seen_kernel(const int* __restrict__ tokens, const int* __restrict__ rows,
                                  unsigned char* __restrict__ seen, int V, int T) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x * blockDim.x + threadIdx.x;
     if (t >= T) return;
     const int tok = tokens[t], r = rows[t];
@@ -182,6 +188,6 @@ __global__ void mark_seen_kernel(const int* __restrict__ tokens, const int* __re
 }
 QNN_API int qnn_mark_seen(const int* tokens, const int* rows, unsigned char* seen, int V, int T, cudaStream_t st) {
     if (T <= 0) return 0;
-    mark_seen_kernel<<<(T + 255) / 256, 256, 0, st>>>(tokens, rows, seen, V, T);
+    qnn::launch_pdl(mark_seen_kernel, dim3((T + 255) / 256), dim3(256), 0, st, tokens, rows, seen, V, T);
     QNN_LAUNCH_CHECK();
 }

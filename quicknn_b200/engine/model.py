@@ -127,9 +127,15 @@ class Model:
         """Logits (float32, [wanted rows, vocab]) of the rows in ``step.want_rows``."""
         spec = self.spec
         x = ops.embed(step.tokens, self.embedding, spec.embedding.scale)
-        for e in spec.schedule:
+        normed = None
+        sched = spec.schedule
+        for i, e in enumerate(sched):
             line = cache.line(e.cache, writes=e.writes_cache)
-            x = self.blocks[e.layer].forward(x, step, line)
+            # the first norm of the layer that runs next is applied by this one, in the kernel
+            # that adds this layer's last sublayer to the residual stream
+            nxt = self.blocks[sched[i + 1].layer].first_norm() if i + 1 < len(sched) else None
+            out = self.blocks[e.layer].forward(x, step, line, normed=normed, next_norm=nxt)
+            x, normed = out if nxt is not None else (out, None)
         return self.logits_of_rows(x, step.want_rows, step.act_dtype)
 
     def logits_of_rows(self, x: torch.Tensor, rows: torch.Tensor, act_dtype: torch.dtype) -> torch.Tensor:

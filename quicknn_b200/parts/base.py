@@ -135,5 +135,13 @@ class FeedForward(Part):
 
 
 class Block(Part):
-    def forward(self, resid, step, line):  # pragma: no cover - interface
+    def first_norm(self):
+        """The norm that this block applies to its input first, or None.  When it gives one,
+        the block that runs before it may apply it (fused with its own last add) and hand
+        the result over as ``normed``."""
+        return None
+
+    def forward(self, resid, step, line, normed=None, next_norm=None):  # pragma: no cover - interface
+        """Update the float32 residual stream in place.  Returns it, or the pair
+        (residual stream, next_norm(residual stream)) when ``next_norm`` is given."""
         raise NotImplementedError

@@ -6,7 +6,9 @@ is added:  x += post(mixer(pre(x)));  x += post(ff(pre(x))).
 ``prenorm``: x += mixer(pre(x));  x += ff(pre(x)).
 
 The residual stream is float32 in both precisions.  When the norms are RMSNorm the
-post-norm, the add and the next pre-norm run as one kernel.
+post-norm, the add and the next pre-norm run as one kernel; that also holds across the
+border of two layers: ``forward`` may be handed its input already normed (``normed``) and
+may be asked to apply the first norm of the layer that runs next (``next_norm``).
 """
 from __future__ import annotations
 
@@ -61,10 +63,15 @@ class _LayerParts(Block):
 class SandwichBlock(_LayerParts):
     NORM_NAMES = ("pre_mixer", "post_mixer", "pre_ff", "post_ff")
 
-    def forward(self, resid: torch.Tensor, step, line) -> torch.Tensor:
+    def first_norm(self):
+        return self.norms["pre_mixer"]
+
+    def forward(self, resid: torch.Tensor, step, line, normed=None, next_norm=None):
+        """Returns the residual stream, or (residual stream, next_norm(residual stream)) when
+        ``next_norm`` (an RMSNorm) is given."""
         nm = self.norms
         act = step.act_dtype
-        n = nm["pre_mixer"](resid, act)
+        n = normed if normed is not None else nm["pre_mixer"](resid, act)
         y = self.mixer.forward(n, step, line)
         if isinstance(nm["post_mixer"], RMSNorm) and isinstance(nm["pre_ff"], RMSNorm):
             n = nm["post_mixer"].add_to(resid, y, then=nm["pre_ff"], out_dtype=act)
@@ -73,9 +80,13 @@ class SandwichBlock(_LayerParts):
             n = nm["pre_ff"](resid, act)
         y = self.ff.forward(n, step)
         if isinstance(nm["post_ff"], RMSNorm):
+            if isinstance(next_norm, RMSNorm):
+                return resid, nm["post_ff"].add_to(resid, y, then=next_norm, out_dtype=act)
             nm["post_ff"].add_to(resid, y)
         else:
             ops.add_(resid, nm["post_ff"](y, act))
+        if next_norm is not None:
+            return resid, next_norm(resid, act)
         return resid
 
 
@@ -83,8 +94,14 @@ class SandwichBlock(_LayerParts):
 class PreNormBlock(_LayerParts):
     NORM_NAMES = ("pre_mixer", "pre_ff")
 
-    def forward(self, resid: torch.Tensor, step, line) -> torch.Tensor:
+    def first_norm(self):
+        return self.norms["pre_mixer"]
+
+    def forward(self, resid: torch.Tensor, step, line, normed=None, next_norm=None):
         act = step.act_dtype
-        ops.add_(resid, self.mixer.forward(self.norms["pre_mixer"](resid, act), step, line))
+        n = normed if normed is not None else self.norms["pre_mixer"](resid, act)
+        ops.add_(resid, self.mixer.forward(n, step, line))
         ops.add_(resid, self.ff.forward(self.norms["pre_ff"](resid, act), step))
+        if next_norm is not None:
+            return resid, next_norm(resid, act)
         return resid
