@@ -76,6 +76,27 @@ template <> struct Vec16<bf16> {
     }
 };
 
+// Eight consecutive values of runtime dtype, 16-byte aligned, as floats (and back).
+__device__ __forceinline__ void load8_as_f(const void* p, int dtype, size_t i, float* o) {
+    if (dtype == QNN_DT_BF16) {
+        Vec16<bf16> v;
+        v.load((const bf16*)p + i);
+        v.unpack(o);
+    } else {
+        const float4 a = *reinterpret_cast<const float4*>((const float*)p + i);
+        const float4 b = *reinterpret_cast<const float4*>((const float*)p + i + 4);
+        o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w; o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
+    }
+}
+__device__ __forceinline__ void store8_from_f(void* p, int dtype, size_t i, const float* v) {
+    if (dtype == QNN_DT_BF16) {
+        Vec16<bf16>::store((bf16*)p + i, v);
+    } else {
+        *reinterpret_cast<float4*>((float*)p + i) = make_float4(v[0], v[1], v[2], v[3]);
+        *reinterpret_cast<float4*>((float*)p + i + 4) = make_float4(v[4], v[5], v[6], v[7]);
+    }
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

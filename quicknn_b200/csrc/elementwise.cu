@@ -150,12 +150,85 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const void* __rest
     }
 }
 
+// The same with 8 consecutive elements per access (H a multiple of 8, 16-byte aligned rows):
+// CH chunks of 8 per thread.
+template <int CH>
+__global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const void* __restrict__ y, int y_dt,
+                                       const void* __restrict__ w_post, int w_post_dt, float eps_post, float off_post,
+                                       const void* __restrict__ w_next, int w_next_dt, float eps_next, float off_next,
+                                       void* __restrict__ out_next, int out_dt, int H) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float red[32];
+    const size_t base = (size_t)blockIdx.x * H;
+    const int nchunks = H >> 3;
+    float yv[CH][8], rv[CH][8], g1[CH][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < CH; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        if (c < nchunks) {
+            load8_as_f(y, y_dt, base + c * 8, yv[i]);
+            load8_as_f(resid, QNN_DT_F32, base + c * 8, rv[i]);
+            load8_as_f(w_post, w_post_dt, (size_t)c * 8, g1[i]);
+        } else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) yv[i][e] = rv[i][e] = g1[i][e] = 0.f;
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ss += yv[i][e] * yv[i][e];
+    }
+    ss = block_sum(ss, red);
+    const float inv = rsqrtf(ss / (float)H + eps_post);
+    float ss2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < CH; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            rv[i][e] = rv[i][e] + yv[i][e] * inv * (g1[i][e] + off_post);
+            ss2 += (c < nchunks) ? rv[i][e] * rv[i][e] : 0.f;
+        }
+        if (c < nchunks) store8_from_f(resid, QNN_DT_F32, base + c * 8, rv[i]);
+    }
+    if (w_next == nullptr) return;
+    ss2 = block_sum(ss2, red);
+    const float inv2 = rsqrtf(ss2 / (float)H + eps_next);
+#pragma unroll
+    for (int i = 0; i < CH; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        if (c < nchunks) {
+            float g2[8], o[8];
+            load8_as_f(w_next, w_next_dt, (size_t)c * 8, g2);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) o[e] = rv[i][e] * inv2 * (g2[e] + off_next);
+            store8_from_f(out_next, out_dt, base + c * 8, o);
+        }
+    }
+}
+
 QNN_API int qnn_add_rmsnorm(float* resid, const void* y, int y_dt, const void* w_post, int w_post_dt,
                             float eps_post, int unit_post, const void* w_next, int w_next_dt, float eps_next,
                             int unit_next, void* out_next, int out_dt, int T, int H, cudaStream_t st) {
     if (T <= 0) return 0;
-    const int threads = norm_threads(H);
     const float o1 = unit_post ? 1.f : 0.f, o2 = unit_next ? 1.f : 0.f;
+    const bool aligned = ((((uintptr_t)resid | (uintptr_t)y | (uintptr_t)w_post | (uintptr_t)w_next | (uintptr_t)out_next) & 15) == 0);
+    if ((H & 7) == 0 && aligned && H <= 8 * 4 * 1024) {
+        // few rows: many threads per row (latency); many rows: fewer threads, more rows per SM
+        const int chunks = H >> 3;
+        int ch = T <= 64 ? 1 : 2;
+        while ((chunks + ch - 1) / ch > 1024) ch *= 2;
+        const int threads = (((chunks + ch - 1) / ch) + 31) / 32 * 32;
+#define QNN_ARV(CHV)                                                                                                 \
+    qnn::launch_pdl(add_rmsnorm_vec_kernel<CHV>, dim3(T), dim3(threads), 0, st, resid, y, y_dt, w_post, w_post_dt,    \
+                    eps_post, o1, w_next, w_next_dt, eps_next, o2, out_next, out_dt, H)
+        if (ch == 1) QNN_ARV(1);
+        else if (ch == 2) QNN_ARV(2);
+        else QNN_ARV(4);
+#undef QNN_ARV
+        QNN_LAUNCH_CHECK();
+    }
+    const int threads = norm_threads(H);
 #define QNN_ARN(PERV)                                                                                              \
     qnn::launch_pdl(add_rmsnorm_kernel<PERV>, dim3(T), dim3(threads), 0, st, resid, y, y_dt, w_post, w_post_dt,     \
                     eps_post, o1, w_next, w_next_dt, eps_next, o2, out_next, out_dt, H)
@@ -195,9 +268,38 @@ __global__ void gated_act_kernel(const T* __restrict__ gu, T* __restrict__ out, 
     float g = to_f(gu[t * 2 * I + i]), u = to_f(gu[t * 2 * I + I + i]);
     out[id] = from_f<T>(activate(g, act) * u);
 }
+// 8 consecutive columns per thread, one row per blockIdx.y (I a multiple of 8)
+template <typename T>
+__global__ void gated_act_vec_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, int act) {
+    pdl_launch_dependents();
+    pdl_wait();
+    constexpr int VEC = Vec16<T>::N;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c * VEC >= I) return;
+    const size_t row = blockIdx.y;
+    Vec16<T> gv, uv;
+    gv.load(gu + row * 2 * I + (size_t)c * VEC);
+    uv.load(gu + row * 2 * I + I + (size_t)c * VEC);
+    float g[VEC], u[VEC];
+    gv.unpack(g);
+    uv.unpack(u);
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) g[e] = activate(g[e], act) * u[e];
+    Vec16<T>::store(out + row * I + (size_t)c * VEC, g);
+}
+
 QNN_API int qnn_gated_act(const void* gu, void* out, int dtype, int T, int I, int act, cudaStream_t st) {
     size_t n = (size_t)T * I;
     if (n == 0) return 0;
+    const int vec = dtype == QNN_DT_BF16 ? 8 : 4;
+    if (I % vec == 0 && T <= 65535 && ((((uintptr_t)gu | (uintptr_t)out) & 15) == 0)) {
+        dim3 grid((I / vec + 255) / 256, T);
+        if (dtype == QNN_DT_BF16)
+            qnn::launch_pdl(gated_act_vec_kernel<bf16>, grid, dim3(256), 0, st, (const bf16*)gu, (bf16*)out, I, act);
+        else
+            qnn::launch_pdl(gated_act_vec_kernel<float>, grid, dim3(256), 0, st, (const float*)gu, (float*)out, I, act);
+        QNN_LAUNCH_CHECK();
+    }
     unsigned blocks = (unsigned)((n + 255) / 256);
     if (dtype == QNN_DT_BF16)
         qnn::launch_pdl(gated_act_kernel<bf16>, dim3(blocks), dim3(256), 0, st, (const bf16*)gu, (bf16*)out, I, act, n);
