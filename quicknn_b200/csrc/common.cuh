@@ -141,6 +141,17 @@ __device__ __forceinline__ float silu(float x) { return x / (1.f + expf(-x)); }
 __device__ __forceinline__ float activate(float x, int act) {
     return act == QNN_ACT_SILU ? silu(x) : gelu_tanh(x);
 }
+// The same for results that are rounded to bfloat16 anyway: the hardware tanh (error about
+// 2^-11, below bfloat16's rounding) and the fast exponential.
+__device__ __forceinline__ float tanh_approx(float x) {
+    float r;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
+__device__ __forceinline__ float activate_fast(float x, int act) {
+    if (act == QNN_ACT_SILU) return __fdividef(x, 1.f + __expf(-x));
+    return 0.5f * x * (1.f + tanh_approx(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+}
 
 }  // namespace qnn
 

@@ -284,7 +284,7 @@ __global__ void gated_act_vec_kernel(const T* __restrict__ gu, T* __restrict__ o
     gv.unpack(g);
     uv.unpack(u);
 #pragma unroll
-    for (int e = 0; e < VEC; ++e) g[e] = activate(g[e], act) * u[e];
+    for (int e = 0; e < VEC; ++e) g[e] = (sizeof(T) == 2 ? activate_fast(g[e], act) : activate(g[e], act)) * u[e];
     Vec16<T>::store(out + row * I + (size_t)c * VEC, g);
 }
 

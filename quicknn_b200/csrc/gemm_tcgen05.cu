@@ -1,0 +1,305 @@
+// Whole-prompt matrix products on the 5th-generation tensor cores:
+//     C[M, N] = A[M, K] * B[N, K]^T      bfloat16 in, float32 accumulation in tensor memory
+// with the epilogues that follow the products in the model (none, or the gated activation
+// act(gate) * up for a weight matrix that stacks [gate; up]).
+//
+// Reference: the 64x64 fp32-FMA tile of src/backends/vulkan/shaders/gemm.comp:4-6 and the separate
+// GO_GEGLU dispatch (src/models/QuickNN.Models.Gemma2.pas:184-186).  Here:
+//   * one CTA computes a 128 x 256 tile; K is walked in slabs of 64 (128-byte rows, 128-byte swizzle);
+//   * warp 0 (one lane) is the producer: TMA (cp.async.bulk.tensor) loads of the A and B slabs into a
+//     4-stage ring in shared memory, completion counted in bytes on an mbarrier per stage;
+//   * warp 1 (one lane) issues tcgen05.mma (M 128, N 256, K 16; four per slab) from shared-memory
+//     descriptors into a 256-column accumulator in tensor memory, and tcgen05.commit hands each stage
+//     back to the producer and, after the last slab, the accumulator to the epilogue;
+//   * warps 2..5 are the epilogue: tcgen05.ld (32 lanes x 32 columns at a time), activation, convert,
+//     16-byte stores.  For the gated epilogue the B slab holds 128 gate rows and the 128 matching up
+//     rows, so one accumulator holds both halves.
+// Rows and columns beyond M, N, K are zero-filled by TMA and never stored.
+//
+// Every wait on an mbarrier is bounded: when it runs out, the thread sets a word in global memory
+// (`status`), stops waiting, and the CTA still frees its tensor memory and returns; the host reads
+// the word and raises.  No wait here can hang the GPU.
+#include "common.cuh"
+#include <cuda.h>
+
+using namespace qnn;
+
+#define EPI_NONE 0
+#define EPI_GATED 2
+
+namespace {
+
+constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4, UMMA_K = 16;
+constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int TMEM_COLS = 256;
+constexpr int GEMM_THREADS = 192;
+constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;   // SM clock cycles before a wait gives up
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// true when the phase with this parity has completed; false when the time limit ran out
+// (about a second of SM clock; a slab of this kernel takes microseconds)
+__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity) {
+    const long long start = clock64();
+    for (;;) {
+        unsigned done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done) : "r"(bar), "r"(parity), "r"(1000u) : "memory");     // suspend at most ~1 us per try
+        if (done) return true;
+        if (clock64() - start > WAIT_LIMIT_CYCLES) return false;
+    }
+}
+__device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap* map, unsigned bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+// K-major operand, 128-byte swizzle: rows of 128 bytes, groups of 8 rows 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc(unsigned smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);        // start address
+    d |= (uint64_t)1 << 16;                             // leading byte offset (unused for this layout)
+    d |= (uint64_t)(1024 >> 4) << 32;                   // stride byte offset: 8 rows x 128 B
+    d |= (uint64_t)1 << 46;                             // descriptor version of this architecture
+    d |= (uint64_t)2 << 61;                             // 128-byte swizzle
+    return d;
+}
+__device__ __forceinline__ void umma_bf16(unsigned tmem_d, uint64_t adesc, uint64_t bdesc, unsigned idesc, unsigned accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(unsigned bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(unsigned taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+struct __align__(8) Barriers {
+    uint64_t full[STAGES];
+    uint64_t empty[STAGES];
+    uint64_t acc_ready;
+    uint32_t tmem_base;
+    uint32_t failed;
+};
+
+template <int EPI>
+__global__ void __launch_bounds__(GEMM_THREADS)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    bf16* __restrict__ C, int M, int N, int K, int act, int* __restrict__ status) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    // the operand ring wants 1024-byte alignment (8 swizzled rows); the barriers follow it
+    unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    Barriers* bars = reinterpret_cast<Barriers*>(smem + STAGES * STAGE_BYTES);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.x * BM;
+    const int Nout = (EPI == EPI_GATED) ? N / 2 : N;
+    const int n0 = blockIdx.y * ((EPI == EPI_GATED) ? BN / 2 : BN);    // first output column of this tile
+    const int nk = (K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(smem_u32(&bars->full[s]), 1);
+            mbar_init(smem_u32(&bars->empty[s]), 1);
+        }
+        mbar_init(smem_u32(&bars->acc_ready), 1);
+        bars->failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {   // this warp owns the tensor memory: allocates it here, frees it at the end
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(&bars->tmem_base)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const unsigned tmem = bars->tmem_base;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // ---- producer -------------------------------------------------------------------
+            for (int kb = 0; kb < nk; ++kb) {
+                const int s = kb % STAGES;
+                if (kb >= STAGES && !mbar_wait(smem_u32(&bars->empty[s]), ((kb / STAGES) - 1) & 1)) {
+                    atomicOr(status, 1);
+                    bars->failed = 1;
+                    break;
+                }
+                const unsigned full = smem_u32(&bars->full[s]);
+                const unsigned a_dst = smem_u32(smem + s * STAGE_BYTES), b_dst = a_dst + A_BYTES;
+                mbar_expect_tx(full, STAGE_BYTES);
+                tma_load_2d(a_dst, &map_a, full, kb * BK, m0);
+                if (EPI == EPI_GATED) {
+                    tma_load_2d(b_dst, &map_b, full, kb * BK, n0);                        // 128 gate rows
+                    tma_load_2d(b_dst + B_BYTES / 2, &map_b, full, kb * BK, Nout + n0);   // the 128 up rows
+                } else {
+                    tma_load_2d(b_dst, &map_b, full, kb * BK, n0);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // ---- tensor-core issue ------------------------------------------------------------
+            // instruction descriptor: D float32, A and B bfloat16, both K-major, N >> 3, M >> 4
+            const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(BN >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
+            bool ok = true;
+            for (int kb = 0; kb < nk && ok; ++kb) {
+                const int s = kb % STAGES;
+                if (!mbar_wait(smem_u32(&bars->full[s]), (kb / STAGES) & 1)) {
+                    atomicOr(status, 2);
+                    bars->failed = 1;
+                    ok = false;
+                    break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const unsigned a_addr = smem_u32(smem + s * STAGE_BYTES), b_addr = a_addr + A_BYTES;
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k) {
+                    // 16 elements further along K = 32 bytes inside the 128-byte swizzled row
+                    umma_bf16(tmem, umma_desc(a_addr + k * UMMA_K * 2), umma_desc(b_addr + k * UMMA_K * 2), idesc,
+                              (kb > 0 || k > 0) ? 1u : 0u);
+                }
+                umma_commit(smem_u32(&bars->empty[s]));     // the stage is free once these MMAs have read it
+            }
+            umma_commit(smem_u32(&bars->acc_ready));        // arrives when everything issued so far is done
+        }
+    } else {
+        // ---- epilogue: warps 2..5, each owns the 32 accumulator lanes (rows) of its quarter ----------
+        const bool ok = mbar_wait(smem_u32(&bars->acc_ready), 0);
+        if (!ok) atomicOr(status, 4);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (ok && *reinterpret_cast<volatile uint32_t*>(&bars->failed) == 0) {
+            const int quarter = warp & 3;
+            const int m = m0 + quarter * 32 + lane;
+            const unsigned lane_addr = tmem + ((unsigned)(quarter * 32) << 16);
+            constexpr int OUT_COLS = (EPI == EPI_GATED) ? BN / 2 : BN;
+#pragma unroll 1
+            for (int c0 = 0; c0 < OUT_COLS; c0 += 32) {
+                uint32_t v[32];
+                tmem_ld32(lane_addr + c0, v);
+                float f[32];
+                if (EPI == EPI_GATED) {
+                    uint32_t u[32];
+                    tmem_ld32(lane_addr + BN / 2 + c0, u);
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) f[j] = activate_fast(__uint_as_float(v[j]), act) * __uint_as_float(u[j]);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+                }
+                if (m < M) {
+                    bf16* dst = C + (size_t)m * Nout + n0 + c0;
+                    if (n0 + c0 + 32 <= Nout && ((Nout & 7) == 0)) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 8) Vec16<bf16>::store(dst + j, f + j);
+                    } else {
+                        for (int j = 0; j < 32; ++j)
+                            if (n0 + c0 + j < Nout) dst[j] = __float2bfloat16_rn(f[j]);
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encoder() {
+    static EncodeTiled fn = nullptr;
+    if (fn == nullptr) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiled>(p);
+    }
+    return fn;
+}
+
+// rows x K bfloat16, row-major; box = 64 columns x box_rows rows, 128-byte swizzle, zero fill outside
+int make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) {
+    EncodeTiled enc = encoder();
+    if (enc == nullptr) return QNN_ERR_UNSUPPORTED;
+    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : QNN_ERR_ARGUMENT;
+}
+
+}  // namespace
+
+// C = A B^T (epi 0) or act(A Bgate^T) * (A Bup^T) with B = [gate; up] (epi 2; C is [M, N/2]).
+// `status` is one int in device memory that the caller zeroed: a non-zero value after the kernel
+// means a bounded wait ran out (bit 0 producer, bit 1 tensor-core issue, bit 2 epilogue) and C is
+// not valid.  K must be a multiple of 8 (16-byte row pitch) and the bases 16-byte aligned.
+QNN_API int qnn_gemm_tcgen05(const void* A, const void* B, void* C, int M, int N, int K, int epi, int act,
+                             int* status, cudaStream_t st) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0 || (K & 7) || ((((uintptr_t)A | (uintptr_t)B | (uintptr_t)C) & 15) != 0)) return QNN_ERR_UNSUPPORTED;
+    if (epi != EPI_NONE && epi != EPI_GATED) return QNN_ERR_ARGUMENT;
+    if (epi == EPI_GATED && (N & 1)) return QNN_ERR_ARGUMENT;
+    CUtensorMap map_a, map_b;
+    int rc = make_map(&map_a, A, M, K, BM);
+    if (rc) return rc;
+    rc = make_map(&map_b, B, N, K, epi == EPI_GATED ? BN / 2 : BN);
+    if (rc) return rc;
+    const int Nout = epi == EPI_GATED ? N / 2 : N;
+    const int cols = epi == EPI_GATED ? BN / 2 : BN;
+    dim3 grid((M + BM - 1) / BM, (Nout + cols - 1) / cols);
+    if (grid.y > 65535) return QNN_ERR_UNSUPPORTED;
+    const size_t smem = (size_t)STAGES * STAGE_BYTES + sizeof(Barriers) + 1024;
+    if (epi == EPI_GATED) {
+        auto kern = gemm_tcgen05_kernel<EPI_GATED>;
+        static bool configured = false;
+        if (!configured) {
+            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return (int)e;
+            configured = true;
+        }
+        cudaError_t e = qnn::launch_pdl(kern, grid, dim3(GEMM_THREADS), smem, st, map_a, map_b, (bf16*)C, M, N, K, act, status);
+        return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
+    }
+    auto kern = gemm_tcgen05_kernel<EPI_NONE>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    cudaError_t e = qnn::launch_pdl(kern, grid, dim3(GEMM_THREADS), smem, st, map_a, map_b, (bf16*)C, M, N, K, act, status);
+    return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
+}

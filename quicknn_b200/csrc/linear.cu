@@ -167,7 +167,7 @@ __global__ void __launch_bounds__(NW * 32) skinny_bf16_kernel(const bf16* __rest
             float u = 0.f;
 #pragma unroll
             for (int w = 0; w < NW; ++w) u += red[w][row][col];
-            v = activate(v, act) * u;
+            v = activate_fast(v, act) * u;          // bfloat16 inputs and output: the fast activation
         } else if (EPI == EPI_SOFTCAP) {
             v = softcap(v, cap);
         }

@@ -16,6 +16,7 @@ import torch
 
 from ..cache import PAGE, CacheFull, KVCache
 from ..kernels import lib as _klib
+from ..kernels import ops as _kops
 from .batch import StepBatch
 from .model import Model
 
@@ -157,6 +158,8 @@ class Engine:
                          seq_row0=views[6], seq_len=views[7])
         logits = self.model.forward(step, self.cache)
         self.steps_run += 1
+        if mode == "prefill":
+            _kops.check_gemm_status(self.device)      # a bounded wait of the tcgen05 product ran out?
         return logits
 
     # ---- decode with ids that are already on the device -------------------------------

@@ -9,6 +9,7 @@ captured in a CUDA graph).  Library matrix products (cuBLAS through
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -180,12 +181,60 @@ def rope_cache_write(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, 
         page_size, ring, _p(slot_len), int(write_cache), _stream()), "rope_cache_write")
 
 
+_gemm_status = {}
+
+
+def _status_word(device) -> torch.Tensor:
+    t = _gemm_status.get(device)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=device)
+        _gemm_status[device] = t
+    return t
+
+
+def check_gemm_status(device) -> None:
+    """Raise if a bounded wait inside the tcgen05 product ran out since the last check (one
+    4-byte read; call it where the host synchronises anyway)."""
+    t = _gemm_status.get(torch.device(device))
+    if t is None:
+        return
+    v = int(t.item())
+    if v:
+        t.zero_()
+        raise _lib.KernelError(f"the tcgen05 matrix product gave up waiting (status {v}: 1 loads, 2 tensor-core "
+                               f"issue, 4 epilogue); its result is not valid")
+
+
+def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, *, epilogue: int = EPI_NONE, activation: str = "gelu_tanh"):
+    """x w^T for whole prompts on the 5th-generation tensor cores (bfloat16, any M; K a multiple of 8).
+    Epilogues: none, or gated (w = [gate; up] stacked).  Returns None when the sizes are refused."""
+    _req(x, "x", torch.bfloat16, 2)
+    _req(w, "w", torch.bfloat16, 2)
+    M, K = x.shape
+    N = w.shape[0]
+    if epilogue not in (EPI_NONE, EPI_GATED) or K % 8 or w.shape[1] != K:
+        return None
+    n_out = N // 2 if epilogue == EPI_GATED else N
+    out = torch.empty((M, n_out), dtype=torch.bfloat16, device=x.device)
+    L = _lib.load()
+    code = L.qnn_gemm_tcgen05(_p(x), _p(w), _p(out), M, N, K, epilogue, ACT_CODES[activation],
+                              _p(_status_word(x.device)), _stream())
+    if code == _lib.ERR_UNSUPPORTED:
+        return None
+    _lib.check(code, "gemm_tcgen05")
+    return out
+
+
+USE_TCGEN05 = os.environ.get("QNN_GEMM", "tcgen05") != "cublas"
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, *, epilogue: int = EPI_NONE, cap: Optional[float] = None,
            activation: str = "gelu_tanh", out_dtype: Optional[torch.dtype] = None):
     """y = x w^T with an optional epilogue.  x: [M, K]; w: [N, K] (gated: [2*N_out, K]).
 
-    float32: FFMA kernels only.  bfloat16: the tensor-core small-M kernel up to 64 rows,
-    a library product (cuBLAS) above that, followed by the epilogue as a kernel."""
+    float32: FFMA kernels only.  bfloat16: the tensor-core small-M kernel up to 64 rows, the
+    tcgen05/TMA kernel above that (a library product, cuBLAS, only for the softcap epilogue of
+    many rows, for sizes the kernel refuses, or when QNN_GEMM=cublas is set)."""
     _req(x, "x", None, 2)
     _req(w, "w", None, 2)
     M, K = x.shape
@@ -221,6 +270,10 @@ def linear(x: torch.Tensor, w: torch.Tensor, *, epilogue: int = EPI_NONE, cap: O
         _lib.check(L.qnn_skinny_bf16(_p(x), _p(w), _p(out), dt_code(out), M, N, K, epilogue, capv, act, _stream()),
                    "skinny_bf16")
         return out
+    if USE_TCGEN05 and epilogue in (EPI_NONE, EPI_GATED) and out_dtype == torch.bfloat16:
+        y = gemm_tcgen05(x, w, epilogue=epilogue, activation=activation)
+        if y is not None:
+            return y
     y = torch.matmul(x, w.t())
     if epilogue == EPI_GATED:
         return gated_act(y, activation)

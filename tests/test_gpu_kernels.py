@@ -147,6 +147,32 @@ def test_bf16_large_m_library_product_with_epilogues(ops, M):
     assert_close(y, P.softcap(bf16_round(ref), 3.0), torch.float32, "gemm softcap", mult=4000)
 
 
+@pytest.mark.parametrize("M,N_,K", [(65, 24, 8), (128, 256, 64), (200, 300, 96), (130, 1000, 200), (300, 2304, 2304),
+                                     (2048, 512, 4160), (1, 40, 72)])
+def test_tcgen05_product(ops, M, N_, K):
+    """The TMA + tcgen05 kernel alone: tiles that are cut by every edge (M, N, K not multiples of
+    128, 256, 64), one slab and many, plain and gated epilogue."""
+    rng = np.random.default_rng(M + N_ + K)
+    x, w = bf16_round(rng.normal(size=(M, K))), bf16_round(rng.normal(size=(N_, K)) / math.sqrt(K))
+    ref = x @ w.T
+    y = ops.gemm_tcgen05(T(x, torch.bfloat16), T(w, torch.bfloat16))
+    torch.cuda.synchronize()
+    ops.check_gemm_status(DEV)
+    assert y is not None and y.dtype == torch.bfloat16 and tuple(y.shape) == (M, N_)
+    assert_close(y, ref, torch.bfloat16, "tcgen05 product")
+    y = ops.gemm_tcgen05(T(x, torch.bfloat16), T(w, torch.bfloat16), epilogue=ops.EPI_GATED, activation="gelu_tanh")
+    torch.cuda.synchronize()
+    ops.check_gemm_status(DEV)
+    h = N_ // 2
+    assert tuple(y.shape) == (M, h)
+    assert_close(y, P.gelu_tanh(ref[:, :h]) * ref[:, h:], torch.bfloat16, "tcgen05 gated product", mult=1.5)
+    y = ops.gemm_tcgen05(T(x, torch.bfloat16), T(w, torch.bfloat16), epilogue=ops.EPI_GATED, activation="silu")
+    g = ref[:, :h]
+    assert_close(y, g / (1 + np.exp(-g)) * ref[:, h:], torch.bfloat16, "tcgen05 silu-gated product", mult=1.5)
+    assert ops.gemm_tcgen05(torch.zeros(70, 12, dtype=torch.bfloat16, device=DEV),
+                            torch.zeros(8, 12, dtype=torch.bfloat16, device=DEV)) is None      # refused, not wrong
+
+
 @pytest.mark.parametrize("M", [1, 3, 8, 9, 70, 130])
 @pytest.mark.parametrize("N_,K", [(50, 96), (130, 50), (1000, 200), (7, 3)])
 def test_fp32_products_are_true_fp32(ops, M, N_, K):
