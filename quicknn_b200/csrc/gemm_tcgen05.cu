@@ -5,7 +5,9 @@
 //
 // Reference: the 64x64 fp32-FMA tile of src/backends/vulkan/shaders/gemm.comp:4-6 and the separate
 // GO_GEGLU dispatch (src/models/QuickNN.Models.Gemma2.pas:184-186).  Here:
-//   * one CTA computes a 128 x 256 tile; K is walked in slabs of 64 (128-byte rows, 128-byte swizzle);
+//   * a persistent CTA per SM computes 128 x 256 tiles; K is walked in slabs of 64 (128-byte rows,
+//     128-byte swizzle); two accumulators in tensor memory let the epilogue of one tile overlap
+//     the products of the next;
 //   * warp 0 (one lane) is the producer: TMA (cp.async.bulk.tensor) loads of the A and B slabs into a
 //     4-stage ring in shared memory, completion counted in bytes on an mbarrier per stage;
 //   * warp 1 (one lane) issues tcgen05.mma (M 128, N 256, K 16; four per slab) from shared-memory
@@ -96,13 +98,20 @@ __device__ __forceinline__ void tmem_ld32(unsigned taddr, uint32_t (&r)[32]) {
 }
 
 struct __align__(8) Barriers {
-    uint64_t full[STAGES];
-    uint64_t empty[STAGES];
-    uint64_t acc_ready;
+    uint64_t full[STAGES];      // a slab has landed (TMA bytes)
+    uint64_t empty[STAGES];     // the MMAs that read a slab are done
+    uint64_t acc_ready[2];      // an accumulator is complete
+    uint64_t acc_free[2];       // the epilogue has read an accumulator out of tensor memory
     uint32_t tmem_base;
     uint32_t failed;
 };
 
+__device__ __forceinline__ bool has_failed(Barriers* b) { return *reinterpret_cast<volatile uint32_t*>(&b->failed) != 0; }
+
+// Persistent: a CTA per SM walks over tiles t = blockIdx.x, blockIdx.x + gridDim.x, ... (row tiles
+// fastest, so the CTAs that run together share their B slabs in L2).  Tensor memory holds two
+// accumulators of 256 columns; while the epilogue warps drain one, the MMAs of the next tile fill
+// the other, and the TMA ring runs on across tile borders.
 template <int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -114,9 +123,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     Barriers* bars = reinterpret_cast<Barriers*>(smem + STAGES * STAGE_BYTES);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.x * BM;
     const int Nout = (EPI == EPI_GATED) ? N / 2 : N;
-    const int n0 = blockIdx.y * ((EPI == EPI_GATED) ? BN / 2 : BN);    // first output column of this tile
+    constexpr int OUT_COLS = (EPI == EPI_GATED) ? BN / 2 : BN;          // output columns of a tile
+    const int m_tiles = (M + BM - 1) / BM, n_tiles = (Nout + OUT_COLS - 1) / OUT_COLS;
+    const int ntiles = m_tiles * n_tiles;
     const int nk = (K + BK - 1) / BK;
 
     if (threadIdx.x == 0) {
@@ -124,13 +134,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             mbar_init(smem_u32(&bars->full[s]), 1);
             mbar_init(smem_u32(&bars->empty[s]), 1);
         }
-        mbar_init(smem_u32(&bars->acc_ready), 1);
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(smem_u32(&bars->acc_ready[a]), 1);
+            mbar_init(smem_u32(&bars->acc_free[a]), 4);     // one arrival per epilogue warp
+        }
         bars->failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {   // this warp owns the tensor memory: allocates it here, frees it at the end
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(smem_u32(&bars->tmem_base)), "r"(TMEM_COLS) : "memory");
+                     ::"r"(smem_u32(&bars->tmem_base)), "r"(2 * TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -141,22 +154,26 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (warp == 0) {
         if (lane == 0) {
             // ---- producer -------------------------------------------------------------------
-            for (int kb = 0; kb < nk; ++kb) {
-                const int s = kb % STAGES;
-                if (kb >= STAGES && !mbar_wait(smem_u32(&bars->empty[s]), ((kb / STAGES) - 1) & 1)) {
-                    atomicOr(status, 1);
-                    bars->failed = 1;
-                    break;
-                }
-                const unsigned full = smem_u32(&bars->full[s]);
-                const unsigned a_dst = smem_u32(smem + s * STAGE_BYTES), b_dst = a_dst + A_BYTES;
-                mbar_expect_tx(full, STAGE_BYTES);
-                tma_load_2d(a_dst, &map_a, full, kb * BK, m0);
-                if (EPI == EPI_GATED) {
-                    tma_load_2d(b_dst, &map_b, full, kb * BK, n0);                        // 128 gate rows
-                    tma_load_2d(b_dst + B_BYTES / 2, &map_b, full, kb * BK, Nout + n0);   // the 128 up rows
-                } else {
-                    tma_load_2d(b_dst, &map_b, full, kb * BK, n0);
+            int it = 0;                                    // slabs issued so far, over all tiles
+            for (int tile = blockIdx.x; tile < ntiles && !has_failed(bars); tile += gridDim.x) {
+                const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * OUT_COLS;
+                for (int kb = 0; kb < nk; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    if (it >= STAGES && !mbar_wait(smem_u32(&bars->empty[s]), ((it / STAGES) - 1) & 1)) {
+                        atomicOr(status, 1);
+                        bars->failed = 1;
+                        break;
+                    }
+                    const unsigned full = smem_u32(&bars->full[s]);
+                    const unsigned a_dst = smem_u32(smem + s * STAGE_BYTES), b_dst = a_dst + A_BYTES;
+                    mbar_expect_tx(full, STAGE_BYTES);
+                    tma_load_2d(a_dst, &map_a, full, kb * BK, m0);
+                    if (EPI == EPI_GATED) {
+                        tma_load_2d(b_dst, &map_b, full, kb * BK, n0);                        // 128 gate rows
+                        tma_load_2d(b_dst + B_BYTES / 2, &map_b, full, kb * BK, Nout + n0);   // the 128 up rows
+                    } else {
+                        tma_load_2d(b_dst, &map_b, full, kb * BK, n0);
+                    }
                 }
             }
         }
@@ -165,37 +182,55 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             // ---- tensor-core issue ------------------------------------------------------------
             // instruction descriptor: D float32, A and B bfloat16, both K-major, N >> 3, M >> 4
             const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(BN >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
-            bool ok = true;
-            for (int kb = 0; kb < nk && ok; ++kb) {
-                const int s = kb % STAGES;
-                if (!mbar_wait(smem_u32(&bars->full[s]), (kb / STAGES) & 1)) {
-                    atomicOr(status, 2);
+            int it = 0, i = 0;                             // slabs consumed; tiles done by this CTA
+            for (int tile = blockIdx.x; tile < ntiles && !has_failed(bars); tile += gridDim.x, ++i) {
+                const int a = i & 1;
+                if (i >= 2 && !mbar_wait(smem_u32(&bars->acc_free[a]), ((i >> 1) - 1) & 1)) {
+                    atomicOr(status, 8);
                     bars->failed = 1;
-                    ok = false;
                     break;
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const unsigned a_addr = smem_u32(smem + s * STAGE_BYTES), b_addr = a_addr + A_BYTES;
+                const unsigned acc = tmem + a * TMEM_COLS;
+                bool ok = true;
+                for (int kb = 0; kb < nk; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    if (!mbar_wait(smem_u32(&bars->full[s]), (it / STAGES) & 1)) {
+                        atomicOr(status, 2);
+                        bars->failed = 1;
+                        ok = false;
+                        break;
+                    }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const unsigned a_addr = smem_u32(smem + s * STAGE_BYTES), b_addr = a_addr + A_BYTES;
 #pragma unroll
-                for (int k = 0; k < BK / UMMA_K; ++k) {
-                    // 16 elements further along K = 32 bytes inside the 128-byte swizzled row
-                    umma_bf16(tmem, umma_desc(a_addr + k * UMMA_K * 2), umma_desc(b_addr + k * UMMA_K * 2), idesc,
-                              (kb > 0 || k > 0) ? 1u : 0u);
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        // 16 elements further along K = 32 bytes inside the 128-byte swizzled row
+                        umma_bf16(acc, umma_desc(a_addr + k * UMMA_K * 2), umma_desc(b_addr + k * UMMA_K * 2), idesc,
+                                  (kb > 0 || k > 0) ? 1u : 0u);
+                    }
+                    umma_commit(smem_u32(&bars->empty[s]));     // the stage is free once these MMAs have read it
                 }
-                umma_commit(smem_u32(&bars->empty[s]));     // the stage is free once these MMAs have read it
+                umma_commit(smem_u32(&bars->acc_ready[a]));     // arrives when everything issued so far is done
+                if (!ok) break;
             }
-            umma_commit(smem_u32(&bars->acc_ready));        // arrives when everything issued so far is done
         }
     } else {
         // ---- epilogue: warps 2..5, each owns the 32 accumulator lanes (rows) of its quarter ----------
-        const bool ok = mbar_wait(smem_u32(&bars->acc_ready), 0);
-        if (!ok) atomicOr(status, 4);
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (ok && *reinterpret_cast<volatile uint32_t*>(&bars->failed) == 0) {
-            const int quarter = warp & 3;
+        const int quarter = warp & 3;
+        int i = 0;
+        for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++i) {
+            const int a = i & 1;
+            const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * OUT_COLS;
+            if (!mbar_wait(smem_u32(&bars->acc_ready[a]), (i >> 1) & 1)) {
+                atomicOr(status, 4);
+                bars->failed = 1;
+                break;
+            }
+            if (has_failed(bars)) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int m = m0 + quarter * 32 + lane;
-            const unsigned lane_addr = tmem + ((unsigned)(quarter * 32) << 16);
-            constexpr int OUT_COLS = (EPI == EPI_GATED) ? BN / 2 : BN;
+            const unsigned lane_addr = tmem + a * TMEM_COLS + ((unsigned)(quarter * 32) << 16);
 #pragma unroll 1
             for (int c0 = 0; c0 < OUT_COLS; c0 += 32) {
                 uint32_t v[32];
@@ -209,6 +244,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 } else {
 #pragma unroll
                     for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+                }
+                if (c0 + 32 >= OUT_COLS) {
+                    // the last columns are in registers: hand the accumulator back before storing them
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&bars->acc_free[a])) : "memory");
                 }
                 if (m < M) {
                     bf16* dst = C + (size_t)m * Nout + n0 + c0;
@@ -226,7 +267,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 1) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(2 * TMEM_COLS) : "memory");
     }
 }
 
@@ -264,7 +305,7 @@ int make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) 
 
 // C = A B^T (epi 0) or act(A Bgate^T) * (A Bup^T) with B = [gate; up] (epi 2; C is [M, N/2]).
 // `status` is one int in device memory that the caller zeroed: a non-zero value after the kernel
-// means a bounded wait ran out (bit 0 producer, bit 1 tensor-core issue, bit 2 epilogue) and C is
+// means a bounded wait ran out (bit 0 producer, bits 1 and 3 tensor-core issue, bit 2 epilogue) and C is
 // not valid.  K must be a multiple of 8 (16-byte row pitch) and the bases 16-byte aligned.
 QNN_API int qnn_gemm_tcgen05(const void* A, const void* B, void* C, int M, int N, int K, int epi, int act,
                              int* status, cudaStream_t st) {
@@ -279,8 +320,16 @@ QNN_API int qnn_gemm_tcgen05(const void* A, const void* B, void* C, int M, int N
     if (rc) return rc;
     const int Nout = epi == EPI_GATED ? N / 2 : N;
     const int cols = epi == EPI_GATED ? BN / 2 : BN;
-    dim3 grid((M + BM - 1) / BM, (Nout + cols - 1) / cols);
-    if (grid.y > 65535) return QNN_ERR_UNSUPPORTED;
+    static int sm_count = 0;
+    if (sm_count == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0)
+            sm_count = 148;
+    }
+    const long long ntiles = (long long)((M + BM - 1) / BM) * ((Nout + cols - 1) / cols);
+    if (ntiles > 0x7fffffffLL) return QNN_ERR_UNSUPPORTED;
+    dim3 grid((unsigned)(ntiles < sm_count ? ntiles : sm_count));
     const size_t smem = (size_t)STAGES * STAGE_BYTES + sizeof(Barriers) + 1024;
     if (epi == EPI_GATED) {
         auto kern = gemm_tcgen05_kernel<EPI_GATED>;
