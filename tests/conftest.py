@@ -41,7 +41,18 @@ TINY_B = dict(
     hidden_activation="gelu_pytorch_tanh", tie_word_embeddings=True)
 TINY_B_SEED, TINY_B_NORM_STD = 1, 0.2
 
-TINY = {"A": (TINY_A, TINY_A_SEED, TINY_A_NORM_STD), "B": (TINY_B, TINY_B_SEED, TINY_B_NORM_STD)}
+# Small C: head size 64 and a window of 96, so that the engine's bfloat16 path runs the tensor-core
+# attention kernels (head sizes 64/128/256) and the tcgen05 product, not only the generic ones.
+TINY_C = dict(
+    architectures=["Gemma2ForCausalLM"], model_type="gemma2",
+    hidden_size=192, intermediate_size=320, num_attention_heads=6, num_key_value_heads=2, head_dim=64,
+    vocab_size=1536, num_hidden_layers=3, max_position_embeddings=1024, rope_theta=50000.0,
+    rms_norm_eps=1e-6, sliding_window=96, attn_logit_softcapping=30.0, final_logit_softcapping=20.0,
+    query_pre_attn_scalar=48, eos_token_id=1, bos_token_id=2, initializer_range=0.04,
+    hidden_activation="gelu_pytorch_tanh", tie_word_embeddings=True)
+
+TINY = {"A": (TINY_A, TINY_A_SEED, TINY_A_NORM_STD), "B": (TINY_B, TINY_B_SEED, TINY_B_NORM_STD),
+        "C": (TINY_C, 2, 0.15)}
 
 
 def make_folder(tmp, name, storage, peaky=False):

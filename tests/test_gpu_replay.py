@@ -15,7 +15,8 @@ from conftest import ROOT, TINY, close, prompts_for
 
 pytestmark = pytest.mark.gpu
 
-LENGTHS = [70, 33, 129, 45, 100, 64]      # crossing the 64-token page edge, longer than both windows
+LENGTHS = [70, 33, 129, 45, 100, 64]      # crossing the 64-token page edge, longer than the windows of A and B
+LENGTHS_C = [170, 33, 257, 45, 100, 64]   # for C: longer than its window of 96, several 64-row attention tiles
 
 
 class Replay:
@@ -104,15 +105,20 @@ def run_all_cuttings(replay, requests, ref, dtype):
 
 @pytest.mark.parametrize("name,dtype,peaky", [("A", "float32", False), ("A", "bfloat16", False),
                                               ("B", "float32", False), ("B", "bfloat16", False),
-                                              ("B", "float32", True), ("A", "bfloat16", True)])
+                                              ("B", "float32", True), ("A", "bfloat16", True),
+                                              ("C", "bfloat16", False), ("C", "float32", True)])
 def test_every_cutting_gives_the_plain_logits(folders, plain_models, tmp_path, name, dtype, peaky):
+    # The peaky variant of C is run in float32 only: with its head size and depth the bfloat16
+    # rounding of the activations alone (whatever kernels compute the attention) moves the logits
+    # by a tenth of their size, which says nothing about masks or cache addressing.
     storage = dtype                      # weights are stored in the precision that is tested
     folder = folders(name, storage, peaky)
     plain = plain_models(name, storage, peaky)
-    requests = prompts_for(name, LENGTHS)
+    requests = prompts_for(name, LENGTHS_C if name == "C" else LENGTHS)
     ref = [plain.logits(t) for t in requests]
     # the largest set of live requests is batch ([0,1,2]): 70 + 33 + 129 -> 128 + 64 + 192 tokens
-    replay = Replay(folder, dtype, tmp_path, max_tokens=384)
+    # (C: 170 + 33 + 257 -> 192 + 64 + 320)
+    replay = Replay(folder, dtype, tmp_path, max_tokens=576 if name == "C" else 384)
     try:
         worst = run_all_cuttings(replay, requests, ref, dtype)
     finally:
