@@ -1,0 +1,373 @@
+// Matrix products of a few rows (decode batches of 9..128 sequences) against a big weight matrix:
+//     C[M, N] = A[M, K] * B[N, K]^T,  M <= 128,  bfloat16 in, float32 accumulation
+// These are bound by reading B once from HBM, and a matrix with few rows (N = hidden size) gives
+// too few output tiles to keep 148 SMs busy.  So a thread-block cluster of KS CTAs shares one
+// 128-row tile of B and splits K among its CTAs:
+//   * each CTA streams its part of K through a 4-stage TMA ring (A slab 128 x 64 with the rows
+//     beyond M zero-filled, B slab 128 x 64) and accumulates with tcgen05.mma in tensor memory;
+//   * its epilogue warps move the float32 accumulator (rows < M) to shared memory;
+//   * after a cluster barrier every CTA sums a slice of the columns over all CTAs of the cluster,
+//     reading the others' shared memory (distributed shared memory), always in rank order, applies
+//     the epilogue (none, softcap -> float32, or gated activation) and stores.
+// Reference: the matvec shaders of src/backends/vulkan/shaders/tensor.comp:87-120 (one row).
+// Every mbarrier wait is bounded in time; on expiry a status word is set, and the CTA still takes
+// part in both cluster barriers, frees its tensor memory and returns.
+#include "common.cuh"
+#include <cuda.h>
+
+using namespace qnn;
+
+#define EPI_NONE 0
+#define EPI_SOFTCAP 1
+#define EPI_GATED 2
+
+namespace {
+
+constexpr int BM = 128, BN = 128, BK = 64, STAGES = 4, UMMA_K = 16;
+constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int TMEM_COLS = 128;
+constexpr int THREADS = 192;
+constexpr int PART_LD = BN + 4;                          // row pitch of the partial tile in floats
+constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity) {
+    const long long start = clock64();
+    for (;;) {
+        unsigned done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done) : "r"(bar), "r"(parity), "r"(1000u) : "memory");
+        if (done) return true;
+        if (clock64() - start > WAIT_LIMIT_CYCLES) return false;
+    }
+}
+__device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap* map, unsigned bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ uint64_t umma_desc(unsigned smem_addr) {   // K-major, 128-byte swizzle
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+__device__ __forceinline__ void umma_bf16(unsigned tmem_d, uint64_t adesc, uint64_t bdesc, unsigned idesc, unsigned accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(unsigned bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(unsigned taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ unsigned cluster_rank() {
+    unsigned r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_dsmem(unsigned local_addr, unsigned rank) {
+    unsigned remote;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
+
+__device__ __forceinline__ float4 ld_dsmem4(unsigned local_addr, unsigned rank) {
+    unsigned remote;
+    float4 v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(remote) : "memory");
+    return v;
+}
+
+struct __align__(8) Barriers {
+    uint64_t full[STAGES];
+    uint64_t empty[STAGES];
+    uint64_t acc_ready;
+    uint32_t tmem_base;
+    uint32_t failed;
+};
+
+// grid.x = output tiles x KS, cluster (KS, 1, 1): the CTAs of a cluster share a tile, rank = K part.
+template <int EPI>
+__global__ void __launch_bounds__(THREADS)
+gemm_skinny_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                           void* __restrict__ C, int M, int N, int K, int KS, float cap, int act,
+                           int* __restrict__ status) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    float* part = reinterpret_cast<float*>(smem + STAGES * STAGE_BYTES);        // [BM][PART_LD], rows < M used
+    Barriers* bars = reinterpret_cast<Barriers*>(smem + STAGES * STAGE_BYTES + BM * PART_LD * sizeof(float));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const unsigned rank = cluster_rank();
+    const int tile = blockIdx.x / KS;
+    const int Nout = (EPI == EPI_GATED) ? N / 2 : N;
+    constexpr int OUT_COLS = (EPI == EPI_GATED) ? BN / 2 : BN;
+    const int n0 = tile * OUT_COLS;
+    const int nk = (K + BK - 1) / BK;
+    const int per = (nk + KS - 1) / KS;
+    const int kb0 = min((int)rank * per, nk), kb1 = min(kb0 + per, nk);        // this CTA's slabs
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(smem_u32(&bars->full[s]), 1);
+            mbar_init(smem_u32(&bars->empty[s]), 1);
+        }
+        mbar_init(smem_u32(&bars->acc_ready), 1);
+        bars->failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(&bars->tmem_base)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const unsigned tmem = bars->tmem_base;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int kb = kb0, it = 0; kb < kb1; ++kb, ++it) {
+                const int s = it % STAGES;
+                if (it >= STAGES && !mbar_wait(smem_u32(&bars->empty[s]), ((it / STAGES) - 1) & 1)) {
+                    atomicOr(status, 1);
+                    bars->failed = 1;
+                    break;
+                }
+                const unsigned full = smem_u32(&bars->full[s]);
+                const unsigned a_dst = smem_u32(smem + s * STAGE_BYTES), b_dst = a_dst + A_BYTES;
+                mbar_expect_tx(full, STAGE_BYTES);
+                tma_load_2d(a_dst, &map_a, full, kb * BK, 0);
+                if (EPI == EPI_GATED) {
+                    tma_load_2d(b_dst, &map_b, full, kb * BK, n0);                        // 64 gate rows
+                    tma_load_2d(b_dst + B_BYTES / 2, &map_b, full, kb * BK, Nout + n0);   // the 64 up rows
+                } else {
+                    tma_load_2d(b_dst, &map_b, full, kb * BK, n0);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(BN >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
+            for (int kb = kb0, it = 0; kb < kb1; ++kb, ++it) {
+                const int s = it % STAGES;
+                if (!mbar_wait(smem_u32(&bars->full[s]), (it / STAGES) & 1)) {
+                    atomicOr(status, 2);
+                    bars->failed = 1;
+                    break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const unsigned a_addr = smem_u32(smem + s * STAGE_BYTES), b_addr = a_addr + A_BYTES;
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k)
+                    umma_bf16(tmem, umma_desc(a_addr + k * UMMA_K * 2), umma_desc(b_addr + k * UMMA_K * 2), idesc,
+                              (it > 0 || k > 0) ? 1u : 0u);
+                umma_commit(smem_u32(&bars->empty[s]));
+            }
+            umma_commit(smem_u32(&bars->acc_ready));
+        }
+    } else {
+        // accumulator (rows < M) -> shared memory, float32; a CTA without slabs contributes zeros
+        const int quarter = warp & 3;
+        const int row = quarter * 32 + lane;
+        bool ok = true;
+        if (kb1 > kb0) {
+            ok = mbar_wait(smem_u32(&bars->acc_ready), 0);
+            if (!ok) {
+                atomicOr(status, 4);
+                bars->failed = 1;
+            }
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (quarter * 32 < M) {                               // warp-uniform: tcgen05.ld is warp-wide
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t v[32];
+                if (kb1 > kb0 && ok) {
+                    tmem_ld32(tmem + ((unsigned)(quarter * 32) << 16) + c0, v);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = 0u;
+                }
+                if (row < M) {
+                    float4* dst = reinterpret_cast<float4*>(part + (size_t)row * PART_LD + c0);
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4)
+                        dst[j / 4] = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]), __uint_as_float(v[j + 2]),
+                                                 __uint_as_float(v[j + 3]));
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+    }
+    cluster_sync();      // every CTA's partial tile is complete and visible in the cluster
+
+    // Rank r finishes output columns [r * cpr, (r + 1) * cpr) of the tile, four at a time: sum over
+    // the ranks in ascending order, epilogue, store.  (OUT_COLS / KS is a multiple of 4: KS <= 8.)
+    {
+        const int cpr = OUT_COLS / KS;
+        const int c_lo = (int)rank * cpr;
+        const int groups = cpr / 4;
+        const unsigned part_addr = smem_u32(part);
+        for (int idx = threadIdx.x; idx < M * groups; idx += THREADS) {
+            const int row = idx / groups, col = c_lo + (idx % groups) * 4;
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f), up = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int q = 0; q < KS; ++q) {
+                const float4 v = ld_dsmem4(part_addr + ((unsigned)row * PART_LD + col) * 4u, q);
+                acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+                if (EPI == EPI_GATED) {
+                    const float4 w = ld_dsmem4(part_addr + ((unsigned)row * PART_LD + BN / 2 + col) * 4u, q);
+                    up.x += w.x; up.y += w.y; up.z += w.z; up.w += w.w;
+                }
+            }
+            const float a4[4] = {acc.x, acc.y, acc.z, acc.w}, u4[4] = {up.x, up.y, up.z, up.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int n = n0 + col + j;
+                if (n >= Nout) continue;
+                if (EPI == EPI_GATED) {
+                    reinterpret_cast<bf16*>(C)[(size_t)row * Nout + n] = __float2bfloat16_rn(activate_fast(a4[j], act) * u4[j]);
+                } else if (EPI == EPI_SOFTCAP) {
+                    reinterpret_cast<float*>(C)[(size_t)row * Nout + n] = softcap(a4[j], cap);
+                } else {
+                    reinterpret_cast<bf16*>(C)[(size_t)row * Nout + n] = __float2bfloat16_rn(a4[j]);
+                }
+            }
+        }
+    }
+    cluster_sync();      // nobody leaves while its shared memory may still be read
+}
+
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encoder() {
+    static EncodeTiled fn = nullptr;
+    if (fn == nullptr) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiled>(p);
+    }
+    return fn;
+}
+
+int make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) {
+    EncodeTiled enc = encoder();
+    if (enc == nullptr) return QNN_ERR_UNSUPPORTED;
+    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : QNN_ERR_ARGUMENT;
+}
+
+template <int EPI>
+int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, void* C, int M, int N, int K, int KS, float cap, int act,
+           int* status, unsigned tiles, cudaStream_t st) {
+    auto kern = gemm_skinny_tcgen05_kernel<EPI>;
+    const size_t smem = (size_t)STAGES * STAGE_BYTES + (size_t)BM * PART_LD * sizeof(float) + sizeof(Barriers) + 1024;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(tiles * KS);
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = KS;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = qnn::pdl_enabled() ? 2 : 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, map_a, map_b, C, M, N, K, KS, cap, act, status);
+    return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
+}
+
+}  // namespace
+
+// C = A B^T for M <= 128 rows.  epi 0: bfloat16 out; 1: softcap, float32 out; 2: gated (B = [gate; up],
+// C is [M, N/2], bfloat16).  `status` as in qnn_gemm_tcgen05.  Returns QNN_ERR_UNSUPPORTED for sizes it
+// does not take.
+QNN_API int qnn_gemm_skinny_tcgen05(const void* A, const void* B, void* C, int M, int N, int K, int epi, float cap,
+                                    int act, int* status, cudaStream_t st) {
+    if (M <= 0 || N <= 0) return 0;
+    if (M > BM || K <= 0 || (K & 7) || ((((uintptr_t)A | (uintptr_t)B | (uintptr_t)C) & 15) != 0)) return QNN_ERR_UNSUPPORTED;
+    if (epi == EPI_GATED && (N & 1)) return QNN_ERR_ARGUMENT;
+    CUtensorMap map_a, map_b;
+    int rc = make_map(&map_a, A, M, K, BM);
+    if (rc) return rc;
+    rc = make_map(&map_b, B, N, K, epi == EPI_GATED ? BN / 2 : BN);
+    if (rc) return rc;
+    const int Nout = epi == EPI_GATED ? N / 2 : N;
+    const int cols = epi == EPI_GATED ? BN / 2 : BN;
+    const long long tiles = (Nout + cols - 1) / cols;
+    if (tiles > 0x3fffffffLL) return QNN_ERR_UNSUPPORTED;
+    // split K over a cluster when the tiles alone do not fill the GPU; every CTA keeps >= 2 slabs
+    static int sm_count = 0;
+    if (sm_count == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0)
+            sm_count = 148;
+    }
+    const int nk = (K + 63) / 64;
+    int KS = 1;
+    while (KS < 8 && tiles * KS < sm_count && nk / (KS * 2) >= 2) KS *= 2;
+    switch (epi) {
+        case EPI_NONE: return launch<EPI_NONE>(map_a, map_b, C, M, N, K, KS, cap, act, status, (unsigned)tiles, st);
+        case EPI_SOFTCAP: return launch<EPI_SOFTCAP>(map_a, map_b, C, M, N, K, KS, cap, act, status, (unsigned)tiles, st);
+        case EPI_GATED: return launch<EPI_GATED>(map_a, map_b, C, M, N, K, KS, cap, act, status, (unsigned)tiles, st);
+    }
+    return QNN_ERR_ARGUMENT;
+}

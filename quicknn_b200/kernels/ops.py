@@ -225,7 +225,34 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, *, epilogue: int = EPI_NONE, 
     return out
 
 
+def gemm_skinny_tcgen05(x: torch.Tensor, w: torch.Tensor, *, epilogue: int = EPI_NONE, cap: Optional[float] = None,
+                        activation: str = "gelu_tanh"):
+    """x w^T for up to 128 rows: TMA + tcgen05 with K split over a thread-block cluster and summed
+    through distributed shared memory.  Epilogues: none (bfloat16), softcap (float32), gated.
+    Returns None when the sizes are refused."""
+    _req(x, "x", torch.bfloat16, 2)
+    _req(w, "w", torch.bfloat16, 2)
+    M, K = x.shape
+    N = w.shape[0]
+    if M > 128 or K % 8 or w.shape[1] != K:
+        return None
+    n_out = N // 2 if epilogue == EPI_GATED else N
+    out = torch.empty((M, n_out), dtype=torch.float32 if epilogue == EPI_SOFTCAP else torch.bfloat16, device=x.device)
+    L = _lib.load()
+    code = L.qnn_gemm_skinny_tcgen05(_p(x), _p(w), _p(out), M, N, K, epilogue, float(cap or 0.0),
+                                     ACT_CODES[activation], _p(_status_word(x.device)), _stream())
+    if code == _lib.ERR_UNSUPPORTED:
+        return None
+    _lib.check(code, "gemm_skinny_tcgen05")
+    return out
+
+
 USE_TCGEN05 = os.environ.get("QNN_GEMM", "tcgen05") != "cublas"
+# From this many rows on, products against big matrices (>= 2^24 weights) take the cluster split-K
+# tcgen05 kernel instead of the mma.sync small-M kernel (measured on B200: at 16 rows and below, and
+# for the small q/k/v and o matrices up to 64 rows, the mma.sync kernel is the faster one).
+SKINNY_TCGEN05_FROM = int(os.environ.get("QNN_SKINNY_TCGEN05_FROM", "17"))
+SKINNY_TCGEN05_MIN_WEIGHTS = 1 << 24
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, *, epilogue: int = EPI_NONE, cap: Optional[float] = None,
@@ -265,6 +292,11 @@ def linear(x: torch.Tensor, w: torch.Tensor, *, epilogue: int = EPI_NONE, cap: O
     # bfloat16
     if K % 8:
         raise _lib.KernelError(f"bfloat16 products need an inner size that is a multiple of 8 (got {K})")
+    if USE_TCGEN05 and SKINNY_TCGEN05_FROM <= M <= 128 and (M > SKINNY_MAX_ROWS or N * K >= SKINNY_TCGEN05_MIN_WEIGHTS) \
+            and out_dtype == (torch.float32 if epilogue == EPI_SOFTCAP else torch.bfloat16):
+        y = gemm_skinny_tcgen05(x, w, epilogue=epilogue, cap=cap, activation=activation)
+        if y is not None:
+            return y
     if M <= SKINNY_MAX_ROWS:
         out = torch.empty((M, n_out), dtype=out_dtype, device=x.device)
         _lib.check(L.qnn_skinny_bf16(_p(x), _p(w), _p(out), dt_code(out), M, N, K, epilogue, capv, act, _stream()),

@@ -173,6 +173,31 @@ def test_tcgen05_product(ops, M, N_, K):
                             torch.zeros(8, 12, dtype=torch.bfloat16, device=DEV)) is None      # refused, not wrong
 
 
+@pytest.mark.parametrize("M,N_,K", [(1, 128, 64), (17, 300, 96), (64, 256, 512), (128, 1000, 200), (33, 2304, 2048),
+                                     (64, 130, 4160), (9, 24, 8)])
+def test_cluster_split_k_tcgen05_product(ops, M, N_, K):
+    """The small-M tcgen05 kernel alone: K split over 1..8 CTAs of a cluster (chosen from the sizes)
+    and summed through distributed shared memory; all three epilogues; edges in M, N and K."""
+    rng = np.random.default_rng(M * 7 + N_ + K)
+    x, w = bf16_round(rng.normal(size=(M, K))), bf16_round(rng.normal(size=(N_, K)) / math.sqrt(K))
+    ref = x @ w.T
+    y = ops.gemm_skinny_tcgen05(T(x, torch.bfloat16), T(w, torch.bfloat16))
+    torch.cuda.synchronize()
+    ops.check_gemm_status(DEV)
+    assert y is not None and y.dtype == torch.bfloat16 and tuple(y.shape) == (M, N_)
+    assert_close(y, ref, torch.bfloat16, "cluster product")
+    y = ops.gemm_skinny_tcgen05(T(x, torch.bfloat16), T(w, torch.bfloat16), epilogue=ops.EPI_SOFTCAP, cap=2.0)
+    assert y.dtype == torch.float32
+    assert_close(y, P.softcap(ref, 2.0), torch.float32, "cluster product with softcap", mult=50)
+    y = ops.gemm_skinny_tcgen05(T(x, torch.bfloat16), T(w, torch.bfloat16), epilogue=ops.EPI_GATED)
+    h = N_ // 2
+    assert_close(y, P.gelu_tanh(ref[:, :h]) * ref[:, h:], torch.bfloat16, "cluster gated product", mult=1.5)
+    torch.cuda.synchronize()
+    ops.check_gemm_status(DEV)
+    assert ops.gemm_skinny_tcgen05(torch.zeros(129, 16, dtype=torch.bfloat16, device=DEV),
+                                   torch.zeros(8, 16, dtype=torch.bfloat16, device=DEV)) is None
+
+
 @pytest.mark.parametrize("M", [1, 3, 8, 9, 70, 130])
 @pytest.mark.parametrize("N_,K", [(50, 96), (130, 50), (1000, 200), (7, 3)])
 def test_fp32_products_are_true_fp32(ops, M, N_, K):
