@@ -155,7 +155,7 @@ def timed_decode(engine, batch, steps, warmup, torch, with_clocks=False, context
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--steps", type=int, default=256)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=SIZES["num_hidden_layers"],
@@ -199,7 +199,7 @@ def main():
     points = {}
     if not args.skip_points:
         for b in (1, 64):
-            points[f"decode_b{b}"] = round(timed_decode(eng, b, min(args.steps, 64), args.warmup, torch)["tok_s"], 1)
+            points[f"decode_b{b}"] = round(timed_decode(eng, b, min(args.steps, 128), args.warmup, torch)["tok_s"], 1)
 
     # ---- prefill of 2,048 tokens -----------------------------------------------------------
     ids = torch.randint(1, cfg["vocab_size"], (PREFILL_TOKENS,)).tolist()
@@ -223,7 +223,7 @@ def main():
     # ---- end to end through the Python entry point ------------------------------------------
     e2e = None
     if not args.skip_e2e:
-        new = min(args.steps, 64)
+        new = min(args.steps, 128)
         plen = CONTEXT - new - 1
         prompts = [torch.randint(1, cfg["vocab_size"], (plen,)).tolist() for _ in range(BATCH)]
         llm.max_batch = BATCH

@@ -5,9 +5,9 @@
 // Formulas: those of attention.cu (reference: src/backends/vulkan/shaders/attention.comp:18-38,
 // which gives every (query row, head) a workgroup of its own).  Here a CTA of 4 warps owns 64
 // query rows of one sequence and one query head and walks over the 64-key tiles that those rows
-// can see (from the window's edge to the diagonal), keys and values double-buffered in shared
-// memory by cp.async:
-//     S[16 x 64] = Q K^T      per warp, mma.m16n8k16, Q and K fragments by ldmatrix
+// can see (from the window's edge to the diagonal) in tiles of BN keys (64, or 32 at head size 256 so
+// that two CTAs fit an SM), keys and values double-buffered in shared memory by cp.async:
+//     S[16 x BN] = Q K^T      per warp, mma.m16n8k16, Q and K fragments by ldmatrix
 //     scale, softcap, mask (key <= row, key > row - window, key < length), online softmax in float32
 //     O[16 x hd] += P V       P taken from S's accumulators, V fragments by ldmatrix.trans
 // K and V are read from this step's own projections (rows of the qkv buffer), so a prompt longer
@@ -20,7 +20,7 @@ using namespace qnn;
 
 namespace {
 
-constexpr int BM = 64, BN = 64, PF_WARPS = 4;
+constexpr int BM = 64, PF_WARPS = 4;
 
 __device__ __forceinline__ void cp_async_16(unsigned smem_dst, const void* gmem_src, bool valid) {
     const int bytes = valid ? 16 : 0;
@@ -52,8 +52,8 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&h);
 }
 
-template <int HD>
-__global__ void __launch_bounds__(PF_WARPS * 32)
+template <int HD, int BN>
+__global__ void __launch_bounds__(PF_WARPS * 32, (BM + 4 * BN) * HD * 2 <= 112 * 1024 ? 2 : 1)
 attn_prefill_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const bf16* __restrict__ v,
                         size_t row_stride, bf16* __restrict__ out, size_t out_stride,
                         const int* __restrict__ seq_row0, const int* __restrict__ seq_len, int nq, int nkv, float scale,
@@ -224,11 +224,11 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, 
     }
 }
 
-template <int HD>
+template <int HD, int BN>
 int launch(const void* q, const void* k, const void* v, long long row_stride, void* out, long long out_stride,
            const int* seq_row0, const int* seq_len, int B, int max_len, int nq, int nkv, float scale, float cap,
            int window, cudaStream_t st) {
-    auto kern = attn_prefill_mma_kernel<HD>;
+    auto kern = attn_prefill_mma_kernel<HD, BN>;
     const size_t smem = (size_t)(BM + 4 * BN) * HD * 2;
     static bool configured = false;
     if (!configured) {
@@ -258,9 +258,10 @@ QNN_API int qnn_attn_prefill_mma(const void* q, const void* k, const void* v, lo
         (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v) & 15) || ((uintptr_t)out & 3))
         return QNN_ERR_ARGUMENT;
     switch (hd) {
-        case 64: return launch<64>(q, k, v, row_stride, out, out_stride, seq_row0, seq_len, B, max_len, nq, nkv, scale, cap, window, st);
-        case 128: return launch<128>(q, k, v, row_stride, out, out_stride, seq_row0, seq_len, B, max_len, nq, nkv, scale, cap, window, st);
-        case 256: return launch<256>(q, k, v, row_stride, out, out_stride, seq_row0, seq_len, B, max_len, nq, nkv, scale, cap, window, st);
+        case 64: return launch<64, 64>(q, k, v, row_stride, out, out_stride, seq_row0, seq_len, B, max_len, nq, nkv, scale, cap, window, st);
+        case 128: return launch<128, 64>(q, k, v, row_stride, out, out_stride, seq_row0, seq_len, B, max_len, nq, nkv, scale, cap, window, st);
+        case 256: return launch<256, 32>(q, k, v,      // 32-key tiles: 96 KB of shared memory, two CTAs per SM
+                                          row_stride, out, out_stride, seq_row0, seq_len, B, max_len, nq, nkv, scale, cap, window, st);
         default: return QNN_ERR_UNSUPPORTED;
     }
 }

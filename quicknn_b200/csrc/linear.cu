@@ -79,8 +79,10 @@ __global__ void __launch_bounds__(NW * 32) skinny_bf16_kernel(const bf16* __rest
     const bf16* u1 = W + (size_t)(Nout + r1) * K;
 
     // The weights do not depend on the kernel before this one: pull this warp's share of them
-    // towards L2 while that kernel is still running, then wait for the activations.
-    if (t == 0) {
+    // towards L2 while that kernel is still running, then wait for the activations.  Only for the
+    // smaller matrices, whose kernels are too short to reach full bandwidth on their own; for the
+    // big ones the extra instructions only fill the load queue.
+    if (t == 0 && (size_t)N * K <= ((size_t)1 << 24)) {
         for (int kb = warp; kb < nkb; kb += NW) {
             const size_t ko = (size_t)kb * 32;
             if (ko < (size_t)K) {
