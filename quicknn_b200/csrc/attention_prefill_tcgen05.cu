@@ -1,0 +1,467 @@
+// Prefill attention on the 5th-generation tensor cores, bfloat16, head size 256: whole prompts
+// packed one after another, causal, optional sliding window, optional tanh softcap, grouped
+// query heads.  Formulas: attention.cu (reference: src/backends/vulkan/shaders/attention.comp:18-38).
+//
+// A CTA owns 128 query rows of one sequence and one query head and walks over 64-key tiles:
+//   warp 0 (one lane)  TMA producer: Q once (four 128 x 64 boxes), then K and V tiles (four 64 x 64
+//                      boxes each) into a 2-stage ring; everything 128-byte swizzled.
+//   warp 1 (one lane)  tensor-core issue:  S_j[128 x 64] = Q K_j^T   (16 tcgen05.mma, K-major operands)
+//                                           O[128 x 256] += P_j V_j   ( 4 tcgen05.mma, V as MN-major operand)
+//                      S_{j+1} is issued before P_j V_j, so it runs while the softmax of tile j does.
+//   warps 2..5         softmax, one thread per query row (tensor-memory lane = row, so row maxima and
+//                      sums need no shuffles): tcgen05.ld of S, scale, softcap, mask, exp; P_j goes to
+//                      shared memory as bfloat16 in the swizzled K-major layout the next product reads;
+//                      O is rescaled in tensor memory only when a row maximum has grown by more than 8
+//                      since the value the row's exponentials are taken against (the stale maximum
+//                      cancels in the final division; P stays below e^8).
+// Tensor memory: S double-buffered (2 x 64 columns), O 256 columns.  All softmax arithmetic is float32.
+// Keys of other sequences that a tile drags in are masked; rows beyond the sequence are never stored.
+// Every mbarrier wait is bounded in time; on expiry a status word is set and the CTA winds down.
+#include "common.cuh"
+#include <cuda.h>
+#include <math_constants.h>
+
+using namespace qnn;
+
+namespace {
+
+constexpr int HD = 256, BM = 128, BN = 64, KV_STAGES = 2, UMMA_K = 16;
+constexpr int Q_BYTES = BM * HD * 2;                 // 64 KB: four [128 x 64] blocks
+constexpr int K_BYTES = BN * HD * 2, V_BYTES = BN * HD * 2;   // 32 KB each: four [64 x 64] blocks
+constexpr int P_BYTES = BM * BN * 2;                 // 16 KB
+constexpr int THREADS = 192;
+constexpr int TMEM_COLS = 512, S_COL = 0, O_COL = 128;
+constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;
+constexpr float RESCALE_STEP = 8.f;
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(unsigned bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity) {
+    const long long start = clock64();
+    for (;;) {
+        unsigned done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done) : "r"(bar), "r"(parity), "r"(1000u) : "memory");
+        if (done) return true;
+        if (clock64() - start > WAIT_LIMIT_CYCLES) return false;
+    }
+}
+// the same for a whole warp: either every lane goes on or none does (the tcgen05.ld / st and votes
+// that follow are warp-wide)
+__device__ __forceinline__ bool mbar_wait_warp(unsigned bar, unsigned parity) {
+    return __all_sync(0xffffffffu, mbar_wait(bar, parity));
+}
+__device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap* map, unsigned bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+// shared-memory operand descriptor, 128-byte swizzle; lbo/sbo in bytes
+__device__ __forceinline__ uint64_t umma_desc(unsigned smem_addr, unsigned lbo, unsigned sbo) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+    d |= (uint64_t)((lbo >> 4) & 0x3FFF) << 16;
+    d |= (uint64_t)((sbo >> 4) & 0x3FFF) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+__device__ __forceinline__ void umma_bf16(unsigned tmem_d, uint64_t adesc, uint64_t bdesc, unsigned idesc, unsigned accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(unsigned bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(unsigned taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_st32(unsigned taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+          "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+          "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float tanh_fast(float x) {
+    float r;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
+__device__ __forceinline__ float exp2_fast(float x) {
+    float r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+
+struct __align__(8) Barriers {
+    uint64_t q_full;
+    uint64_t kv_full[KV_STAGES];
+    uint64_t kv_empty[KV_STAGES];
+    uint64_t s_ready[2];      // S_j is complete in tensor memory
+    uint64_t p_ready[2];      // P_j is in shared memory and O has been corrected
+    uint64_t pv_done[2];      // O += P_j V_j has completed
+    uint32_t tmem_base;
+    uint32_t failed;
+};
+
+__device__ __forceinline__ bool has_failed(Barriers* b) { return *reinterpret_cast<volatile uint32_t*>(&b->failed) != 0; }
+
+__global__ void __launch_bounds__(THREADS)
+attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
+                            bf16* __restrict__ out, size_t out_stride, const int* __restrict__ seq_row0,
+                            const int* __restrict__ seq_len, int nq, int nkv, float scale, float cap, int window,
+                            int* __restrict__ status) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    unsigned char* sQ = smem;
+    unsigned char* sKV = sQ + Q_BYTES;                              // [stage][K | V]
+    unsigned char* sP = sKV + KV_STAGES * (K_BYTES + V_BYTES);      // [2][P]
+    Barriers* bars = reinterpret_cast<Barriers*>(sP + 2 * P_BYTES);
+
+    const int b = blockIdx.y, h = blockIdx.z;
+    const int len = seq_len[b];
+    const int ntiles_q = (len + BM - 1) / BM;
+    if ((int)blockIdx.x >= ntiles_q) return;                         // before any barrier or tensor memory
+    const int qt = ntiles_q - 1 - blockIdx.x;                        // the longest rows first
+    const int r0 = qt * BM, row0 = seq_row0[b];
+    const int kh = h / (nq / nkv);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int last_row = min(r0 + BM, len) - 1;
+    const int kv_lo = (window > 0 && r0 - window + 1 > 0) ? r0 - window + 1 : 0;
+    const int jt0 = kv_lo / BN, jt1 = last_row / BN;                 // key tiles jt0 .. jt1
+    const int nt = jt1 - jt0 + 1;
+
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bars->q_full), 1);
+        for (int s = 0; s < KV_STAGES; ++s) {
+            mbar_init(smem_u32(&bars->kv_full[s]), 1);
+            mbar_init(smem_u32(&bars->kv_empty[s]), 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(smem_u32(&bars->s_ready[i]), 1);
+            mbar_init(smem_u32(&bars->p_ready[i]), 4);               // one arrival per softmax warp
+            mbar_init(smem_u32(&bars->pv_done[i]), 1);
+        }
+        bars->failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(&bars->tmem_base)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const unsigned tmem = bars->tmem_base;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // ---- producer -------------------------------------------------------------------------
+            const unsigned qf = smem_u32(&bars->q_full);
+            mbar_expect_tx(qf, Q_BYTES);
+            for (int d = 0; d < HD / 64; ++d)
+                tma_load_2d(smem_u32(sQ + d * (BM * 128)), &map_q, qf, h * HD + d * 64, row0 + r0);
+            const int kx = (nq + kh) * HD, vx = (nq + nkv + kh) * HD;     // columns of K and V in the qkv rows
+            for (int j = 0; j < nt; ++j) {
+                const int s = j % KV_STAGES;
+                if (j >= KV_STAGES && !mbar_wait(smem_u32(&bars->kv_empty[s]), ((j / KV_STAGES) - 1) & 1)) {
+                    atomicOr(status, 16);
+                    bars->failed = 1;
+                    break;
+                }
+                const unsigned full = smem_u32(&bars->kv_full[s]);
+                unsigned char* kdst = sKV + s * (K_BYTES + V_BYTES);
+                unsigned char* vdst = kdst + K_BYTES;
+                const int y = row0 + (jt0 + j) * BN;
+                mbar_expect_tx(full, K_BYTES + V_BYTES);
+                for (int d = 0; d < HD / 64; ++d) {
+                    tma_load_2d(smem_u32(kdst + d * (BN * 128)), &map_kv, full, kx + d * 64, y);
+                    tma_load_2d(smem_u32(vdst + d * (BN * 128)), &map_kv, full, vx + d * 64, y);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // ---- tensor-core issue -----------------------------------------------------------------
+            // S: M 128, N 64, both operands K-major.  O: M 128, N 256, A (P) K-major, B (V) MN-major.
+            const unsigned idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(BN >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
+            const unsigned idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((unsigned)(HD >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
+            bool ok = mbar_wait(smem_u32(&bars->q_full), 0);
+            if (!ok) { atomicOr(status, 32); bars->failed = 1; }
+            auto issue_s = [&](int j) {       // S_j = Q K_j^T into S buffer j & 1
+                const unsigned kaddr = smem_u32(sKV + (j % KV_STAGES) * (K_BYTES + V_BYTES));
+                const unsigned qaddr = smem_u32(sQ);
+                const unsigned acc = tmem + S_COL + (j & 1) * BN;
+#pragma unroll
+                for (int d = 0; d < HD / 64; ++d)
+#pragma unroll
+                    for (int k = 0; k < 64 / UMMA_K; ++k)
+                        umma_bf16(acc, umma_desc(qaddr + d * (BM * 128) + k * 32, 16, 1024),
+                                  umma_desc(kaddr + d * (BN * 128) + k * 32, 16, 1024), idesc_s, (d > 0 || k > 0) ? 1u : 0u);
+                umma_commit(smem_u32(&bars->s_ready[j & 1]));
+            };
+            if (ok) {
+                ok = mbar_wait(smem_u32(&bars->kv_full[0]), 0);
+                if (!ok) { atomicOr(status, 2); bars->failed = 1; }
+            }
+            if (ok) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                issue_s(0);
+            }
+            for (int j = 0; j < nt && ok; ++j) {
+                if (j + 1 < nt) {
+                    ok = mbar_wait(smem_u32(&bars->kv_full[(j + 1) % KV_STAGES]), ((j + 1) / KV_STAGES) & 1);
+                    if (!ok) { atomicOr(status, 2); bars->failed = 1; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    issue_s(j + 1);
+                }
+                ok = mbar_wait(smem_u32(&bars->p_ready[j & 1]), (j >> 1) & 1);
+                if (!ok) { atomicOr(status, 8); bars->failed = 1; break; }
+                if (has_failed(bars)) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const unsigned vaddr = smem_u32(sKV + (j % KV_STAGES) * (K_BYTES + V_BYTES) + K_BYTES);
+                const unsigned paddr = smem_u32(sP + (j & 1) * P_BYTES);
+#pragma unroll
+                for (int k = 0; k < BN / UMMA_K; ++k)
+                    // P: 16 keys further = 32 bytes in the swizzled row.  V (keys x dims, dims contiguous):
+                    // 16 keys further = 16 rows of 128 bytes; the four 64-dim blocks are BN*128 bytes apart.
+                    umma_bf16(tmem + O_COL, umma_desc(paddr + k * 32, 16, 1024),
+                              umma_desc(vaddr + k * UMMA_K * 128, BN * 128, 1024), idesc_o, (j > 0 || k > 0) ? 1u : 0u);
+                umma_commit(smem_u32(&bars->kv_empty[j % KV_STAGES]));
+                umma_commit(smem_u32(&bars->pv_done[j & 1]));
+            }
+        }
+    } else {
+        // ---- softmax: thread = query row ---------------------------------------------------------------
+        const int quarter = warp & 3;
+        const int rloc = quarter * 32 + lane;                 // row within the tile = tensor-memory lane
+        const int row = r0 + rloc;                            // position in the sequence
+        const unsigned lane_base = tmem + ((unsigned)(quarter * 32) << 16);
+        const float LOG2E = 1.4426950408889634f;
+        const float inv_cap = cap > 0.f ? 1.f / cap : 0.f;
+        float m_used = 0.f, m_run = -CUDART_INF_F, l_sum = 0.f;
+        bool alive = true;
+        for (int j = 0; j < nt && alive; ++j) {
+            const int bsel = j & 1;
+            if (!mbar_wait_warp(smem_u32(&bars->s_ready[bsel]), (j >> 1) & 1)) {
+                atomicOr(status, 4);
+                bars->failed = 1;
+                alive = false;
+                break;
+            }
+            if (__any_sync(0xffffffffu, has_failed(bars))) { alive = false; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            float s[BN];
+            {
+                uint32_t v[32];
+                tmem_ld32(lane_base + S_COL + bsel * BN, v);
+#pragma unroll
+                for (int c = 0; c < 32; ++c) s[c] = __uint_as_float(v[c]);
+                tmem_ld32(lane_base + S_COL + bsel * BN + 32, v);
+#pragma unroll
+                for (int c = 0; c < 32; ++c) s[32 + c] = __uint_as_float(v[c]);
+            }
+            const int col0 = (jt0 + j) * BN;
+            float mx = -CUDART_INF_F;
+#pragma unroll
+            for (int c = 0; c < BN; ++c) {
+                const int col = col0 + c;
+                float x = s[c] * scale;
+                if (cap > 0.f) x = cap * tanh_fast(fminf(fmaxf(x * inv_cap, -20.f), 20.f));
+                const bool seen = col <= row && col < len && (window <= 0 || col > row - window);
+                x = seen ? x : -CUDART_INF_F;
+                s[c] = x;
+                mx = fmaxf(mx, x);
+            }
+            m_run = fmaxf(m_run, mx);
+            float corr = 1.f;
+            bool rescale = false;
+            if (m_run != -CUDART_INF_F && (j == 0 || m_run > m_used + RESCALE_STEP || l_sum == 0.f)) {
+                // take the exponentials against the new maximum from here on
+                corr = (l_sum == 0.f) ? 0.f : exp2_fast((m_used - m_run) * LOG2E);
+                rescale = (j > 0);
+                m_used = m_run;
+            }
+            float rs = 0.f;
+            const float moff = m_used * LOG2E;
+#pragma unroll
+            for (int c = 0; c < BN; ++c) {
+                const float p = exp2_fast(fmaf(s[c], LOG2E, -moff));      // exp(-inf) = 0 for masked keys
+                s[c] = p;
+                rs += p;
+            }
+            l_sum = l_sum * corr + rs;
+            // P_j overwrites the buffer that P_{j-2} V_{j-2} read; O may only be touched once P_{j-1} V_{j-1} is done
+            if (j >= 2 && !mbar_wait_warp(smem_u32(&bars->pv_done[bsel]), ((j >> 1) - 1) & 1)) {
+                atomicOr(status, 64);
+                bars->failed = 1;
+                alive = false;
+                break;
+            }
+            {
+                unsigned char* prow = sP + bsel * P_BYTES + rloc * 128;
+#pragma unroll
+                for (int ch = 0; ch < BN / 8; ++ch) {
+                    uint4 pk;
+                    pk.x = pack_bf16(s[ch * 8 + 0], s[ch * 8 + 1]);
+                    pk.y = pack_bf16(s[ch * 8 + 2], s[ch * 8 + 3]);
+                    pk.z = pack_bf16(s[ch * 8 + 4], s[ch * 8 + 5]);
+                    pk.w = pack_bf16(s[ch * 8 + 6], s[ch * 8 + 7]);
+                    *reinterpret_cast<uint4*>(prow + ((ch ^ (rloc & 7)) << 4)) = pk;
+                }
+            }
+            if (__any_sync(0xffffffffu, rescale)) {
+                if (j >= 1 && !mbar_wait_warp(smem_u32(&bars->pv_done[(j - 1) & 1]), ((j - 1) >> 1) & 1)) {
+                    atomicOr(status, 64);
+                    bars->failed = 1;
+                    alive = false;
+                    break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const float f = rescale ? corr : 1.f;
+#pragma unroll 1
+                for (int c0 = 0; c0 < HD; c0 += 32) {
+                    uint32_t v[32];
+                    tmem_ld32(lane_base + O_COL + c0, v);
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) v[c] = __float_as_uint(__uint_as_float(v[c]) * f);
+                    tmem_st32(lane_base + O_COL + c0, v);
+                }
+            }
+            // make P (generic-proxy writes) visible to the tensor core's reads, then hand over
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bars->p_ready[bsel]));
+        }
+        // the last product, then O / l -> bfloat16 -> global
+        if (alive) {
+            const int jl = nt - 1;
+            if (!mbar_wait_warp(smem_u32(&bars->pv_done[jl & 1]), (jl >> 1) & 1)) {
+                atomicOr(status, 64);
+                bars->failed = 1;
+                alive = false;
+            }
+        }
+        if (alive && !__any_sync(0xffffffffu, has_failed(bars))) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
+            bf16* dst = out + (size_t)(row0 + row) * out_stride + (size_t)h * HD;
+#pragma unroll 1
+            for (int c0 = 0; c0 < HD; c0 += 32) {
+                uint32_t v[32];
+                tmem_ld32(lane_base + O_COL + c0, v);
+                if (row < len) {
+                    float f[32];
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) f[c] = __uint_as_float(v[c]) * inv;
+#pragma unroll
+                    for (int c = 0; c < 32; c += 8) Vec16<bf16>::store(dst + c0 + c, f + c);
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encoder() {
+    static EncodeTiled fn = nullptr;
+    if (fn == nullptr) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiled>(p);
+    }
+    return fn;
+}
+
+// the packed qkv buffer: rows x width bfloat16; box = 64 columns x box_rows rows
+int make_map(CUtensorMap* map, const void* base, long long rows, long long width, int box_rows) {
+    EncodeTiled enc = encoder();
+    if (enc == nullptr) return QNN_ERR_UNSUPPORTED;
+    const cuuint64_t dims[2] = {(cuuint64_t)width, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)width * 2};
+    const cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : QNN_ERR_ARGUMENT;
+}
+
+}  // namespace
+
+// qkv: this step's projections, [T rows, (nq + 2 nkv) * 256] bfloat16, rotated; sequence b occupies rows
+// seq_row0[b] .. + seq_len[b] - 1.  Returns QNN_ERR_UNSUPPORTED unless head_dim is 256.  `status` as in
+// qnn_gemm_tcgen05 (bits: 2 K/V wait, 4 S wait, 8 P wait, 16 ring wait, 32 Q wait, 64 product wait).
+QNN_API int qnn_attn_prefill_tcgen05(const void* qkv, long long total_rows, void* out, long long out_stride,
+                                     const int* seq_row0, const int* seq_len, int B, int max_len, int nq, int nkv,
+                                     int hd, float scale, float cap, int window, int* status, cudaStream_t st) {
+    if (B <= 0 || max_len <= 0) return 0;
+    if (hd != HD) return QNN_ERR_UNSUPPORTED;
+    if (nkv <= 0 || nq % nkv) return QNN_ERR_ARGUMENT;
+    if (B > 65535 || nq > 65535) return QNN_ERR_UNSUPPORTED;
+    if (((uintptr_t)qkv & 15) || ((uintptr_t)out & 15) || (out_stride * 2) % 16) return QNN_ERR_UNSUPPORTED;
+    const long long width = (long long)(nq + 2 * nkv) * HD;
+    CUtensorMap map_q, map_kv;
+    int rc = make_map(&map_q, qkv, total_rows, width, BM);
+    if (rc) return rc;
+    rc = make_map(&map_kv, qkv, total_rows, width, BN);
+    if (rc) return rc;
+    const size_t smem = (size_t)Q_BYTES + KV_STAGES * (K_BYTES + V_BYTES) + 2 * P_BYTES + sizeof(Barriers) + 1024;
+    auto kern = attn_prefill_tcgen05_kernel;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    dim3 grid((max_len + BM - 1) / BM, B, nq);
+    cudaError_t e = qnn::launch_pdl(kern, grid, dim3(THREADS), smem, st, map_q, map_kv, (bf16*)out, (size_t)out_stride,
+                                    seq_row0, seq_len, nq, nkv, scale, cap, window, status);
+    return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
+}

@@ -314,6 +314,9 @@ def linear(x: torch.Tensor, w: torch.Tensor, *, epilogue: int = EPI_NONE, cap: O
     return y if out_dtype == y.dtype else cast(y, out_dtype)
 
 
+ATTN_TCGEN05 = os.environ.get("QNN_ATTN", "tcgen05") != "mma"
+
+
 def attn_prefill(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, tok_pos: torch.Tensor,
                  tok_row0: torch.Tensor, scale: float, cap: Optional[float], window: Optional[int],
                  seq_row0: Optional[torch.Tensor] = None, seq_len: Optional[torch.Tensor] = None,
@@ -334,6 +337,14 @@ def attn_prefill(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, tok_
             and head_dim in (64, 128, 256)):
         _req(seq_row0, "seq_row0", torch.int32, 1)
         _req(seq_len, "seq_len", torch.int32, 1)
+        if head_dim == 256 and ATTN_TCGEN05:
+            code = L.qnn_attn_prefill_tcgen05(
+                _p(qkv), T, _p(out), out.shape[1], _p(seq_row0), _p(seq_len), seq_row0.numel(), int(max_len),
+                n_heads, n_kv, head_dim, float(scale), float(cap or 0.0), int(window or 0),
+                _p(_status_word(qkv.device)), _stream())
+            if code != _lib.ERR_UNSUPPORTED:
+                _lib.check(code, "attn_prefill_tcgen05")
+                return out
         code = L.qnn_attn_prefill_mma(
             ctypes.c_void_p(q_ptr), ctypes.c_void_p(k_ptr), ctypes.c_void_p(v_ptr), qkv.shape[1], _p(out),
             out.shape[1], _p(seq_row0), _p(seq_len), seq_row0.numel(), int(max_len), n_heads, n_kv, head_dim,
