@@ -51,8 +51,18 @@ TINY_C = dict(
     query_pre_attn_scalar=48, eos_token_id=1, bos_token_id=2, initializer_range=0.04,
     hidden_activation="gelu_pytorch_tanh", tie_word_embeddings=True)
 
+# Small D: head size 256 (the benchmark's), two query heads on one kv head, so that the engine runs the
+# tcgen05 prefill attention and the head-256 decode attention end to end.
+TINY_D = dict(
+    architectures=["Gemma2ForCausalLM"], model_type="gemma2",
+    hidden_size=256, intermediate_size=384, num_attention_heads=2, num_key_value_heads=1, head_dim=256,
+    vocab_size=1280, num_hidden_layers=2, max_position_embeddings=1024, rope_theta=10000.0,
+    rms_norm_eps=1e-6, sliding_window=80, attn_logit_softcapping=50.0, final_logit_softcapping=30.0,
+    query_pre_attn_scalar=256, eos_token_id=1, bos_token_id=2, initializer_range=0.03,
+    hidden_activation="gelu_pytorch_tanh", tie_word_embeddings=True)
+
 TINY = {"A": (TINY_A, TINY_A_SEED, TINY_A_NORM_STD), "B": (TINY_B, TINY_B_SEED, TINY_B_NORM_STD),
-        "C": (TINY_C, 2, 0.15)}
+        "C": (TINY_C, 2, 0.15), "D": (TINY_D, 3, 0.1)}
 
 
 def make_folder(tmp, name, storage, peaky=False):

@@ -106,7 +106,8 @@ def run_all_cuttings(replay, requests, ref, dtype):
 @pytest.mark.parametrize("name,dtype,peaky", [("A", "float32", False), ("A", "bfloat16", False),
                                               ("B", "float32", False), ("B", "bfloat16", False),
                                               ("B", "float32", True), ("A", "bfloat16", True),
-                                              ("C", "bfloat16", False), ("C", "float32", True)])
+                                              ("C", "bfloat16", False), ("C", "float32", True),
+                                              ("D", "bfloat16", False), ("D", "float32", False)])
 def test_every_cutting_gives_the_plain_logits(folders, plain_models, tmp_path, name, dtype, peaky):
     # The peaky variant of C is run in float32 only: with its head size and depth the bfloat16
     # rounding of the activations alone (whatever kernels compute the attention) moves the logits
@@ -114,11 +115,11 @@ def test_every_cutting_gives_the_plain_logits(folders, plain_models, tmp_path, n
     storage = dtype                      # weights are stored in the precision that is tested
     folder = folders(name, storage, peaky)
     plain = plain_models(name, storage, peaky)
-    requests = prompts_for(name, LENGTHS_C if name == "C" else LENGTHS)
+    requests = prompts_for(name, LENGTHS_C if name in ("C", "D") else LENGTHS)
     ref = [plain.logits(t) for t in requests]
     # the largest set of live requests is batch ([0,1,2]): 70 + 33 + 129 -> 128 + 64 + 192 tokens
     # (C: 170 + 33 + 257 -> 192 + 64 + 320)
-    replay = Replay(folder, dtype, tmp_path, max_tokens=576 if name == "C" else 384)
+    replay = Replay(folder, dtype, tmp_path, max_tokens=576 if name in ("C", "D") else 384)
     try:
         worst = run_all_cuttings(replay, requests, ref, dtype)
     finally:
