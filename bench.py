@@ -32,6 +32,13 @@ SIZES = dict(
     max_position_embeddings=8192, rope_theta=10000.0, rms_norm_eps=1e-6, sliding_window=4096,
     attn_logit_softcapping=50.0, final_logit_softcapping=30.0, query_pre_attn_scalar=256, eos_token_id=1,
     initializer_range=0.02)
+# BASELINE.json configs[3] and configs[4]: the 9B and 27B layer sizes (only with --model)
+OTHER_SIZES = {
+    "9b": dict(hidden_size=3584, intermediate_size=14336, num_attention_heads=16, num_key_value_heads=8, head_dim=256,
+               num_hidden_layers=42, query_pre_attn_scalar=256),
+    "27b": dict(hidden_size=4608, intermediate_size=36864, num_attention_heads=32, num_key_value_heads=16, head_dim=128,
+                num_hidden_layers=46, query_pre_attn_scalar=144),
+}
 CONTEXT = 8192
 BATCH = 8
 PREFILL_TOKENS = 2048
@@ -120,12 +127,12 @@ def prefill_flops(cfg, T):
     return total + 2 * H * cfg["vocab_size"]
 
 
-def timed_decode(engine, batch, steps, warmup, torch, with_clocks=False, context=CONTEXT):
+def timed_decode(engine, batch, steps, warmup, torch, with_clocks=False, context=CONTEXT, vocab=256000):
     """Tokens per second of `steps` decode steps of `batch` sequences ending at `context` tokens."""
     start_len = context - steps - warmup - 1
     slots = [engine.new_sequence() for _ in range(batch)]
     engine.fill_synthetic(slots, [start_len] * batch)
-    tokens = torch.randint(1, SIZES["vocab_size"], (batch,), dtype=torch.int32, device=engine.device)
+    tokens = torch.randint(1, vocab, (batch,), dtype=torch.int32, device=engine.device)
     engine.decode(slots, tokens)          # eager pass, captures the graph
     for _ in range(warmup):
         engine.decode(slots, tokens)
@@ -158,8 +165,10 @@ def main():
     ap.add_argument("--steps", type=int, default=256)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--layers", type=int, default=SIZES["num_hidden_layers"],
+    ap.add_argument("--layers", type=int, default=None,
                     help="fewer layers than the configuration has (reported in config)")
+    ap.add_argument("--model", default="2b", choices=["2b", "9b", "27b"],
+                    help="layer sizes; the record is for 2b (BASELINE.json configs[2])")
     ap.add_argument("--batch", type=int, default=BATCH, help="batch of the timed decode (the record is for 8)")
     ap.add_argument("--context", type=int, default=CONTEXT, help="context that the timed decode ends at")
     ap.add_argument("--no-graph", action="store_true", help="launch decode steps eagerly (for profilers)")
@@ -185,20 +194,33 @@ def main():
     from quicknn_b200.sampling import GenerationOptions
 
     pk = peaks()
-    cfg = dict(SIZES, num_hidden_layers=args.layers)
-    max_b = 64 if not args.skip_points else args.batch
+    base = dict(SIZES, **OTHER_SIZES.get(args.model, {}))
+    if args.layers is None:
+        args.layers = base["num_hidden_layers"]
+    cfg = dict(base, num_hidden_layers=args.layers)
+    # the large-batch point: 64 sequences, or the largest power of two whose cache fits beside the weights
+    per_seq = sum(min(args.context, cfg["sliding_window"]) if i % 2 == 0 else args.context
+                  for i in range(args.layers)) * cfg["num_key_value_heads"] * cfg["head_dim"] * 4
+    weights = 2 * (cfg["vocab_size"] * cfg["hidden_size"] + args.layers * (
+        cfg["hidden_size"] * (2 * cfg["num_attention_heads"] + 2 * cfg["num_key_value_heads"]) * cfg["head_dim"]
+        + 3 * cfg["hidden_size"] * cfg["intermediate_size"]))
+    big = 64
+    while big > args.batch and big * per_seq + weights > 150e9:
+        big //= 2
+    max_b = max(big, args.batch) if not args.skip_points else args.batch
     llm = LLM.random(cfg, SEED, dtype="bfloat16", max_context=CONTEXT, max_batch=max_b,
                      max_tokens=max_b * CONTEXT)
     eng = llm.engine
     eng.use_graphs = not args.no_graph
 
     # ---- the headline: decode, batch 8 --------------------------------------------------
-    main_run = timed_decode(eng, args.batch, args.steps, args.warmup, torch, with_clocks=True, context=args.context)
+    main_run = timed_decode(eng, args.batch, args.steps, args.warmup, torch, with_clocks=True, context=args.context,
+                            vocab=cfg["vocab_size"])
     achieved = main_run["bytes_per_step"] / (main_run["ms_per_step"] / 1e3) / 1e9
 
     points = {}
     if not args.skip_points:
-        for b in (1, 64):
+        for b in (1, big):
             points[f"decode_b{b}"] = round(timed_decode(eng, b, min(args.steps, 128), args.warmup, torch)["tok_s"], 1)
 
     # ---- prefill of 2,048 tokens -----------------------------------------------------------
@@ -234,12 +256,12 @@ def main():
                "d2h_bytes_per_step": BATCH * 4 + 4, "prefill_seconds": round(max(r.time_to_first_token_seconds for r in res), 3)}
 
     out = {
-        "metric": f"decode tokens/s, Gemma 2 2B layer sizes, batch {args.batch}, context {args.context}", "value": round(main_run["tok_s"], 1),
+        "metric": f"decode tokens/s, Gemma 2 {args.model.upper()} layer sizes, batch {args.batch}, context {args.context}", "value": round(main_run["tok_s"], 1),
         "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(main_run["ms_per_step"], 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
-        "config": {"model": "gemma2-2b-sizes", "global_batch": args.batch, "seq_len": args.context, "parallelism": "none",
-                   "layers": args.layers, "layers_of_config": SIZES["num_hidden_layers"],
+        "config": {"model": f"gemma2-{args.model}-sizes", "global_batch": args.batch, "seq_len": args.context, "parallelism": "none",
+                   "layers": args.layers, "layers_of_config": base["num_hidden_layers"],
                    "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
                    "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
                    "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],

@@ -247,7 +247,6 @@ attn_decode_kernel(const T* __restrict__ q, size_t q_stride, const T* __restrict
                    const int* __restrict__ slots, const int* __restrict__ slot_len, int nq, int nkv, int hd, int LPT,
                    float scale, float cap, int window, float* __restrict__ part_o, float* __restrict__ part_ml,
                    int n_splits) {
-    pdl_launch_dependents();
     pdl_wait();
     constexpr int VEC = Vec16<T>::N;
     extern __shared__ float smem[];  // [DEC_WARPS][GT][hd + 2]
@@ -316,7 +315,6 @@ attn_decode_tiled_kernel(const T* __restrict__ q, size_t q_stride, const T* __re
                          int page_size, int ring, const int* __restrict__ slots, const int* __restrict__ slot_len,
                          int nq, int nkv, int hd, int LPT, float scale, float cap, int window,
                          float* __restrict__ part_o, float* __restrict__ part_ml, int n_splits) {
-    pdl_launch_dependents();
     pdl_wait();
     constexpr int VEC = Vec16<T>::N;
     constexpr int NV = GT * TT;
@@ -505,7 +503,6 @@ attn_decode_tiled_kernel(const T* __restrict__ q, size_t q_stride, const T* __re
 template <typename T>
 __global__ void attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                     T* __restrict__ out, size_t out_stride, int nq, int hd, int n_splits) {
-    pdl_launch_dependents();
     pdl_wait();
     extern __shared__ float coef[];  // [n_splits] weights of the splits, then 1/sum
     const int b = blockIdx.x / nq, h = blockIdx.x % nq;
@@ -547,7 +544,6 @@ attn_prefill_generic_kernel(const T* __restrict__ q, size_t q_stride, const T* _
                             const int* __restrict__ tok_row0, int n_tokens, int nq, int nkv, int hd, int LPT,
                             float scale, float cap, int window, const int* __restrict__ page_table, int max_pages,
                             int page_size, int ring) {
-    pdl_launch_dependents();
     pdl_wait();
     constexpr int VEC = Vec16<T>::N;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;

@@ -65,7 +65,6 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, size_t q_stride, const bf16* 
                        int page_size, int ring, const int* __restrict__ slots, const int* __restrict__ slot_len,
                        int nq, int nkv, float scale, float cap, int window, float* __restrict__ part_o,
                        float* __restrict__ part_ml, int n_splits) {
-    pdl_launch_dependents();
     pdl_wait();
     constexpr int KSTEPS = HD / 16;              // k16 steps of S^T, and 16-row tiles of O^T
     constexpr int CH = HD / 8;                   // 16-byte chunks per row

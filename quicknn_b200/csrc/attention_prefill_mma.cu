@@ -58,7 +58,6 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, 
                         size_t row_stride, bf16* __restrict__ out, size_t out_stride,
                         const int* __restrict__ seq_row0, const int* __restrict__ seq_len, int nq, int nkv, float scale,
                         float cap, int window) {
-    pdl_launch_dependents();
     pdl_wait();
     constexpr int KSTEPS = HD / 16, CH = HD / 8, ROWB = HD * 2, NDT = HD / 8;
     constexpr int TILEB = BN * ROWB;

@@ -19,7 +19,6 @@ using namespace qnn;
 template <typename W>
 __global__ void embed_kernel(const int* __restrict__ tokens, const W* __restrict__ table, float scale,
                              float* __restrict__ out, int H, int V) {
-    pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
     const int tok = tokens[t];
@@ -48,7 +47,6 @@ QNN_API int qnn_embed(const int* tokens, const void* table, int table_dtype, flo
 // ---------------------------------------------------------------------------------
 __global__ void rmsnorm_kernel(const void* __restrict__ x, int x_dt, const void* __restrict__ w, int w_dt,
                                float eps, float offset, void* __restrict__ out, int out_dt, int H) {
-    pdl_launch_dependents();
     pdl_wait();
     __shared__ float red[32];
     const size_t base = (size_t)blockIdx.x * H;
@@ -88,7 +86,6 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const void* __rest
                                    const void* __restrict__ w_post, int w_post_dt, float eps_post, float off_post,
                                    const void* __restrict__ w_next, int w_next_dt, float eps_next, float off_next,
                                    void* __restrict__ out_next, int out_dt, int H) {
-    pdl_launch_dependents();
     pdl_wait();
     __shared__ float red[32];
     const size_t base = (size_t)blockIdx.x * H;
@@ -157,7 +154,6 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const void* __
                                        const void* __restrict__ w_post, int w_post_dt, float eps_post, float off_post,
                                        const void* __restrict__ w_next, int w_next_dt, float eps_next, float off_next,
                                        void* __restrict__ out_next, int out_dt, int H) {
-    pdl_launch_dependents();
     pdl_wait();
     __shared__ float red[32];
     const size_t base = (size_t)blockIdx.x * H;
@@ -243,7 +239,6 @@ QNN_API int qnn_add_rmsnorm(float* resid, const void* y, int y_dt, const void* w
 
 // resid[i] += y[i]   (generic residual add for blocks that do not fuse)
 __global__ void add_kernel(float* __restrict__ resid, const void* __restrict__ y, int y_dt, size_t n) {
-    pdl_launch_dependents();
     pdl_wait();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) resid[i] += load_as_f(y, y_dt, i);
@@ -259,7 +254,6 @@ QNN_API int qnn_add(float* resid, const void* y, int y_dt, long long n, cudaStre
 // ---------------------------------------------------------------------------------
 template <typename T>
 __global__ void gated_act_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, int act, size_t n) {
-    pdl_launch_dependents();
     pdl_wait();
     size_t id = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (id >= n) return;
@@ -271,7 +265,6 @@ __global__ void gated_act_kernel(const T* __restrict__ gu, T* __restrict__ out, 
 // 8 consecutive columns per thread, one row per blockIdx.y (I a multiple of 8)
 template <typename T>
 __global__ void gated_act_vec_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, int act) {
-    pdl_launch_dependents();
     pdl_wait();
     constexpr int VEC = Vec16<T>::N;
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
@@ -312,7 +305,6 @@ QNN_API int qnn_gated_act(const void* gu, void* out, int dtype, int T, int I, in
 // out[i] = softcap(x[i])  -> float32 (the logits)
 // ---------------------------------------------------------------------------------
 __global__ void softcap_kernel(const void* __restrict__ x, int x_dt, float* __restrict__ out, float cap, size_t n) {
-    pdl_launch_dependents();
     pdl_wait();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) out[i] = softcap(load_as_f(x, x_dt, i), cap);
@@ -328,7 +320,6 @@ QNN_API int qnn_softcap(const void* x, int x_dt, float* out, float cap, long lon
 // ---------------------------------------------------------------------------------
 __global__ void gather_rows_kernel(const void* __restrict__ src, int src_dt, const int* __restrict__ rows,
                                    void* __restrict__ dst, int dst_dt, int H) {
-    pdl_launch_dependents();
     pdl_wait();
     const size_t s = (size_t)rows[blockIdx.x] * H, d = (size_t)blockIdx.x * H;
     for (int j = threadIdx.x; j < H; j += blockDim.x) store_from_f(dst, dst_dt, d + j, load_as_f(src, src_dt, s + j));
@@ -342,7 +333,6 @@ QNN_API int qnn_gather_rows(const void* src, int src_dt, const int* rows, void* 
 
 // dst = convert(src)
 __global__ void cast_kernel(const void* __restrict__ src, int src_dt, void* __restrict__ dst, int dst_dt, size_t n) {
-    pdl_launch_dependents();
     pdl_wait();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) store_from_f(dst, dst_dt, i, load_as_f(src, src_dt, i));
@@ -355,7 +345,6 @@ QNN_API int qnn_cast(const void* src, int src_dt, void* dst, int dst_dt, long lo
 
 // flag |= 1 when any value is NaN or Inf
 __global__ void finite_kernel(const float* __restrict__ x, size_t n, int* __restrict__ flag) {
-    pdl_launch_dependents();
     pdl_wait();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) {

@@ -124,7 +124,6 @@ __global__ void __launch_bounds__(THREADS)
 gemm_skinny_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                            void* __restrict__ C, int M, int N, int K, int KS, float cap, int act,
                            int* __restrict__ status) {
-    pdl_launch_dependents();
     pdl_wait();
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -329,7 +328,7 @@ int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, void* C, int M, i
     attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = qnn::pdl_enabled() ? 2 : 1;
+    cfg.numAttrs = (qnn::pdl_enabled() && (long long)tiles * KS <= qnn::pdl_max_grid()) ? 2 : 1;
     cudaError_t e = cudaLaunchKernelEx(&cfg, kern, map_a, map_b, C, M, N, K, KS, cap, act, status);
     return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }

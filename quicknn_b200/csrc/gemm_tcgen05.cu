@@ -116,7 +116,6 @@ template <int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     bf16* __restrict__ C, int M, int N, int K, int act, int* __restrict__ status) {
-    pdl_launch_dependents();
     pdl_wait();
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     // the operand ring wants 1024-byte alignment (8 swizzled rows); the barriers follow it

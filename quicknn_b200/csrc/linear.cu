@@ -48,7 +48,6 @@ template <int NT, int EPI, int NW>
 __global__ void __launch_bounds__(NW * 32) skinny_bf16_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W,
                                                           void* __restrict__ out, int out_dt, int M, int N, int K,
                                                           float cap, int act) {
-    pdl_launch_dependents();
     constexpr int COLS = NT * 8;
     constexpr int THREADS = NW * 32;
     __shared__ float red[NW][16][COLS + 1];
@@ -230,7 +229,6 @@ QNN_API int qnn_skinny_bf16(const void* x, const void* W, void* out, int out_dt,
 template <int MT, int EPI>
 __global__ void gemv_f32_kernel(const float* __restrict__ x, const float* __restrict__ W, float* __restrict__ out,
                                 int M, int N, int K, int m0, float cap, int act) {
-    pdl_launch_dependents();
     pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int Nout = (EPI == EPI_GATED) ? N / 2 : N;
@@ -307,7 +305,6 @@ QNN_API int qnn_gemv_f32(const float* x, const float* W, float* out, int M, int 
 template <int EPI>
 __global__ void __launch_bounds__(256) sgemm_f32_kernel(const float* __restrict__ A, const float* __restrict__ B,
                                                         float* __restrict__ C, int M, int N, int K, float cap) {
-    pdl_launch_dependents();
     pdl_wait();
     __shared__ float As[16][64 + 4];
     __shared__ float Bs[16][64 + 4];

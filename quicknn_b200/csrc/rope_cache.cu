@@ -22,7 +22,6 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, int nq, int nkv, int hd, 
                                   const int* __restrict__ tok_slot, T* __restrict__ k_pool, T* __restrict__ v_pool,
                                   const int* __restrict__ page_table, int max_pages, int page_size, int ring,
                                   const int* __restrict__ slot_len, int write_cache) {
-    pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
     const int pos = tok_pos[t];
@@ -87,7 +86,6 @@ __global__ void rope_cache_vec_kernel(T* __restrict__ qkv, int nq, int nkv, int 
                                       const int* __restrict__ tok_slot, T* __restrict__ k_pool,
                                       T* __restrict__ v_pool, const int* __restrict__ page_table, int max_pages,
                                       int page_size, int ring, const int* __restrict__ slot_len, int write_cache) {
-    pdl_launch_dependents();
     pdl_wait();
     constexpr int VEC = Vec16<T>::N;
     const int t = blockIdx.x;

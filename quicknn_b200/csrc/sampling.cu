@@ -55,7 +55,6 @@ __device__ __forceinline__ void block_argmax(float& v, unsigned& id, float* sv, 
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_tile_kernel(const float* __restrict__ logits, int V, int k, float penalty, const unsigned char* __restrict__ seen,
                    const int* __restrict__ seen_rows, float2* __restrict__ cand, int* __restrict__ error_flag) {
-    pdl_launch_dependents();
     pdl_wait();
     __shared__ float sv[32];
     __shared__ unsigned si[32];
@@ -99,7 +98,6 @@ __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_merge_kernel(float2* __restrict__ cand, int ncand, int k, float temperature, float top_p,
                     unsigned* __restrict__ rng_state, int* __restrict__ out_tokens, unsigned char* __restrict__ seen,
                     const int* __restrict__ seen_rows, int V) {
-    pdl_launch_dependents();
     pdl_wait();
     __shared__ float sv[32];
     __shared__ unsigned si[32];
@@ -179,7 +177,6 @@ QNN_API int qnn_sample_scratch_bytes(int R, int V, int top_k) {
 // seen[rows[t]][tokens[t]] = 1   (prompt tokens; rows[t] < 0 is skipped)
 __global__ void mark_seen_kernel(const int* __restrict__ tokens, const int* __restrict__ rows,
                                  unsigned char* __restrict__ seen, int V, int T) {
-    pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x * blockDim.x + threadIdx.x;
     if (t >= T) return;

@@ -48,6 +48,12 @@ class Engine:
         self._fixed_splits = int(decode_splits) if decode_splits else None
         self._max_splits = max(1, min(64, max_seq // 128))
         self._kv_groups = max([getattr(b.mixer, "n_kv", 1) for b in model.blocks] or [1])
+        # blocks of the decode attention kernel that the device holds at once: its shared
+        # memory is 384 bytes per element of a head, so two fit on an SM at head size 256,
+        # four at 128, eight at 64
+        head = max([getattr(b.mixer, "head_dim", 256) for b in model.blocks] or [256])
+        sms = torch.cuda.get_device_properties(self.device).multi_processor_count if self.device.type == "cuda" else 148
+        self._resident = sms * max(1, min(8, 512 // max(1, head)))
         self.decode_splits = self._fixed_splits or self._max_splits
         self._scratch: Dict[int, Tuple[torch.Tensor, torch.Tensor]] = {}
         self._decode_state: Dict[int, dict] = {}
@@ -71,7 +77,7 @@ class Engine:
         if self._fixed_splits:
             return self._fixed_splits
         pairs = batch * self._kv_groups
-        resident = 296                       # 148 SMs x 2 CTAs of the decode attention kernel
+        resident = self._resident
         if pairs >= resident // 2:
             return min(2, self._max_splits)
         return max(1, min(self._max_splits, resident // pairs))
