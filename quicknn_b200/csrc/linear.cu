@@ -14,7 +14,11 @@
 //   qnn_sgemm_f32   : true fp32 tiled GEMM (FFMA only) for whole prompts.
 //
 // Epilogues: 0 none; 1 softcap (float32 out); 2 gated: W = [gate; up] stacked, the CTA
-// computes rows n and N/2+n and stores act(gate)*up.
+// computes rows n and N/2+n and stores act(gate)*up; 3 rotate and append: W = [q; k; v]
+// stacked, the CTA computes 8 columns of a head with their partners half a head away, rotates
+// the pairs by the token's position and writes K and V to the paged cache as well (what
+// rope_cache.cu does as a kernel of its own; reference: Gemma2.pas:167-175 runs three
+// projections, two rotations and a cache write as six dispatches).
 #include "common.cuh"
 
 using namespace qnn;
@@ -22,6 +26,22 @@ using namespace qnn;
 #define EPI_NONE 0
 #define EPI_SOFTCAP 1
 #define EPI_GATED 2
+#define EPI_ROPE 3
+
+// What the rotate-and-append epilogue needs; the meaning of each field is that of the argument
+// of the same name of qnn_rope_cache_write.
+struct RopeEpi {
+    int nq, nkv, hd;
+    const float* inv_freq;
+    const int* tok_pos;
+    const int* tok_slot;
+    bf16* k_pool;
+    bf16* v_pool;
+    const int* page_table;
+    int max_pages, page_size, ring;
+    const int* slot_len;
+    int write_cache;
+};
 
 __device__ __forceinline__ void store_out(void* out, int out_dt, size_t i, float v) { store_from_f(out, out_dt, i, v); }
 
@@ -43,18 +63,39 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint3
 }
 
 __device__ __forceinline__ uint4 ldg16(const bf16* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
+// The same load as a volatile statement: it keeps its place relative to the dependency wait.
+__device__ __forceinline__ uint4 ldg16_early(const bf16* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
 
 template <int NT, int EPI, int NW>
 __global__ void __launch_bounds__(NW * 32) skinny_bf16_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W,
                                                           void* __restrict__ out, int out_dt, int M, int N, int K,
-                                                          float cap, int act) {
+                                                          float cap, int act, const RopeEpi rp) {
     constexpr int COLS = NT * 8;
     constexpr int THREADS = NW * 32;
     __shared__ float red[NW][16][COLS + 1];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int Nout = (EPI == EPI_GATED) ? N / 2 : N;
     const int n0 = blockIdx.x * 16;
-    const int r0 = min(n0 + g, Nout - 1), r1 = min(n0 + g + 8, Nout - 1);
+    int r0 = min(n0 + g, Nout - 1), r1 = min(n0 + g + 8, Nout - 1);
+    // rotate and append: fragment rows 0-7 are columns j0..j0+7 of a head, rows 8-15 their partners
+    int rope_base0 = 0, rope_base1 = 0, rope_blocks = 0;
+    if constexpr (EPI == EPI_ROPE) {
+        const int per = rp.hd / 16;
+        rope_blocks = (rp.nq + rp.nkv) * per;
+        if ((int)blockIdx.x < rope_blocks) {
+            rope_base0 = ((int)blockIdx.x / per) * rp.hd + ((int)blockIdx.x % per) * 8;
+            rope_base1 = rope_base0 + rp.hd / 2;
+        } else {
+            rope_base0 = (rp.nq + rp.nkv) * rp.hd + ((int)blockIdx.x - rope_blocks) * 16;
+            rope_base1 = rope_base0 + 8;
+        }
+        r0 = rope_base0 + g;
+        r1 = rope_base1 + g;
+    }
     const int nchunks = K / 8;
     const int nkb = (nchunks + 3) / 4;
     const uint4 zero4 = make_uint4(0, 0, 0, 0);
@@ -77,12 +118,28 @@ __global__ void __launch_bounds__(NW * 32) skinny_bf16_kernel(const bf16* __rest
     const bf16* u0 = W + (size_t)(Nout + r0) * K;
     const bf16* u1 = W + (size_t)(Nout + r1) * K;
 
-    // The weights do not depend on the kernel before this one: pull this warp's share of them
-    // towards L2 while that kernel is still running, then wait for the activations.  Only for the
-    // smaller matrices, whose kernels are too short to reach full bandwidth on their own; for the
-    // big ones the extra instructions only fill the load queue.
+    // The weights do not depend on the kernel before this one, the activations do.  So each thread
+    // takes its first PRE blocks of weights into registers, and asks for the rest of a small
+    // matrix to be brought to L2, before it waits for that kernel: launched while the (short,
+    // bandwidth-idle) kernel before it still runs, this kernel has most of its weight traffic
+    // behind it when its activations arrive.  For the big matrices the L2 requests would only fill
+    // the load queue.  The loads are volatile asm so that they stay in front of the wait.
+    constexpr int PRE = (EPI == EPI_GATED) ? 2 : 4;
+    uint4 pa_lo[PRE], pa_hi[PRE], pg_lo[(EPI == EPI_GATED) ? PRE : 1], pg_hi[(EPI == EPI_GATED) ? PRE : 1];
+#pragma unroll
+    for (int i = 0; i < PRE; ++i) {
+        const int c = (warp + i * NW) * 4 + t;
+        const bool valid = c < nchunks;
+        const size_t ko = (size_t)c * 8;
+        pa_lo[i] = valid ? ldg16_early(w0 + ko) : zero4;
+        pa_hi[i] = valid ? ldg16_early(w1 + ko) : zero4;
+        if (EPI == EPI_GATED) {
+            pg_lo[i] = valid ? ldg16_early(u0 + ko) : zero4;
+            pg_hi[i] = valid ? ldg16_early(u1 + ko) : zero4;
+        }
+    }
     if (t == 0 && (size_t)N * K <= ((size_t)1 << 24)) {
-        for (int kb = warp; kb < nkb; kb += NW) {
+        for (int kb = warp + PRE * NW; kb < nkb; kb += NW) {
             const size_t ko = (size_t)kb * 32;
             if (ko < (size_t)K) {
                 asm volatile("prefetch.global.L2 [%0];" ::"l"(w0 + ko));
@@ -96,8 +153,25 @@ __global__ void __launch_bounds__(NW * 32) skinny_bf16_kernel(const bf16* __rest
     }
     pdl_wait();
 
+#pragma unroll
+    for (int i = 0; i < PRE; ++i) {
+        const int c = (warp + i * NW) * 4 + t;
+        const bool valid = c < nchunks;
+        const size_t ko = (size_t)c * 8;
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            const int m = nt * 8 + g;
+            uint4 b = (valid && m < M) ? ldg16(x + (size_t)m * K + ko) : zero4;
+            mma_bf16_16816(acc[nt], pa_lo[i].x, pa_hi[i].x, pa_lo[i].y, pa_hi[i].y, b.x, b.y);
+            mma_bf16_16816(acc[nt], pa_lo[i].z, pa_hi[i].z, pa_lo[i].w, pa_hi[i].w, b.z, b.w);
+            if (EPI == EPI_GATED) {
+                mma_bf16_16816(accu[nt], pg_lo[i].x, pg_hi[i].x, pg_lo[i].y, pg_hi[i].y, b.x, b.y);
+                mma_bf16_16816(accu[nt], pg_lo[i].z, pg_hi[i].z, pg_lo[i].w, pg_hi[i].w, b.z, b.w);
+            }
+        }
+    }
 #pragma unroll 4
-    for (int kb = warp; kb < nkb; kb += NW) {
+    for (int kb = warp + PRE * NW; kb < nkb; kb += NW) {
         const int c = kb * 4 + t;
         const bool valid = c < nchunks;
         const size_t ko = (size_t)c * 8;
@@ -135,6 +209,54 @@ __global__ void __launch_bounds__(NW * 32) skinny_bf16_kernel(const bf16* __rest
         red[warp][g + 8][nt * 8 + 2 * t + 1] = acc[nt][3];
     }
     __syncthreads();
+    if constexpr (EPI == EPI_ROPE) {
+        // one thread per (pair, token): the two sums are rounded to bfloat16 first, as the product
+        // without this epilogue would store them, then rotated in float32
+        bf16* o = reinterpret_cast<bf16*>(out);
+        const int hd = rp.hd, half = hd / 2;
+        const size_t head_stride = (size_t)rp.page_size * hd;
+        for (int e = threadIdx.x; e < 8 * COLS; e += THREADS) {
+            const int j = e % 8, m = e / 8;
+            if (m >= M) continue;
+            float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+            for (int w = 0; w < NW; ++w) { s0 += red[w][j][m]; s1 += red[w][j + 8][m]; }
+            const bf16 a = __float2bfloat16(s0), b = __float2bfloat16(s1);
+            const int pos = rp.tok_pos[m], slot = rp.tok_slot[m];
+            bool wr = rp.write_cache && slot >= 0;
+            if (wr && rp.ring > 0 && pos + rp.ring < rp.slot_len[slot]) wr = false;
+            size_t cache_base = 0;
+            if (wr) {
+                const int r = rp.ring > 0 ? pos % rp.ring : pos;
+                const int page = rp.page_table[(size_t)slot * rp.max_pages + r / rp.page_size];
+                cache_base = ((size_t)page * rp.nkv * rp.page_size + (r % rp.page_size)) * hd;
+            }
+            bf16* orow = o + (size_t)m * N;
+            if ((int)blockIdx.x < rope_blocks) {
+                const int h = rope_base0 / hd, d = rope_base0 % hd + j;
+                float sn, cs;
+                sincosf((float)pos * rp.inv_freq[d], &sn, &cs);
+                const float fa = __bfloat162float(a), fb = __bfloat162float(b);
+                const bf16 ra = __float2bfloat16(fa * cs - fb * sn), rb = __float2bfloat16(fa * sn + fb * cs);
+                orow[h * hd + d] = ra;
+                orow[h * hd + d + half] = rb;
+                if (h >= rp.nq && wr) {
+                    bf16* dst = rp.k_pool + cache_base + (size_t)(h - rp.nq) * head_stride;
+                    dst[d] = ra;
+                    dst[d + half] = rb;
+                }
+            } else {
+                orow[rope_base0 + j] = a;
+                orow[rope_base1 + j] = b;
+                if (wr) {
+                    const int c = rope_base0 - (rp.nq + rp.nkv) * hd + j;     // column of V; c + 8 is in the same head
+                    bf16* dst = rp.v_pool + cache_base + (size_t)(c / hd) * head_stride + c % hd;
+                    dst[0] = a;
+                    dst[8] = b;
+                }
+            }
+        }
+    } else {
 #pragma unroll
     for (int sl = 0; sl < SLOTS; ++sl) {
         const int e = threadIdx.x + sl * THREADS;
@@ -174,6 +296,7 @@ __global__ void __launch_bounds__(NW * 32) skinny_bf16_kernel(const bf16* __rest
         }
         if (n < Nout && m < M) store_out(out, out_dt, (size_t)m * Nout + n, v);
     }
+    }
 }
 
 // The K range of a 16-row tile is split over the NW warps of its CTA.  Matrices with few rows
@@ -181,7 +304,7 @@ __global__ void __launch_bounds__(NW * 32) skinny_bf16_kernel(const bf16* __rest
 // least two 32-wide blocks and the partial tiles fit in shared memory.
 template <int EPI>
 static int launch_skinny(const bf16* x, const bf16* W, void* out, int out_dt, int M, int N, int K, float cap, int act,
-                         cudaStream_t st) {
+                         cudaStream_t st, const RopeEpi rp = RopeEpi()) {
     const int Nout = (EPI == EPI_GATED) ? N / 2 : N;
     const unsigned blocks = (unsigned)((Nout + 15) / 16);
     const int nt = (M + 7) / 8;
@@ -191,11 +314,11 @@ static int launch_skinny(const bf16* x, const bf16* W, void* out, int out_dt, in
     if (nt == 1 && blocks * 16u < 3000u && kblocks >= 64) nw = 32;
 #define QNN_SK(NTV)                                                                                            \
     if (nw == 32 && NTV == 1)                                                                                  \
-        qnn::launch_pdl(skinny_bf16_kernel<1, EPI, 32>, dim3(blocks), dim3(1024), 0, st, x, W, out, out_dt, M, N, K, cap, act);         \
+        qnn::launch_pdl(skinny_bf16_kernel<1, EPI, 32>, dim3(blocks), dim3(1024), 0, st, x, W, out, out_dt, M, N, K, cap, act, rp);         \
     else if (nw >= 16 && NTV <= 2)                                                                             \
-        qnn::launch_pdl(skinny_bf16_kernel<(NTV <= 2 ? NTV : 1), EPI, 16>, dim3(blocks), dim3(512), 0, st, x, W, out, out_dt, M, N, K, cap, act); \
+        qnn::launch_pdl(skinny_bf16_kernel<(NTV <= 2 ? NTV : 1), EPI, 16>, dim3(blocks), dim3(512), 0, st, x, W, out, out_dt, M, N, K, cap, act, rp); \
     else                                                                                                       \
-        qnn::launch_pdl(skinny_bf16_kernel<NTV, EPI, 8>, dim3(blocks), dim3(256), 0, st, x, W, out, out_dt, M, N, K, cap, act);         \
+        qnn::launch_pdl(skinny_bf16_kernel<NTV, EPI, 8>, dim3(blocks), dim3(256), 0, st, x, W, out, out_dt, M, N, K, cap, act, rp);         \
     break;
     switch (nt) {
         case 1: QNN_SK(1)
@@ -220,6 +343,27 @@ QNN_API int qnn_skinny_bf16(const void* x, const void* W, void* out, int out_dt,
         case EPI_GATED: return launch_skinny<EPI_GATED>((const bf16*)x, (const bf16*)W, out, out_dt, M, N, K, cap, act, st);
     }
     return QNN_ERR_ARGUMENT;
+}
+
+// qkv[M, (nq+2nkv)*hd] = x[M,K] W^T with Q and K rotated by each row's position and K, V appended to
+// the paged cache: qnn_skinny_bf16 followed by qnn_rope_cache_write (full-width rotation) in one
+// kernel.  Head sizes in steps of 16; M <= 64.
+QNN_API int qnn_skinny_qkv_rope(const void* x, const void* W, void* qkv, int M, int K, int nq, int nkv, int hd,
+                                const float* inv_freq, const int* tok_pos, const int* tok_slot, void* k_pool,
+                                void* v_pool, const int* page_table, int max_pages, int page_size, int ring,
+                                const int* slot_len, int write_cache, cudaStream_t st) {
+    if (M <= 0) return 0;
+    if (M > 64 || K % 8 != 0 || K <= 0 || nq < 1 || nkv < 1 || hd < 16 || hd % 16) return QNN_ERR_UNSUPPORTED;
+    if (((uintptr_t)x | (uintptr_t)W) & 15) return QNN_ERR_ARGUMENT;
+    if (write_cache && (!k_pool || !v_pool || !page_table || !slot_len || page_size < 1)) return QNN_ERR_ARGUMENT;
+    RopeEpi rp;
+    rp.nq = nq; rp.nkv = nkv; rp.hd = hd;
+    rp.inv_freq = inv_freq; rp.tok_pos = tok_pos; rp.tok_slot = tok_slot;
+    rp.k_pool = (bf16*)k_pool; rp.v_pool = (bf16*)v_pool;
+    rp.page_table = page_table; rp.max_pages = max_pages; rp.page_size = page_size; rp.ring = ring;
+    rp.slot_len = slot_len; rp.write_cache = write_cache;
+    return launch_skinny<EPI_ROPE>((const bf16*)x, (const bf16*)W, qkv, QNN_DT_BF16, M, (nq + 2 * nkv) * hd, K, 0.f, 0,
+                                   st, rp);
 }
 
 // ---------------------------------------------------------------------------------

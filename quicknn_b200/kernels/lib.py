@@ -30,6 +30,8 @@ _SIGNATURES: Dict[str, list] = {
     "qnn_rope_cache_write": [c_vp, c_int, c_int, c_int, c_int, c_int, c_int, c_vp, c_vp, c_vp, c_vp, c_vp,
                              c_vp, c_int, c_int, c_int, c_vp, c_int, c_vp],
     "qnn_skinny_bf16": [c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_vp],
+    "qnn_skinny_qkv_rope": [c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_int, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp,
+                            c_int, c_int, c_int, c_vp, c_int, c_vp],
     "qnn_gemv_f32": [c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_float, c_int, c_vp],
     "qnn_sgemm_f32": [c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_float, c_vp],
     "qnn_gemm_tcgen05": [c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_int, c_vp, c_vp],

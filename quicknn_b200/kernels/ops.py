@@ -181,6 +181,53 @@ def rope_cache_write(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, 
         page_size, ring, _p(slot_len), int(write_cache), _stream()), "rope_cache_write")
 
 
+def qkv_rope_cache_fusable(x: torch.Tensor, w: torch.Tensor, head_dim: int, rot_dim: int) -> bool:
+    """Whether qkv_rope_cache takes this product: bfloat16 on both sides, few rows, a matrix
+    that the small-M kernel would multiply anyway, a rotation over the whole head."""
+    M, K = x.shape
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or os.environ.get("QNN_FUSE_ROPE", "1") == "0":
+        return False
+    if M > SKINNY_MAX_ROWS or K % 8 or head_dim % 16 or rot_dim != head_dim:
+        return False
+    return not (USE_TCGEN05 and M >= SKINNY_TCGEN05_FROM and w.shape[0] * K >= SKINNY_TCGEN05_MIN_WEIGHTS)
+
+
+def qkv_rope_cache(x: torch.Tensor, w: torch.Tensor, n_heads: int, n_kv: int, head_dim: int,
+                   inv_freq: torch.Tensor, tok_pos: torch.Tensor, tok_slot: torch.Tensor,
+                   k_pool: Optional[torch.Tensor], v_pool: Optional[torch.Tensor],
+                   page_table: Optional[torch.Tensor], page_size: int, ring: int,
+                   slot_len: Optional[torch.Tensor], write_cache: bool) -> torch.Tensor:
+    """linear(x, w) followed by rope_cache_write(...) as one kernel: the stacked q|k|v product
+    with Q and K rotated and K, V appended to the cache in its epilogue.  Returns qkv."""
+    _req(x, "x", torch.bfloat16, 2)
+    _req(w, "w", torch.bfloat16, 2)
+    M, K = x.shape
+    N = (n_heads + 2 * n_kv) * head_dim
+    if tuple(w.shape) != (N, K):
+        raise ValueError(f"qkv_rope_cache: w is {tuple(w.shape)}, expected {(N, K)}")
+    _req(inv_freq, "inv_freq", torch.float32, 1)
+    if inv_freq.numel() != head_dim // 2:
+        raise ValueError("qkv_rope_cache: inv_freq has the wrong length")
+    _req(tok_pos, "tok_pos", torch.int32, 1)
+    _req(tok_slot, "tok_slot", torch.int32, 1)
+    if tok_pos.numel() < M or tok_slot.numel() < M:
+        raise ValueError("qkv_rope_cache: fewer positions than rows")
+    if write_cache:
+        for n, t in (("k_pool", k_pool), ("v_pool", v_pool)):
+            _req(t, n, torch.bfloat16, 4)
+            if tuple(t.shape[1:]) != (n_kv, page_size, head_dim):
+                raise ValueError(f"{n} has shape {tuple(t.shape)}, expected [pages, {n_kv}, {page_size}, {head_dim}]")
+        _req(page_table, "page_table", torch.int32, 2)
+        _req(slot_len, "slot_len", torch.int32, 1)
+    qkv = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    L = _lib.load()
+    _lib.check(L.qnn_skinny_qkv_rope(
+        _p(x), _p(w), _p(qkv), M, K, n_heads, n_kv, head_dim, _p(inv_freq), _p(tok_pos), _p(tok_slot),
+        _p(k_pool), _p(v_pool), _p(page_table), page_table.shape[1] if page_table is not None else 0,
+        page_size, ring, _p(slot_len), int(write_cache), _stream()), "skinny_qkv_rope")
+    return qkv
+
+
 _gemm_status = {}
 
 

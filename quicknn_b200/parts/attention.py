@@ -5,7 +5,8 @@ Order of operations as in the reference's layer body
 (src/models/QuickNN.Models.Gemma2.pas:167-180): Q, K, V projections; rotation of Q and K;
 append K, V to the cache; attention with scale 1/sqrt(query_pre_attn_scalar), softcap
 and window; output projection.  The three projections are one product against the
-stacked matrix; rotation and append are one kernel.
+stacked matrix; rotation and append are one kernel, or, for the few rows of a decode
+step, the epilogue of that product.
 """
 from __future__ import annotations
 
@@ -62,10 +63,17 @@ class AttentionMixer(Mixer):
         return CacheNeed(self.n_kv, self.head_dim, self.window)
 
     def forward(self, x: torch.Tensor, step, line) -> torch.Tensor:
-        qkv = project(x, self.w_qkv)
-        ops.rope_cache_write(qkv, self.n_heads, self.n_kv, self.head_dim, self.position.rotary_dim,
-                             self.position.inv_freq, step.tok_pos, step.tok_slot, line.k, line.v,
-                             line.page_table, line.page_size, line.ring, line.slot_len, line.writes)
+        if step.mode == "decode" and ops.qkv_rope_cache_fusable(x, self.w_qkv, self.head_dim,
+                                                                self.position.rotary_dim):
+            # few rows: rotation and append ride in the product's epilogue
+            qkv = ops.qkv_rope_cache(x, self.w_qkv, self.n_heads, self.n_kv, self.head_dim,
+                                     self.position.inv_freq, step.tok_pos, step.tok_slot, line.k, line.v,
+                                     line.page_table, line.page_size, line.ring, line.slot_len, line.writes)
+        else:
+            qkv = project(x, self.w_qkv)
+            ops.rope_cache_write(qkv, self.n_heads, self.n_kv, self.head_dim, self.position.rotary_dim,
+                                 self.position.inv_freq, step.tok_pos, step.tok_slot, line.k, line.v,
+                                 line.page_table, line.page_size, line.ring, line.slot_len, line.writes)
         if step.mode == "prefill" and not line.writes:
             # the keys of this line were written by another layer earlier in this step
             if line.ring and step.max_q_len > line.ring:

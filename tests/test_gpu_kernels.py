@@ -265,6 +265,62 @@ def test_rope_and_cache_write(ops, dtype, nq, nkv, hd, rot, theta):
     assert float(np.abs(kp[5, :, 6:, :]).sum()) != 0.0 and float(np.abs(kp[3, :, 6:, :]).sum()) == 0.0
 
 
+@pytest.mark.parametrize("M,K,nq,nkv,hd,ring", [(5, 200, 3, 1, 48, 0), (8, 264, 4, 2, 16, 128), (19, 136, 2, 2, 80, 0),
+                                                (1, 2056, 2, 1, 32, 64)])
+def test_qkv_product_with_rotate_and_append_epilogue(ops, M, K, nq, nkv, hd, ring):
+    """The fused product against the product, rotation and append as separate kernels (same
+    sums, so at most an ulp apart) and against the plain rotation of the plain product."""
+    rng = np.random.default_rng(M * K + hd)
+    Nw = (nq + 2 * nkv) * hd
+    x = bf16_round(rng.normal(size=(M, K)))
+    w = bf16_round(rng.normal(size=(Nw, K)) / math.sqrt(K))
+    theta = 1e4
+    pos = (rng.integers(0, 190, size=M)).astype(np.int32)
+    slot = rng.permutation(M + 2)[:M].astype(np.int32)
+    if M > 2:
+        slot[1] = -1                                                      # a padding row writes nothing
+    pages = 3
+    table = np.zeros((M + 2, pages), dtype=np.int32)
+    table[:, :] = 1 + rng.permutation((M + 2) * pages).reshape(M + 2, pages)
+    slot_len = np.zeros(M + 2, dtype=np.int32)
+    for r in range(M):
+        if slot[r] >= 0:
+            slot_len[slot[r]] = pos[r] + 1
+    inv = torch.exp(-math.log(theta) * 2.0 * torch.arange(hd // 2, dtype=torch.float64) / hd).float().to(DEV)
+    args = (T(pos, torch.int32), T(slot, torch.int32))
+    tab, sl = T(table, torch.int32), T(slot_len, torch.int32)
+    k1, v1 = _pools((M + 2) * pages + 1, nkv, hd, torch.bfloat16)
+    k2, v2 = _pools((M + 2) * pages + 1, nkv, hd, torch.bfloat16)
+    xt, wt = T(x, torch.bfloat16), T(w, torch.bfloat16)
+    fused = ops.qkv_rope_cache(xt, wt, nq, nkv, hd, inv, *args, k1, v1, tab, 64, ring, sl, True)
+    sep = ops.linear(xt, wt)
+    plain_qkv = N(sep).copy()
+    ops.rope_cache_write(sep, nq, nkv, hd, hd, inv, *args, k2, v2, tab, 64, ring, sl, True)
+    ulp = 2.0 ** -7
+    for name, a, b in (("qkv", fused, sep), ("k pool", k1, k2), ("v pool", v1, v2)):
+        a, b = N(a), N(b)
+        assert np.all(np.abs(a - b) <= ulp * np.maximum(np.abs(b), 2.0 ** -20)), name
+    assert np.array_equal(N(v1), N(v2))
+    q = plain_qkv[:, :nq * hd].reshape(M, nq, hd)
+    k = plain_qkv[:, nq * hd:(nq + nkv) * hd].reshape(M, nkv, hd)
+    got = N(fused)
+    assert_close(got[:, :nq * hd], P.rope(q, pos, theta).reshape(M, -1), torch.bfloat16, "q", mult=2)
+    kr = P.rope(k, pos, theta)
+    kp = N(k1)
+    for r in range(M):
+        if slot[r] < 0:
+            continue
+        c = pos[r] % ring if ring else pos[r]
+        assert_close(kp[table[slot[r], c // 64], :, c % 64, :], kr[r], torch.bfloat16, "cached k", mult=2)
+    assert float(np.abs(kp[0]).sum()) == 0.0
+    written = sum(1 for r in range(M) if slot[r] >= 0)
+    assert int((np.abs(N(v1)).sum(axis=(1, 3)) != 0).sum()) == written     # one cell per live row, no more
+    # without the append nothing is written
+    k3, v3 = _pools(4, nkv, hd, torch.bfloat16)
+    again = ops.qkv_rope_cache(xt, wt, nq, nkv, hd, inv, *args, None, None, None, 64, ring, None, False)
+    assert np.array_equal(N(again), N(fused))
+
+
 def test_cache_write_ring_and_padding(ops):
     """A prompt longer than the ring leaves its last `ring` positions, each in its place; a
     row with a negative slot writes nothing."""
