@@ -643,7 +643,8 @@ extern "C" int qnn_attn_decode_mma_split(const void* q, long long q_stride, cons
                                          const int* page_table, int max_pages, int page_size, int ring,
                                          const int* slots, const int* slot_len, int B, int nq, int nkv, int hd,
                                          float scale, float cap, int window, float* part_o, float* part_ml,
-                                         int n_splits, cudaStream_t st);
+                                         int n_splits, void* out, long long out_stride, int* combined,
+                                         cudaStream_t st);
 
 template <typename T>
 static int decode_launch(const void* q, long long q_stride, const void* k_pool, const void* v_pool,
@@ -666,9 +667,11 @@ static int decode_launch(const void* q, long long q_stride, const void* k_pool, 
     if (page_size <= 0 || (page_size & (page_size - 1)) || (ring > 0 && ring < 8 * 32)) tt = 0;   // the tiled kernel's address arithmetic
     bool launched = false;
     if (sizeof(T) == 2) {   // bfloat16: the tensor-core kernel where it takes the sizes
+        int combined = 0;
         const int rc = qnn_attn_decode_mma_split(q, q_stride, k_pool, v_pool, page_table, max_pages, page_size, ring,
                                                  slots, slot_len, B, nq, nkv, hd, scale, cap, window, part_o, part_ml,
-                                                 n_splits, st);
+                                                 n_splits, out, out_stride, &combined, st);
+        if (rc == 0 && combined) return 0;            // merged inside the kernel's clusters
         if (rc == 0) launched = true;
         else if (rc != QNN_ERR_UNSUPPORTED) return rc;
     }

@@ -13,9 +13,13 @@
 // P^T is rearranged from the accumulator layout of S^T with eight shuffles.  Softmax state
 // (max, sum) is float32, one pair of heads per lane; O^T accumulates in float32.
 //
-// Grid (splits, kv heads x head tiles, sequences), 4 warps per CTA; the warps of a CTA interleave
-// the 16-key tiles of the CTA's key range and are merged through shared memory in warp order; the
-// CTA writes (max, sum, O) of its range to the scratch that qnn_attn_combine reads.
+// Grid (splits, kv heads x head tiles, sequences), 2 warps per CTA; the warps of a CTA interleave
+// the 16-key tiles of the CTA's key range and are merged through shared memory in warp order.
+// With up to 4 splits the CTAs of one (sequence, kv head) form a thread-block cluster: each leaves
+// (max, sum, O) of its range in its own shared memory, and after a cluster barrier every CTA
+// merges a share of the output elements over all ranks, in rank order, reading the others through
+// distributed shared memory, and writes bfloat16 output: no scratch, no second kernel.  With more
+// splits the CTA writes (max, sum, O) to the scratch that the combine kernel of attention.cu reads.
 #include "common.cuh"
 #include <math_constants.h>
 #include <stdlib.h>
@@ -24,7 +28,6 @@ using namespace qnn;
 
 namespace {
 
-constexpr int MMA_STAGES = 3;
 constexpr int TILE = 16;   // keys per warp step
 
 __device__ __forceinline__ void cp_async_16(unsigned smem_dst, const void* gmem_src, bool valid) {
@@ -53,19 +56,75 @@ __device__ __forceinline__ float tanh_fast(float x) {
     asm("tanh.approx.f32 %0, %1;" : "=f"(r) : "f"(x));
     return r;
 }
+__device__ __forceinline__ unsigned cluster_rank() {
+    unsigned r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_barrier() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// float at `local_addr` (a shared-memory address of this CTA) in the CTA of rank `rank`
+__device__ __forceinline__ float ld_cluster(unsigned local_addr, unsigned rank) {
+    unsigned remote;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&h);
 }
 
-template <int HD, int MMA_WARPS>
+// out[h, d] = sum_r e^{m_r - M} O_r[d] / sum_r e^{m_r - M} l_r over the ranks of the cluster in
+// ascending order: the sums that the combine kernel forms from the scratch.  `cs` is this CTA's
+// [head][HD + 2] (O, max, sum) in shared memory, at the same address in every CTA of the cluster;
+// every CTA merges a share of the (head, d) pairs.  Kept out of line so that the main loop of the
+// kernel compiles as it does without it.
+template <int HD>
+__device__ __noinline__ void cluster_merge(const float* cs, int S, int heads, bf16* __restrict__ out) {
+    constexpr int ROW = HD + 2;
+    cluster_barrier();
+    const unsigned rank = cluster_rank();
+    const unsigned cs_addr = (unsigned)__cvta_generic_to_shared(cs);
+    for (int i = rank * blockDim.x + threadIdx.x; i < heads * HD; i += S * blockDim.x) {
+        const int hh = i / HD, d = i % HD;
+        const unsigned row = cs_addr + (unsigned)(hh * ROW) * 4u;
+        float mr[8], lr[8], orr[8];
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+            const bool on = r < S;
+            mr[r] = on ? ld_cluster(row + HD * 4u, r) : -CUDART_INF_F;
+            lr[r] = on ? ld_cluster(row + (HD + 1) * 4u, r) : 0.f;
+            orr[r] = on ? ld_cluster(row + (unsigned)d * 4u, r) : 0.f;
+        }
+        float mm = -CUDART_INF_F;
+#pragma unroll
+        for (int r = 0; r < 8; ++r) mm = fmaxf(mm, mr[r]);
+        float ll = 0.f, acc = 0.f;
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+            const float c = (mr[r] == -CUDART_INF_F) ? 0.f : expf(mr[r] - mm);
+            ll += c * lr[r];
+            acc += c * orr[r];
+        }
+        const float inv = ll > 0.f ? 1.f / ll : 0.f;
+        out[(size_t)hh * HD + d] = __float2bfloat16(acc * inv);
+    }
+    cluster_barrier();                            // nobody leaves while its memory is still read
+}
+
+template <int HD, int MMA_WARPS, int MMA_STAGES>
 __global__ void __launch_bounds__(MMA_WARPS * 32)
 attn_decode_mma_kernel(const bf16* __restrict__ q, size_t q_stride, const bf16* __restrict__ k_pool,
                        const bf16* __restrict__ v_pool, const int* __restrict__ page_table, int max_pages,
                        int page_size, int ring, const int* __restrict__ slots, const int* __restrict__ slot_len,
                        int nq, int nkv, float scale, float cap, int window, float* __restrict__ part_o,
-                       float* __restrict__ part_ml, int n_splits) {
+                       float* __restrict__ part_ml, int n_splits, bf16* __restrict__ out, size_t out_stride) {
     pdl_wait();
+    const bool CLUSTER = out != nullptr;         // launched as clusters of n_splits CTAs that merge their ranges
     constexpr int KSTEPS = HD / 16;              // k16 steps of S^T, and 16-row tiles of O^T
     constexpr int CH = HD / 8;                   // 16-byte chunks per row
     constexpr int ROW_BYTES = HD * 2;
@@ -253,6 +312,7 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, size_t q_stride, const bf16* 
         r0[ROW + HD + 1] = l1;
     }
     __syncthreads();
+    float* cs = ms + (size_t)MMA_WARPS * 8 * ROW;      // cluster mode: this CTA's merged [head][HD + 2]
     for (int hh = 0; hh < 8; ++hh) {
         if (h0 + hh >= G) break;
         const int h = kh * G + h0 + hh;
@@ -268,55 +328,139 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, size_t q_stride, const bf16* 
         for (int d = threadIdx.x; d < HD; d += blockDim.x) {
             float acc = 0.f;
             for (int w = 0; w < MMA_WARPS; ++w) acc += coef[w] * ms[((size_t)w * 8 + hh) * ROW + d];
-            part_o[pbase * HD + d] = acc;
+            if (CLUSTER) cs[hh * ROW + d] = acc;
+            else part_o[pbase * HD + d] = acc;
         }
         if (threadIdx.x == 0) {
-            part_ml[pbase * 2] = mm;
-            part_ml[pbase * 2 + 1] = ll;
+            if (CLUSTER) {
+                cs[hh * ROW + HD] = mm;
+                cs[hh * ROW + HD + 1] = ll;
+            } else {
+                part_ml[pbase * 2] = mm;
+                part_ml[pbase * 2 + 1] = ll;
+            }
         }
     }
+    if (CLUSTER)
+        cluster_merge<HD>(cs, n_splits, min(8, G - h0), out + (size_t)b * out_stride + (size_t)(kh * G + h0) * HD);
+}
+
+// Largest cluster that merges in the kernel.  Clusters of 8 CTAs with 98 KB of shared memory each
+// (head size 256) fit the device only just, and a step with them measured 28 % slower than the
+// plain grid followed by the combine kernel; clusters of 2 and 4 measured equal or slightly faster.
+constexpr int CLUSTER_MAX = 4;
+
+template <int HD, bool CLUSTER>
+constexpr int stages() { return 3; }   // of the cp.async pipeline
+
+template <int HD, int MMA_WARPS, bool CLUSTER>
+size_t smem_bytes(int max_pages) {
+    constexpr int MMA_STAGES = stages<HD, CLUSTER>();
+    size_t smem = (size_t)MMA_WARPS * MMA_STAGES * 2 * TILE * HD * 2;
+    const size_t merge = (size_t)(MMA_WARPS + 1) * 8 * (HD + 2) * sizeof(float);
+    if (smem < merge) smem = merge;
+    return smem + ((size_t)max_pages + 2) * sizeof(int);
+}
+
+// Whether the device can hold a cluster of CLUSTER_MAX CTAs of this kernel (asked once).
+template <int HD, int MMA_WARPS>
+bool cluster_fits(size_t smem) {
+    constexpr int ST = stages<HD, true>();
+    static int fits = -1;
+    if (fits < 0) {
+        const char* e = getenv("QNN_ATTN_CLUSTER");
+        fits = 0;
+        if (!(e && e[0] == '0')) {
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(CLUSTER_MAX, 1, 1);
+            cfg.blockDim = dim3(MMA_WARPS * 32);
+            cfg.dynamicSmemBytes = smem;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeClusterDimension;
+            attr[0].val.clusterDim.x = CLUSTER_MAX;
+            attr[0].val.clusterDim.y = 1;
+            attr[0].val.clusterDim.z = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
+            int n = 0;
+            if (cudaOccupancyMaxActiveClusters(&n, attn_decode_mma_kernel<HD, MMA_WARPS, ST>, &cfg) == cudaSuccess && n > 0)
+                fits = 1;
+            else
+                (void)cudaGetLastError();
+        }
+    }
+    return fits == 1;
 }
 
 template <int HD, int MMA_WARPS>
 int launch(const void* q, long long q_stride, const void* k_pool, const void* v_pool, const int* page_table,
            int max_pages, int page_size, int ring, const int* slots, const int* slot_len, int B, int nq, int nkv,
-           float scale, float cap, int window, float* part_o, float* part_ml, int n_splits, cudaStream_t st) {
-    auto kern = attn_decode_mma_kernel<HD, MMA_WARPS>;
-    size_t smem = (size_t)MMA_WARPS * MMA_STAGES * 2 * TILE * HD * 2;
-    const size_t merge = (size_t)MMA_WARPS * 8 * (HD + 2) * sizeof(float);
-    if (smem < merge) smem = merge;
-    smem += ((size_t)max_pages + 2) * sizeof(int);
-    if (smem > 220 * 1024) return QNN_ERR_UNSUPPORTED;
+           float scale, float cap, int window, float* part_o, float* part_ml, int n_splits, void* out,
+           long long out_stride, int* combined, cudaStream_t st) {
+    const size_t smem = smem_bytes<HD, MMA_WARPS, false>(max_pages);
+    const size_t smem_c = smem_bytes<HD, MMA_WARPS, true>(max_pages);
+    if (smem > 220 * 1024 || smem_c > 220 * 1024) return QNN_ERR_UNSUPPORTED;
+    constexpr int ST = stages<HD, false>(), STC = stages<HD, true>();
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_mma_kernel<HD, MMA_WARPS, ST>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(attn_decode_mma_kernel<HD, MMA_WARPS, STC>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
     const int G = nq / nkv;
     dim3 grid(n_splits, nkv * ((G + 7) / 8), B);
-    qnn::launch_pdl(kern, dim3(grid), dim3(MMA_WARPS * 32), smem, st, (const bf16*)q, (size_t)q_stride, (const bf16*)k_pool, (const bf16*)v_pool,
+    *combined = 0;
+    if (out != nullptr && n_splits <= CLUSTER_MAX && cluster_fits<HD, MMA_WARPS>(smem_c)) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = grid;
+        cfg.blockDim = dim3(MMA_WARPS * 32);
+        cfg.dynamicSmemBytes = smem_c;
+        cfg.stream = st;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = n_splits;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = (qnn::pdl_enabled() && (long long)grid.x * grid.y * grid.z <= qnn::pdl_max_grid()) ? 2 : 1;
+        cudaError_t e = cudaLaunchKernelEx(&cfg, attn_decode_mma_kernel<HD, MMA_WARPS, STC>, (const bf16*)q,
+                                           (size_t)q_stride, (const bf16*)k_pool, (const bf16*)v_pool, page_table,
+                                           max_pages, page_size, ring, slots, slot_len, nq, nkv, scale, cap, window,
+                                           part_o, part_ml, n_splits, (bf16*)out, (size_t)out_stride);
+        if (e != cudaSuccess) return (int)e;
+        *combined = 1;
+        return (int)cudaGetLastError();
+    }
+    qnn::launch_pdl(attn_decode_mma_kernel<HD, MMA_WARPS, ST>, dim3(grid), dim3(MMA_WARPS * 32), smem, st, (const bf16*)q, (size_t)q_stride, (const bf16*)k_pool, (const bf16*)v_pool,
                                              page_table, max_pages, page_size, ring, slots, slot_len, nq, nkv, scale,
-                                             cap, window, part_o, part_ml, n_splits);
+                                             cap, window, part_o, part_ml, n_splits, (bf16*)nullptr, (size_t)0);
     return (int)cudaGetLastError();
 }
 
 }  // namespace
 
-// The split pass of decode attention for bfloat16 on the tensor cores.  Returns
-// QNN_ERR_UNSUPPORTED for sizes it does not take (the caller then uses the generic kernel);
-// on success the caller still has to run the combine pass over part_o / part_ml.
+// Decode attention for bfloat16 on the tensor cores.  Returns QNN_ERR_UNSUPPORTED for sizes it
+// does not take (the caller then uses the generic kernel).  On success *combined says whether
+// `out` ([B, out_stride] bfloat16, may be null) already holds the result (up to 4 splits, merged
+// inside a cluster) or the caller still has to run the combine pass over part_o / part_ml.
 extern "C" int qnn_attn_decode_mma_split(const void* q, long long q_stride, const void* k_pool, const void* v_pool,
                                          const int* page_table, int max_pages, int page_size, int ring,
                                          const int* slots, const int* slot_len, int B, int nq, int nkv, int hd,
                                          float scale, float cap, int window, float* part_o, float* part_ml,
-                                         int n_splits, cudaStream_t st) {
+                                         int n_splits, void* out, long long out_stride, int* combined,
+                                         cudaStream_t st) {
     if (nkv <= 0 || nq % nkv) return QNN_ERR_ARGUMENT;
     if (page_size < TILE || (page_size & (page_size - 1))) return QNN_ERR_UNSUPPORTED;
     if (ring > 0 && (ring % page_size)) return QNN_ERR_UNSUPPORTED;
     if ((q_stride * 2) % 4 || ((uintptr_t)q & 3)) return QNN_ERR_UNSUPPORTED;
 #define QNN_MMA_ARGS q, q_stride, k_pool, v_pool, page_table, max_pages, page_size, ring, slots, slot_len, B, nq, nkv, \
-                     scale, cap, window, part_o, part_ml, n_splits, st
+                     scale, cap, window, part_o, part_ml, n_splits, out, out_stride, combined, st
     static int warps = 0;
     if (warps == 0) {
         const char* e = getenv("QNN_MMA_WARPS");

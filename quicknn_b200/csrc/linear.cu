@@ -124,7 +124,7 @@ __global__ void __launch_bounds__(NW * 32) skinny_bf16_kernel(const bf16* __rest
     // bandwidth-idle) kernel before it still runs, this kernel has most of its weight traffic
     // behind it when its activations arrive.  For the big matrices the L2 requests would only fill
     // the load queue.  The loads are volatile asm so that they stay in front of the wait.
-    constexpr int PRE = (EPI == EPI_GATED) ? 2 : 4;
+    constexpr int PRE = (EPI == EPI_GATED) ? 1 : 4;
     uint4 pa_lo[PRE], pa_hi[PRE], pg_lo[(EPI == EPI_GATED) ? PRE : 1], pg_hi[(EPI == EPI_GATED) ? PRE : 1];
 #pragma unroll
     for (int i = 0; i < PRE; ++i) {

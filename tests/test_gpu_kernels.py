@@ -437,7 +437,8 @@ def _fill_cache(k, v, tables, dtype, pages, ring=0):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("nq,nkv,hd", GEOMS)
-@pytest.mark.parametrize("window,cap,splits", [(None, 50.0, 1), (None, None, 5), (40, 30.0, 3), (128, None, 4)])
+@pytest.mark.parametrize("window,cap,splits", [(None, 50.0, 1), (None, None, 5), (40, 30.0, 3), (128, None, 4),
+                                               (None, 30.0, 8), (128, 50.0, 9), (None, None, 20)])
 def test_attention_decode(ops, dtype, nq, nkv, hd, window, cap, splits):
     rng = np.random.default_rng(nq + hd + splits)
     lens = [200, 1, 65, 130]
