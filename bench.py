@@ -252,8 +252,9 @@ def main():
         res = llm.generate(prompts, GenerationOptions.greedy(new), stop_ids=[])
         dec = max(r.decode_seconds for r in res)
         gen = sum(r.generated_tokens - 1 for r in res)
-        e2e = {"value": round(gen / dec, 1), "unit": "tokens/s", "h2d_bytes_per_step": 2 * BATCH * 4,
-               "d2h_bytes_per_step": BATCH * 4 + 4, "prefill_seconds": round(max(r.time_to_first_token_seconds for r in res), 3)}
+        e2e = {"value": round(gen / dec, 1), "unit": "tokens/s",
+               "h2d_bytes_per_step": round(llm.last_io["h2d_bytes_per_step"], 1),
+               "d2h_bytes_per_step": round(llm.last_io["d2h_bytes_per_step"], 1), "prefill_seconds": round(max(r.time_to_first_token_seconds for r in res), 3)}
 
     out = {
         "metric": f"decode tokens/s, Gemma 2 {args.model.upper()} layer sizes, batch {args.batch}, context {args.context}", "value": round(main_run["tok_s"], 1),

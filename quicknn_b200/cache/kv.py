@@ -28,6 +28,7 @@ import torch
 
 from ..parts.base import CacheNeed, StateNeed
 from .pages import CacheFull, PagePool, SlotTable
+from .upload import PinnedUploader
 
 PAGE = 64
 
@@ -98,6 +99,7 @@ class KVCache:
             for i, line in enumerate(lines):
                 self._line_group[line] = (len(self.groups), i)
             self.groups.append(g)
+        self.uploader = PinnedUploader(device, entries=32)
         self.lengths_host = np.zeros(max_slots, dtype=np.int32)
         self.lengths_dev = torch.zeros(max_slots, dtype=torch.int32, device=device)
         self._lengths_dirty = False
@@ -171,13 +173,13 @@ class KVCache:
             if g.dirty:
                 rows = sorted(g.dirty)
                 if len(rows) > 8:
-                    g.table_dev.copy_(torch.from_numpy(g.table_host))
+                    self.uploader.send(g.table_dev, g.table_host)
                 else:
                     for r in rows:
-                        g.table_dev[r].copy_(torch.from_numpy(g.table_host[r]))
+                        self.uploader.send(g.table_dev[r], g.table_host[r])
                 g.dirty.clear()
         if self._lengths_dirty:
-            self.lengths_dev.copy_(torch.from_numpy(self.lengths_host))
+            self.uploader.send(self.lengths_dev, self.lengths_host)
             self._lengths_dirty = False
 
     # ---- views ------------------------------------------------------------------------

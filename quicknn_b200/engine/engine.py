@@ -152,7 +152,8 @@ class Engine:
         lens = np.asarray([len(t) for _, t in entries], np.int32)
         starts = np.concatenate([[0], np.cumsum(lens)[:-1]]).astype(np.int32)
         packed = np.concatenate([tokens, tok_pos, tok_slot, tok_row0, slots, rows, starts, lens])
-        dev = torch.from_numpy(packed).to(self.device)
+        dev = torch.empty(packed.size, dtype=torch.int32, device=self.device)
+        self.cache.uploader.send(dev, packed.astype(np.int32, copy=False))
         o = 0
         views = []
         for n in (T, T, T, T, B, len(rows), B, B):
@@ -200,7 +201,7 @@ class Engine:
                              self.splits_for(B), part_o, part_ml)
             st = {"meta": meta, "step": step, "graph": None, "logits": None}
             self._decode_state[B] = st
-        st["meta"].copy_(torch.from_numpy(np.concatenate([np.asarray(starts, np.int32), np.asarray(slots, np.int32)])))
+        self.cache.uploader.send(st["meta"], np.concatenate([np.asarray(starts, np.int32), np.asarray(slots, np.int32)]))
         st["step"].tokens.copy_(tokens_dev.reshape(-1))
         self.steps_run += 1
         if not use_graph:

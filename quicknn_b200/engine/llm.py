@@ -11,6 +11,7 @@ import numpy as np
 import torch
 
 from ..config.base import Architecture, ModelConfig, find_architecture
+from ..cache.pages import CacheFull
 from ..sampling import GenerationOptions, Sampler
 from ..weights.random_init import random_tensors
 from .engine import Engine
@@ -21,14 +22,46 @@ PAGE = 64
 
 
 class _Backend(GenerationBackend):
-    def __init__(self, engine: Engine, sampler: Sampler, max_batch: int):
+    """The engine and the sampler behind the generation loop.
+
+    One step ahead: before the host waits for the ids of a step, the next step (for the same
+    rows, fed those ids on the device) is already queued, so the device does not idle while
+    the host reads ids, looks for stop tokens and prepares the next launch.  If the loop then
+    drops a row, the step that ran ahead has computed one token too many for it; that token
+    is thrown away with the row's slot, and the other rows' ids do not depend on it.  A step
+    runs ahead only if every row has room for one more token."""
+
+    def __init__(self, engine: Engine, sampler: Sampler, max_batch: int, run_ahead: bool = True):
         self.engine, self.sampler = engine, sampler
         self.max_batch = max_batch
         self.max_tokens = engine.cache.max_tokens
         self.max_seq = engine.max_seq
         self.vocab_size = engine.model.spec.embedding.vocab_size
+        self.run_ahead = run_ahead
         self.slots: List[int] = []
-        self.last: Optional[torch.Tensor] = None
+        self.cur: Optional[torch.Tensor] = None      # ids of the step last returned to the loop, rows = slots
+        self.ahead: Optional[torch.Tensor] = None    # ids of the step after it, if that step already runs
+        self.decode_steps = 0                        # decode steps launched, and the bytes they sent and read
+        self.h2d_bytes = 0
+        self.d2h_bytes = 0
+
+    def _decode(self, tokens: torch.Tensor) -> torch.Tensor:
+        up = self.engine.cache.uploader
+        before = up.bytes_sent
+        logits = self.engine.decode(self.slots, tokens)
+        self.h2d_bytes += up.bytes_sent - before
+        self.d2h_bytes += 4 * (len(self.slots) + 1)
+        self.decode_steps += 1
+        return self.sampler(logits).clone()
+
+    def _launch_ahead(self) -> Optional[torch.Tensor]:
+        eng = self.engine
+        if not self.run_ahead or any(eng.cache.length(s) + 1 > self.max_seq for s in self.slots):
+            return None
+        try:
+            return self._decode(self.cur)
+        except CacheFull:
+            return None
 
     def begin(self, first_index: int, prompts: Sequence[Sequence[int]]) -> np.ndarray:
         eng = self.engine
@@ -39,31 +72,37 @@ class _Backend(GenerationBackend):
             rows = torch.tensor([r for r, p in enumerate(prompts) for _ in p], dtype=torch.int32, device=eng.device)
             self.sampler.mark_prompt(toks, rows)
         logits = eng.step(list(zip(self.slots, prompts)), "last")
-        self.last = self.sampler(logits)
-        return self.sampler.read(self.last)
+        self.cur = self.sampler(logits).clone()
+        self.sampler.post(self.cur)
+        self.ahead = self._launch_ahead()
+        return self.sampler.collect()
 
     def advance(self, keep_rows: Sequence[int]) -> np.ndarray:
         eng = self.engine
         keep = list(keep_rows)
+        idx = None
         if len(keep) != len(self.slots):
             for r, s in enumerate(self.slots):
                 if r not in keep:
                     eng.release(s)
             self.slots = [self.slots[r] for r in keep]
             idx = torch.tensor(keep, dtype=torch.long, device=eng.device)
-            tokens = self.last[idx].contiguous()
             self.sampler.compact(keep)
+        if self.ahead is not None:
+            self.cur = self.ahead if idx is None else self.ahead[idx].contiguous()
         else:
-            tokens = self.last
-        logits = eng.decode(self.slots, tokens)
-        self.last = self.sampler(logits)
-        return self.sampler.read(self.last)
+            tokens = self.cur if idx is None else self.cur[idx].contiguous()
+            self.cur = self._decode(tokens)
+        self.sampler.post(self.cur)
+        self.ahead = self._launch_ahead()
+        return self.sampler.collect()
 
     def finish(self) -> None:
         for s in self.slots:
             self.engine.release(s)
         self.slots = []
-        self.last = None
+        self.cur = None
+        self.ahead = None
 
 
 class LLM:
@@ -89,6 +128,8 @@ class LLM:
         self.max_batch = max_batch
         self.engine = Engine(model, max_tokens=max_tokens, max_slots=max(max_batch, 1), max_seq=max_context,
                              decode_splits=decode_splits)
+        self.run_ahead = True            # queue each decode step before the host reads the ids of the one before
+        self.last_io: Dict[str, float] = {}
         self._samplers: Dict[tuple, Sampler] = {}
 
     @classmethod
@@ -124,9 +165,14 @@ class LLM:
         up to ``max_batch``, one batch after another."""
         options = options or GenerationOptions()
         options.validate()
-        backend = _Backend(self.engine, self._sampler(options), self.max_batch)
+        backend = _Backend(self.engine, self._sampler(options), self.max_batch, self.run_ahead)
         stops = self.stop_ids if stop_ids is None else list(stop_ids)
-        return generate(backend, prompts, options, stops, on_token, should_cancel)
+        try:
+            return generate(backend, prompts, options, stops, on_token, should_cancel)
+        finally:
+            n = max(backend.decode_steps, 1)
+            self.last_io = {"decode_steps": backend.decode_steps, "h2d_bytes_per_step": backend.h2d_bytes / n,
+                            "d2h_bytes_per_step": backend.d2h_bytes / n}
 
     def evaluate_tokens(self, ids: Sequence[int]) -> np.ndarray:
         """Logits after the last of ``ids`` as a host array (``EvaluateTokens``, LLM.pas:1064-1088)."""

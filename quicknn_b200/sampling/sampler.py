@@ -29,6 +29,10 @@ class Sampler:
         if nbytes < 0:
             raise ValueError("sampling scratch would exceed 2 GiB; lower the batch")
         self.scratch = torch.empty(max(nbytes, 8), dtype=torch.uint8, device=device)
+        self._pinned: Optional[torch.Tensor] = None
+        self._event = None
+        self._posted = 0
+        self.bytes_read = 0
         self.penalised = options.repetition_penalty != 1.0
         self.seen: Optional[torch.Tensor] = None
         if self.penalised:
@@ -67,7 +71,25 @@ class Sampler:
 
     def read(self, tokens: torch.Tensor) -> np.ndarray:
         """Chosen ids and the error word in one device-to-host read."""
-        both = torch.cat([tokens, self.flag]).cpu().numpy()
+        self.post(tokens)
+        return self.collect()
+
+    def post(self, tokens: torch.Tensor) -> None:
+        """Queue the read of ``tokens`` (and the error word) into pinned memory; what is
+        launched after this call does not delay it."""
+        n = tokens.numel()
+        if self._pinned is None:
+            self._pinned = torch.empty(self.max_rows + 1, dtype=torch.int32, pin_memory=True)
+            self._event = torch.cuda.Event()
+        self._pinned[:n + 1].copy_(torch.cat([tokens.reshape(-1), self.flag]), non_blocking=True)
+        self._event.record()
+        self._posted = n
+        self.bytes_read += 4 * (n + 1)
+
+    def collect(self) -> np.ndarray:
+        """Wait for the read queued by ``post`` and return the ids."""
+        self._event.synchronize()
+        both = self._pinned[:self._posted + 1].numpy().copy()
         if both[-1] != 0:
             self.flag.zero_()
             raise NonFiniteLogits("the model produced non-finite logits")

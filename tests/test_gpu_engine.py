@@ -141,6 +141,39 @@ def test_more_requests_than_slots_reuse_them(folders, plain_models):
     assert llm.memory_status()["live_sequences"] == 0
 
 
+def test_running_one_step_ahead_changes_no_token(folders, plain_models):
+    """The entry point queues each decode step before it reads the ids of the one before; rows
+    that end (stop token, budget, full context) are dropped a step late and their extra token is
+    thrown away.  Same tokens, same finish reasons, no slot or page lost, with and without."""
+    from quicknn_b200.engine import LLM
+    from quicknn_b200.sampling import GenerationOptions
+    plain = plain_models("B", "float32")
+    llm = LLM(folders("B", "float32"), max_context=40, max_batch=3, dtype="float32")
+    prompts = prompts_for("B", [3, 30, 9, 1, 22], seed=4)         # 30 and 22 run into the context of 40
+    ref = [plain.greedy(p, 14) for p in prompts]
+    stop = [ref[2][4]]                                            # request 2 ends early; others may too
+    runs = {}
+    for ahead in (True, False):
+        llm.run_ahead = ahead
+        out = llm.generate(prompts, GenerationOptions.greedy(14), stop_ids=stop)
+        runs[ahead] = [(r.tokens, r.finish_reason) for r in out]
+        assert llm.engine.cache.slots.live() == []
+        llm.engine.cache.audit()
+        assert llm.last_io["decode_steps"] > 0
+    assert runs[True] == runs[False]
+    for (toks, why), p, full in zip(runs[True], prompts, ref):
+        want = plain.greedy(p, min(14, 40 - len(p)), stop_ids=stop)
+        assert toks == want, (len(p), why)
+    assert runs[True][1][1] == "context_full" and runs[True][2][1] == "eos"
+    # sampling with a repetition penalty: the generator and the table of seen ids advance alike
+    opt = GenerationOptions(max_new_tokens=10, temperature=0.9, top_k=8, repetition_penalty=1.3, seed=7)
+    llm.run_ahead = True
+    a = [r.tokens for r in llm.generate(prompts, opt, stop_ids=stop)]
+    llm.run_ahead = False
+    b = [r.tokens for r in llm.generate(prompts, opt, stop_ids=stop)]
+    assert a == b
+
+
 def test_temperature_sampling_is_seeded_and_follows_the_plain_sampler(folders, plain_models):
     from quicknn_b200.engine import LLM
     from quicknn_b200.sampling import GenerationOptions
