@@ -4,7 +4,8 @@
 //
 // A CTA owns 128 query rows of one sequence and one query head and walks over 64-key tiles:
 //   warp 0 (one lane)  TMA producer: Q once (four 128 x 64 boxes), then K and V tiles (four 64 x 64
-//                      boxes each) into a 2-stage ring; everything 128-byte swizzled.
+//                      boxes each) into two 2-stage rings (a K stage is free once S has been formed, a V
+//                      stage only after the second product); everything 128-byte swizzled.
 //   warp 1 (one lane)  tensor-core issue:  S_j[128 x 64] = Q K_j^T   (16 tcgen05.mma, K-major operands)
 //                                           O[128 x 256] += P_j V_j   ( 4 tcgen05.mma, V as MN-major operand)
 //                      S_{j+1} is issued before P_j V_j, so it runs while the softmax of tile j does.
@@ -127,8 +128,10 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 
 struct __align__(8) Barriers {
     uint64_t q_full;
-    uint64_t kv_full[KV_STAGES];
-    uint64_t kv_empty[KV_STAGES];
+    uint64_t k_full[KV_STAGES];
+    uint64_t k_empty[KV_STAGES];   // S_j has read K_j
+    uint64_t v_full[KV_STAGES];
+    uint64_t v_empty[KV_STAGES];   // O += P_j V_j has read V_j
     uint64_t s_ready[2];      // S_j is complete in tensor memory
     uint64_t p_ready[2];      // P_j is in shared memory and O has been corrected
     uint64_t pv_done[2];      // O += P_j V_j has completed
@@ -167,8 +170,10 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     if (threadIdx.x == 0) {
         mbar_init(smem_u32(&bars->q_full), 1);
         for (int s = 0; s < KV_STAGES; ++s) {
-            mbar_init(smem_u32(&bars->kv_full[s]), 1);
-            mbar_init(smem_u32(&bars->kv_empty[s]), 1);
+            mbar_init(smem_u32(&bars->k_full[s]), 1);
+            mbar_init(smem_u32(&bars->k_empty[s]), 1);
+            mbar_init(smem_u32(&bars->v_full[s]), 1);
+            mbar_init(smem_u32(&bars->v_empty[s]), 1);
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(smem_u32(&bars->s_ready[i]), 1);
@@ -196,21 +201,50 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             for (int d = 0; d < HD / 64; ++d)
                 tma_load_2d(smem_u32(sQ + d * (BM * 128)), &map_q, qf, h * HD + d * 64, row0 + r0);
             const int kx = (nq + kh) * HD, vx = (nq + nkv + kh) * HD;     // columns of K and V in the qkv rows
+            // K_j is free again as soon as S_j has been formed, V_j only after O += P_j V_j: two rings, so
+            // that the next keys are on their way while the softmax of this tile has not even begun
             for (int j = 0; j < nt; ++j) {
                 const int s = j % KV_STAGES;
-                if (j >= KV_STAGES && !mbar_wait(smem_u32(&bars->kv_empty[s]), ((j / KV_STAGES) - 1) & 1)) {
+                const unsigned par = ((j / KV_STAGES) - 1) & 1;
+                unsigned char* kdst = sKV + s * (K_BYTES + V_BYTES);
+                const int y = row0 + (jt0 + j) * BN;
+                if (j >= KV_STAGES && !mbar_wait(smem_u32(&bars->k_empty[s]), par)) {
                     atomicOr(status, 16);
                     bars->failed = 1;
                     break;
                 }
-                const unsigned full = smem_u32(&bars->kv_full[s]);
-                unsigned char* kdst = sKV + s * (K_BYTES + V_BYTES);
-                unsigned char* vdst = kdst + K_BYTES;
-                const int y = row0 + (jt0 + j) * BN;
-                mbar_expect_tx(full, K_BYTES + V_BYTES);
-                for (int d = 0; d < HD / 64; ++d) {
-                    tma_load_2d(smem_u32(kdst + d * (BN * 128)), &map_kv, full, kx + d * 64, y);
-                    tma_load_2d(smem_u32(vdst + d * (BN * 128)), &map_kv, full, vx + d * 64, y);
+                const unsigned kfull = smem_u32(&bars->k_full[s]);
+                mbar_expect_tx(kfull, K_BYTES);
+                for (int d = 0; d < HD / 64; ++d)
+                    tma_load_2d(smem_u32(kdst + d * (BN * 128)), &map_kv, kfull, kx + d * 64, y);
+                // the values of the tile before: their stage was freed a product earlier
+                if (j >= 1) {
+                    const int jv = j - 1, sv = jv % KV_STAGES;
+                    if (jv >= KV_STAGES && !mbar_wait(smem_u32(&bars->v_empty[sv]), ((jv / KV_STAGES) - 1) & 1)) {
+                        atomicOr(status, 16);
+                        bars->failed = 1;
+                        break;
+                    }
+                    const unsigned vfull = smem_u32(&bars->v_full[sv]);
+                    unsigned char* vd = sKV + sv * (K_BYTES + V_BYTES) + K_BYTES;
+                    mbar_expect_tx(vfull, V_BYTES);
+                    for (int d = 0; d < HD / 64; ++d)
+                        tma_load_2d(smem_u32(vd + d * (BN * 128)), &map_kv, vfull, vx + d * 64, row0 + (jt0 + jv) * BN);
+                }
+            }
+            if (!has_failed(bars)) {          // the values of the last tile
+                const int jv = nt - 1, sv = jv % KV_STAGES;
+                bool ok = true;
+                if (jv >= KV_STAGES) ok = mbar_wait(smem_u32(&bars->v_empty[sv]), ((jv / KV_STAGES) - 1) & 1);
+                if (!ok) {
+                    atomicOr(status, 16);
+                    bars->failed = 1;
+                } else {
+                    const unsigned vfull = smem_u32(&bars->v_full[sv]);
+                    unsigned char* vd = sKV + sv * (K_BYTES + V_BYTES) + K_BYTES;
+                    mbar_expect_tx(vfull, V_BYTES);
+                    for (int d = 0; d < HD / 64; ++d)
+                        tma_load_2d(smem_u32(vd + d * (BN * 128)), &map_kv, vfull, vx + d * 64, row0 + (jt0 + jv) * BN);
                 }
             }
         }
@@ -232,10 +266,11 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     for (int k = 0; k < 64 / UMMA_K; ++k)
                         umma_bf16(acc, umma_desc(qaddr + d * (BM * 128) + k * 32, 16, 1024),
                                   umma_desc(kaddr + d * (BN * 128) + k * 32, 16, 1024), idesc_s, (d > 0 || k > 0) ? 1u : 0u);
+                umma_commit(smem_u32(&bars->k_empty[j % KV_STAGES]));
                 umma_commit(smem_u32(&bars->s_ready[j & 1]));
             };
             if (ok) {
-                ok = mbar_wait(smem_u32(&bars->kv_full[0]), 0);
+                ok = mbar_wait(smem_u32(&bars->k_full[0]), 0);
                 if (!ok) { atomicOr(status, 2); bars->failed = 1; }
             }
             if (ok) {
@@ -244,7 +279,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             }
             for (int j = 0; j < nt && ok; ++j) {
                 if (j + 1 < nt) {
-                    ok = mbar_wait(smem_u32(&bars->kv_full[(j + 1) % KV_STAGES]), ((j + 1) / KV_STAGES) & 1);
+                    ok = mbar_wait(smem_u32(&bars->k_full[(j + 1) % KV_STAGES]), ((j + 1) / KV_STAGES) & 1);
                     if (!ok) { atomicOr(status, 2); bars->failed = 1; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     issue_s(j + 1);
@@ -252,6 +287,8 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 ok = mbar_wait(smem_u32(&bars->p_ready[j & 1]), (j >> 1) & 1);
                 if (!ok) { atomicOr(status, 8); bars->failed = 1; break; }
                 if (has_failed(bars)) break;
+                ok = mbar_wait(smem_u32(&bars->v_full[j % KV_STAGES]), (j / KV_STAGES) & 1);
+                if (!ok) { atomicOr(status, 2); bars->failed = 1; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const unsigned vaddr = smem_u32(sKV + (j % KV_STAGES) * (K_BYTES + V_BYTES) + K_BYTES);
                 const unsigned paddr = smem_u32(sP + (j & 1) * P_BYTES);
@@ -261,7 +298,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     // 16 keys further = 16 rows of 128 bytes; the four 64-dim blocks are BN*128 bytes apart.
                     umma_bf16(tmem + O_COL, umma_desc(paddr + k * 32, 16, 1024),
                               umma_desc(vaddr + k * UMMA_K * 128, BN * 128, 1024), idesc_o, (j > 0 || k > 0) ? 1u : 0u);
-                umma_commit(smem_u32(&bars->kv_empty[j % KV_STAGES]));
+                umma_commit(smem_u32(&bars->v_empty[j % KV_STAGES]));
                 umma_commit(smem_u32(&bars->pv_done[j & 1]));
             }
         }
@@ -272,7 +309,9 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const int row = r0 + rloc;                            // position in the sequence
         const unsigned lane_base = tmem + ((unsigned)(quarter * 32) << 16);
         const float LOG2E = 1.4426950408889634f;
-        const float inv_cap = cap > 0.f ? 1.f / cap : 0.f;
+        const float k1 = cap > 0.f ? scale / cap : scale;
+        const float k2 = (cap > 0.f ? cap : 1.f) * LOG2E;
+        const float step = RESCALE_STEP / (cap > 0.f ? cap : 1.f);   // a growth of the maximum by 8 in the exponent
         float m_used = 0.f, m_run = -CUDART_INF_F, l_sum = 0.f;
         bool alive = true;
         for (int j = 0; j < nt && alive; ++j) {
@@ -295,35 +334,50 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
                 for (int c = 0; c < 32; ++c) s[32 + c] = __uint_as_float(v[c]);
             }
+            // Scores in the unit the maximum is tracked in: tanh(score / cap) with a softcap (the clamp of
+            // its argument to +-20 changes nothing: tanh.approx saturates), the scaled score without;
+            // either times k2 is the exponent to base 2.  Tiles wholly inside every row's range of keys
+            // skip the mask.
             const int col0 = (jt0 + j) * BN;
-            float mx = -CUDART_INF_F;
+            const bool interior = col0 + BN - 1 <= r0 && col0 + BN - 1 < len && (window <= 0 || col0 > r0 + BM - 1 - window);
+            float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+            if (interior) {
 #pragma unroll
-            for (int c = 0; c < BN; ++c) {
-                const int col = col0 + c;
-                float x = s[c] * scale;
-                if (cap > 0.f) x = cap * tanh_fast(fminf(fmaxf(x * inv_cap, -20.f), 20.f));
-                const bool seen = col <= row && col < len && (window <= 0 || col > row - window);
-                x = seen ? x : -CUDART_INF_F;
-                s[c] = x;
-                mx = fmaxf(mx, x);
+                for (int c = 0; c < BN; ++c) {
+                    const float x = cap > 0.f ? tanh_fast(s[c] * k1) : s[c] * k1;
+                    s[c] = x;
+                    mx4[c & 3] = fmaxf(mx4[c & 3], x);
+                }
+            } else {
+#pragma unroll
+                for (int c = 0; c < BN; ++c) {
+                    const int col = col0 + c;
+                    float x = cap > 0.f ? tanh_fast(s[c] * k1) : s[c] * k1;
+                    const bool seen = col <= row && col < len && (window <= 0 || col > row - window);
+                    x = seen ? x : -CUDART_INF_F;
+                    s[c] = x;
+                    mx4[c & 3] = fmaxf(mx4[c & 3], x);
+                }
             }
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             m_run = fmaxf(m_run, mx);
             float corr = 1.f;
             bool rescale = false;
-            if (m_run != -CUDART_INF_F && (j == 0 || m_run > m_used + RESCALE_STEP || l_sum == 0.f)) {
+            if (m_run != -CUDART_INF_F && (j == 0 || m_run > m_used + step || l_sum == 0.f)) {
                 // take the exponentials against the new maximum from here on
-                corr = (l_sum == 0.f) ? 0.f : exp2_fast((m_used - m_run) * LOG2E);
+                corr = (l_sum == 0.f) ? 0.f : exp2_fast((m_used - m_run) * k2);
                 rescale = (j > 0);
                 m_used = m_run;
             }
-            float rs = 0.f;
-            const float moff = m_used * LOG2E;
+            const float moff = m_used * k2;
+            float rs4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int c = 0; c < BN; ++c) {
-                const float p = exp2_fast(fmaf(s[c], LOG2E, -moff));      // exp(-inf) = 0 for masked keys
+                const float p = exp2_fast(fmaf(s[c], k2, -moff));         // exp(-inf) = 0 for masked keys
                 s[c] = p;
-                rs += p;
+                rs4[c & 3] += p;
             }
+            const float rs = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
             l_sum = l_sum * corr + rs;
             // P_j overwrites the buffer that P_{j-2} V_{j-2} read; O may only be touched once P_{j-1} V_{j-1} is done
             if (j >= 2 && !mbar_wait_warp(smem_u32(&bars->pv_done[bsel]), ((j >> 1) - 1) & 1)) {
