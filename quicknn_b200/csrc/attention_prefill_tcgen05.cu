@@ -97,8 +97,8 @@ __device__ __forceinline__ void tmem_ld32(unsigned taddr, uint32_t (&r)[32]) {
           "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
           "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_st32(unsigned taddr, const uint32_t (&r)[32]) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
@@ -313,6 +313,10 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const float k2 = (cap > 0.f ? cap : 1.f) * LOG2E;
         const float step = RESCALE_STEP / (cap > 0.f ? cap : 1.f);   // a growth of the maximum by 8 in the exponent
         float m_used = 0.f, m_run = -CUDART_INF_F, l_sum = 0.f;
+        // the keys this row sees: key_lo .. key_hi (none when the row lies beyond the sequence)
+        const int key_hi = min(row, len - 1);
+        const int key_lo = (window > 0 && row - window + 1 > 0) ? row - window + 1 : 0;
+        const unsigned key_span = key_hi >= key_lo ? (unsigned)(key_hi - key_lo) : 0u;
         bool alive = true;
         for (int j = 0; j < nt && alive; ++j) {
             const int bsel = j & 1;
@@ -326,13 +330,14 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             float s[BN];
             {
-                uint32_t v[32];
-                tmem_ld32(lane_base + S_COL + bsel * BN, v);
+                uint32_t v0[32], v1[32];
+                tmem_ld32(lane_base + S_COL + bsel * BN, v0);
+                tmem_ld32(lane_base + S_COL + bsel * BN + 32, v1);
+                tmem_ld_wait();
 #pragma unroll
-                for (int c = 0; c < 32; ++c) s[c] = __uint_as_float(v[c]);
-                tmem_ld32(lane_base + S_COL + bsel * BN + 32, v);
+                for (int c = 0; c < 32; ++c) s[c] = __uint_as_float(v0[c]);
 #pragma unroll
-                for (int c = 0; c < 32; ++c) s[32 + c] = __uint_as_float(v[c]);
+                for (int c = 0; c < 32; ++c) s[32 + c] = __uint_as_float(v1[c]);
             }
             // Scores in the unit the maximum is tracked in: tanh(score / cap) with a softcap (the clamp of
             // its argument to +-20 changes nothing: tanh.approx saturates), the scaled score without;
@@ -351,9 +356,8 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             } else {
 #pragma unroll
                 for (int c = 0; c < BN; ++c) {
-                    const int col = col0 + c;
                     float x = cap > 0.f ? tanh_fast(s[c] * k1) : s[c] * k1;
-                    const bool seen = col <= row && col < len && (window <= 0 || col > row - window);
+                    const bool seen = (unsigned)(col0 + c - key_lo) <= key_span;      // key_lo <= column <= key_hi
                     x = seen ? x : -CUDART_INF_F;
                     s[c] = x;
                     mx4[c & 3] = fmaxf(mx4[c & 3], x);
@@ -379,13 +383,9 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             }
             const float rs = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
             l_sum = l_sum * corr + rs;
-            // P_j overwrites the buffer that P_{j-2} V_{j-2} read; O may only be touched once P_{j-1} V_{j-1} is done
-            if (j >= 2 && !mbar_wait_warp(smem_u32(&bars->pv_done[bsel]), ((j >> 1) - 1) & 1)) {
-                atomicOr(status, 64);
-                bars->failed = 1;
-                alive = false;
-                break;
-            }
+            // P_j overwrites the buffer that P_{j-2} V_{j-2} read.  That product was issued before S_j and
+            // the commit behind S_j covers everything issued before it, so s_ready[j] already said that it
+            // is done.  (O may only be touched once P_{j-1} V_{j-1} is done: see the rescale below.)
             {
                 unsigned char* prow = sP + bsel * P_BYTES + rloc * 128;
 #pragma unroll
@@ -411,6 +411,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 for (int c0 = 0; c0 < HD; c0 += 32) {
                     uint32_t v[32];
                     tmem_ld32(lane_base + O_COL + c0, v);
+                    tmem_ld_wait();
 #pragma unroll
                     for (int c = 0; c < 32; ++c) v[c] = __float_as_uint(__uint_as_float(v[c]) * f);
                     tmem_st32(lane_base + O_COL + c0, v);
@@ -431,21 +432,44 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 alive = false;
             }
         }
-        if (alive && !__any_sync(0xffffffffu, has_failed(bars))) {
+        // Every product is done, so the Q tile's shared memory is free: each thread leaves its row there as
+        // bfloat16 (16-byte chunks XOR-ed with the row number, so that neither side conflicts), and the
+        // warps then write whole 512-byte rows to global memory.
+        const bool good = alive && !__any_sync(0xffffffffu, has_failed(bars));
+        if (good) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
-            bf16* dst = out + (size_t)(row0 + row) * out_stride + (size_t)h * HD;
+            unsigned char* orow = sQ + rloc * (HD * 2);
 #pragma unroll 1
-            for (int c0 = 0; c0 < HD; c0 += 32) {
-                uint32_t v[32];
-                tmem_ld32(lane_base + O_COL + c0, v);
-                if (row < len) {
-                    float f[32];
+            for (int c0 = 0; c0 < HD; c0 += 64) {
+                uint32_t v0[32], v1[32];
+                tmem_ld32(lane_base + O_COL + c0, v0);
+                tmem_ld32(lane_base + O_COL + c0 + 32, v1);
+                tmem_ld_wait();
 #pragma unroll
-                    for (int c = 0; c < 32; ++c) f[c] = __uint_as_float(v[c]) * inv;
-#pragma unroll
-                    for (int c = 0; c < 32; c += 8) Vec16<bf16>::store(dst + c0 + c, f + c);
+                for (int c8 = 0; c8 < 4; ++c8) {
+                    uint4 pk;
+                    pk.x = pack_bf16(__uint_as_float(v0[c8 * 8 + 0]) * inv, __uint_as_float(v0[c8 * 8 + 1]) * inv);
+                    pk.y = pack_bf16(__uint_as_float(v0[c8 * 8 + 2]) * inv, __uint_as_float(v0[c8 * 8 + 3]) * inv);
+                    pk.z = pack_bf16(__uint_as_float(v0[c8 * 8 + 4]) * inv, __uint_as_float(v0[c8 * 8 + 5]) * inv);
+                    pk.w = pack_bf16(__uint_as_float(v0[c8 * 8 + 6]) * inv, __uint_as_float(v0[c8 * 8 + 7]) * inv);
+                    *reinterpret_cast<uint4*>(orow + (((c0 / 8 + c8) ^ (rloc & 31)) << 4)) = pk;
+                    pk.x = pack_bf16(__uint_as_float(v1[c8 * 8 + 0]) * inv, __uint_as_float(v1[c8 * 8 + 1]) * inv);
+                    pk.y = pack_bf16(__uint_as_float(v1[c8 * 8 + 2]) * inv, __uint_as_float(v1[c8 * 8 + 3]) * inv);
+                    pk.z = pack_bf16(__uint_as_float(v1[c8 * 8 + 4]) * inv, __uint_as_float(v1[c8 * 8 + 5]) * inv);
+                    pk.w = pack_bf16(__uint_as_float(v1[c8 * 8 + 6]) * inv, __uint_as_float(v1[c8 * 8 + 7]) * inv);
+                    *reinterpret_cast<uint4*>(orow + (((c0 / 8 + 4 + c8) ^ (rloc & 31)) << 4)) = pk;
                 }
+            }
+        }
+        __syncwarp();      // a warp stores the 32 rows that its own lanes wrote
+        if (good) {
+            for (int rr = 0; rr < 32; ++rr) {
+                const int rl = quarter * 32 + rr;
+                if (r0 + rl >= len) break;
+                const uint4 pk = *reinterpret_cast<const uint4*>(sQ + rl * (HD * 2) + (lane << 4));
+                bf16* dst = out + (size_t)(row0 + r0 + rl) * out_stride + (size_t)h * HD + ((lane ^ (rl & 31)) << 3);
+                *reinterpret_cast<uint4*>(dst) = pk;
             }
         }
     }
