@@ -252,9 +252,15 @@ def check_gemm_status(device) -> None:
                                f"issue, 4 epilogue); its result is not valid")
 
 
-def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, *, epilogue: int = EPI_NONE, activation: str = "gelu_tanh"):
+GEMM_2CTA = os.environ.get("QNN_GEMM_2CTA", "1") != "0"
+
+
+def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, *, epilogue: int = EPI_NONE, activation: str = "gelu_tanh",
+                 pair: Optional[bool] = None):
     """x w^T for whole prompts on the 5th-generation tensor cores (bfloat16, any M; K a multiple of 8).
-    Epilogues: none, or gated (w = [gate; up] stacked).  Returns None when the sizes are refused."""
+    Epilogues: none, or gated (w = [gate; up] stacked).  With more than 128 rows pairs of CTAs
+    compute 256 x 256 tiles (``pair``; QNN_GEMM_2CTA=0 keeps one CTA per tile).  Returns None when
+    the sizes are refused."""
     _req(x, "x", torch.bfloat16, 2)
     _req(w, "w", torch.bfloat16, 2)
     M, K = x.shape
@@ -264,6 +270,14 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, *, epilogue: int = EPI_NONE, 
     n_out = N // 2 if epilogue == EPI_GATED else N
     out = torch.empty((M, n_out), dtype=torch.bfloat16, device=x.device)
     L = _lib.load()
+    if pair is None:
+        pair = GEMM_2CTA and M > 128
+    if pair:
+        code = L.qnn_gemm_tcgen05_2cta(_p(x), _p(w), _p(out), M, N, K, epilogue, ACT_CODES[activation],
+                                       _p(_status_word(x.device)), _stream())
+        if code != _lib.ERR_UNSUPPORTED:
+            _lib.check(code, "gemm_tcgen05_2cta")
+            return out
     code = L.qnn_gemm_tcgen05(_p(x), _p(w), _p(out), M, N, K, epilogue, ACT_CODES[activation],
                               _p(_status_word(x.device)), _stream())
     if code == _lib.ERR_UNSUPPORTED:

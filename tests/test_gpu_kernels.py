@@ -147,11 +147,16 @@ def test_bf16_large_m_library_product_with_epilogues(ops, M):
     assert_close(y, P.softcap(bf16_round(ref), 3.0), torch.float32, "gemm softcap", mult=4000)
 
 
+@pytest.mark.parametrize("pair", [False, True])
 @pytest.mark.parametrize("M,N_,K", [(65, 24, 8), (128, 256, 64), (200, 300, 96), (130, 1000, 200), (300, 2304, 2304),
-                                     (2048, 512, 4160), (1, 40, 72)])
-def test_tcgen05_product(ops, M, N_, K):
-    """The TMA + tcgen05 kernel alone: tiles that are cut by every edge (M, N, K not multiples of
-    128, 256, 64), one slab and many, plain and gated epilogue."""
+                                     (2048, 512, 4160), (1, 40, 72), (700, 5000, 520)])
+def test_tcgen05_product(ops, M, N_, K, pair):
+    """The TMA + tcgen05 kernels alone (one CTA per 128 x 256 tile, and a pair of CTAs per 256 x 256
+    tile): tiles that are cut by every edge (M, N, K not multiples of 128 or 256, 256, 64; an odd
+    number of 128-row tiles), one slab and many, more tiles than CTAs, plain and gated epilogue."""
+    import functools
+    ops = type("O", (), {k: getattr(ops, k) for k in dir(ops) if not k.startswith("__")})
+    ops.gemm_tcgen05 = staticmethod(functools.partial(ops.gemm_tcgen05, pair=pair))
     rng = np.random.default_rng(M + N_ + K)
     x, w = bf16_round(rng.normal(size=(M, K))), bf16_round(rng.normal(size=(N_, K)) / math.sqrt(K))
     ref = x @ w.T
