@@ -124,7 +124,6 @@ __global__ void __launch_bounds__(THREADS)
 gemm_skinny_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                            void* __restrict__ C, int M, int N, int K, int KS, float cap, int act,
                            int* __restrict__ status) {
-    pdl_wait();
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     float* part = reinterpret_cast<float*>(smem + STAGES * STAGE_BYTES);        // [BM][PART_LD], rows < M used
@@ -157,6 +156,9 @@ gemm_skinny_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const unsigned tmem = bars->tmem_base;
+    // Barriers and tensor memory are set up; only now wait for the kernels before this one (whose output
+    // the loads below read), so that the set-up overlaps their tail.
+    pdl_wait();
 
     if (warp == 0) {
         if (lane == 0) {

@@ -116,7 +116,6 @@ template <int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     bf16* __restrict__ C, int M, int N, int K, int act, int* __restrict__ status) {
-    pdl_wait();
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     // the operand ring wants 1024-byte alignment (8 swizzled rows); the barriers follow it
     unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -149,6 +148,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const unsigned tmem = bars->tmem_base;
+    // Barriers and tensor memory are set up; only now wait for the kernels before this one (whose output
+    // the loads below read), so that the set-up overlaps their tail.
+    pdl_wait();
 
     if (warp == 0) {
         if (lane == 0) {

@@ -15,6 +15,8 @@
 //   * tcgen05.commit.cta_group::2 with a CTA mask hands a stage back to both producers and, after the
 //     last slab, an accumulator to the epilogue warps of both CTAs, each of which drains its own 128
 //     rows; they return the accumulator with remote arrivals on the leader's barrier;
+//   * the epilogue goes through shared memory (128 rows x 128 columns at a time) so that global memory
+//     is written in whole 256-byte row pieces;
 //   * tensor memory is allocated and freed with the .cta_group::2 forms by the same warp of both CTAs,
 //     with cluster barriers after set-up and before the release.
 // For the gated epilogue rank 0 loads the 128 gate rows and rank 1 the 128 matching up rows, so every
@@ -35,6 +37,7 @@ namespace {
 constexpr int BM = 128, BN = 256, BK = 64, STAGES = 6, UMMA_K = 16;       // BM: rows per CTA; the pair does 256
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = (BN / 2) * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;   // per CTA
 constexpr int TMEM_COLS = 256;
+constexpr int STAGING_BYTES = BM * 128 * 2;          // the epilogue's 128 rows x 128 columns of bfloat16
 constexpr int GEMM_THREADS = 192;
 constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;   // SM clock cycles before a wait gives up
 
@@ -119,6 +122,11 @@ __device__ __forceinline__ void tmem_ld32(unsigned taddr, uint32_t (&r)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+
 struct __align__(8) Barriers {
     uint64_t full[STAGES];      // leader only: the slabs of both CTAs have landed (TMA bytes)
     uint64_t empty[STAGES];     // in each CTA: the MMAs that read the stage are done
@@ -136,10 +144,10 @@ template <int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS)
 gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                          bf16* __restrict__ C, int M, int N, int K, int act, int* __restrict__ status) {
-    pdl_wait();
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    Barriers* bars = reinterpret_cast<Barriers*>(smem + STAGES * STAGE_BYTES);
+    unsigned char* staging = smem + STAGES * STAGE_BYTES;
+    Barriers* bars = reinterpret_cast<Barriers*>(staging + STAGING_BYTES);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const unsigned rank = cluster_rank();                 // 0: leader
     const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
@@ -171,6 +179,9 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     cluster_barrier();           // the peer's barriers exist before anything is sent to them
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const unsigned tmem = bars->tmem_base;
+    // Barriers and tensor memory are set up; only now wait for the kernels before this one (whose output
+    // the loads below read), so that the set-up overlaps their tail.
+    pdl_wait();
 
     if (warp == 0) {
         if (lane == 0) {
@@ -251,6 +262,59 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int m = m0 + quarter * 32 + lane;
             const unsigned lane_addr = tmem + a * TMEM_COLS + ((unsigned)(quarter * 32) << 16);
+            if ((Nout & 7) == 0) {
+                // Through shared memory, 128 columns at a time: each thread leaves its row as bfloat16
+                // (16-byte chunks XOR-ed with the row number, so that neither side has bank conflicts), then
+                // the warp writes its 32 rows to global memory two rows (2 x 256 bytes) per instruction.
+                // A thread-per-row store straight from registers touches 32 lines per instruction and made
+                // the epilogue 4.4 us of a 19 us product.
+                unsigned char* mine = staging + quarter * (32 * 256);
+#pragma unroll 1
+                for (int h0 = 0; h0 < OUT_COLS; h0 += 128) {
+#pragma unroll 1
+                    for (int c0 = h0; c0 < h0 + 128; c0 += 32) {
+                        uint32_t v[32];
+                        tmem_ld32(lane_addr + c0, v);
+                        float f[32];
+                        if (EPI == EPI_GATED) {
+                            uint32_t u[32];
+                            tmem_ld32(lane_addr + BN / 2 + c0, u);
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) f[j] = activate_fast(__uint_as_float(v[j]), act) * __uint_as_float(u[j]);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+                        }
+                        if (c0 + 32 >= OUT_COLS) {
+                            // the last columns are in registers: hand the accumulator back to the leader
+                            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive_cluster(map_to_rank(smem_u32(&bars->acc_free[a]), 0));
+                        }
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const int ch = (c0 - h0) / 8 + j;
+                            uint4 pk;
+                            pk.x = pack_bf16(f[j * 8 + 0], f[j * 8 + 1]);
+                            pk.y = pack_bf16(f[j * 8 + 2], f[j * 8 + 3]);
+                            pk.z = pack_bf16(f[j * 8 + 4], f[j * 8 + 5]);
+                            pk.w = pack_bf16(f[j * 8 + 6], f[j * 8 + 7]);
+                            *reinterpret_cast<uint4*>(mine + lane * 256 + ((ch ^ (lane & 15)) << 4)) = pk;
+                        }
+                    }
+                    __syncwarp();
+#pragma unroll 4
+                    for (int rr = 0; rr < 32; rr += 2) {
+                        const int r = rr + (lane >> 4), pos = lane & 15;
+                        const int row = m0 + quarter * 32 + r;
+                        const int col = n0 + h0 + ((pos ^ (r & 15)) << 3);
+                        const uint4 pk = *reinterpret_cast<const uint4*>(mine + r * 256 + (pos << 4));
+                        if (row < M && col < Nout) *reinterpret_cast<uint4*>(C + (size_t)row * Nout + col) = pk;
+                    }
+                    __syncwarp();
+                }
+                continue;
+            }
 #pragma unroll 1
             for (int c0 = 0; c0 < OUT_COLS; c0 += 32) {
                 uint32_t v[32];
@@ -349,7 +413,7 @@ QNN_API int qnn_gemm_tcgen05_2cta(const void* A, const void* B, void* C, int M, 
     }
     const long long ntiles = (long long)((M + 2 * BM - 1) / (2 * BM)) * ((Nout + cols - 1) / cols);
     if (ntiles > 0x3fffffffLL) return QNN_ERR_UNSUPPORTED;
-    const size_t smem = (size_t)STAGES * STAGE_BYTES + sizeof(Barriers) + 1024;
+    const size_t smem = (size_t)STAGES * STAGE_BYTES + STAGING_BYTES + sizeof(Barriers) + 1024;
     void (*kern)(CUtensorMap, CUtensorMap, bf16*, int, int, int, int, int*) =
         epi == EPI_GATED ? gemm_tcgen05_2cta_kernel<EPI_GATED> : gemm_tcgen05_2cta_kernel<EPI_NONE>;
     static bool configured[2] = {false, false};
