@@ -499,12 +499,17 @@ attn_decode_tiled_kernel(const T* __restrict__ q, size_t q_stride, const T* __re
                                  n_splits, part_o, part_ml);
 }
 
-// out[b, h, :] = sum_s e^{m_s - M} O_s / sum_s e^{m_s - M} l_s, splits in ascending order.
+// out[b, h, :] = sum_s e^{m_s - M} O_s / sum_s e^{m_s - M} l_s.  The block is cut into G groups of hd/4
+// threads; group g adds up splits g, g + G, g + 2G, ... (four head elements per thread, 16-byte loads that
+// do not wait for one another), and the G partial sums are added in ascending order of g: an order that
+// depends on the number of splits and the head size only.
 template <typename T>
 __global__ void attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                     T* __restrict__ out, size_t out_stride, int nq, int hd, int n_splits) {
     pdl_wait();
-    extern __shared__ float coef[];  // [n_splits] weights of the splits, then 1/sum
+    extern __shared__ __align__(16) float comb[];  // [G][hd] partial sums, then [n_splits] weights and 1/sum
+    const int lpg = hd / 4, G = max(1, min((int)blockDim.x / lpg, n_splits));
+    float* coef = comb + (size_t)G * hd;
     const int b = blockIdx.x / nq, h = blockIdx.x % nq;
     const size_t pbase = ((size_t)b * nq + h) * n_splits;
     if (threadIdx.x < 32) {
@@ -523,10 +528,25 @@ __global__ void attn_combine_kernel(const float* __restrict__ part_o, const floa
         }
     }
     __syncthreads();
+    const int g = threadIdx.x / lpg, c = (threadIdx.x % lpg) * 4;
+    if (g < G) {
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+        for (int s = g; s < n_splits; s += G) {
+            const float w = coef[s];
+            const float4 v = *reinterpret_cast<const float4*>(part_o + (pbase + s) * hd + c);
+            acc.x += w * v.x;
+            acc.y += w * v.y;
+            acc.z += w * v.z;
+            acc.w += w * v.w;
+        }
+        *reinterpret_cast<float4*>(comb + (size_t)g * hd + c) = acc;
+    }
+    __syncthreads();
     const float inv = coef[n_splits];
     for (int d = threadIdx.x; d < hd; d += blockDim.x) {
         float acc = 0.f;
-        for (int s = 0; s < n_splits; ++s) acc += coef[s] * part_o[(pbase + s) * hd + d];
+        for (int gg = 0; gg < G; ++gg) acc += comb[(size_t)gg * hd + d];
         out[(size_t)b * out_stride + (size_t)h * hd + d] = from_f<T>(acc * inv);
     }
 }
@@ -646,6 +666,14 @@ extern "C" int qnn_attn_decode_mma_split(const void* q, long long q_stride, cons
                                          int n_splits, void* out, long long out_stride, int* combined,
                                          cudaStream_t st);
 
+// groups of the combine kernel's block of 256 threads (see attn_combine_kernel)
+static int combine_groups(int hd, int n_splits) {
+    const int lpg = hd / 4;
+    int g = lpg > 0 ? 256 / lpg : 1;
+    if (g > n_splits) g = n_splits;
+    return g < 1 ? 1 : g;
+}
+
 template <typename T>
 static int decode_launch(const void* q, long long q_stride, const void* k_pool, const void* v_pool,
                          const int* page_table, int max_pages, int page_size, int ring, const int* slots,
@@ -702,7 +730,7 @@ static int decode_launch(const void* q, long long q_stride, const void* k_pool, 
 #undef QNN_DEC_ARGS
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
-    qnn::launch_pdl(attn_combine_kernel<T>, dim3(B * nq), dim3(hd >= 256 ? 256 : 128), (n_splits + 1) * sizeof(float), st, part_o, part_ml, (T*)out, (size_t)out_stride, nq, hd, n_splits);
+    qnn::launch_pdl(attn_combine_kernel<T>, dim3(B * nq), dim3(256), ((size_t)combine_groups(hd, n_splits) * hd + n_splits + 1) * sizeof(float), st, part_o, part_ml, (T*)out, (size_t)out_stride, nq, hd, n_splits);
     QNN_LAUNCH_CHECK();
 }
 
