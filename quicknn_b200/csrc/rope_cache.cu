@@ -104,6 +104,15 @@ __global__ void rope_cache_vec_kernel(T* __restrict__ qkv, int nq, int nkv, int 
         cache_base = ((size_t)page * nkv * page_size + (r % page_size)) * hd;
     }
     const size_t head_stride = (size_t)page_size * hd;
+    // The angles depend on the position and the pair only, not on the head: the block forms each
+    // (cos, sin) once (sincosf is the expensive part of this kernel) and every head reads it.
+    extern __shared__ float2 angles[];             // [rh]
+    for (int j = threadIdx.x; j < rh; j += blockDim.x) {
+        float sn, cs;
+        sincosf((float)pos * inv_freq[j], &sn, &cs);
+        angles[j] = make_float2(cs, sn);
+    }
+    __syncthreads();
     const int rc = rh / VEC;                       // rotating items per head
     const int pc = (hd - rot) / VEC;               // pass-through items per kv head
     const int vc = hd / VEC;                       // value items per kv head
@@ -121,8 +130,7 @@ __global__ void rope_cache_vec_kernel(T* __restrict__ qkv, int nq, int nkv, int 
             bv.unpack(b);
 #pragma unroll
             for (int e = 0; e < VEC; ++e) {
-                float sn, cs;
-                sincosf((float)pos * inv_freq[j + e], &sn, &cs);
+                const float cs = angles[j + e].x, sn = angles[j + e].y;
                 ra[e] = a[e] * cs - b[e] * sn;
                 rb[e] = a[e] * sn + b[e] * cs;
             }
@@ -159,11 +167,11 @@ QNN_API int qnn_rope_cache_write(void* qkv, int dtype, int T, int nq, int nkv, i
         const int items = (nq + nkv) * (rot / 2) / vec + nkv * (hd - rot) / vec + nkv * hd / vec;
         const int threads = items >= 256 ? 256 : (items >= 128 ? 128 : 64);
         if (dtype == QNN_DT_BF16)
-            qnn::launch_pdl(rope_cache_vec_kernel<bf16>, dim3(T), dim3(threads), 0, st, (bf16*)qkv, nq, nkv, hd, rot,
+            qnn::launch_pdl(rope_cache_vec_kernel<bf16>, dim3(T), dim3(threads), (size_t)(rot / 2) * sizeof(float2), st, (bf16*)qkv, nq, nkv, hd, rot,
                             inv_freq, tok_pos, tok_slot, (bf16*)k_pool, (bf16*)v_pool, page_table, max_pages, page_size,
                             ring, slot_len, write_cache);
         else
-            qnn::launch_pdl(rope_cache_vec_kernel<float>, dim3(T), dim3(threads), 0, st, (float*)qkv, nq, nkv, hd, rot,
+            qnn::launch_pdl(rope_cache_vec_kernel<float>, dim3(T), dim3(threads), (size_t)(rot / 2) * sizeof(float2), st, (float*)qkv, nq, nkv, hd, rot,
                             inv_freq, tok_pos, tok_slot, (float*)k_pool, (float*)v_pool, page_table, max_pages,
                             page_size, ring, slot_len, write_cache);
         QNN_LAUNCH_CHECK();
