@@ -15,6 +15,10 @@
 //                      O is rescaled in tensor memory only when a row maximum has grown by more than 8
 //                      since the value the row's exponentials are taken against (the stale maximum
 //                      cancels in the final division; P stays below e^8).
+// With few CTAs (one short prompt: 16 query tiles x 8 heads on 148 SMs, the last tile walking 16 times as
+// many keys as the first) the grid is launched as clusters of two: the CTAs of a pair take alternate key
+// tiles of the same query tile; when both are done, rank 1 pushes its (reference maximum, sum, O) into
+// rank 0's shared memory through the cluster's distributed shared memory and rank 0 merges and writes.
 // Tensor memory: S double-buffered (2 x 64 columns), O 256 columns.  All softmax arithmetic is float32.
 // Keys of other sequences that a tile drags in are masked; rows beyond the sequence are never stored.
 // Every mbarrier wait is bounded in time; on expiry a status word is set and the CTA winds down.
@@ -34,6 +38,7 @@ constexpr int THREADS = 192;
 constexpr int TMEM_COLS = 512, S_COL = 0, O_COL = 128;
 constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;
 constexpr float RESCALE_STEP = 8.f;
+constexpr int MERGE_O_BYTES = BM * HD * 4, MERGE_ML_BYTES = BM * 8;   // what rank 1 of a pair hands to rank 0
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
@@ -126,6 +131,20 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&h);
 }
 
+__device__ __forceinline__ void cluster_barrier() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Copy `bytes` (a multiple of 16) from this CTA's shared memory to the same address in the CTA of rank
+// `rank`; completion is counted in bytes on that CTA's mbarrier at `bar_local`.
+__device__ __forceinline__ void bulk_copy_to_rank(unsigned local_addr, unsigned bytes, unsigned bar_local, unsigned rank) {
+    unsigned dst, bar;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(dst) : "r"(local_addr), "r"(rank));
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(bar) : "r"(bar_local), "r"(rank));
+    asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "r"(local_addr), "r"(bytes), "r"(bar) : "memory");
+}
+
 struct __align__(8) Barriers {
     uint64_t q_full;
     uint64_t k_full[KV_STAGES];
@@ -135,6 +154,7 @@ struct __align__(8) Barriers {
     uint64_t s_ready[2];      // S_j is complete in tensor memory
     uint64_t p_ready[2];      // P_j is in shared memory and O has been corrected
     uint64_t pv_done[2];      // O += P_j V_j has completed
+    uint64_t merge_full;      // rank 0 of a pair: rank 1's partial result has arrived (bytes)
     uint32_t tmem_base;
     uint32_t failed;
 };
@@ -145,7 +165,7 @@ __global__ void __launch_bounds__(THREADS)
 attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
                             bf16* __restrict__ out, size_t out_stride, const int* __restrict__ seq_row0,
                             const int* __restrict__ seq_len, int nq, int nkv, float scale, float cap, int window,
-                            int* __restrict__ status) {
+                            int* __restrict__ status, int split) {
     pdl_wait();
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -154,18 +174,24 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     unsigned char* sP = sKV + KV_STAGES * (K_BYTES + V_BYTES);      // [2][P]
     Barriers* bars = reinterpret_cast<Barriers*>(sP + 2 * P_BYTES);
 
-    const int b = blockIdx.y, h = blockIdx.z;
+    // grid (heads [x 2 ranks], sequences, query tiles): the query tile is the slowest index, so that CTAs are
+    // handed out from the heaviest tiles of all heads down to the lightest
+    const int b = blockIdx.y, h = split ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
     const int len = seq_len[b];
     const int ntiles_q = (len + BM - 1) / BM;
-    if ((int)blockIdx.x >= ntiles_q) return;                         // before any barrier or tensor memory
-    const int qt = ntiles_q - 1 - blockIdx.x;                        // the longest rows first
+    // split: blockIdx.x = 2 * head + rank in the pair (both CTAs of a pair return here or neither)
+    const int rank = split ? (int)(blockIdx.x & 1) : 0, stride = split ? 2 : 1;
+    const int qx = (int)blockIdx.z;
+    if (qx >= ntiles_q) return;                                      // before any barrier or tensor memory
+    const int qt = ntiles_q - 1 - qx;                                // the longest rows first
     const int r0 = qt * BM, row0 = seq_row0[b];
     const int kh = h / (nq / nkv);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int last_row = min(r0 + BM, len) - 1;
     const int kv_lo = (window > 0 && r0 - window + 1 > 0) ? r0 - window + 1 : 0;
-    const int jt0 = kv_lo / BN, jt1 = last_row / BN;                 // key tiles jt0 .. jt1
-    const int nt = jt1 - jt0 + 1;
+    const int jt1 = last_row / BN;                                   // key tiles kv_lo / BN .. jt1 of the query tile,
+    const int jt0 = kv_lo / BN + rank;                               // of which this CTA takes jt0, jt0 + stride, ...
+    const int nt = jt1 >= jt0 ? (jt1 - jt0) / stride + 1 : 0;        // (none for rank 1 when there is a single tile)
 
     if (threadIdx.x == 0) {
         mbar_init(smem_u32(&bars->q_full), 1);
@@ -180,6 +206,8 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             mbar_init(smem_u32(&bars->p_ready[i]), 4);               // one arrival per softmax warp
             mbar_init(smem_u32(&bars->pv_done[i]), 1);
         }
+        mbar_init(smem_u32(&bars->merge_full), 1);
+        if (split && rank == 0) mbar_expect_tx(smem_u32(&bars->merge_full), MERGE_O_BYTES + MERGE_ML_BYTES);
         bars->failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -192,6 +220,19 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const unsigned tmem = bars->tmem_base;
+
+    // The softmax warps' view of their row (warps 2..5; thread = query row), kept past the role branches
+    // for the merge of a pair and the output.
+    const int quarter = warp & 3;
+    const int rloc = quarter * 32 + lane;                 // row within the tile = tensor-memory lane
+    const int row = r0 + rloc;                            // position in the sequence
+    const unsigned lane_base = tmem + ((unsigned)(quarter * 32) << 16);
+    const float LOG2E = 1.4426950408889634f;
+    const float k1 = cap > 0.f ? scale / cap : scale;
+    const float k2 = (cap > 0.f ? cap : 1.f) * LOG2E;
+    const float step = RESCALE_STEP / (cap > 0.f ? cap : 1.f);   // a growth of the maximum by 8 in the exponent
+    float m_used = 0.f, l_sum = 0.f;                      // reference maximum of the exponentials, their sum
+    bool alive = true;
 
     if (warp == 0) {
         if (lane == 0) {
@@ -207,7 +248,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 const int s = j % KV_STAGES;
                 const unsigned par = ((j / KV_STAGES) - 1) & 1;
                 unsigned char* kdst = sKV + s * (K_BYTES + V_BYTES);
-                const int y = row0 + (jt0 + j) * BN;
+                const int y = row0 + (jt0 + j * stride) * BN;
                 if (j >= KV_STAGES && !mbar_wait(smem_u32(&bars->k_empty[s]), par)) {
                     atomicOr(status, 16);
                     bars->failed = 1;
@@ -229,10 +270,10 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     unsigned char* vd = sKV + sv * (K_BYTES + V_BYTES) + K_BYTES;
                     mbar_expect_tx(vfull, V_BYTES);
                     for (int d = 0; d < HD / 64; ++d)
-                        tma_load_2d(smem_u32(vd + d * (BN * 128)), &map_kv, vfull, vx + d * 64, row0 + (jt0 + jv) * BN);
+                        tma_load_2d(smem_u32(vd + d * (BN * 128)), &map_kv, vfull, vx + d * 64, row0 + (jt0 + jv * stride) * BN);
                 }
             }
-            if (!has_failed(bars)) {          // the values of the last tile
+            if (nt > 0 && !has_failed(bars)) {          // the values of the last tile
                 const int jv = nt - 1, sv = jv % KV_STAGES;
                 bool ok = true;
                 if (jv >= KV_STAGES) ok = mbar_wait(smem_u32(&bars->v_empty[sv]), ((jv / KV_STAGES) - 1) & 1);
@@ -244,7 +285,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     unsigned char* vd = sKV + sv * (K_BYTES + V_BYTES) + K_BYTES;
                     mbar_expect_tx(vfull, V_BYTES);
                     for (int d = 0; d < HD / 64; ++d)
-                        tma_load_2d(smem_u32(vd + d * (BN * 128)), &map_kv, vfull, vx + d * 64, row0 + (jt0 + jv) * BN);
+                        tma_load_2d(smem_u32(vd + d * (BN * 128)), &map_kv, vfull, vx + d * 64, row0 + (jt0 + jv * stride) * BN);
                 }
             }
         }
@@ -269,6 +310,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 umma_commit(smem_u32(&bars->k_empty[j % KV_STAGES]));
                 umma_commit(smem_u32(&bars->s_ready[j & 1]));
             };
+            if (nt == 0) ok = false;                      // nothing to multiply (and nobody waits for it)
             if (ok) {
                 ok = mbar_wait(smem_u32(&bars->k_full[0]), 0);
                 if (!ok) { atomicOr(status, 2); bars->failed = 1; }
@@ -304,20 +346,11 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         }
     } else {
         // ---- softmax: thread = query row ---------------------------------------------------------------
-        const int quarter = warp & 3;
-        const int rloc = quarter * 32 + lane;                 // row within the tile = tensor-memory lane
-        const int row = r0 + rloc;                            // position in the sequence
-        const unsigned lane_base = tmem + ((unsigned)(quarter * 32) << 16);
-        const float LOG2E = 1.4426950408889634f;
-        const float k1 = cap > 0.f ? scale / cap : scale;
-        const float k2 = (cap > 0.f ? cap : 1.f) * LOG2E;
-        const float step = RESCALE_STEP / (cap > 0.f ? cap : 1.f);   // a growth of the maximum by 8 in the exponent
-        float m_used = 0.f, m_run = -CUDART_INF_F, l_sum = 0.f;
+        float m_run = -CUDART_INF_F;
         // the keys this row sees: key_lo .. key_hi (none when the row lies beyond the sequence)
         const int key_hi = min(row, len - 1);
         const int key_lo = (window > 0 && row - window + 1 > 0) ? row - window + 1 : 0;
         const unsigned key_span = key_hi >= key_lo ? (unsigned)(key_hi - key_lo) : 0u;
-        bool alive = true;
         for (int j = 0; j < nt && alive; ++j) {
             const int bsel = j & 1;
             if (!mbar_wait_warp(smem_u32(&bars->s_ready[bsel]), (j >> 1) & 1)) {
@@ -343,7 +376,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             // its argument to +-20 changes nothing: tanh.approx saturates), the scaled score without;
             // either times k2 is the exponent to base 2.  Tiles wholly inside every row's range of keys
             // skip the mask.
-            const int col0 = (jt0 + j) * BN;
+            const int col0 = (jt0 + j * stride) * BN;
             const bool interior = col0 + BN - 1 <= r0 && col0 + BN - 1 < len && (window <= 0 || col0 > r0 + BM - 1 - window);
             float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
             if (interior) {
@@ -424,7 +457,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             if (lane == 0) mbar_arrive(smem_u32(&bars->p_ready[bsel]));
         }
         // the last product, then O / l -> bfloat16 -> global
-        if (alive) {
+        if (alive && nt > 0) {
             const int jl = nt - 1;
             if (!mbar_wait_warp(smem_u32(&bars->pv_done[jl & 1]), (jl >> 1) & 1)) {
                 atomicOr(status, 64);
@@ -432,32 +465,109 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 alive = false;
             }
         }
+    }
+
+    // ---- a pair's second half hands its result to the first ---------------------------------------------
+    // Rank 1 lays its O (float32, row by row, the 16-byte chunks XOR-ed with the row number) over its own
+    // K/V stages and (reference maximum, sum) over its P buffer, and the copy engine moves both to the same
+    // places in rank 0, whose operands no product reads any more (first cluster barrier).  Rank 0 waits for
+    // the bytes on an mbarrier; the second cluster barrier keeps rank 1 alive until they have been read out
+    // of its memory.
+    float m_other = 0.f, l_other = 0.f;
+    if (split) {
+        if (warp >= 2 && rank == 1) {
+            const bool have = alive && nt > 0 && !has_failed(bars);
+            if (have) asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            unsigned char* orow = sKV + rloc * (HD * 4);
+#pragma unroll 1
+            for (int c0 = 0; c0 < HD; c0 += 32) {
+                uint32_t v[32];
+                if (have) {
+                    tmem_ld32(lane_base + O_COL + c0, v);
+                    tmem_ld_wait();
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) v[c] = 0u;
+                }
+#pragma unroll
+                for (int c4 = 0; c4 < 8; ++c4)
+                    *reinterpret_cast<uint4*>(orow + ((((c0 >> 2) + c4) ^ (rloc & 7)) << 4)) =
+                        make_uint4(v[c4 * 4], v[c4 * 4 + 1], v[c4 * 4 + 2], v[c4 * 4 + 3]);
+            }
+            *reinterpret_cast<float2*>(sP + rloc * 8) = make_float2(m_used, have ? l_sum : 0.f);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // visible to the copy engine
+        }
+        __syncthreads();
+        cluster_barrier();                  // both CTAs are past their last product; rank 1's part is laid out
+        if (rank == 1 && threadIdx.x == 64) {
+            bulk_copy_to_rank(smem_u32(sKV), MERGE_O_BYTES, smem_u32(&bars->merge_full), 0);
+            bulk_copy_to_rank(smem_u32(sP), MERGE_ML_BYTES, smem_u32(&bars->merge_full), 0);
+        }
+        if (warp >= 2 && rank == 0) {
+            if (!mbar_wait_warp(smem_u32(&bars->merge_full), 0)) {
+                atomicOr(status, 128);
+                bars->failed = 1;
+                alive = false;
+            } else {
+                const float2 ml = *reinterpret_cast<const float2*>(sP + rloc * 8);
+                m_other = ml.x;
+                l_other = ml.y;
+            }
+        }
+        __syncthreads();
+        cluster_barrier();                  // the bytes have left rank 1's memory: it may go
+    }
+
+    if (warp >= 2 && rank == 0) {
         // Every product is done, so the Q tile's shared memory is free: each thread leaves its row there as
         // bfloat16 (16-byte chunks XOR-ed with the row number, so that neither side conflicts), and the
         // warps then write whole 512-byte rows to global memory.
         const bool good = alive && !__any_sync(0xffffffffu, has_failed(bars));
         if (good) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
+            // weights of the two halves against the larger reference maximum (a half without keys has sum 0)
+            const bool have0 = l_sum > 0.f, have1 = l_other > 0.f;
+            const float mm = fmaxf(have0 ? m_used : -CUDART_INF_F, have1 ? m_other : -CUDART_INF_F);
+            const float w0 = have0 ? exp2_fast((m_used - mm) * k2) : 0.f;
+            const float w1 = have1 ? exp2_fast((m_other - mm) * k2) : 0.f;
+            const float l_row = l_sum * w0 + l_other * w1;
+            const float inv = l_row > 0.f ? 1.f / l_row : 0.f;
+            const float f0 = w0 * inv, f1 = w1 * inv;
             unsigned char* orow = sQ + rloc * (HD * 2);
+            const unsigned char* prow = sKV + rloc * (HD * 4);
 #pragma unroll 1
             for (int c0 = 0; c0 < HD; c0 += 64) {
                 uint32_t v0[32], v1[32];
                 tmem_ld32(lane_base + O_COL + c0, v0);
                 tmem_ld32(lane_base + O_COL + c0 + 32, v1);
                 tmem_ld_wait();
+                float o0[32], o1[32];
+#pragma unroll
+                for (int c = 0; c < 32; ++c) {
+                    o0[c] = __uint_as_float(v0[c]) * f0;
+                    o1[c] = __uint_as_float(v1[c]) * f0;
+                }
+                if (have1) {
+#pragma unroll
+                    for (int c4 = 0; c4 < 8; ++c4) {
+                        const float4 a = *reinterpret_cast<const float4*>(prow + ((((c0 >> 2) + c4) ^ (rloc & 7)) << 4));
+                        const float4 b = *reinterpret_cast<const float4*>(prow + ((((c0 >> 2) + 8 + c4) ^ (rloc & 7)) << 4));
+                        o0[c4 * 4 + 0] += a.x * f1; o0[c4 * 4 + 1] += a.y * f1; o0[c4 * 4 + 2] += a.z * f1; o0[c4 * 4 + 3] += a.w * f1;
+                        o1[c4 * 4 + 0] += b.x * f1; o1[c4 * 4 + 1] += b.y * f1; o1[c4 * 4 + 2] += b.z * f1; o1[c4 * 4 + 3] += b.w * f1;
+                    }
+                }
 #pragma unroll
                 for (int c8 = 0; c8 < 4; ++c8) {
                     uint4 pk;
-                    pk.x = pack_bf16(__uint_as_float(v0[c8 * 8 + 0]) * inv, __uint_as_float(v0[c8 * 8 + 1]) * inv);
-                    pk.y = pack_bf16(__uint_as_float(v0[c8 * 8 + 2]) * inv, __uint_as_float(v0[c8 * 8 + 3]) * inv);
-                    pk.z = pack_bf16(__uint_as_float(v0[c8 * 8 + 4]) * inv, __uint_as_float(v0[c8 * 8 + 5]) * inv);
-                    pk.w = pack_bf16(__uint_as_float(v0[c8 * 8 + 6]) * inv, __uint_as_float(v0[c8 * 8 + 7]) * inv);
+                    pk.x = pack_bf16(o0[c8 * 8 + 0], o0[c8 * 8 + 1]);
+                    pk.y = pack_bf16(o0[c8 * 8 + 2], o0[c8 * 8 + 3]);
+                    pk.z = pack_bf16(o0[c8 * 8 + 4], o0[c8 * 8 + 5]);
+                    pk.w = pack_bf16(o0[c8 * 8 + 6], o0[c8 * 8 + 7]);
                     *reinterpret_cast<uint4*>(orow + (((c0 / 8 + c8) ^ (rloc & 31)) << 4)) = pk;
-                    pk.x = pack_bf16(__uint_as_float(v1[c8 * 8 + 0]) * inv, __uint_as_float(v1[c8 * 8 + 1]) * inv);
-                    pk.y = pack_bf16(__uint_as_float(v1[c8 * 8 + 2]) * inv, __uint_as_float(v1[c8 * 8 + 3]) * inv);
-                    pk.z = pack_bf16(__uint_as_float(v1[c8 * 8 + 4]) * inv, __uint_as_float(v1[c8 * 8 + 5]) * inv);
-                    pk.w = pack_bf16(__uint_as_float(v1[c8 * 8 + 6]) * inv, __uint_as_float(v1[c8 * 8 + 7]) * inv);
+                    pk.x = pack_bf16(o1[c8 * 8 + 0], o1[c8 * 8 + 1]);
+                    pk.y = pack_bf16(o1[c8 * 8 + 2], o1[c8 * 8 + 3]);
+                    pk.z = pack_bf16(o1[c8 * 8 + 4], o1[c8 * 8 + 5]);
+                    pk.w = pack_bf16(o1[c8 * 8 + 6], o1[c8 * 8 + 7]);
                     *reinterpret_cast<uint4*>(orow + (((c0 / 8 + 4 + c8) ^ (rloc & 31)) << 4)) = pk;
                 }
             }
@@ -514,14 +624,14 @@ int make_map(CUtensorMap* map, const void* base, long long rows, long long width
 
 // qkv: this step's projections, [T rows, (nq + 2 nkv) * 256] bfloat16, rotated; sequence b occupies rows
 // seq_row0[b] .. + seq_len[b] - 1.  Returns QNN_ERR_UNSUPPORTED unless head_dim is 256.  `status` as in
-// qnn_gemm_tcgen05 (bits: 2 K/V wait, 4 S wait, 8 P wait, 16 ring wait, 32 Q wait, 64 product wait).
+// qnn_gemm_tcgen05 (bits: 2 K/V wait, 4 S wait, 8 P wait, 16 ring wait, 32 Q wait, 64 product wait, 128 wait for the other half of a pair).
 QNN_API int qnn_attn_prefill_tcgen05(const void* qkv, long long total_rows, void* out, long long out_stride,
                                      const int* seq_row0, const int* seq_len, int B, int max_len, int nq, int nkv,
                                      int hd, float scale, float cap, int window, int* status, cudaStream_t st) {
     if (B <= 0 || max_len <= 0) return 0;
     if (hd != HD) return QNN_ERR_UNSUPPORTED;
     if (nkv <= 0 || nq % nkv) return QNN_ERR_ARGUMENT;
-    if (B > 65535 || nq > 65535) return QNN_ERR_UNSUPPORTED;
+    if (B > 65535 || (max_len + BM - 1) / BM > 65535) return QNN_ERR_UNSUPPORTED;
     if (((uintptr_t)qkv & 15) || ((uintptr_t)out & 15) || (out_stride * 2) % 16) return QNN_ERR_UNSUPPORTED;
     const long long width = (long long)(nq + 2 * nkv) * HD;
     CUtensorMap map_q, map_kv;
@@ -537,8 +647,52 @@ QNN_API int qnn_attn_prefill_tcgen05(const void* qkv, long long total_rows, void
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    dim3 grid((max_len + BM - 1) / BM, B, nq);
-    cudaError_t e = qnn::launch_pdl(kern, grid, dim3(THREADS), smem, st, map_q, map_kv, (bf16*)out, (size_t)out_stride,
-                                    seq_row0, seq_len, nq, nkv, scale, cap, window, status);
+    const int ntq = (max_len + BM - 1) / BM;
+    static int sm_count = 0;
+    if (sm_count == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0)
+            sm_count = 148;
+    }
+    // Few CTAs and several query tiles: pairs of CTAs share a query tile's keys (see the head of this file).
+    // With many CTAs the heavy ones are started first and the rest fills in behind them.
+    static int split_ok = -1;                      // the device holds a pair of these CTAs (asked once)
+    // (measured at 8 heads: 1024 tokens 29.9 -> 26.8 us, 2048 tokens 51.8 -> 49.1 us; with 4096 tokens, 256 CTAs
+    // unsplit, pairs were slower, 126 against 94 us)
+    const bool want_split = ntq >= 2 && (long long)ntq * B * nq <= sm_count && !getenv("QNN_ATTN_NO_SPLIT");
+    cudaLaunchConfig_t cfg = {};
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = 2;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    if (want_split && split_ok < 0) {
+        cfg.gridDim = dim3(2, 1, 1);
+        cfg.attrs = attr + 1;
+        cfg.numAttrs = 1;
+        int n = 0;
+        split_ok = (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) == cudaSuccess && n > 0) ? 1 : 0;
+        if (!split_ok) (void)cudaGetLastError();
+        cfg.attrs = attr;
+    }
+    const int split = (want_split && split_ok == 1) ? 1 : 0;
+    cfg.gridDim = dim3((unsigned)(split ? 2 * nq : nq), B, ntq);
+    const long long ctas = (long long)cfg.gridDim.x * B * nq;
+    const bool pdl = qnn::pdl_enabled() && ctas <= qnn::pdl_max_grid();
+    if (split) {
+        if (!pdl) cfg.attrs = attr + 1;
+        cfg.numAttrs = pdl ? 2 : 1;
+    } else {
+        cfg.numAttrs = pdl ? 1 : 0;
+    }
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, map_q, map_kv, (bf16*)out, (size_t)out_stride, seq_row0, seq_len, nq,
+                                       nkv, scale, cap, window, status, split);
     return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }
