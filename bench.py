@@ -245,7 +245,9 @@ def main():
     # ---- end to end through the Python entry point ------------------------------------------
     e2e = None
     if not args.skip_e2e:
-        new = min(args.steps, 128)
+        # as many steps as the device-timed run: the first 25 or so after the prompts run at a reduced SM clock
+        # (the prefill of 8 x 8000 tokens hits the power cap; the clock takes about 80 ms to come back)
+        new = min(args.steps, 512)
         plen = CONTEXT - new - 1
         prompts = [torch.randint(1, cfg["vocab_size"], (plen,)).tolist() for _ in range(BATCH)]
         llm.max_batch = BATCH

@@ -170,10 +170,14 @@ class Engine:
         return logits
 
     # ---- decode with ids that are already on the device -------------------------------
-    def decode(self, slots: Sequence[int], tokens_dev: torch.Tensor, use_graph: Optional[bool] = None) -> torch.Tensor:
+    def decode(self, slots: Sequence[int], tokens_dev: torch.Tensor, use_graph: Optional[bool] = None,
+               tail=None) -> torch.Tensor:
         """One token for each sequence in ``slots``; ``tokens_dev`` ([B] int32) stays on the
         device (the reference feeds the sampled id from device memory too,
-        src/models/QuickNN.Models.LLM.pas:802-807).  Returns the logits of every row.
+        src/models/QuickNN.Models.LLM.pas:802-807).  Returns the logits of every row, or, with
+        ``tail`` (a callable on the logits that launches device work only, such as a sampler),
+        what ``tail`` returns: it then runs as part of the same graph, and its result lives in a
+        buffer that the next step of this batch size overwrites.
 
         The launch sequence of a batch size is captured in a CUDA graph the first time it
         runs and replayed afterwards; lengths, page tables and ids are read from device
@@ -191,7 +195,8 @@ class Engine:
         self.cache.extend([(s, p + 1) for s, p in zip(slots, starts)])
         self.cache.sync()
         use_graph = self.use_graphs if use_graph is None else use_graph
-        st = self._decode_state.get(B)
+        key = (B, id(tail) if tail is not None else None)
+        st = self._decode_state.get(key)
         if st is None:
             meta = torch.zeros(2 * B, dtype=torch.int32, device=self.device)
             ar = torch.arange(B, dtype=torch.int32, device=self.device)
@@ -199,20 +204,24 @@ class Engine:
             tokens = torch.zeros(B, dtype=torch.int32, device=self.device)
             step = StepBatch("decode", B, B, tokens, meta[:B], meta[B:], ar, meta[B:], ar, self.model.dtype,
                              self.splits_for(B), part_o, part_ml)
-            st = {"meta": meta, "step": step, "graph": None, "logits": None}
-            self._decode_state[B] = st
+            st = {"meta": meta, "step": step, "graph": None, "logits": None, "tail": tail}    # holds `tail` alive: its id is the key
+            self._decode_state[key] = st
         self.cache.uploader.send(st["meta"], np.concatenate([np.asarray(starts, np.int32), np.asarray(slots, np.int32)]))
         st["step"].tokens.copy_(tokens_dev.reshape(-1))
         self.steps_run += 1
+        def run():
+            logits = self.model.forward(st["step"], self.cache)
+            return logits if tail is None else tail(logits)
+
         if not use_graph:
-            return self.model.forward(st["step"], self.cache)
+            return run()
         if st["graph"] is None:
-            logits = self.model.forward(st["step"], self.cache)      # eager: also warms everything up
+            logits = run()                                            # eager: also warms everything up
             torch.cuda.synchronize(self.device)
             g = torch.cuda.CUDAGraph()
             before = _klib.launches
             with torch.cuda.graph(g):
-                st["logits"] = self.model.forward(st["step"], self.cache)
+                st["logits"] = run()
             st["kernels"] = _klib.launches - before      # our kernels in one replay of this graph
             _klib.launches = before
             st["graph"] = g

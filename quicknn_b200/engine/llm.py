@@ -48,11 +48,13 @@ class _Backend(GenerationBackend):
     def _decode(self, tokens: torch.Tensor) -> torch.Tensor:
         up = self.engine.cache.uploader
         before = up.bytes_sent
-        logits = self.engine.decode(self.slots, tokens)
+        # the sampler runs inside the step's graph; its ids stay valid until the next step of this batch
+        # size is launched, and everything that reads them is queued before that
+        ids = self.engine.decode(self.slots, tokens, tail=self.sampler)
         self.h2d_bytes += up.bytes_sent - before
         self.d2h_bytes += 4 * (len(self.slots) + 1)
         self.decode_steps += 1
-        return self.sampler(logits).clone()
+        return ids
 
     def _launch_ahead(self) -> Optional[torch.Tensor]:
         eng = self.engine

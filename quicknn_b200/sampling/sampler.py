@@ -23,8 +23,10 @@ class Sampler:
         options.validate()
         self.vocab, self.max_rows, self.options, self.device = vocab_size, max_rows, options, device
         self.rng = torch.zeros(max_rows, dtype=torch.int32, device=device)
-        self.out = torch.zeros(max_rows, dtype=torch.int32, device=device)
-        self.flag = torch.zeros(1, dtype=torch.int32, device=device)
+        # chosen ids of the rows, then the error word: one buffer, so that both are read in one copy
+        self._both = torch.zeros(max_rows + 1, dtype=torch.int32, device=device)
+        self.out = self._both[:max_rows]
+        self.flag = self._both[max_rows:]
         nbytes = ops.sample_scratch_bytes(max_rows, vocab_size, options.top_k)
         if nbytes < 0:
             raise ValueError("sampling scratch would exceed 2 GiB; lower the batch")
@@ -81,7 +83,8 @@ class Sampler:
         if self._pinned is None:
             self._pinned = torch.empty(self.max_rows + 1, dtype=torch.int32, pin_memory=True)
             self._event = torch.cuda.Event()
-        self._pinned[:n + 1].copy_(torch.cat([tokens.reshape(-1), self.flag]), non_blocking=True)
+        self._pinned[:n].copy_(tokens.reshape(-1), non_blocking=True)
+        self._pinned[n:n + 1].copy_(self.flag, non_blocking=True)
         self._event.record()
         self._posted = n
         self.bytes_read += 4 * (n + 1)
