@@ -62,11 +62,13 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, 
     constexpr int KSTEPS = HD / 16, CH = HD / 8, ROWB = HD * 2, NDT = HD / 8;
     constexpr int TILEB = BN * ROWB;
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    const int b = blockIdx.y, h = blockIdx.z;
+    // grid (heads, sequences, query tiles): the tile is the slowest index, so that CTAs are handed out from
+    // the heaviest tiles of all heads down to the lightest
+    const int b = blockIdx.y, h = blockIdx.x;
     const int len = seq_len[b];
     const int ntiles = (len + BM - 1) / BM;
-    if ((int)blockIdx.x >= ntiles) return;
-    const int tile = ntiles - 1 - blockIdx.x;          // the longest rows first
+    if ((int)blockIdx.z >= ntiles) return;
+    const int tile = ntiles - 1 - blockIdx.z;          // the longest rows first
     const int r0 = tile * BM, row0 = seq_row0[b];
     const int kh = h / (nq / nkv);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
@@ -235,7 +237,7 @@ int launch(const void* q, const void* k, const void* v, long long row_stride, vo
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    dim3 grid((max_len + BM - 1) / BM, B, nq);
+    dim3 grid(nq, B, (max_len + BM - 1) / BM);
     qnn::launch_pdl(kern, dim3(grid), dim3(PF_WARPS * 32), smem, st, (const bf16*)q, (const bf16*)k, (const bf16*)v, (size_t)row_stride,
                                             (bf16*)out, (size_t)out_stride, seq_row0, seq_len, nq, nkv, scale, cap,
                                             window);
@@ -252,7 +254,7 @@ QNN_API int qnn_attn_prefill_mma(const void* q, const void* k, const void* v, lo
                                  int nq, int nkv, int hd, float scale, float cap, int window, cudaStream_t st) {
     if (B <= 0 || max_len <= 0) return 0;
     if (nkv <= 0 || nq % nkv) return QNN_ERR_ARGUMENT;
-    if (B > 65535 || nq > 65535) return QNN_ERR_UNSUPPORTED;
+    if (B > 65535 || (max_len + BM - 1) / BM > 65535) return QNN_ERR_UNSUPPORTED;
     if ((row_stride * 2) % 16 || (out_stride * 2) % 4 ||
         (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v) & 15) || ((uintptr_t)out & 3))
         return QNN_ERR_ARGUMENT;
