@@ -313,3 +313,225 @@ def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
         for s in slots:
             eng.release(s)
     eng.cache.audit()
+
+
+# ---- a second toy architecture: a feed-forward with routing and another position encoding ---------
+
+def _define_toy2():
+    from quicknn_b200.config.base import (Architecture, ModelConfig, as_float, as_int, register_architecture)
+    from quicknn_b200.kernels import ops
+    from quicknn_b200.parts import (FEED_FORWARDS, MIXERS, POSITIONS, EmbeddingSpec, FeedForward, HeadSpec, LayerSpec,
+                                    Mixer, ModelSpec, PartSpec, Positions, ScheduleEntry, StateNeed)
+
+    @FEED_FORWARDS.register("toy_routed", replace=True)
+    class RoutedFF(FeedForward):
+        """E small experts; the router's logits are float32, a token goes to its best expert
+        and the expert's output is weighted with the softmax probability of that choice."""
+
+        def __init__(self, spec):
+            super().__init__(spec)
+            p = spec.params
+            self.H, self.E, self.I = int(p["hidden_size"]), int(p["experts"]), int(p["inner"])
+
+        @classmethod
+        def param_shapes(cls, spec):
+            p = spec.params
+            H, E, I = int(p["hidden_size"]), int(p["experts"]), int(p["inner"])
+            M = cls.PARAM_ROLE_MATRIX
+            return {"router": ((E, H), M), "w_in": ((E * I, H), M), "w_out": ((E * H, I), M)}
+
+        def load(self, tensors, compute_dtype, device):
+            self.router = tensors["router"].float().contiguous()
+            self.w_in = tensors["w_in"].contiguous().view(self.E, self.I, self.H)
+            self.w_out = tensors["w_out"].contiguous().view(self.E, self.H, self.I)
+
+        def weight_bytes(self):
+            return sum(t.numel() * t.element_size() for t in (self.router, self.w_in, self.w_out))
+
+        def forward(self, x, step):
+            logits = ops.linear(x.float().contiguous(), self.router)            # router in float32
+            prob = torch.softmax(logits, dim=-1)
+            best = prob.argmax(dim=-1)
+            out = torch.zeros_like(x)
+            for e in range(self.E):                                           # a toy: expert by expert
+                rows = (best == e).nonzero().flatten()
+                if rows.numel() == 0:
+                    continue
+                h = ops.linear(x[rows].contiguous(), self.w_in[e].contiguous())
+                h = torch.relu(h.float()).to(x.dtype)
+                y = ops.linear(h.contiguous(), self.w_out[e].contiguous())
+                out[rows] = (y.float() * prob[rows, e].unsqueeze(1)).to(x.dtype)
+            return out
+
+    @POSITIONS.register("toy_sinusoid", replace=True)
+    class SinusoidAdd(Positions):
+        """Adds sin(position * rate_j) to element j: an absolute encoding, nothing rotated."""
+
+        def __init__(self, spec):
+            super().__init__(spec)
+            self.size, self.base = int(spec.params["size"]), float(spec.params["base"])
+            self.rotary_dim, self.inv_freq = 0, None
+
+        def prepare(self, device):
+            j = torch.arange(self.size, dtype=torch.float64)
+            self.rates = torch.exp(-math.log(self.base) * j / self.size).float().to(device)
+
+        def apply(self, x, tok_pos):
+            return (x.float() + torch.sin(tok_pos.float().unsqueeze(1) * self.rates.unsqueeze(0))).to(x.dtype)
+
+    @MIXERS.register("toy_posdecay", replace=True)
+    class PosDecayMixer(Mixer):
+        """The decaying sum of the first toy, over inputs that carry their position."""
+
+        def __init__(self, spec):
+            super().__init__(spec)
+            self.hidden, self.decay = int(spec.params["hidden_size"]), float(spec.params["decay"])
+            pos = spec.params["position"]
+            self.position = POSITIONS.get(pos.kind)(pos)
+
+        @classmethod
+        def param_shapes(cls, spec):
+            h = int(spec.params["hidden_size"])
+            return {"mix": ((h, h), cls.PARAM_ROLE_MATRIX)}
+
+        def load(self, tensors, compute_dtype, device):
+            self.w = tensors["mix"].contiguous()
+            self.position.prepare(device)
+
+        def weight_bytes(self):
+            return self.w.numel() * self.w.element_size()
+
+        def state_need(self):
+            return StateNeed((self.hidden,), "float32")
+
+        def forward(self, x, step, line):
+            xf = self.position.apply(x, step.tok_pos).float()
+            out = torch.empty_like(xf)
+            for t, s in enumerate(step.tok_slot.cpu().tolist()):
+                if s < 0:
+                    out[t] = 0
+                    continue
+                line.state[s].mul_(self.decay).add_(xf[t])
+                out[t] = line.state[s]
+            return ops.linear(out.to(x.dtype).contiguous(), self.w)
+
+    def _f(conv, **kw):
+        return dataclasses.field(default=kw.get("default"), metadata={"convert": conv, "required": "default" not in kw})
+
+    @dataclasses.dataclass(frozen=True)
+    class Toy2Config(ModelConfig):
+        hidden_size: int = _f(as_int)
+        vocab_size: int = _f(as_int)
+        n_heads: int = _f(as_int)
+        n_kv_heads: int = _f(as_int)
+        head_dim: int = _f(as_int)
+        rotary_dim: int = _f(as_int)
+        inner: int = _f(as_int)
+        experts: int = _f(as_int)
+        expert_inner: int = _f(as_int)
+        decay: float = _f(as_float)
+        eps: float = _f(as_float)
+        max_position_embeddings: int = _f(as_int)
+
+    def toy2_spec(c):
+        H = c.hidden_size
+        norm = PartSpec("rmsnorm", {"size": H, "eps": c.eps, "unit_offset": True})
+        dense = PartSpec("gated_mlp", {"hidden_size": H, "intermediate_size": c.inner, "activation": "gelu_tanh"})
+        routed = PartSpec("toy_routed", {"hidden_size": H, "experts": c.experts, "inner": c.expert_inner})
+        attn = PartSpec("attention", {"hidden_size": H, "n_heads": c.n_heads, "n_kv_heads": c.n_kv_heads,
+                                      "head_dim": c.head_dim, "scale": c.head_dim ** -0.5, "softcap": 20.0, "window": 6,
+                                      "position": PartSpec("rotary", {"head_dim": c.head_dim, "theta": 500.0,
+                                                                      "rotary_dim": c.rotary_dim})})
+        posmix = PartSpec("toy_posdecay", {"hidden_size": H, "decay": c.decay,
+                                           "position": PartSpec("toy_sinusoid", {"size": H, "base": 50.0})})
+        n4 = {k: norm for k in ("pre_mixer", "pre_ff")}
+        l0 = {"mixer.mix": "a.mix", "ff.router": "a.router", "ff.w_in": "a.w_in", "ff.w_out": "a.w_out",
+              "norms.pre_mixer.weight": "a.n1", "norms.pre_ff.weight": "a.n2"}
+        l1 = {f"mixer.{x}_proj": f"b.{x}" for x in "qkvo"}
+        l1.update({f"ff.{n}_proj": f"b.{n}" for n in ("gate", "up", "down")})
+        l1.update({"norms.pre_mixer.weight": "b.n1", "norms.pre_ff.weight": "b.n2"})
+        layers = (LayerSpec(PartSpec("prenorm", {}), posmix, routed, n4, l0),
+                  LayerSpec(PartSpec("prenorm", {}), attn, dense, n4, l1))
+        schedule = (ScheduleEntry(0, 0), ScheduleEntry(1, 1))
+        return ModelSpec("Toy2ForTest", H, EmbeddingSpec(c.vocab_size, H, 1.0, "emb"), layers, schedule,
+                         HeadSpec(c.vocab_size, H, True, None, None, norm, "nf"), c.max_position_embeddings,
+                         init_std=0.3, init_norm_std=0.2)
+
+    arch = register_architecture(Architecture("Toy2ForTest", Toy2Config, toy2_spec), replace=True)
+    return arch, Toy2Config
+
+
+def _toy2_plain(w, cfg, ids):
+    """The second toy model in NumPy, whole sequence."""
+    H, nh, nkv, hd, rd = cfg["hidden_size"], cfg["n_heads"], cfg["n_kv_heads"], cfg["head_dim"], cfg["rotary_dim"]
+    E, EI = cfg["experts"], cfg["expert_inner"]
+    norm = lambda x, g: x / np.sqrt((x * x).mean(-1, keepdims=True) + cfg["eps"]) * (1.0 + g)  # noqa: E731
+    x = w["emb"][ids].astype(np.float64)
+    T = len(ids)
+    pos = np.arange(T)
+    # layer 0: positions added, decaying sum, then the routed feed-forward
+    n = norm(x, w["a.n1"])
+    rates = np.exp(-math.log(50.0) * np.arange(H) / H).astype(np.float32).astype(np.float64)
+    n = n + np.sin(pos[:, None] * rates[None, :])
+    s, out = np.zeros(H), np.zeros_like(n)
+    for t in range(T):
+        s = cfg["decay"] * s + n[t]
+        out[t] = s
+    x = x + out @ w["a.mix"].T
+    n = norm(x, w["a.n2"])
+    logits = n @ w["a.router"].T
+    prob = np.exp(logits - logits.max(-1, keepdims=True))
+    prob /= prob.sum(-1, keepdims=True)
+    best = prob.argmax(-1)
+    w_in, w_out = w["a.w_in"].reshape(E, EI, H), w["a.w_out"].reshape(E, H, EI)
+    y = np.zeros_like(x)
+    for t in range(T):
+        e = best[t]
+        y[t] = (w_out[e] @ np.maximum(w_in[e] @ n[t], 0.0)) * prob[t, e]
+    x = x + y
+    # layer 1: windowed, softcapped attention with a partly rotated head, dense feed-forward
+    n = norm(x, w["b.n1"])
+    q = (n @ w["b.q"].T).reshape(T, nh, hd)
+    k = (n @ w["b.k"].T).reshape(T, nkv, hd)
+    v = (n @ w["b.v"].T).reshape(T, nkv, hd)
+    rot = lambda z: np.concatenate([P.rope(z[..., :rd], pos, 500.0), z[..., rd:]], axis=-1)  # noqa: E731
+    a = P.attention(rot(q), rot(k), v, hd ** -0.5, 20.0, 6).reshape(T, -1)
+    x = x + a @ w["b.o"].T
+    n = norm(x, w["b.n2"])
+    x = x + (P.gelu_tanh(n @ w["b.gate"].T) * (n @ w["b.up"].T)) @ w["b.down"].T
+    return norm(x, w["nf"]) @ w["emb"].T, best
+
+
+def test_toy_routed_feed_forward_and_another_position_encoding(tmp_path):
+    """A feed-forward with a router and experts, a position part that is not a rotation, and an
+    attention layer with a partly rotated head, a window and a softcap: chosen layer by layer through
+    the registries, defined in this file, stepped by the unchanged engine."""
+    from quicknn_b200.engine import Engine, Model
+    from quicknn_b200.weights import write_model_folder
+    arch, Toy2Config = _define_toy2()
+    raw = dict(architectures=["Toy2ForTest"], hidden_size=48, vocab_size=70, n_heads=4, n_kv_heads=2, head_dim=16,
+               rotary_dim=8, inner=72, experts=3, expert_inner=40, decay=0.6, eps=1e-5, max_position_embeddings=128)
+    cfg = Toy2Config.from_dict(raw)
+    folder = write_model_folder(str(tmp_path / "toy2"), arch, cfg, 11, torch.float32)
+    model = Model.from_folder(folder, "float32", DEV)
+    eng = Engine(model, max_tokens=256, decode_splits=2)
+    w = P.read_safetensors(os.path.join(folder, "model.safetensors"))
+    rng = np.random.default_rng(3)
+    seqs = [rng.integers(0, 70, n).tolist() for n in (26, 9, 17)]
+    refs = [_toy2_plain(w, raw, s) for s in seqs]
+    assert len(set(np.concatenate([b for _, b in refs]).tolist())) > 1          # the router does choose
+    slots = [eng.new_sequence() for _ in seqs]
+    first = (15, 4, 17)
+    got = host(eng.step([(s, q[:n]) for s, q, n in zip(slots, seqs, first)], "all"))
+    want = np.concatenate([r[:n] for (r, _), n in zip(refs, first)])
+    assert np.abs(got - want).max() < 2e-4 * max(1.0, np.abs(want).max())
+    eng.release(slots[2])                                                        # the whole one is done
+    pos = [15, 4]
+    for _ in range(5):
+        got = host(eng.step([(s, [q[p]]) for s, q, p in zip(slots[:2], seqs[:2], pos)]))
+        for r in range(2):
+            assert np.abs(got[r] - refs[r][0][pos[r]]).max() < 2e-4 * max(1.0, np.abs(refs[r][0]).max())
+            pos[r] += 1
+    for s in slots[:2]:
+        eng.release(s)
+    eng.cache.audit()
