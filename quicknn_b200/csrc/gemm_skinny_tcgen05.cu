@@ -1,14 +1,21 @@
-// Matrix products of a few rows (decode batches of 9..128 sequences) against a big weight matrix:
-//     C[M, N] = A[M, K] * B[N, K]^T,  M <= 128,  bfloat16 in, float32 accumulation
-// These are bound by reading B once from HBM, and a matrix with few rows (N = hidden size) gives
-// too few output tiles to keep 148 SMs busy.  So a thread-block cluster of KS CTAs shares one
-// 128-row tile of B and splits K among its CTAs:
-//   * each CTA streams its part of K through a 4-stage TMA ring (A slab 128 x 64 with the rows
-//     beyond M zero-filled, B slab 128 x 64) and accumulates with tcgen05.mma in tensor memory;
-//   * its epilogue warps move the float32 accumulator (rows < M) to shared memory;
-//   * after a cluster barrier every CTA sums a slice of the columns over all CTAs of the cluster,
+// Matrix products of a few rows (decode batches of 17..128 sequences) against a big weight matrix:
+//     C[M, N] = X[M, K] * W[N, K]^T,  M <= 128,  bfloat16 in, float32 accumulation
+// These are bound by reading W once from HBM.  The product is taken transposed so that the WEIGHTS fill
+// the 128-row side of tcgen05.mma and the few activation rows are its N (a multiple of 16):
+//     D[128 weight rows x NM] += W_tile[128 x 64] * X_slab[NM x 64]^T
+// A stage of the TMA ring is then 16 KB of weights and only NM x 128 bytes of activations, so 5 to 9
+// stages fit and an SM keeps 80 to 144 KB of weights in flight (with the activations on the 128-row side a
+// stage was half activations, four stages fit, and the products ran at a third of the memory bandwidth).
+// A matrix with few rows (N = hidden size) gives too few tiles for 148 SMs, so a thread-block cluster of
+// KS CTAs shares one 128-row tile of W and splits K:
+//   * each CTA streams its part of K and accumulates in tensor memory (lane = weight row, column =
+//     activation row);
+//   * its epilogue warps move the float32 accumulator to shared memory (over the ring, which is idle by
+//     then);
+//   * after a cluster barrier every CTA sums a slice of the weight rows over all CTAs of the cluster,
 //     reading the others' shared memory (distributed shared memory), always in rank order, applies
 //     the epilogue (none, softcap -> float32, or gated activation) and stores.
+// For the gated epilogue a tile is 64 gate rows and the 64 matching up rows.
 // Reference: the matvec shaders of src/backends/vulkan/shaders/tensor.comp:87-120 (one row).
 // Every mbarrier wait is bounded in time; on expiry a status word is set, and the CTA still takes
 // part in both cluster barriers, frees its tensor memory and returns.
@@ -23,11 +30,9 @@ using namespace qnn;
 
 namespace {
 
-constexpr int BM = 128, BN = 128, BK = 64, STAGES = 4, UMMA_K = 16;
-constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int TMEM_COLS = 128;
+constexpr int BW = 128, BK = 64, MAX_STAGES = 10, UMMA_K = 16;     // BW: weight rows of a tile
+constexpr int W_BYTES = BW * BK * 2;
 constexpr int THREADS = 192;
-constexpr int PART_LD = BN + 4;                          // row pitch of the partial tile in floats
 constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -94,14 +99,6 @@ __device__ __forceinline__ void cluster_sync() {
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-__device__ __forceinline__ float ld_dsmem(unsigned local_addr, unsigned rank) {
-    unsigned remote;
-    float v;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
-    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
-    return v;
-}
-
 __device__ __forceinline__ float4 ld_dsmem4(unsigned local_addr, unsigned rank) {
     unsigned remote;
     float4 v;
@@ -111,35 +108,38 @@ __device__ __forceinline__ float4 ld_dsmem4(unsigned local_addr, unsigned rank) 
 }
 
 struct __align__(8) Barriers {
-    uint64_t full[STAGES];
-    uint64_t empty[STAGES];
+    uint64_t full[MAX_STAGES];
+    uint64_t empty[MAX_STAGES];
     uint64_t acc_ready;
     uint32_t tmem_base;
     uint32_t failed;
 };
 
 // grid.x = output tiles x KS, cluster (KS, 1, 1): the CTAs of a cluster share a tile, rank = K part.
+// NM: activation rows rounded up to 16; stages: depth of the ring; tmem_cols: power of two >= max(32, NM).
 template <int EPI>
 __global__ void __launch_bounds__(THREADS)
-gemm_skinny_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                           void* __restrict__ C, int M, int N, int K, int KS, float cap, int act,
-                           int* __restrict__ status) {
+gemm_skinny_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                           void* __restrict__ C, int M, int N, int K, int KS, int NM, int stages, int tmem_cols,
+                           float cap, int act, int* __restrict__ status) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    float* part = reinterpret_cast<float*>(smem + STAGES * STAGE_BYTES);        // [BM][PART_LD], rows < M used
-    Barriers* bars = reinterpret_cast<Barriers*>(smem + STAGES * STAGE_BYTES + BM * PART_LD * sizeof(float));
+    const int x_bytes = NM * BK * 2, stage_bytes = W_BYTES + x_bytes;
+    const int PL = NM + 4;                                   // row pitch of the partial tile in floats
+    float* part = reinterpret_cast<float*>(smem);            // [BW][PL], over the ring once the products are done
+    Barriers* bars = reinterpret_cast<Barriers*>(smem + (size_t)stages * stage_bytes);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const unsigned rank = cluster_rank();
     const int tile = blockIdx.x / KS;
     const int Nout = (EPI == EPI_GATED) ? N / 2 : N;
-    constexpr int OUT_COLS = (EPI == EPI_GATED) ? BN / 2 : BN;
-    const int n0 = tile * OUT_COLS;
+    constexpr int OUT_ROWS = (EPI == EPI_GATED) ? BW / 2 : BW;   // output columns (weight rows) of a tile
+    const int n0 = tile * OUT_ROWS;
     const int nk = (K + BK - 1) / BK;
     const int per = (nk + KS - 1) / KS;
     const int kb0 = min((int)rank * per, nk), kb1 = min(kb0 + per, nk);        // this CTA's slabs
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; ++s) {
+        for (int s = 0; s < stages; ++s) {
             mbar_init(smem_u32(&bars->full[s]), 1);
             mbar_init(smem_u32(&bars->empty[s]), 1);
         }
@@ -149,7 +149,7 @@ gemm_skinny_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(smem_u32(&bars->tmem_base)), "r"(TMEM_COLS) : "memory");
+                     ::"r"(smem_u32(&bars->tmem_base)), "r"(tmem_cols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -163,48 +163,50 @@ gemm_skinny_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
     if (warp == 0) {
         if (lane == 0) {
             for (int kb = kb0, it = 0; kb < kb1; ++kb, ++it) {
-                const int s = it % STAGES;
-                if (it >= STAGES && !mbar_wait(smem_u32(&bars->empty[s]), ((it / STAGES) - 1) & 1)) {
+                const int s = it % stages;
+                if (it >= stages && !mbar_wait(smem_u32(&bars->empty[s]), ((it / stages) - 1) & 1)) {
                     atomicOr(status, 1);
                     bars->failed = 1;
                     break;
                 }
                 const unsigned full = smem_u32(&bars->full[s]);
-                const unsigned a_dst = smem_u32(smem + s * STAGE_BYTES), b_dst = a_dst + A_BYTES;
-                mbar_expect_tx(full, STAGE_BYTES);
-                tma_load_2d(a_dst, &map_a, full, kb * BK, 0);
+                const unsigned w_dst = smem_u32(smem + (size_t)s * stage_bytes), x_dst = w_dst + W_BYTES;
+                mbar_expect_tx(full, (unsigned)stage_bytes);
                 if (EPI == EPI_GATED) {
-                    tma_load_2d(b_dst, &map_b, full, kb * BK, n0);                        // 64 gate rows
-                    tma_load_2d(b_dst + B_BYTES / 2, &map_b, full, kb * BK, Nout + n0);   // the 64 up rows
+                    tma_load_2d(w_dst, &map_w, full, kb * BK, n0);                        // 64 gate rows
+                    tma_load_2d(w_dst + W_BYTES / 2, &map_w, full, kb * BK, Nout + n0);   // the 64 up rows
                 } else {
-                    tma_load_2d(b_dst, &map_b, full, kb * BK, n0);
+                    tma_load_2d(w_dst, &map_w, full, kb * BK, n0);
                 }
+                tma_load_2d(x_dst, &map_x, full, kb * BK, 0);
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(BN >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
+            // D float32, A (weights) and B (activations) bfloat16, both K-major, N = NM, M = 128
+            const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(NM >> 3) << 17) | ((unsigned)(BW >> 4) << 24);
             for (int kb = kb0, it = 0; kb < kb1; ++kb, ++it) {
-                const int s = it % STAGES;
-                if (!mbar_wait(smem_u32(&bars->full[s]), (it / STAGES) & 1)) {
+                const int s = it % stages;
+                if (!mbar_wait(smem_u32(&bars->full[s]), (it / stages) & 1)) {
                     atomicOr(status, 2);
                     bars->failed = 1;
                     break;
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const unsigned a_addr = smem_u32(smem + s * STAGE_BYTES), b_addr = a_addr + A_BYTES;
+                const unsigned w_addr = smem_u32(smem + (size_t)s * stage_bytes), x_addr = w_addr + W_BYTES;
 #pragma unroll
                 for (int k = 0; k < BK / UMMA_K; ++k)
-                    umma_bf16(tmem, umma_desc(a_addr + k * UMMA_K * 2), umma_desc(b_addr + k * UMMA_K * 2), idesc,
+                    umma_bf16(tmem, umma_desc(w_addr + k * UMMA_K * 2), umma_desc(x_addr + k * UMMA_K * 2), idesc,
                               (it > 0 || k > 0) ? 1u : 0u);
                 umma_commit(smem_u32(&bars->empty[s]));
             }
             umma_commit(smem_u32(&bars->acc_ready));
         }
     } else {
-        // accumulator (rows < M) -> shared memory, float32; a CTA without slabs contributes zeros
+        // accumulator -> shared memory, float32, [weight row][activation row]; a CTA without slabs contributes
+        // zeros.  The ring is idle once acc_ready has come (every slab has been multiplied).
         const int quarter = warp & 3;
-        const int row = quarter * 32 + lane;
+        const int wrow = quarter * 32 + lane;
         bool ok = true;
         if (kb1 > kb0) {
             ok = mbar_wait(smem_u32(&bars->acc_ready), 0);
@@ -214,62 +216,62 @@ gemm_skinny_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
             }
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (quarter * 32 < M) {                               // warp-uniform: tcgen05.ld is warp-wide
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
-                uint32_t v[32];
-                if (kb1 > kb0 && ok) {
-                    tmem_ld32(tmem + ((unsigned)(quarter * 32) << 16) + c0, v);
-                } else {
+        for (int c0 = 0; c0 < NM; c0 += 32) {
+            uint32_t v[32];
+            if (kb1 > kb0 && ok) {
+                tmem_ld32(tmem + ((unsigned)(quarter * 32) << 16) + c0, v);
+            } else {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) v[j] = 0u;
-                }
-                if (row < M) {
-                    float4* dst = reinterpret_cast<float4*>(part + (size_t)row * PART_LD + c0);
-#pragma unroll
-                    for (int j = 0; j < 32; j += 4)
-                        dst[j / 4] = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]), __uint_as_float(v[j + 2]),
-                                                 __uint_as_float(v[j + 3]));
-                }
+                for (int j = 0; j < 32; ++j) v[j] = 0u;
             }
+            float4* dst = reinterpret_cast<float4*>(part + (size_t)wrow * PL + c0);
+#pragma unroll
+            for (int j = 0; j < 32; j += 4)
+                if (c0 + j < NM)
+                    dst[j / 4] = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]), __uint_as_float(v[j + 2]),
+                                             __uint_as_float(v[j + 3]));
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 1) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(tmem_cols) : "memory");
     }
     cluster_sync();      // every CTA's partial tile is complete and visible in the cluster
 
-    // Rank r finishes output columns [r * cpr, (r + 1) * cpr) of the tile, four at a time: sum over
-    // the ranks in ascending order, epilogue, store.  (OUT_COLS / KS is a multiple of 4: KS <= 8.)
+    // Rank r finishes weight rows [r * rpr, (r + 1) * rpr) of the tile, four activation rows at a time: sum
+    // over the ranks in ascending order, epilogue, store.  Consecutive threads take consecutive weight rows,
+    // i.e. consecutive elements of a row of C.
     {
-        const int cpr = OUT_COLS / KS;
-        const int c_lo = (int)rank * cpr;
-        const int groups = cpr / 4;
+        const int rpr = OUT_ROWS / KS;
+        const int r_lo = (int)rank * rpr;
+        const int mgroups = (M + 3) / 4;
         const unsigned part_addr = smem_u32(part);
-        for (int idx = threadIdx.x; idx < M * groups; idx += THREADS) {
-            const int row = idx / groups, col = c_lo + (idx % groups) * 4;
+        for (int idx = threadIdx.x; idx < rpr * mgroups; idx += THREADS) {
+            const int nn = r_lo + idx % rpr, m4 = (idx / rpr) * 4;
             float4 acc = make_float4(0.f, 0.f, 0.f, 0.f), up = make_float4(0.f, 0.f, 0.f, 0.f);
             for (int q = 0; q < KS; ++q) {
-                const float4 v = ld_dsmem4(part_addr + ((unsigned)row * PART_LD + col) * 4u, q);
+                const float4 v = ld_dsmem4(part_addr + ((unsigned)nn * PL + m4) * 4u, q);
                 acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
                 if (EPI == EPI_GATED) {
-                    const float4 w = ld_dsmem4(part_addr + ((unsigned)row * PART_LD + BN / 2 + col) * 4u, q);
+                    const float4 w = ld_dsmem4(part_addr + ((unsigned)(nn + BW / 2) * PL + m4) * 4u, q);
                     up.x += w.x; up.y += w.y; up.z += w.z; up.w += w.w;
                 }
             }
+            const int n = n0 + nn;
+            if (n >= Nout) continue;
             const float a4[4] = {acc.x, acc.y, acc.z, acc.w}, u4[4] = {up.x, up.y, up.z, up.w};
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                const int n = n0 + col + j;
-                if (n >= Nout) continue;
+                const int m = m4 + j;
+                if (m >= M) continue;
                 if (EPI == EPI_GATED) {
-                    reinterpret_cast<bf16*>(C)[(size_t)row * Nout + n] = __float2bfloat16_rn(activate_fast(a4[j], act) * u4[j]);
+                    reinterpret_cast<bf16*>(C)[(size_t)m * Nout + n] = __float2bfloat16_rn(activate_fast(a4[j], act) * u4[j]);
                 } else if (EPI == EPI_SOFTCAP) {
-                    reinterpret_cast<float*>(C)[(size_t)row * Nout + n] = softcap(a4[j], cap);
+                    reinterpret_cast<float*>(C)[(size_t)m * Nout + n] = softcap(a4[j], cap);
                 } else {
-                    reinterpret_cast<bf16*>(C)[(size_t)row * Nout + n] = __float2bfloat16_rn(a4[j]);
+                    reinterpret_cast<bf16*>(C)[(size_t)m * Nout + n] = __float2bfloat16_rn(a4[j]);
                 }
             }
         }
@@ -301,22 +303,24 @@ int make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) 
     const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
     const cuuint32_t estr[2] = {1, 1};
     const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? 0 : QNN_ERR_ARGUMENT;
 }
 
 template <int EPI>
-int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, void* C, int M, int N, int K, int KS, float cap, int act,
-           int* status, unsigned tiles, cudaStream_t st) {
+int launch(const CUtensorMap& map_x, const CUtensorMap& map_w, void* C, int M, int N, int K, int KS, int NM, int stages,
+           float cap, int act, int* status, unsigned tiles, cudaStream_t st) {
     auto kern = gemm_skinny_tcgen05_kernel<EPI>;
-    const size_t smem = (size_t)STAGES * STAGE_BYTES + (size_t)BM * PART_LD * sizeof(float) + sizeof(Barriers) + 1024;
+    const size_t smem = (size_t)stages * (W_BYTES + NM * BK * 2) + sizeof(Barriers) + 1024;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
+    int tmem_cols = 32;
+    while (tmem_cols < NM) tmem_cols *= 2;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(tiles * KS);
     cfg.blockDim = dim3(THREADS);
@@ -331,28 +335,29 @@ int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, void* C, int M, i
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = (qnn::pdl_enabled() && (long long)tiles * KS <= qnn::pdl_max_grid()) ? 2 : 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, map_a, map_b, C, M, N, K, KS, cap, act, status);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, map_x, map_w, C, M, N, K, KS, NM, stages, tmem_cols, cap, act, status);
     return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }
 
 }  // namespace
 
-// C = A B^T for M <= 128 rows.  epi 0: bfloat16 out; 1: softcap, float32 out; 2: gated (B = [gate; up],
+// C = X W^T for M <= 128 rows.  epi 0: bfloat16 out; 1: softcap, float32 out; 2: gated (W = [gate; up],
 // C is [M, N/2], bfloat16).  `status` as in qnn_gemm_tcgen05.  Returns QNN_ERR_UNSUPPORTED for sizes it
 // does not take.
 QNN_API int qnn_gemm_skinny_tcgen05(const void* A, const void* B, void* C, int M, int N, int K, int epi, float cap,
                                     int act, int* status, cudaStream_t st) {
     if (M <= 0 || N <= 0) return 0;
-    if (M > BM || K <= 0 || (K & 7) || ((((uintptr_t)A | (uintptr_t)B | (uintptr_t)C) & 15) != 0)) return QNN_ERR_UNSUPPORTED;
+    if (M > 128 || K <= 0 || (K & 7) || ((((uintptr_t)A | (uintptr_t)B | (uintptr_t)C) & 15) != 0)) return QNN_ERR_UNSUPPORTED;
     if (epi == EPI_GATED && (N & 1)) return QNN_ERR_ARGUMENT;
-    CUtensorMap map_a, map_b;
-    int rc = make_map(&map_a, A, M, K, BM);
+    const int NM = (M + 15) / 16 * 16;
+    CUtensorMap map_x, map_w;
+    int rc = make_map(&map_x, A, M, K, NM);
     if (rc) return rc;
-    rc = make_map(&map_b, B, N, K, epi == EPI_GATED ? BN / 2 : BN);
+    rc = make_map(&map_w, B, N, K, epi == EPI_GATED ? BW / 2 : BW);
     if (rc) return rc;
     const int Nout = epi == EPI_GATED ? N / 2 : N;
-    const int cols = epi == EPI_GATED ? BN / 2 : BN;
-    const long long tiles = (Nout + cols - 1) / cols;
+    const int rows = epi == EPI_GATED ? BW / 2 : BW;
+    const long long tiles = (Nout + rows - 1) / rows;
     if (tiles > 0x3fffffffLL) return QNN_ERR_UNSUPPORTED;
     // split K over a cluster when the tiles alone do not fill the GPU; every CTA keeps >= 2 slabs
     static int sm_count = 0;
@@ -364,11 +369,55 @@ QNN_API int qnn_gemm_skinny_tcgen05(const void* A, const void* B, void* C, int M
     }
     const int nk = (K + 63) / 64;
     int KS = 1;
-    while (KS < 8 && tiles * KS < sm_count && nk / (KS * 2) >= 2) KS *= 2;
+    while (KS < 8 && tiles * KS * 2 <= sm_count && nk / (KS * 2) >= 2) KS *= 2;      // the doubled grid still fits one round
+    // Depth of the ring: what fits beside the barriers, if the device then holds all clusters at once (clusters
+    // of 8 CTAs with 217 KB each do not: 15 of them fit); else, and with several rounds of CTAs anyway, half of
+    // that, so that two CTAs share an SM (and one's set-up and epilogue hide behind the other's main loop).
+    // The partial tile (128 x (NM + 4) floats) lies over the ring.
+    const int stage_bytes = W_BYTES + NM * BK * 2;
+    const int part_bytes = BW * (NM + 4) * 4;
+    const int per = (nk + KS - 1) / KS;
+    auto depth = [&](int kib) {
+        int st = (int)(((long long)kib * 1024 - 1024 - (long long)sizeof(Barriers)) / stage_bytes);
+        if (st > MAX_STAGES) st = MAX_STAGES;
+        if (st > per) st = per < 2 ? 2 : per;
+        while ((long long)st * stage_bytes < part_bytes) ++st;
+        return st;
+    };
+    int stages = depth(227);
+    if (tiles * KS > 2ll * sm_count) {
+        stages = depth(113);
+    } else if (KS > 1) {
+        static int fits[4][MAX_STAGES + 1];                // clusters of 2^i CTAs that the device holds, by depth (0: not asked)
+        int ki = KS == 2 ? 1 : (KS == 4 ? 2 : 3);
+        if (fits[ki][stages] == 0) {
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(KS * 64);
+            cfg.blockDim = dim3(THREADS);
+            cfg.dynamicSmemBytes = (size_t)stages * stage_bytes + sizeof(Barriers) + 1024;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeClusterDimension;
+            attr[0].val.clusterDim.x = KS;
+            attr[0].val.clusterDim.y = 1;
+            attr[0].val.clusterDim.z = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
+            int n = 0;
+            (void)cudaFuncSetAttribute(gemm_skinny_tcgen05_kernel<EPI_NONE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+            if (cudaOccupancyMaxActiveClusters(&n, gemm_skinny_tcgen05_kernel<EPI_NONE>, &cfg) != cudaSuccess || n <= 0) {
+                (void)cudaGetLastError();
+                n = -1;
+            }
+            fits[ki][stages] = n;
+        }
+        if (fits[ki][stages] < tiles) stages = depth(113);
+    }
+    if (stages > MAX_STAGES || (long long)stages * stage_bytes + (long long)sizeof(Barriers) + 1024 > 227 * 1024)
+        return QNN_ERR_UNSUPPORTED;
     switch (epi) {
-        case EPI_NONE: return launch<EPI_NONE>(map_a, map_b, C, M, N, K, KS, cap, act, status, (unsigned)tiles, st);
-        case EPI_SOFTCAP: return launch<EPI_SOFTCAP>(map_a, map_b, C, M, N, K, KS, cap, act, status, (unsigned)tiles, st);
-        case EPI_GATED: return launch<EPI_GATED>(map_a, map_b, C, M, N, K, KS, cap, act, status, (unsigned)tiles, st);
+        case EPI_NONE: return launch<EPI_NONE>(map_x, map_w, C, M, N, K, KS, NM, stages, cap, act, status, (unsigned)tiles, st);
+        case EPI_SOFTCAP: return launch<EPI_SOFTCAP>(map_x, map_w, C, M, N, K, KS, NM, stages, cap, act, status, (unsigned)tiles, st);
+        case EPI_GATED: return launch<EPI_GATED>(map_x, map_w, C, M, N, K, KS, NM, stages, cap, act, status, (unsigned)tiles, st);
     }
     return QNN_ERR_ARGUMENT;
 }

@@ -189,7 +189,7 @@ def qkv_rope_cache_fusable(x: torch.Tensor, w: torch.Tensor, head_dim: int, rot_
         return False
     if M > SKINNY_MAX_ROWS or K % 8 or head_dim % 16 or rot_dim != head_dim:
         return False
-    return not (USE_TCGEN05 and M >= SKINNY_TCGEN05_FROM and w.shape[0] * K >= SKINNY_TCGEN05_MIN_WEIGHTS)
+    return not _takes_skinny_tcgen05(M, w.shape[0], K)
 
 
 def qkv_rope_cache(x: torch.Tensor, w: torch.Tensor, n_heads: int, n_kv: int, head_dim: int,
@@ -311,9 +311,15 @@ def gemm_skinny_tcgen05(x: torch.Tensor, w: torch.Tensor, *, epilogue: int = EPI
 USE_TCGEN05 = os.environ.get("QNN_GEMM", "tcgen05") != "cublas"
 # From this many rows on, products against big matrices (>= 2^24 weights) take the cluster split-K
 # tcgen05 kernel instead of the mma.sync small-M kernel (measured on B200: at 16 rows and below, and
-# for the small q/k/v and o matrices up to 64 rows, the mma.sync kernel is the faster one).
+# for the small q/k/v and o matrices up to about 30 rows, the mma.sync kernel is the faster one).
 SKINNY_TCGEN05_FROM = int(os.environ.get("QNN_SKINNY_TCGEN05_FROM", "17"))
 SKINNY_TCGEN05_MIN_WEIGHTS = 1 << 24
+SKINNY_TCGEN05_ANY_FROM = 32          # from this many rows on, the small matrices too (q|k|v at 32 rows: 10.7 against 13.0 us)
+
+
+def _takes_skinny_tcgen05(M: int, N: int, K: int) -> bool:
+    return USE_TCGEN05 and SKINNY_TCGEN05_FROM <= M <= 128 and (M >= SKINNY_TCGEN05_ANY_FROM or
+                                                                N * K >= SKINNY_TCGEN05_MIN_WEIGHTS)
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, *, epilogue: int = EPI_NONE, cap: Optional[float] = None,
@@ -353,8 +359,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, *, epilogue: int = EPI_NONE, cap: O
     # bfloat16
     if K % 8:
         raise _lib.KernelError(f"bfloat16 products need an inner size that is a multiple of 8 (got {K})")
-    if USE_TCGEN05 and SKINNY_TCGEN05_FROM <= M <= 128 and (M > SKINNY_MAX_ROWS or N * K >= SKINNY_TCGEN05_MIN_WEIGHTS) \
-            and out_dtype == (torch.float32 if epilogue == EPI_SOFTCAP else torch.bfloat16):
+    if _takes_skinny_tcgen05(M, N, K) and out_dtype == (torch.float32 if epilogue == EPI_SOFTCAP else torch.bfloat16):
         y = gemm_skinny_tcgen05(x, w, epilogue=epilogue, cap=cap, activation=activation)
         if y is not None:
             return y
