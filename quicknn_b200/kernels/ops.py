@@ -310,9 +310,10 @@ def gemm_skinny_tcgen05(x: torch.Tensor, w: torch.Tensor, *, epilogue: int = EPI
 
 USE_TCGEN05 = os.environ.get("QNN_GEMM", "tcgen05") != "cublas"
 # From this many rows on, products against big matrices (>= 2^24 weights) take the cluster split-K
-# tcgen05 kernel instead of the mma.sync small-M kernel (measured on B200: at 16 rows and below, and
-# for the small q/k/v and o matrices up to about 30 rows, the mma.sync kernel is the faster one).
-SKINNY_TCGEN05_FROM = int(os.environ.get("QNN_SKINNY_TCGEN05_FROM", "17"))
+# tcgen05 kernel instead of the mma.sync small-M kernel (measured on B200: up to 8 rows, one 8-row
+# tile of mma.sync, and for the small q/k/v and o matrices up to about 30 rows, the mma.sync kernel is
+# the faster one; at 12 and 16 rows the step gains 8-9 % with the tcgen05 kernel for the big matrices).
+SKINNY_TCGEN05_FROM = int(os.environ.get("QNN_SKINNY_TCGEN05_FROM", "9"))
 SKINNY_TCGEN05_MIN_WEIGHTS = 1 << 24
 SKINNY_TCGEN05_ANY_FROM = 32          # from this many rows on, the small matrices too (q|k|v at 32 rows: 10.7 against 13.0 us)
 
