@@ -56,7 +56,7 @@ class Engine:
         self._resident = sms * max(1, min(8, 512 // max(1, head)))
         self.decode_splits = self._fixed_splits or self._max_splits
         self._scratch: Dict[int, Tuple[torch.Tensor, torch.Tensor]] = {}
-        self._decode_state: Dict[int, dict] = {}
+        self._decode_state: Dict[tuple, dict] = {}
         self.use_graphs = True
         self.graph_kernels_replayed = 0
         self.error_flag = torch.zeros(1, dtype=torch.int32, device=self.device)
@@ -228,6 +228,11 @@ class Engine:
         st["graph"].replay()
         self.graph_kernels_replayed += st["kernels"]
         return st["logits"]
+
+    def forget_tail(self, tail) -> None:
+        """Drop the graphs that were captured with ``tail`` (a sampler that is no longer used)."""
+        for key in [k for k in self._decode_state if k[1] == id(tail)]:
+            del self._decode_state[key]
 
     def kernels_launched(self) -> int:
         """Kernels of this library launched so far, eagerly or inside replayed graphs."""

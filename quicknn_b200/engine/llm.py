@@ -154,6 +154,8 @@ class LLM:
         s = self._samplers.get(key)
         if s is None:
             if len(self._samplers) > 4:
+                for old in self._samplers.values():
+                    self.engine.forget_tail(old)          # and the decode graphs that embed them
                 self._samplers.clear()
             s = Sampler(self.model.spec.embedding.vocab_size, self.max_batch, options, self.engine.device)
             self._samplers[key] = s

@@ -228,3 +228,21 @@ def test_step_rules_and_loud_failures(folders):
     with pytest.raises(Exception):
         from quicknn_b200.engine import Model
         Model.from_folder(folders("A", "float32"), "float32", "cpu").forward(None, None)
+
+
+def test_many_option_sets_do_not_pile_up_graphs(folders):
+    """Every distinct option set gets a sampler and decode graphs of its own; the entry point keeps a
+    handful and lets the engine drop the graphs of those it forgets."""
+    from quicknn_b200.engine import LLM
+    from quicknn_b200.sampling import GenerationOptions
+    llm = LLM(folders("A", "bfloat16"), max_context=64, max_batch=2, dtype="bfloat16")
+    prompts = prompts_for("A", [4, 7])
+    first = None
+    for seed in range(8):
+        out = llm.generate(prompts, GenerationOptions(max_new_tokens=4, temperature=0.7, seed=seed), stop_ids=[])
+        first = first or [r.tokens for r in out]
+        assert len(llm._samplers) <= 5
+        assert len({k[1] for k in llm.engine._decode_state}) <= 5
+    again = llm.generate(prompts, GenerationOptions(max_new_tokens=4, temperature=0.7, seed=0), stop_ids=[])
+    assert [r.tokens for r in again] == first
+    assert llm.engine.cache.slots.live() == []
