@@ -1,13 +1,13 @@
-// Prefill attention on the 5th-generation tensor cores, bfloat16, head size 256: whole prompts
+// Prefill attention on the 5th-generation tensor cores, bfloat16, head sizes 64, 128 and 256: whole prompts
 // packed one after another, causal, optional sliding window, optional tanh softcap, grouped
 // query heads.  Formulas: attention.cu (reference: src/backends/vulkan/shaders/attention.comp:18-38).
 //
 // A CTA owns 128 query rows of one sequence and one query head and walks over 64-key tiles:
-//   warp 0 (one lane)  TMA producer: Q once (four 128 x 64 boxes), then K and V tiles (four 64 x 64
+//   warp 0 (one lane)  TMA producer: Q once (hd/64 boxes of 128 x 64), then K and V tiles (hd/64 boxes of 64 x 64
 //                      boxes each) into two 2-stage rings (a K stage is free once S has been formed, a V
 //                      stage only after the second product); everything 128-byte swizzled.
-//   warp 1 (one lane)  tensor-core issue:  S_j[128 x 64] = Q K_j^T   (16 tcgen05.mma, K-major operands)
-//                                           O[128 x 256] += P_j V_j   ( 4 tcgen05.mma, V as MN-major operand)
+//   warp 1 (one lane)  tensor-core issue:  S_j[128 x 64] = Q K_j^T   (hd/16 tcgen05.mma, K-major operands)
+//                                           O[128 x hd]  += P_j V_j   ( 4 tcgen05.mma, V as MN-major operand)
 //                      S_{j+1} is issued before P_j V_j, so it runs while the softmax of tile j does.
 //   warps 2..5         softmax, one thread per query row (tensor-memory lane = row, so row maxima and
 //                      sums need no shuffles): tcgen05.ld of S, scale, softcap, mask, exp; P_j goes to
@@ -19,7 +19,7 @@
 // many keys as the first) the grid is launched as clusters of two: the CTAs of a pair take alternate key
 // tiles of the same query tile; when both are done, rank 1 pushes its (reference maximum, sum, O) into
 // rank 0's shared memory through the cluster's distributed shared memory and rank 0 merges and writes.
-// Tensor memory: S double-buffered (2 x 64 columns), O 256 columns.  All softmax arithmetic is float32.
+// Tensor memory: S double-buffered (2 x 64 columns), O one column per head element.  All softmax arithmetic is float32.
 // Keys of other sequences that a tile drags in are masked; rows beyond the sequence are never stored.
 // Every mbarrier wait is bounded in time; on expiry a status word is set and the CTA winds down.
 #include "common.cuh"
@@ -30,15 +30,13 @@ using namespace qnn;
 
 namespace {
 
-constexpr int HD = 256, BM = 128, BN = 64, KV_STAGES = 2, UMMA_K = 16;
-constexpr int Q_BYTES = BM * HD * 2;                 // 64 KB: four [128 x 64] blocks
-constexpr int K_BYTES = BN * HD * 2, V_BYTES = BN * HD * 2;   // 32 KB each: four [64 x 64] blocks
+constexpr int BM = 128, BN = 64, KV_STAGES = 2, UMMA_K = 16;
 constexpr int P_BYTES = BM * BN * 2;                 // 16 KB
 constexpr int THREADS = 192;
-constexpr int TMEM_COLS = 512, S_COL = 0, O_COL = 128;
+constexpr int S_COL = 0, O_COL = 128;             // tensor-memory columns of S (two buffers of 64) and of O
 constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;
 constexpr float RESCALE_STEP = 8.f;
-constexpr int MERGE_O_BYTES = BM * HD * 4, MERGE_ML_BYTES = BM * 8;   // what rank 1 of a pair hands to rank 0
+constexpr int MERGE_ML_BYTES = BM * 8;               // (reference maximum, sum) per row that rank 1 of a pair hands to rank 0
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
@@ -161,12 +159,21 @@ struct __align__(8) Barriers {
 
 __device__ __forceinline__ bool has_failed(Barriers* b) { return *reinterpret_cast<volatile uint32_t*>(&b->failed) != 0; }
 
+// HD: head size, 64, 128 or 256 (the operands are walked in blocks of 64 head elements = 128 bytes)
+template <int HD>
 __global__ void __launch_bounds__(THREADS)
 attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
                             bf16* __restrict__ out, size_t out_stride, const int* __restrict__ seq_row0,
                             const int* __restrict__ seq_len, int nq, int nkv, float scale, float cap, int window,
                             int* __restrict__ status, int split) {
     pdl_wait();
+    constexpr int Q_BYTES = BM * HD * 2;                             // HD / 64 blocks of [128 x 64]
+    constexpr int K_BYTES = BN * HD * 2, V_BYTES = BN * HD * 2;      // HD / 64 blocks of [64 x 64] each
+    constexpr int MERGE_O_BYTES = BM * HD * 4;                       // O of rank 1 of a pair, float32
+    constexpr int TMEM_COLS = HD > 128 ? 512 : 256;                  // 128 for S and HD for O, a power of two
+    constexpr int CPR = HD / 8;                                      // 16-byte chunks of a bfloat16 output row
+    static_assert(HD == 64 || HD == 128 || HD == 256, "head sizes 64, 128, 256");
+    static_assert(MERGE_O_BYTES <= KV_STAGES * (K_BYTES + V_BYTES) && MERGE_ML_BYTES <= 2 * P_BYTES, "the pair's hand-over fits");
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     unsigned char* sQ = smem;
@@ -292,7 +299,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     } else if (warp == 1) {
         if (lane == 0) {
             // ---- tensor-core issue -----------------------------------------------------------------
-            // S: M 128, N 64, both operands K-major.  O: M 128, N 256, A (P) K-major, B (V) MN-major.
+            // S: M 128, N 64, both operands K-major.  O: M 128, N hd, A (P) K-major, B (V) MN-major.
             const unsigned idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(BN >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
             const unsigned idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((unsigned)(HD >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
             bool ok = mbar_wait(smem_u32(&bars->q_full), 0);
@@ -521,7 +528,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     if (warp >= 2 && rank == 0) {
         // Every product is done, so the Q tile's shared memory is free: each thread leaves its row there as
         // bfloat16 (16-byte chunks XOR-ed with the row number, so that neither side conflicts), and the
-        // warps then write whole 512-byte rows to global memory.
+        // warps then write whole rows of the head to global memory.
         const bool good = alive && !__any_sync(0xffffffffu, has_failed(bars));
         if (good) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -563,22 +570,23 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     pk.y = pack_bf16(o0[c8 * 8 + 2], o0[c8 * 8 + 3]);
                     pk.z = pack_bf16(o0[c8 * 8 + 4], o0[c8 * 8 + 5]);
                     pk.w = pack_bf16(o0[c8 * 8 + 6], o0[c8 * 8 + 7]);
-                    *reinterpret_cast<uint4*>(orow + (((c0 / 8 + c8) ^ (rloc & 31)) << 4)) = pk;
+                    *reinterpret_cast<uint4*>(orow + (((c0 / 8 + c8) ^ (rloc & (CPR - 1))) << 4)) = pk;
                     pk.x = pack_bf16(o1[c8 * 8 + 0], o1[c8 * 8 + 1]);
                     pk.y = pack_bf16(o1[c8 * 8 + 2], o1[c8 * 8 + 3]);
                     pk.z = pack_bf16(o1[c8 * 8 + 4], o1[c8 * 8 + 5]);
                     pk.w = pack_bf16(o1[c8 * 8 + 6], o1[c8 * 8 + 7]);
-                    *reinterpret_cast<uint4*>(orow + (((c0 / 8 + 4 + c8) ^ (rloc & 31)) << 4)) = pk;
+                    *reinterpret_cast<uint4*>(orow + (((c0 / 8 + 4 + c8) ^ (rloc & (CPR - 1))) << 4)) = pk;
                 }
             }
         }
         __syncwarp();      // a warp stores the 32 rows that its own lanes wrote
         if (good) {
-            for (int rr = 0; rr < 32; ++rr) {
-                const int rl = quarter * 32 + rr;
-                if (r0 + rl >= len) break;
-                const uint4 pk = *reinterpret_cast<const uint4*>(sQ + rl * (HD * 2) + (lane << 4));
-                bf16* dst = out + (size_t)(row0 + r0 + rl) * out_stride + (size_t)h * HD + ((lane ^ (rl & 31)) << 3);
+            constexpr int RPI = 32 / CPR;                        // rows that one warp-wide store covers
+            for (int rr = 0; rr < 32; rr += RPI) {
+                const int rl = quarter * 32 + rr + lane / CPR, pos = lane % CPR;
+                if (r0 + rl >= len) continue;
+                const uint4 pk = *reinterpret_cast<const uint4*>(sQ + rl * (HD * 2) + (pos << 4));
+                bf16* dst = out + (size_t)(row0 + r0 + rl) * out_stride + (size_t)h * HD + ((pos ^ (rl & (CPR - 1))) << 3);
                 *reinterpret_cast<uint4*>(dst) = pk;
             }
         }
@@ -620,27 +628,18 @@ int make_map(CUtensorMap* map, const void* base, long long rows, long long width
     return r == CUDA_SUCCESS ? 0 : QNN_ERR_ARGUMENT;
 }
 
-}  // namespace
-
-// qkv: this step's projections, [T rows, (nq + 2 nkv) * 256] bfloat16, rotated; sequence b occupies rows
-// seq_row0[b] .. + seq_len[b] - 1.  Returns QNN_ERR_UNSUPPORTED unless head_dim is 256.  `status` as in
-// qnn_gemm_tcgen05 (bits: 2 K/V wait, 4 S wait, 8 P wait, 16 ring wait, 32 Q wait, 64 product wait, 128 wait for the other half of a pair).
-QNN_API int qnn_attn_prefill_tcgen05(const void* qkv, long long total_rows, void* out, long long out_stride,
-                                     const int* seq_row0, const int* seq_len, int B, int max_len, int nq, int nkv,
-                                     int hd, float scale, float cap, int window, int* status, cudaStream_t st) {
-    if (B <= 0 || max_len <= 0) return 0;
-    if (hd != HD) return QNN_ERR_UNSUPPORTED;
-    if (nkv <= 0 || nq % nkv) return QNN_ERR_ARGUMENT;
-    if (B > 65535 || (max_len + BM - 1) / BM > 65535) return QNN_ERR_UNSUPPORTED;
-    if (((uintptr_t)qkv & 15) || ((uintptr_t)out & 15) || (out_stride * 2) % 16) return QNN_ERR_UNSUPPORTED;
+template <int HD>
+int launch_attn(const void* qkv, long long total_rows, void* out, long long out_stride, const int* seq_row0,
+                const int* seq_len, int B, int max_len, int nq, int nkv, float scale, float cap, int window,
+                int* status, cudaStream_t st) {
     const long long width = (long long)(nq + 2 * nkv) * HD;
     CUtensorMap map_q, map_kv;
     int rc = make_map(&map_q, qkv, total_rows, width, BM);
     if (rc) return rc;
     rc = make_map(&map_kv, qkv, total_rows, width, BN);
     if (rc) return rc;
-    const size_t smem = (size_t)Q_BYTES + KV_STAGES * (K_BYTES + V_BYTES) + 2 * P_BYTES + sizeof(Barriers) + 1024;
-    auto kern = attn_prefill_tcgen05_kernel;
+    const size_t smem = (size_t)BM * HD * 2 + (size_t)KV_STAGES * 2 * BN * HD * 2 + 2 * P_BYTES + sizeof(Barriers) + 1024;
+    auto kern = attn_prefill_tcgen05_kernel<HD>;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -657,9 +656,9 @@ QNN_API int qnn_attn_prefill_tcgen05(const void* qkv, long long total_rows, void
     }
     // Few CTAs and several query tiles: pairs of CTAs share a query tile's keys (see the head of this file).
     // With many CTAs the heavy ones are started first and the rest fills in behind them.
+    // (measured at 8 heads of 256: 1024 tokens 29.9 -> 26.8 us, 2048 tokens 51.8 -> 49.1 us; with 4096 tokens,
+    // 256 CTAs unsplit, pairs were slower, 126 against 94 us)
     static int split_ok = -1;                      // the device holds a pair of these CTAs (asked once)
-    // (measured at 8 heads: 1024 tokens 29.9 -> 26.8 us, 2048 tokens 51.8 -> 49.1 us; with 4096 tokens, 256 CTAs
-    // unsplit, pairs were slower, 126 against 94 us)
     const bool want_split = ntq >= 2 && (long long)ntq * B * nq <= sm_count && !getenv("QNN_ATTN_NO_SPLIT");
     cudaLaunchConfig_t cfg = {};
     cfg.blockDim = dim3(THREADS);
@@ -684,7 +683,7 @@ QNN_API int qnn_attn_prefill_tcgen05(const void* qkv, long long total_rows, void
     }
     const int split = (want_split && split_ok == 1) ? 1 : 0;
     cfg.gridDim = dim3((unsigned)(split ? 2 * nq : nq), B, ntq);
-    const long long ctas = (long long)cfg.gridDim.x * B * nq;
+    const long long ctas = (long long)cfg.gridDim.x * B * ntq;
     const bool pdl = qnn::pdl_enabled() && ctas <= qnn::pdl_max_grid();
     if (split) {
         if (!pdl) cfg.attrs = attr + 1;
@@ -695,4 +694,27 @@ QNN_API int qnn_attn_prefill_tcgen05(const void* qkv, long long total_rows, void
     cudaError_t e = cudaLaunchKernelEx(&cfg, kern, map_q, map_kv, (bf16*)out, (size_t)out_stride, seq_row0, seq_len, nq,
                                        nkv, scale, cap, window, status, split);
     return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
+}
+
+}  // namespace
+
+// qkv: this step's projections, [T rows, (nq + 2 nkv) * hd] bfloat16, rotated; sequence b occupies rows
+// seq_row0[b] .. + seq_len[b] - 1.  Head sizes 64, 128 and 256; QNN_ERR_UNSUPPORTED for others.  `status` as in
+// qnn_gemm_tcgen05 (bits: 2 K/V wait, 4 S wait, 8 P wait, 16 ring wait, 32 Q wait, 64 product wait, 128 wait for
+// the other half of a pair).
+QNN_API int qnn_attn_prefill_tcgen05(const void* qkv, long long total_rows, void* out, long long out_stride,
+                                     const int* seq_row0, const int* seq_len, int B, int max_len, int nq, int nkv,
+                                     int hd, float scale, float cap, int window, int* status, cudaStream_t st) {
+    if (B <= 0 || max_len <= 0) return 0;
+    if (hd != 64 && hd != 128 && hd != 256) return QNN_ERR_UNSUPPORTED;
+    if (nkv <= 0 || nq % nkv) return QNN_ERR_ARGUMENT;
+    if (B > 65535 || nq > 32767 || (max_len + BM - 1) / BM > 65535) return QNN_ERR_UNSUPPORTED;
+    if (((uintptr_t)qkv & 15) || ((uintptr_t)out & 15) || (out_stride * 2) % 16) return QNN_ERR_UNSUPPORTED;
+#define QNN_ATTN_ARGS qkv, total_rows, out, out_stride, seq_row0, seq_len, B, max_len, nq, nkv, scale, cap, window, status, st
+    switch (hd) {
+        case 64: return launch_attn<64>(QNN_ATTN_ARGS);
+        case 128: return launch_attn<128>(QNN_ATTN_ARGS);
+        default: return launch_attn<256>(QNN_ATTN_ARGS);
+    }
+#undef QNN_ATTN_ARGS
 }

@@ -404,7 +404,7 @@ def attn_prefill(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, tok_
             and head_dim in (64, 128, 256)):
         _req(seq_row0, "seq_row0", torch.int32, 1)
         _req(seq_len, "seq_len", torch.int32, 1)
-        if head_dim == 256 and ATTN_TCGEN05:
+        if ATTN_TCGEN05:
             code = L.qnn_attn_prefill_tcgen05(
                 _p(qkv), T, _p(out), out.shape[1], _p(seq_row0), _p(seq_len), seq_row0.numel(), int(max_len),
                 n_heads, n_kv, head_dim, float(scale), float(cap or 0.0), int(window or 0),

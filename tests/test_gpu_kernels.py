@@ -383,10 +383,39 @@ def test_attention_prefill(ops, dtype, nq, nkv, hd, window, cap):
 
 @pytest.mark.parametrize("nq,nkv,hd", [(8, 4, 256), (4, 1, 128), (6, 2, 64)])
 @pytest.mark.parametrize("window,cap", [(None, 50.0), (100, None), (64, 30.0)])
-def test_attention_prefill_tensor_core_kernel_long_unequal(ops, nq, nkv, hd, window, cap):
-    """Sequences that span several 64-row tiles, of unequal lengths, against the plain attention."""
+@pytest.mark.parametrize("kernel", ["tcgen05", "mma"])
+def test_attention_prefill_tensor_core_kernel_long_unequal(ops, monkeypatch, kernel, nq, nkv, hd, window, cap):
+    """Sequences that span several 64-row tiles, of unequal lengths, against the plain attention; both
+    tensor-core kernels (tcgen05, and the mma.sync one that stands behind it)."""
+    monkeypatch.setattr(ops, "ATTN_TCGEN05", kernel == "tcgen05")
     rng = np.random.default_rng(hd + (window or 0))
     lens = [200, 1, 65, 130, 64]
+    Tn = sum(lens)
+    qkv = bf16_round(rng.normal(size=(Tn, (nq + 2 * nkv) * hd)))
+    pos = np.concatenate([np.arange(n) for n in lens]).astype(np.int32)
+    starts = np.cumsum([0] + lens[:-1]).astype(np.int32)
+    row0 = np.concatenate([np.full(n, s) for n, s in zip(lens, starts)]).astype(np.int32)
+    scale = 1.0 / math.sqrt(hd)
+    out = ops.attn_prefill(T(qkv, torch.bfloat16), nq, nkv, hd, T(pos, torch.int32), T(row0, torch.int32), scale, cap,
+                           window, T(starts, torch.int32), T(np.array(lens, np.int32), torch.int32), max(lens))
+    r = 0
+    for n in lens:
+        blk = qkv[r:r + n]
+        q = blk[:, :nq * hd].reshape(n, nq, hd)
+        k = blk[:, nq * hd:(nq + nkv) * hd].reshape(n, nkv, hd)
+        v = blk[:, (nq + nkv) * hd:].reshape(n, nkv, hd)
+        ref = P.attention(q, k, v, scale, cap, window).reshape(n, -1)
+        assert_close(out[r:r + n], ref, torch.bfloat16, f"sequence of {n}", mult=4)
+        r += n
+
+
+@pytest.mark.parametrize("hd", [64, 128, 256])
+def test_attention_prefill_tcgen05_with_more_ctas_than_sms(ops, hd):
+    """Enough heads, sequences and query tiles that the kernel runs one CTA per query tile (no pairs),
+    several key tiles each, with a window that begins inside a tile."""
+    nq, nkv, window, cap = 20, 4, 150, 40.0
+    rng = np.random.default_rng(hd)
+    lens = [300, 150, 260, 129]
     Tn = sum(lens)
     qkv = bf16_round(rng.normal(size=(Tn, (nq + 2 * nkv) * hd)))
     pos = np.concatenate([np.arange(n) for n in lens]).astype(np.int32)
