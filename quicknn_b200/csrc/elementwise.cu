@@ -154,11 +154,33 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const void* __
                                        const void* __restrict__ w_post, int w_post_dt, float eps_post, float off_post,
                                        const void* __restrict__ w_next, int w_next_dt, float eps_next, float off_next,
                                        void* __restrict__ out_next, int out_dt, int H) {
-    pdl_wait();
     __shared__ float red[32];
     const size_t base = (size_t)blockIdx.x * H;
     const int nchunks = H >> 3;
     float yv[CH][8], rv[CH][8], g1[CH][8];
+    // The norm weights are written by no kernel of the step: they are fetched before the wait for the
+    // kernel in front, so that their latency is hidden behind its tail (with one chunk per thread, the few
+    // rows of a decode step, also those of the second norm, which otherwise sit behind two reductions).
+    constexpr bool EARLY2 = CH == 1;
+    float g2e[EARLY2 ? 8 : 1];
+#pragma unroll
+    for (int i = 0; i < CH; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        if (c < nchunks) {
+            load8_as_f(w_post, w_post_dt, (size_t)c * 8, g1[i]);
+        } else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) g1[i][e] = 0.f;
+        }
+    }
+    if constexpr (EARLY2) {
+        if (w_next != nullptr && (int)threadIdx.x < nchunks) load8_as_f(w_next, w_next_dt, (size_t)threadIdx.x * 8, g2e);
+        else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) g2e[e] = 0.f;
+        }
+    }
+    pdl_wait();
     float ss = 0.f;
 #pragma unroll
     for (int i = 0; i < CH; ++i) {
@@ -166,10 +188,9 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const void* __
         if (c < nchunks) {
             load8_as_f(y, y_dt, base + c * 8, yv[i]);
             load8_as_f(resid, QNN_DT_F32, base + c * 8, rv[i]);
-            load8_as_f(w_post, w_post_dt, (size_t)c * 8, g1[i]);
         } else {
 #pragma unroll
-            for (int e = 0; e < 8; ++e) yv[i][e] = rv[i][e] = g1[i][e] = 0.f;
+            for (int e = 0; e < 8; ++e) yv[i][e] = rv[i][e] = 0.f;
         }
 #pragma unroll
         for (int e = 0; e < 8; ++e) ss += yv[i][e] * yv[i][e];
@@ -195,7 +216,12 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const void* __
         const int c = threadIdx.x + i * blockDim.x;
         if (c < nchunks) {
             float g2[8], o[8];
-            load8_as_f(w_next, w_next_dt, (size_t)c * 8, g2);
+            if constexpr (EARLY2) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) g2[e] = g2e[e];
+            } else {
+                load8_as_f(w_next, w_next_dt, (size_t)c * 8, g2);
+            }
 #pragma unroll
             for (int e = 0; e < 8; ++e) o[e] = rv[i][e] * inv2 * (g2[e] + off_next);
             store8_from_f(out_next, out_dt, base + c * 8, o);
