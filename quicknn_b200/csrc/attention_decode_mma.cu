@@ -123,7 +123,6 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, size_t q_stride, const bf16* 
                        int page_size, int ring, const int* __restrict__ slots, const int* __restrict__ slot_len,
                        int nq, int nkv, float scale, float cap, int window, float* __restrict__ part_o,
                        float* __restrict__ part_ml, int n_splits, bf16* __restrict__ out, size_t out_stride) {
-    pdl_wait();
     const bool CLUSTER = out != nullptr;         // launched as clusters of n_splits CTAs that merge their ranges
     constexpr int KSTEPS = HD / 16;              // k16 steps of S^T, and 16-row tiles of O^T
     constexpr int CH = HD / 8;                   // 16-byte chunks per row
@@ -155,6 +154,25 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, size_t q_stride, const bf16* 
         begin = kbeg + split * per;
         end = min(begin + per, n);
     }
+    // The sequence's length and page ids come from the host before the step, not from the kernel in front:
+    // this chain of dependent loads (slot -> length -> page row) runs before the wait for that kernel, whose
+    // query row and newest key are read only after it.  (Asking for the first key tiles before the wait as
+    // well, all but the one with the newest key, measured no further gain.)
+    const int page_shift = 31 - __clz(page_size), page_mask = page_size - 1;
+    const int rb0 = ring > 0 ? begin % ring : begin;
+    const int first_pg = rb0 >> page_shift;
+    if (begin < end) {
+        const int* page_row = page_table + (size_t)slot * max_pages;
+        const int npg = ((rb0 + (end - begin) - 1) >> page_shift) - first_pg + 1;
+        const int ring_pages = ring > 0 ? ring >> page_shift : 0x7fffffff;
+        for (int u = threadIdx.x; u < npg; u += blockDim.x) {
+            int pi = first_pg + u;
+            if (pi >= ring_pages) pi -= ring_pages;
+            pages_s[u] = page_row[pi];
+        }
+    }
+    pdl_wait();
+    __syncthreads();
     if (begin < end) {
         // Q^T fragments: b0 = Q[head g][16 ks + 2t, +1], b1 = Q[head g][16 ks + 8 + 2t, +1]
         uint32_t qf[KSTEPS][2];
@@ -167,18 +185,6 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, size_t q_stride, const bf16* 
                 qf[ks][1] = have ? qrow[ks * 8 + 4 + t] : 0u;
             }
         }
-        const int page_shift = 31 - __clz(page_size), page_mask = page_size - 1;
-        const int* page_row = page_table + (size_t)slot * max_pages;
-        const int rb0 = ring > 0 ? begin % ring : begin;
-        const int first_pg = rb0 >> page_shift;
-        const int npg = ((rb0 + (end - begin) - 1) >> page_shift) - first_pg + 1;
-        const int ring_pages = ring > 0 ? ring >> page_shift : 0x7fffffff;
-        for (int u = threadIdx.x; u < npg; u += blockDim.x) {
-            int pi = first_pg + u;
-            if (pi >= ring_pages) pi -= ring_pages;
-            pages_s[u] = page_row[pi];
-        }
-        __syncthreads();
         const int first = begin + warp * TILE, stride = MMA_WARPS * TILE;
         const int my_tiles = first < end ? (end - first + stride - 1) / stride : 0;
 
@@ -449,6 +455,9 @@ int launch(const void* q, long long q_stride, const void* k_pool, const void* v_
 // does not take (the caller then uses the generic kernel).  On success *combined says whether
 // `out` ([B, out_stride] bfloat16, may be null) already holds the result (up to 4 splits, merged
 // inside a cluster) or the caller still has to run the combine pass over part_o / part_ml.
+// slots, slot_len and page_table are read before the kernel waits for the kernel launched in front of it
+// on the stream (programmatic dependent launch): that kernel must not be the one that writes them.  Copies
+// from the host and kernels further back are complete by then.
 extern "C" int qnn_attn_decode_mma_split(const void* q, long long q_stride, const void* k_pool, const void* v_pool,
                                          const int* page_table, int max_pages, int page_size, int ring,
                                          const int* slots, const int* slot_len, int B, int nq, int nkv, int hd,

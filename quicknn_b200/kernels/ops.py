@@ -449,7 +449,10 @@ def attn_decode(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, k_poo
                 v_pool: torch.Tensor, page_table: torch.Tensor, page_size: int, ring: int,
                 slots: torch.Tensor, slot_len: torch.Tensor, scale: float, cap: Optional[float],
                 window: Optional[int], n_splits: int, part_o: torch.Tensor, part_ml: torch.Tensor):
-    """One query row per sequence against the paged cache.  q = the first nq*hd columns of qkv."""
+    """One query row per sequence against the paged cache.  q = the first nq*hd columns of qkv.
+    ``slots``, ``slot_len`` and ``page_table`` must be complete before the kernel that runs just before
+    this one on the stream starts (host copies and earlier kernels are): the tensor-core kernel reads
+    them while that kernel may still run."""
     _req(qkv, "qkv", None, 2)
     B = qkv.shape[0]
     _req(k_pool, "k_pool", qkv.dtype, 4)
