@@ -156,29 +156,40 @@ gemm_skinny_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __gr
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const unsigned tmem = bars->tmem_base;
-    // Barriers and tensor memory are set up; only now wait for the kernels before this one (whose output
-    // the loads below read), so that the set-up overlaps their tail.
+    // Barriers and tensor memory are set up.  The weights do not depend on the kernel before this one: the
+    // producer asks for the weight tiles of the first ring of stages, and only then waits for that kernel,
+    // whose output the activation loads read; every other thread waits before it touches global memory.
+    const int n_it = kb1 - kb0;
+    const int ahead = (warp == 0 && lane == 0) ? min(stages, n_it) : 0;
+    auto load_weights = [&](int it) {
+        const int s = it % stages, kb = kb0 + it;
+        const unsigned full = smem_u32(&bars->full[s]);
+        const unsigned w_dst = smem_u32(smem + (size_t)s * stage_bytes);
+        mbar_expect_tx(full, (unsigned)stage_bytes);
+        if (EPI == EPI_GATED) {
+            tma_load_2d(w_dst, &map_w, full, kb * BK, n0);                        // 64 gate rows
+            tma_load_2d(w_dst + W_BYTES / 2, &map_w, full, kb * BK, Nout + n0);   // the 64 up rows
+        } else {
+            tma_load_2d(w_dst, &map_w, full, kb * BK, n0);
+        }
+    };
+    for (int it = 0; it < ahead; ++it) load_weights(it);
     pdl_wait();
 
     if (warp == 0) {
         if (lane == 0) {
-            for (int kb = kb0, it = 0; kb < kb1; ++kb, ++it) {
+            for (int it = 0; it < n_it; ++it) {
                 const int s = it % stages;
-                if (it >= stages && !mbar_wait(smem_u32(&bars->empty[s]), ((it / stages) - 1) & 1)) {
-                    atomicOr(status, 1);
-                    bars->failed = 1;
-                    break;
+                if (it >= ahead) {
+                    if (it >= stages && !mbar_wait(smem_u32(&bars->empty[s]), ((it / stages) - 1) & 1)) {
+                        atomicOr(status, 1);
+                        bars->failed = 1;
+                        break;
+                    }
+                    load_weights(it);
                 }
-                const unsigned full = smem_u32(&bars->full[s]);
-                const unsigned w_dst = smem_u32(smem + (size_t)s * stage_bytes), x_dst = w_dst + W_BYTES;
-                mbar_expect_tx(full, (unsigned)stage_bytes);
-                if (EPI == EPI_GATED) {
-                    tma_load_2d(w_dst, &map_w, full, kb * BK, n0);                        // 64 gate rows
-                    tma_load_2d(w_dst + W_BYTES / 2, &map_w, full, kb * BK, Nout + n0);   // the 64 up rows
-                } else {
-                    tma_load_2d(w_dst, &map_w, full, kb * BK, n0);
-                }
-                tma_load_2d(x_dst, &map_x, full, kb * BK, 0);
+                const unsigned x_dst = smem_u32(smem + (size_t)s * stage_bytes) + W_BYTES;
+                tma_load_2d(x_dst, &map_x, smem_u32(&bars->full[s]), (kb0 + it) * BK, 0);
             }
         }
     } else if (warp == 1) {
