@@ -166,7 +166,6 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             bf16* __restrict__ out, size_t out_stride, const int* __restrict__ seq_row0,
                             const int* __restrict__ seq_len, int nq, int nkv, float scale, float cap, int window,
                             int* __restrict__ status, int split) {
-    pdl_wait();
     constexpr int Q_BYTES = BM * HD * 2;                             // HD / 64 blocks of [128 x 64]
     constexpr int K_BYTES = BN * HD * 2, V_BYTES = BN * HD * 2;      // HD / 64 blocks of [64 x 64] each
     constexpr int MERGE_O_BYTES = BM * HD * 4;                       // O of rank 1 of a pair, float32
@@ -227,6 +226,9 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const unsigned tmem = bars->tmem_base;
+    // Barriers and tensor memory are set up; only now wait for the kernel before this one, whose output the
+    // loads below read (seq_row0 and seq_len, read above, come from the host before the step).
+    pdl_wait();
 
     // The softmax warps' view of their row (warps 2..5; thread = query row), kept past the role branches
     // for the merge of a pair and the output.
@@ -654,12 +656,19 @@ int launch_attn(const void* qkv, long long total_rows, void* out, long long out_
             cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0)
             sm_count = 148;
     }
-    // Few CTAs and several query tiles: pairs of CTAs share a query tile's keys (see the head of this file).
-    // With many CTAs the heavy ones are started first and the rest fills in behind them.
-    // (measured at 8 heads of 256: 1024 tokens 29.9 -> 26.8 us, 2048 tokens 51.8 -> 49.1 us; with 4096 tokens,
-    // 256 CTAs unsplit, pairs were slower, 126 against 94 us)
+    // Few CTAs with long key walks: pairs of CTAs share a query tile's keys (see the head of this file).  A pair
+    // pays for the hand-over and doubles the CTAs, so it needs enough key tiles in the heaviest query tile: 12
+    // when the pairs still fit the device at once, 24 when they need a second round.  With more CTAs than SMs
+    // the heavy ones are started first and the rest fills in behind them.  Measured inside a CUDA graph, head
+    // size 256, pairs against single CTAs: 8 heads, 1024 tokens 22.0 / 25.5 us, 2048 tokens 42.7 / 46.6 us;
+    // 4 heads, 2048 tokens 31.9 / 45.7 us; but 8 heads, 512 tokens 16.6 / 15.3 us; 16 heads, 1024 tokens
+    // 33.9 / 26.5 us; 8 heads, 2048 tokens with a window of 512: 37.0 / 20.0 us.
     static int split_ok = -1;                      // the device holds a pair of these CTAs (asked once)
-    const bool want_split = ntq >= 2 && (long long)ntq * B * nq <= sm_count && !getenv("QNN_ATTN_NO_SPLIT");
+    const long long singles = (long long)ntq * B * nq;
+    const int reach = window > 0 ? (max_len < window + BM - 1 ? max_len : window + BM - 1) : max_len;
+    const int key_tiles = (reach + BN - 1) / BN;   // of the heaviest query tile
+    const bool want_split = ntq >= 2 && !getenv("QNN_ATTN_NO_SPLIT") &&
+                            ((2 * singles <= sm_count && key_tiles >= 12) || (singles <= sm_count && key_tiles >= 24));
     cudaLaunchConfig_t cfg = {};
     cfg.blockDim = dim3(THREADS);
     cfg.dynamicSmemBytes = smem;
@@ -701,7 +710,9 @@ int launch_attn(const void* qkv, long long total_rows, void* out, long long out_
 // qkv: this step's projections, [T rows, (nq + 2 nkv) * hd] bfloat16, rotated; sequence b occupies rows
 // seq_row0[b] .. + seq_len[b] - 1.  Head sizes 64, 128 and 256; QNN_ERR_UNSUPPORTED for others.  `status` as in
 // qnn_gemm_tcgen05 (bits: 2 K/V wait, 4 S wait, 8 P wait, 16 ring wait, 32 Q wait, 64 product wait, 128 wait for
-// the other half of a pair).
+// the other half of a pair).  seq_row0 and seq_len are read before the kernel waits for the kernel launched
+// in front of it on the stream: that kernel must not be the one that writes them (copies from the host and
+// kernels further back are complete by then).
 QNN_API int qnn_attn_prefill_tcgen05(const void* qkv, long long total_rows, void* out, long long out_stride,
                                      const int* seq_row0, const int* seq_len, int B, int max_len, int nq, int nkv,
                                      int hd, float scale, float cap, int window, int* status, cudaStream_t st) {

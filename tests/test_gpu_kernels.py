@@ -435,6 +435,33 @@ def test_attention_prefill_tcgen05_with_more_ctas_than_sms(ops, hd):
         r += n
 
 
+@pytest.mark.parametrize("hd", [64, 128, 256])
+@pytest.mark.parametrize("window,cap", [(None, 50.0), (700, None)])
+def test_attention_prefill_tcgen05_pairs_share_long_key_walks(ops, hd, window, cap):
+    """Few heads and a sequence of 13 key tiles: the kernel runs pairs of CTAs that take alternate key
+    tiles of a query tile and merge their halves; beside it a short sequence whose second CTA has nothing."""
+    nq, nkv = 2, 1
+    rng = np.random.default_rng(hd + 1)
+    lens = [800, 130]
+    Tn = sum(lens)
+    qkv = bf16_round(rng.normal(size=(Tn, (nq + 2 * nkv) * hd)))
+    pos = np.concatenate([np.arange(n) for n in lens]).astype(np.int32)
+    starts = np.cumsum([0] + lens[:-1]).astype(np.int32)
+    row0 = np.concatenate([np.full(n, s) for n, s in zip(lens, starts)]).astype(np.int32)
+    scale = 1.0 / math.sqrt(hd)
+    out = ops.attn_prefill(T(qkv, torch.bfloat16), nq, nkv, hd, T(pos, torch.int32), T(row0, torch.int32), scale, cap,
+                           window, T(starts, torch.int32), T(np.array(lens, np.int32), torch.int32), max(lens))
+    r = 0
+    for n in lens:
+        blk = qkv[r:r + n]
+        q = blk[:, :nq * hd].reshape(n, nq, hd)
+        k = blk[:, nq * hd:(nq + nkv) * hd].reshape(n, nkv, hd)
+        v = blk[:, (nq + nkv) * hd:].reshape(n, nkv, hd)
+        ref = P.attention(q, k, v, scale, cap, window).reshape(n, -1)
+        assert_close(out[r:r + n], ref, torch.bfloat16, f"sequence of {n}", mult=4)
+        r += n
+
+
 def test_window_edge_in_the_tensor_core_prefill_kernel(ops):
     nq, nkv, hd, n, W = 2, 1, 64, 300, 100
     k = np.zeros((n, nkv, hd))
