@@ -151,29 +151,6 @@ __global__ void __launch_bounds__(NW * 32) skinny_bf16_kernel(const bf16* __rest
             }
         }
     }
-    // rotate and append: what the epilogue's thread (pair j, token m) needs of its token (position, place in
-    // the cache, angle) comes from the host before the step, so it too is fetched before the wait
-    int ep_pos = 0;
-    bool ep_wr = false;
-    size_t ep_cache = 0;
-    float ep_sn = 0.f, ep_cs = 1.f;
-    // (only where a thread has one item at most: up to 32 tokens with 8 warps)
-    constexpr bool EP_EARLY = EPI == EPI_ROPE && 8 * COLS <= THREADS;
-    if constexpr (EP_EARLY) {
-        const int j = threadIdx.x % 8, m = threadIdx.x / 8;
-        if ((int)threadIdx.x < 8 * COLS && m < M) {
-            ep_pos = rp.tok_pos[m];
-            const int slot = rp.tok_slot[m];
-            ep_wr = rp.write_cache && slot >= 0;
-            if (ep_wr && rp.ring > 0 && ep_pos + rp.ring < rp.slot_len[slot]) ep_wr = false;
-            if (ep_wr) {
-                const int r = rp.ring > 0 ? ep_pos % rp.ring : ep_pos;
-                const int page = rp.page_table[(size_t)slot * rp.max_pages + r / rp.page_size];
-                ep_cache = ((size_t)page * rp.nkv * rp.page_size + (r % rp.page_size)) * rp.hd;
-            }
-            if ((int)blockIdx.x < rope_blocks) sincosf((float)ep_pos * rp.inv_freq[rope_base0 % rp.hd + j], &ep_sn, &ep_cs);
-        }
-    }
     pdl_wait();
 
 #pragma unroll
@@ -245,23 +222,20 @@ __global__ void __launch_bounds__(NW * 32) skinny_bf16_kernel(const bf16* __rest
 #pragma unroll
             for (int w = 0; w < NW; ++w) { s0 += red[w][j][m]; s1 += red[w][j + 8][m]; }
             const bf16 a = __float2bfloat16(s0), b = __float2bfloat16(s1);
-            bool wr = ep_wr;
-            size_t cache_base = ep_cache;
-            float sn = ep_sn, cs = ep_cs;
-            if constexpr (!EP_EARLY) {
-                const int pos = rp.tok_pos[m], slot = rp.tok_slot[m];
-                wr = rp.write_cache && slot >= 0;
-                if (wr && rp.ring > 0 && pos + rp.ring < rp.slot_len[slot]) wr = false;
-                if (wr) {
-                    const int r = rp.ring > 0 ? pos % rp.ring : pos;
-                    const int page = rp.page_table[(size_t)slot * rp.max_pages + r / rp.page_size];
-                    cache_base = ((size_t)page * rp.nkv * rp.page_size + (r % rp.page_size)) * hd;
-                }
-                if ((int)blockIdx.x < rope_blocks) sincosf((float)pos * rp.inv_freq[rope_base0 % hd + j], &sn, &cs);
+            const int pos = rp.tok_pos[m], slot = rp.tok_slot[m];
+            bool wr = rp.write_cache && slot >= 0;
+            if (wr && rp.ring > 0 && pos + rp.ring < rp.slot_len[slot]) wr = false;
+            size_t cache_base = 0;
+            if (wr) {
+                const int r = rp.ring > 0 ? pos % rp.ring : pos;
+                const int page = rp.page_table[(size_t)slot * rp.max_pages + r / rp.page_size];
+                cache_base = ((size_t)page * rp.nkv * rp.page_size + (r % rp.page_size)) * hd;
             }
             bf16* orow = o + (size_t)m * N;
             if ((int)blockIdx.x < rope_blocks) {
                 const int h = rope_base0 / hd, d = rope_base0 % hd + j;
+                float sn, cs;
+                sincosf((float)pos * rp.inv_freq[d], &sn, &cs);
                 const float fa = __bfloat162float(a), fb = __bfloat162float(b);
                 const bf16 ra = __float2bfloat16(fa * cs - fb * sn), rb = __float2bfloat16(fa * sn + fb * cs);
                 orow[h * hd + d] = ra;
