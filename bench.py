@@ -57,7 +57,7 @@ def peaks():
         if "bf16_tflops" in m:
             out["bf16_tflops"] = float(m["bf16_tflops"])
         out["source"] = "measured"
-    except (OSError, ValueError):
+    except (OSError, ValueError, TypeError):
         pass
     return out
 
