@@ -181,11 +181,14 @@ def rope_cache_write(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, 
         page_size, ring, _p(slot_len), int(write_cache), _stream()), "rope_cache_write")
 
 
+FUSE_ROPE = os.environ.get("QNN_FUSE_ROPE", "1") != "0"
+
+
 def qkv_rope_cache_fusable(x: torch.Tensor, w: torch.Tensor, head_dim: int, rot_dim: int) -> bool:
     """Whether qkv_rope_cache takes this product: bfloat16 on both sides, few rows, a matrix
     that the small-M kernel would multiply anyway, a rotation over the whole head."""
     M, K = x.shape
-    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or os.environ.get("QNN_FUSE_ROPE", "1") == "0":
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or not FUSE_ROPE:
         return False
     if M > SKINNY_MAX_ROWS or K % 8 or head_dim % 16 or rot_dim != head_dim:
         return False
