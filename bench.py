@@ -226,7 +226,7 @@ def main():
     # ---- prefill of 2,048 tokens -----------------------------------------------------------
     ids = torch.randint(1, cfg["vocab_size"], (PREFILL_TOKENS,)).tolist()
     times = []
-    for i in range(0 if args.skip_prefill else 4):
+    for i in range(0 if args.skip_prefill else 8):              # 3 warm-ups, 5 timed: the median
         slot = eng.new_sequence()
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -235,7 +235,7 @@ def main():
         e1.record()
         torch.cuda.synchronize()
         eng.release(slot)
-        if i:
+        if i >= 3:
             times.append(e0.elapsed_time(e1))
     pre_ms = statistics.median(times) if times else float("nan")
     flops = prefill_flops(cfg, PREFILL_TOKENS)
