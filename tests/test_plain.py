@@ -115,3 +115,21 @@ def test_sampler_follows_the_shader():
         counts[P.sample(row, 1.0, 5, 1.0, 1.0, None, u)] += 1
     p = np.exp(row - 2.0); p /= p.sum()
     assert np.abs(counts / 4000 - p).max() < 0.03
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_the_torch_plain_implementation_agrees_with_the_numpy_one(plain_models, folders, name):
+    """The second plain implementation (torch operations; it runs the large layer sizes on the GPU
+    and is the timed baseline of the benchmark) gives the logits of the first at every position,
+    for prompts longer than the windows of both tiny models."""
+    import torch
+    from plain.gemma2_torch import TorchGemma2
+    ids = prompts_for(name, [29])[0]
+    ref = plain_models(name).logits(ids)
+    t64 = TorchGemma2(folders(name), "cpu", torch.float64)
+    assert np.abs(t64.logits(ids) - ref).max() < 1e-10
+    assert np.abs(t64.logits(ids, [0, 28]) - ref[[0, 28]]).max() < 1e-10
+    t32 = TorchGemma2(folders(name), "cpu", torch.float32)
+    assert np.abs(t32.logits(ids) - ref).max() < 5e-5
+    assert t64.greedy(ids[:7], 4) == plain_models(name).greedy(ids[:7], 4)
+    assert [t64.layer_window(i) for i in range(2)] == [plain_models(name).layer_window(i) for i in range(2)]
