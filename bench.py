@@ -7,7 +7,7 @@ end-to-end figures on the same JSON line.
 A "step" is one decode step of a batch of 8 sequences whose cached context reaches the
 benchmark context length (8192) at the last timed step.  Weights are random (seeded,
 generated on the device); the cached history of the device-timed runs is random too
-(``Engine.fill_synthetic``), because a decode step's time does not depend on the values.
+(``fill_synthetic``), because a decode step's time does not depend on the values.
 Timing is by CUDA events on the launching stream after W warm-up steps; every step reads all
 weights (5.2 GB) and the live cache, far more than the 126 MB L2, so no L2 flush is needed.
 ``e2e`` runs the same batch through the Python entry point (``LLM.generate``): prompts go in
@@ -127,11 +127,25 @@ def prefill_flops(cfg, T):
     return total + 2 * H * cfg["vocab_size"]
 
 
+def fill_synthetic(engine, slots, lengths, torch, seed=0):
+    """Give sequences a history of the given lengths without computing it: pages are taken as a prompt
+    of that length would take them and every cache line is filled with random keys and values.  For
+    timing decode steps at a chosen context; the logits mean nothing."""
+    engine.cache.extend(list(zip(slots, lengths)))
+    engine.cache.sync()
+    g = torch.Generator(device=engine.device)
+    g.manual_seed(seed)
+    for grp in engine.cache.groups:
+        for t in (grp.k, grp.v):
+            for li in range(t.shape[0]):
+                t[li].normal_(0.0, 1.0, generator=g)
+
+
 def timed_decode(engine, batch, steps, warmup, torch, with_clocks=False, context=CONTEXT, vocab=256000):
     """Tokens per second of `steps` decode steps of `batch` sequences ending at `context` tokens."""
     start_len = context - steps - warmup - 1
     slots = [engine.new_sequence() for _ in range(batch)]
-    engine.fill_synthetic(slots, [start_len] * batch)
+    fill_synthetic(engine, slots, [start_len] * batch, torch)
     tokens = torch.randint(1, vocab, (batch,), dtype=torch.int32, device=engine.device)
     engine.decode(slots, tokens)          # eager pass, captures the graph
     for _ in range(warmup):

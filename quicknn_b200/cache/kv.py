@@ -27,11 +27,8 @@ import numpy as np
 import torch
 
 from ..parts.base import CacheNeed, StateNeed
-from .pages import CacheFull, PagePool, SlotTable
+from .pages import PAGE, CacheFull, PagePool, SlotTable
 from .upload import PinnedUploader
-
-PAGE = 64
-
 
 def _round_up(n: int, m: int) -> int:
     return (n + m - 1) // m * m
@@ -95,7 +92,13 @@ class KVCache:
             if need is not None:
                 by_key.setdefault(need.group_key(), []).append(line)
         for key, lines in by_key.items():
-            g = CacheGroup(needs[lines[0]], lines, n_pages, max_slots, max_seq, dtype, device)
+            # a sequence of a windowed group never holds more than its ring, so that group's pool
+            # needs no more than a ring per slot however many tokens the other groups keep
+            w = needs[lines[0]].window
+            mine = n_pages
+            if w is not None and w < max_seq:
+                mine = min(n_pages, max_slots * (_round_up(w, PAGE) // PAGE) + 1)
+            g = CacheGroup(needs[lines[0]], lines, mine, max_slots, max_seq, dtype, device)
             for i, line in enumerate(lines):
                 self._line_group[line] = (len(self.groups), i)
             self.groups.append(g)
@@ -164,6 +167,25 @@ class KVCache:
                 g.table_host[slot, start:start + extra] = pages
                 g.dirty.add(slot)
         for slot, new_len in slot_lengths:
+            self.lengths_host[slot] = new_len
+        self._lengths_dirty = True
+
+    def truncate(self, slot_lengths: Sequence[Tuple[int, int]]) -> None:
+        """Shorten sequences to earlier lengths and give back the pages beyond them: the undo of
+        an ``extend`` whose step could not be launched.  Cells beyond the new length keep whatever
+        was written; nothing reads them."""
+        for slot, new_len in slot_lengths:
+            if not self.slots.is_live(slot):
+                continue
+            if new_len > self.lengths_host[slot]:
+                raise ValueError(f"slot {slot}: truncate cannot grow a sequence")
+            for g in self.groups:
+                keep = g.pages_for(new_len)
+                if keep < len(g.held[slot]):
+                    g.pool.give_back(g.held[slot][keep:])
+                    g.table_host[slot, keep:] = 0
+                    del g.held[slot][keep:]
+                    g.dirty.add(slot)
             self.lengths_host[slot] = new_len
         self._lengths_dirty = True
 

@@ -7,6 +7,7 @@ from __future__ import annotations
 
 from typing import Iterable, List
 
+PAGE = 64          # positions per page of the cache; everything that rounds token counts uses this one
 
 class CacheFull(RuntimeError):
     """The request does not fit: no free page or no free slot.  Raised on the host

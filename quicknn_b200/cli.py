@@ -41,6 +41,10 @@ def _prompts(args) -> List[List[int]]:
 def cmd_generate(args) -> int:
     from .engine import LLM
     from .sampling import GenerationOptions
+    import torch
+    if not torch.cuda.is_available():
+        print("generate: no CUDA device; quicknn_b200 has no CPU path", file=sys.stderr)
+        return 3
     prompts = _prompts(args)
     opts = GenerationOptions(max_new_tokens=args.max_new_tokens, hard_max_new_tokens=args.hard_max_new_tokens,
                              top_k=args.top_k, auto_continue=args.auto_continue, temperature=args.temperature,

@@ -121,11 +121,12 @@ __device__ __forceinline__ float block_sum(float v, float* smem32) {
     return r;
 }
 
-// cap * tanh(clamp(x / cap, -20, 20)); cap <= 0 switches it off.
+// cap * tanh(clamp(x / cap, -20, 20)); cap <= 0 switches it off.  NaN stays NaN.
 __device__ __forceinline__ float softcap(float x, float cap) {
     if (cap > 0.f) {
         float t = fminf(fmaxf(x / cap, -20.f), 20.f);
-        return cap * tanhf(t);
+        return x == x ? cap * tanhf(t) : x;   // fminf/fmaxf drop a NaN; it has to reach the finite check
+
     }
     return x;
 }

@@ -97,8 +97,15 @@ sample_tile_kernel(const float* __restrict__ logits, int V, int k, float penalty
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_merge_kernel(float2* __restrict__ cand, int ncand, int k, float temperature, float top_p,
                     unsigned* __restrict__ rng_state, int* __restrict__ out_tokens, unsigned char* __restrict__ seen,
-                    const int* __restrict__ seen_rows, int V) {
+                    const int* __restrict__ seen_rows, int V, const int* __restrict__ status_in,
+                    int* __restrict__ error_flag) {
     pdl_wait();
+    // what the kernels of this step reported (a bounded wait that ran out) joins the error word
+    // that the host reads with the chosen ids: bit 1 = "a kernel gave up", its status from bit 8 up
+    if (blockIdx.x == 0 && threadIdx.x == 0 && status_in != nullptr && error_flag != nullptr) {
+        const int s = *status_in;
+        if (s != 0) atomicOr(error_flag, 2 | (s << 8));
+    }
     __shared__ float sv[32];
     __shared__ unsigned si[32];
     __shared__ float top_v[SAMPLE_MAX_K];
@@ -149,7 +156,7 @@ sample_merge_kernel(float2* __restrict__ cand, int ncand, int k, float temperatu
 // Scratch `cand`: R * ceil(V/1024) * k float2.
 QNN_API int qnn_sample(const float* logits, int R, int V, int top_k, float temperature, float top_p, float penalty,
                        unsigned* rng_state, unsigned char* seen, const int* seen_rows, void* cand, int* out_tokens,
-                       int* error_flag, cudaStream_t st) {
+                       int* error_flag, const int* status_in, cudaStream_t st) {
     if (R <= 0) return 0;
     if (V <= 0 || top_k < 1 || !(temperature >= 0.f) || !(top_p > 0.f && top_p <= 1.f) || !(penalty > 0.f))
         return QNN_ERR_ARGUMENT;
@@ -163,7 +170,7 @@ QNN_API int qnn_sample(const float* logits, int R, int V, int top_k, float tempe
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
     qnn::launch_pdl(sample_merge_kernel, dim3(R), dim3(SAMPLE_THREADS), 0, st, (float2*)cand, tiles * k, k, temperature, top_p, rng_state,
-                                                      out_tokens, seen, seen_rows, V);
+                                                      out_tokens, seen, seen_rows, V, status_in, error_flag);
     QNN_LAUNCH_CHECK();
 }
 

@@ -4,6 +4,7 @@ from .engine import Engine, StepError
 from .generate import GenerationBackend, GenerationResult, PromptError, generate, plan_batches
 from .llm import LLM
 from .model import Model, as_dtype
+from ..kernels.lib import KernelError, NonFiniteLogits
 
 __all__ = ["StepBatch", "Engine", "StepError", "GenerationBackend", "GenerationResult", "PromptError",
-           "generate", "plan_batches", "LLM", "Model", "as_dtype"]
+           "generate", "plan_batches", "LLM", "Model", "as_dtype", "KernelError", "NonFiniteLogits"]

@@ -2,7 +2,7 @@
 from __future__ import annotations
 
 import dataclasses
-from typing import Optional
+from typing import Any, Mapping, Optional
 
 import torch
 
@@ -12,11 +12,17 @@ class StepBatch:
     """Device-side description of one step.
 
     ``mode`` is "prefill" when every sequence starts at its first token (the whole
-    prompts, packed one after another) and "decode" when every sequence goes on by
-    one token.  Row t of the packed batch belongs to the sequence in slot
-    ``tok_slot[t]`` (a negative slot marks a padding row: nothing is written for it
-    and it attends to nothing) at position ``tok_pos[t]``; its sequence's first row is
-    ``tok_row0[t]``.
+    prompts, packed one after another), "decode" when every sequence goes on by
+    one token, and "extend" for everything else (sequences that go on by several
+    tokens, or some that start beside others that go on).  Row t of the packed batch
+    belongs to the sequence in slot ``tok_slot[t]`` (a negative slot marks a padding
+    row: nothing is written for it and it attends to nothing) at position
+    ``tok_pos[t]``; its sequence's first row is ``tok_row0[t]``.
+
+    ``max_seq`` (the longest sequence the cache was built for) and ``tuning`` (options
+    that the engine's owner set and that parts may look up by name, for instance
+    ``decode_splits``) let a part choose its schedule; ``scratch`` is the scratch
+    memory that the parts asked for with ``scratch_need`` (bytes; None if none did).
     """
 
     mode: str
@@ -29,9 +35,9 @@ class StepBatch:
     slots: torch.Tensor             # [B] int32
     want_rows: torch.Tensor         # [R] int32: rows whose logits are returned
     act_dtype: torch.dtype
-    decode_splits: int = 1
-    part_o: Optional[torch.Tensor] = None
-    part_ml: Optional[torch.Tensor] = None
     max_q_len: int = 1              # longest run of tokens that one sequence brings
     seq_row0: Optional[torch.Tensor] = None   # [B] int32: first row of each sequence in the packed batch
     seq_len: Optional[torch.Tensor] = None    # [B] int32: tokens that each sequence brings
+    max_seq: int = 0
+    tuning: Mapping[str, Any] = dataclasses.field(default_factory=dict)
+    scratch: Optional[torch.Tensor] = None    # uint8

@@ -5,11 +5,13 @@ runs exactly the tokens it is given as one batch and returns the logits at the
 wanted places.  The reference's counterpart is ``ForwardRows`` for one sequence in
 128-row chunks, returning the last row's logits
 (src/models/QuickNN.Models.LLM.pas:459-493); here a step takes several sequences of
-unequal length, whole prompts at once, then one token each.
+unequal length, whole prompts at once, then one token each; a step may also continue
+sequences by several tokens (the reference's prompts cut into portions and its reused prefix,
+LLM.pas:459-493, 715-745), or start some sequences beside others that go on.
 """
 from __future__ import annotations
 
-from typing import Dict, List, Optional, Sequence, Tuple, Union
+from typing import Any, Dict, List, Mapping, Optional, Sequence, Tuple, Union
 
 import numpy as np
 import torch
@@ -27,7 +29,10 @@ class StepError(ValueError):
 
 class Engine:
     def __init__(self, model: Model, max_tokens: int, max_slots: Optional[int] = None,
-                 max_seq: Optional[int] = None, decode_splits: Optional[int] = None):
+                 max_seq: Optional[int] = None, decode_splits: Optional[int] = None,
+                 tuning: Optional[Mapping[str, Any]] = None):
+        """``tuning``: options by name that the parts may look up in a step (``decode_splits`` fixes
+        the number of key ranges of decode attention; the argument of that name is a shorthand)."""
         self.model = model
         self.device = model.device
         if self.device.type != "cuda":
@@ -42,24 +47,14 @@ class Engine:
         needs, states = model.cache_needs()
         self.cache = KVCache(needs, states, max_tokens, max_slots, max_seq, model.dtype, self.device)
         self.max_seq, self.max_slots = max_seq, max_slots
-        # Key ranges per sequence in decode attention.  A fixed number when given; else chosen per
-        # batch size so that one wave of CTAs covers the GPU (results then differ between batch
-        # sizes by rounding only: the ranges are summed in a fixed order either way).
-        self._fixed_splits = int(decode_splits) if decode_splits else None
-        self._max_splits = max(1, min(64, max_seq // 128))
-        self._kv_groups = max([getattr(b.mixer, "n_kv", 1) for b in model.blocks] or [1])
-        # blocks of the decode attention kernel that the device holds at once: its shared
-        # memory is 384 bytes per element of a head, so two fit on an SM at head size 256,
-        # four at 128, eight at 64
-        head = max([getattr(b.mixer, "head_dim", 256) for b in model.blocks] or [256])
-        sms = torch.cuda.get_device_properties(self.device).multi_processor_count if self.device.type == "cuda" else 148
-        self._resident = sms * max(1, min(8, 512 // max(1, head)))
-        self.decode_splits = self._fixed_splits or self._max_splits
-        self._scratch: Dict[int, Tuple[torch.Tensor, torch.Tensor]] = {}
+        self.tuning: Dict[str, Any] = dict(tuning or {})
+        if decode_splits:
+            self.tuning["decode_splits"] = int(decode_splits)
+        self._scratch: Dict[int, torch.Tensor] = {}         # decode steps: per batch size (their graphs keep the address)
+        self._scratch_other: Optional[torch.Tensor] = None   # every other step: one buffer that grows
         self._decode_state: Dict[tuple, dict] = {}
         self.use_graphs = True
         self.graph_kernels_replayed = 0
-        self.error_flag = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.steps_run = 0
 
     # ---- sequences -------------------------------------------------------------------
@@ -73,23 +68,20 @@ class Engine:
         return self.cache.length(slot)
 
     # ---- the step ----------------------------------------------------------------------
-    def splits_for(self, batch: int) -> int:
-        if self._fixed_splits:
-            return self._fixed_splits
-        pairs = batch * self._kv_groups
-        # as many key ranges as keep one wave of blocks on the device (measured at head size 256, context
-        # 8192: batch 64 one range 9.48 ms against two 9.69; batch 32 two ranges; batch 16 four; batch 8 nine)
-        return max(1, min(self._max_splits, self._resident // max(1, pairs)))
-
-    def _scratch_for(self, batch: int) -> Tuple[torch.Tensor, torch.Tensor]:
-        key = 1
-        while key < batch:
-            key *= 2
-        if key not in self._scratch:
-            po, pm = self.model.decode_scratch(key, max(self._max_splits, self.decode_splits))
-            self._scratch[key] = (torch.empty(max(po, 1), dtype=torch.float32, device=self.device),
-                                  torch.empty(max(pm, 1), dtype=torch.float32, device=self.device))
-        return self._scratch[key]
+    def _give_scratch(self, step: StepBatch) -> None:
+        """Ask the parts what scratch a step of this shape needs and hand it over as ``step.scratch``."""
+        need = (int(self.model.scratch_need(step)) + 255) // 256 * 256
+        if need <= 0:
+            step.scratch = None
+        elif step.mode == "decode":
+            buf = self._scratch.get(step.n_seqs)
+            if buf is None or buf.numel() < need:
+                buf = self._scratch[step.n_seqs] = torch.empty(need, dtype=torch.uint8, device=self.device)
+            step.scratch = buf
+        else:
+            if self._scratch_other is None or self._scratch_other.numel() < need:
+                self._scratch_other = torch.empty(need, dtype=torch.uint8, device=self.device)
+            step.scratch = self._scratch_other
 
     def plan(self, entries: Sequence[Tuple[int, Sequence[int]]],
              want: Union[str, Sequence[Sequence[int]]] = "last"):
@@ -104,69 +96,84 @@ class Engine:
             raise StepError("every sequence of a step brings at least one token")
         starts = [self.cache.length(s) for s in slots]
         if all(p == 0 for p in starts):
-            mode = "prefill"
+            mode = "prefill"          # whole prompts: attention over the step's own rows
         elif all(n == 1 for n in lens):
-            mode = "decode"
+            mode = "decode"           # one token each: attention over the cache
         else:
-            raise StepError("the sequences of a step either all start at their first token or all go on "
-                            "by one token")
+            mode = "extend"           # anything else: cached keys first, then the step's own rows
         V = self.model.spec.embedding.vocab_size
-        for _, toks in entries:
-            for t in toks:
-                if not (0 <= int(t) < V):
-                    raise StepError(f"token id {t} is outside the vocabulary of {V}")
+        arrays = [np.asarray(t, dtype=np.int64).reshape(-1) for _, t in entries]
+        for a in arrays:
+            if a.size and (int(a.min()) < 0 or int(a.max()) >= V):
+                bad = a[(a < 0) | (a >= V)][0]
+                raise StepError(f"token id {int(bad)} is outside the vocabulary of {V}")
         if want == "last":
             want = [[n - 1] for n in lens]
         elif want == "all":
-            want = [list(range(n)) for n in lens]
+            want = [range(n) for n in lens]
         if len(want) != len(entries):
             raise StepError("`want` needs one list per sequence")
         T, B = sum(lens), len(entries)
-        tokens = np.empty(T, np.int32)
-        tok_pos = np.empty(T, np.int32)
-        tok_slot = np.empty(T, np.int32)
-        tok_row0 = np.empty(T, np.int32)
-        rows: List[int] = []
-        r = 0
-        for (s, toks), p0, n, w in zip(entries, starts, lens, want):
-            tokens[r:r + n] = np.asarray(toks, dtype=np.int64)
-            tok_pos[r:r + n] = np.arange(p0, p0 + n)
-            tok_slot[r:r + n] = s
-            tok_row0[r:r + n] = r
-            for i in w:
-                if not (0 <= int(i) < n):
-                    raise StepError(f"wanted place {i} is outside the {n} tokens the sequence brings")
-                rows.append(r + int(i))
-            r += n
+        lens_a = np.asarray(lens, np.int32)
+        row0 = (np.cumsum(lens_a) - lens_a).astype(np.int32)
+        tokens = np.concatenate(arrays).astype(np.int32)
+        tok_row0 = np.repeat(row0, lens_a)
+        tok_pos = (np.arange(T, dtype=np.int32) - tok_row0 + np.repeat(np.asarray(starts, np.int32), lens_a)).astype(np.int32)
+        tok_slot = np.repeat(np.asarray(slots, np.int32), lens_a)
+        rows: List[np.ndarray] = []
+        for r0, n, w in zip(row0, lens, want):
+            w = np.asarray(list(w) if not isinstance(w, range) else w, dtype=np.int64).reshape(-1)
+            if w.size and (int(w.min()) < 0 or int(w.max()) >= n):
+                bad = w[(w < 0) | (w >= n)][0]
+                raise StepError(f"wanted place {int(bad)} is outside the {n} tokens the sequence brings")
+            rows.append(w + int(r0))
+        rows_a = np.concatenate(rows).astype(np.int32) if rows else np.zeros(0, np.int32)
         # only now, with everything checked, does the cache change
         self.cache.extend([(s, p + n) for s, p, n in zip(slots, starts, lens)])
-        return mode, T, B, tokens, tok_pos, tok_slot, tok_row0, np.asarray(slots, np.int32), np.asarray(rows, np.int32)
+        return (mode, T, B, tokens, tok_pos, tok_slot, tok_row0, np.asarray(slots, np.int32), rows_a, row0, lens_a,
+                list(zip(slots, starts)))
 
     def step(self, entries: Sequence[Tuple[int, Sequence[int]]],
              want: Union[str, Sequence[Sequence[int]]] = "last") -> torch.Tensor:
         """Run the given tokens as one batch; return float32 logits ``[wanted, vocab]`` in the
-        order of the entries and of their wanted places."""
-        mode, T, B, tokens, tok_pos, tok_slot, tok_row0, slots, rows = self.plan(entries, want)
+        order of the entries and of their wanted places.  Raises ``NonFiniteLogits`` if they hold
+        NaN or Inf.  If the step cannot be launched, the sequences keep their earlier lengths."""
+        mode, T, B, tokens, tok_pos, tok_slot, tok_row0, slots, rows, row0, lens, before = self.plan(entries, want)
+        try:
+            logits = self._launch_step(mode, T, B, (tokens, tok_pos, tok_slot, tok_row0, slots, rows, row0, lens))
+        except Exception:
+            self.cache.truncate(before)
+            raise
+        self.steps_run += 1
+        self.check()
+        return logits
+
+    def _launch_step(self, mode, T, B, arrays) -> torch.Tensor:
         self.cache.sync()
-        lens = np.asarray([len(t) for _, t in entries], np.int32)
-        starts = np.concatenate([[0], np.cumsum(lens)[:-1]]).astype(np.int32)
-        packed = np.concatenate([tokens, tok_pos, tok_slot, tok_row0, slots, rows, starts, lens])
+        packed = np.concatenate(arrays).astype(np.int32, copy=False)
         dev = torch.empty(packed.size, dtype=torch.int32, device=self.device)
-        self.cache.uploader.send(dev, packed.astype(np.int32, copy=False))
+        self.cache.uploader.send(dev, packed)
         o = 0
         views = []
-        for n in (T, T, T, T, B, len(rows), B, B):
-            views.append(dev[o:o + n])
-            o += n
-        part_o, part_ml = self._scratch_for(B) if mode == "decode" else (None, None)
+        for a in arrays:
+            views.append(dev[o:o + a.size])
+            o += a.size
         step = StepBatch(mode, T, B, views[0], views[1], views[2], views[3], views[4], views[5],
-                         self.model.dtype, self.splits_for(B), part_o, part_ml, max_q_len=int(lens.max()),
-                         seq_row0=views[6], seq_len=views[7])
+                         self.model.dtype, max_q_len=int(arrays[7].max()), seq_row0=views[6], seq_len=views[7],
+                         max_seq=self.max_seq, tuning=self.tuning)
+        self._give_scratch(step)
         logits = self.model.forward(step, self.cache)
-        self.steps_run += 1
-        if mode == "prefill":
-            _kops.check_gemm_status(self.device)      # a bounded wait of the tcgen05 product ran out?
+        if logits.numel():
+            _kops.check_finite(logits)
         return logits
+
+    def check(self) -> None:
+        """Raise ``NonFiniteLogits`` if a forward pass since the last check gave NaN or Inf
+        (the reference flags them after every forward, src/models/QuickNN.Models.Gemma2.pas:196, and raises at
+        the next readback, QuickNN.Vulkan.Context.Implementation.inc:732-756), ``KernelError`` if a
+        bounded wait inside a tcgen05 kernel ran out.  One 8-byte read that waits for the device;
+        ``step`` calls it itself, ``decode`` leaves it to the caller (or to the sampler's error word)."""
+        _kops.raise_on_status(self.device)
 
     # ---- decode with ids that are already on the device -------------------------------
     def decode(self, slots: Sequence[int], tokens_dev: torch.Tensor, use_graph: Optional[bool] = None,
@@ -192,6 +199,14 @@ class Engine:
         if tokens_dev.dtype != torch.int32 or tokens_dev.numel() != B or not tokens_dev.is_cuda:
             raise StepError("decode needs one int32 id per sequence on the device")
         self.cache.extend([(s, p + 1) for s, p in zip(slots, starts)])
+        try:
+            return self._decode(slots, starts, tokens_dev, use_graph, tail)
+        except Exception:
+            self.cache.truncate(list(zip(slots, starts)))
+            raise
+
+    def _decode(self, slots, starts, tokens_dev, use_graph, tail):
+        B = len(slots)
         self.cache.sync()
         use_graph = self.use_graphs if use_graph is None else use_graph
         key = (B, id(tail) if tail is not None else None)
@@ -199,10 +214,10 @@ class Engine:
         if st is None:
             meta = torch.zeros(2 * B, dtype=torch.int32, device=self.device)
             ar = torch.arange(B, dtype=torch.int32, device=self.device)
-            part_o, part_ml = self._scratch_for(B)
             tokens = torch.zeros(B, dtype=torch.int32, device=self.device)
             step = StepBatch("decode", B, B, tokens, meta[:B], meta[B:], ar, meta[B:], ar, self.model.dtype,
-                             self.splits_for(B), part_o, part_ml)
+                             max_seq=self.max_seq, tuning=self.tuning)
+            self._give_scratch(step)
             st = {"meta": meta, "step": step, "graph": None, "logits": None, "tail": tail}    # holds `tail` alive: its id is the key
             self._decode_state[key] = st
         self.cache.uploader.send(st["meta"], np.concatenate([np.asarray(starts, np.int32), np.asarray(slots, np.int32)]))
@@ -210,7 +225,10 @@ class Engine:
         self.steps_run += 1
         def run():
             logits = self.model.forward(st["step"], self.cache)
-            return logits if tail is None else tail(logits)
+            if tail is None:
+                _kops.check_finite(logits)            # read by check(); a sampler tail has its own word
+                return logits
+            return tail(logits)
 
         if not use_graph:
             return run()
@@ -237,19 +255,6 @@ class Engine:
     def kernels_launched(self) -> int:
         """Kernels of this library launched so far, eagerly or inside replayed graphs."""
         return _klib.launches + self.graph_kernels_replayed
-
-    def fill_synthetic(self, slots: Sequence[int], lengths: Sequence[int], seed: int = 0) -> None:
-        """Give sequences a history of the given lengths without computing it: pages are taken
-        as a prompt of that length would take them and every cache line is filled with random
-        keys and values.  For timing decode steps at a chosen context; the logits mean nothing."""
-        self.cache.extend(list(zip(slots, lengths)))
-        self.cache.sync()
-        g = torch.Generator(device=self.device)
-        g.manual_seed(seed)
-        for grp in self.cache.groups:
-            for t in (grp.k, grp.v):
-                for li in range(t.shape[0]):
-                    t[li].normal_(0.0, 1.0, generator=g)
 
     def stats(self) -> Dict[str, int]:
         return {"weight_bytes": self.model.weight_bytes(), "cache_bytes": self.cache.bytes(),

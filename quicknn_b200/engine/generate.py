@@ -23,8 +23,9 @@ import numpy as np
 
 from ..sampling.options import GenerationOptions
 
+from ..cache.pages import PAGE
+
 EOS, MAX_TOKENS, CANCELLED, CONTEXT_FULL, HARD_LIMIT = "eos", "max_tokens", "cancelled", "context_full", "hard_limit"
-PAGE = 64
 
 
 class PromptError(ValueError):
@@ -126,9 +127,10 @@ def generate(backend: GenerationBackend, prompts: Sequence[Sequence[int]], optio
     options.validate()
     stop = set(int(s) for s in stop_ids)
     for i, p in enumerate(prompts):
-        for t in p:
-            if not (0 <= int(t) < backend.vocab_size):
-                raise PromptError(f"request {i}: token id {t} is outside the vocabulary")
+        a = np.asarray(p, dtype=np.int64).reshape(-1)
+        if a.size and (int(a.min()) < 0 or int(a.max()) >= backend.vocab_size):
+            bad = a[(a < 0) | (a >= backend.vocab_size)][0]
+            raise PromptError(f"request {i}: token id {int(bad)} is outside the vocabulary")
     lens = [len(p) for p in prompts]
     batches = plan_batches(lens, options, backend.max_batch, backend.max_tokens, backend.max_seq)
     results = [GenerationResult(i, lens[i]) for i in range(len(prompts))]

@@ -11,15 +11,12 @@ import numpy as np
 import torch
 
 from ..config.base import Architecture, ModelConfig, find_architecture
-from ..cache.pages import CacheFull
+from ..cache.pages import PAGE, CacheFull
 from ..sampling import GenerationOptions, Sampler
 from ..weights.random_init import random_tensors
 from .engine import Engine
 from .generate import GenerationBackend, GenerationResult, generate
 from .model import Model, as_dtype
-
-PAGE = 64
-
 
 class _Backend(GenerationBackend):
     """The engine and the sampler behind the generation loop.

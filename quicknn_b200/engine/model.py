@@ -52,6 +52,9 @@ class Model:
         self.final_norm = NORMS.get(spec.head.norm.kind)(spec.head.norm)
         self.final_norm.load({"weight": tensors[spec.head.norm_tensor]}, self.dtype, self.device)
         self.head = self.embedding if spec.head.tied else tensors[spec.head.tensor].contiguous()
+        why = ops.linear_refusal(self.head.dtype, spec.hidden_size)
+        if why:
+            raise ValueError(f"output head: {why}")
         self._check_schedule()
 
     # ---- construction --------------------------------------------------------------
@@ -101,14 +104,10 @@ class Model:
                 states[e.cache] = self.blocks[e.layer].mixer.state_need()
         return needs, states
 
-    def decode_scratch(self, batch: int, splits: int) -> Tuple[int, int]:
-        po = pm = 0
-        for b in self.blocks:
-            m = b.mixer
-            nq, hd = getattr(m, "n_heads", 0), getattr(m, "head_dim", 0)
-            po = max(po, batch * nq * splits * hd)
-            pm = max(pm, batch * nq * splits * 2)
-        return po, pm
+    def scratch_need(self, step) -> int:
+        """Bytes of scratch that a step of this shape needs: the largest need of the layers that run
+        (they run one after another and share it)."""
+        return max([self.blocks[e.layer].scratch_need(step) for e in self.spec.schedule] or [0])
 
     def weight_bytes(self) -> int:
         n = self.embedding.numel() * self.embedding.element_size()

@@ -39,6 +39,9 @@ _SIGNATURES: Dict[str, list] = {
     "qnn_gemm_skinny_tcgen05": [c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_float, c_int, c_vp, c_vp],
     "qnn_attn_decode": [c_vp, c_ll, c_int, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_vp, c_vp, c_int, c_int,
                         c_int, c_int, c_float, c_float, c_int, c_vp, c_vp, c_int, c_vp, c_ll, c_vp],
+    "qnn_attn_extend": [c_vp, c_vp, c_vp, c_ll, c_int, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_vp, c_ll, c_vp, c_vp,
+                        c_vp, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_vp],
+    "qnn_attn_supports": [c_int, c_int, c_int, c_int],
     "qnn_attn_prefill_generic": [c_vp, c_vp, c_vp, c_ll, c_int, c_vp, c_ll, c_vp, c_vp, c_int, c_int, c_int,
                                  c_int, c_float, c_float, c_int, c_vp],
     "qnn_attn_prefill_mma": [c_vp, c_vp, c_vp, c_ll, c_vp, c_ll, c_vp, c_vp, c_int, c_int, c_int, c_int, c_int,
@@ -48,7 +51,7 @@ _SIGNATURES: Dict[str, list] = {
     "qnn_attn_prefill_paged": [c_vp, c_ll, c_int, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_vp, c_ll, c_vp, c_vp,
                                c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_vp],
     "qnn_sample": [c_vp, c_int, c_int, c_int, c_float, c_float, c_float, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp,
-                   c_vp],
+                   c_vp, c_vp],
     "qnn_sample_scratch_bytes": [c_int, c_int, c_int],
     "qnn_mark_seen": [c_vp, c_vp, c_vp, c_int, c_int, c_vp],
 }
@@ -58,6 +61,12 @@ ERR_UNSUPPORTED, ERR_ARGUMENT = 10001, 10002
 
 class KernelError(RuntimeError):
     pass
+
+
+class NonFiniteLogits(RuntimeError):
+    """NaN or Inf in the logits of a forward pass (the reference flags them after every forward,
+    src/models/QuickNN.Models.Gemma2.pas:196, and raises "non-finite values" at the next readback,
+    QuickNN.Vulkan.Context.Implementation.inc:732-756)."""
 
 
 _lock = threading.Lock()

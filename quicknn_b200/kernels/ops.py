@@ -146,8 +146,12 @@ def cast(x: torch.Tensor, dtype: torch.dtype):
     return out
 
 
-def check_finite(x: torch.Tensor, flag: torch.Tensor):
+def check_finite(x: torch.Tensor, flag: Optional[torch.Tensor] = None):
+    """Set ``flag`` (default: this device's non-finite word, read by ``raise_on_status``) if
+    ``x`` holds NaN or Inf."""
     _req(x, "x", torch.float32)
+    if flag is None:
+        flag = finite_flag(x.device)
     _req(flag, "flag", torch.int32)
     L = _lib.load()
     _lib.check(L.qnn_check_finite(_p(x), x.numel(), _p(flag), _stream()), "check_finite")
@@ -179,6 +183,20 @@ def rope_cache_write(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, 
         _p(qkv), dt_code(qkv), T, n_heads, n_kv, head_dim, rot_dim, _p(inv_freq), _p(tok_pos), _p(tok_slot),
         _p(k_pool), _p(v_pool), _p(page_table), page_table.shape[1] if page_table is not None else 0,
         page_size, ring, _p(slot_len), int(write_cache), _stream()), "rope_cache_write")
+
+
+_no_freq = {}
+
+
+def cache_append(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, tok_pos: torch.Tensor,
+                 tok_slot: torch.Tensor, line) -> None:
+    """Append the keys and values of the packed q|k|v rows to a cache line as they are (no rotation).
+    ``line`` is a cache line view (k, v, page_table, page_size, ring, slot_len)."""
+    f = _no_freq.get(qkv.device)
+    if f is None:
+        f = _no_freq[qkv.device] = torch.zeros(0, dtype=torch.float32, device=qkv.device)
+    rope_cache_write(qkv, n_heads, n_kv, head_dim, 0, f, tok_pos, tok_slot, line.k, line.v, line.page_table,
+                     line.page_size, line.ring, line.slot_len, True)
 
 
 FUSE_ROPE = os.environ.get("QNN_FUSE_ROPE", "1") != "0"
@@ -231,28 +249,50 @@ def qkv_rope_cache(x: torch.Tensor, w: torch.Tensor, n_heads: int, n_kv: int, he
     return qkv
 
 
-_gemm_status = {}
+_status = {}
 
 
-def _status_word(device) -> torch.Tensor:
-    t = _gemm_status.get(device)
+def status_words(device) -> torch.Tensor:
+    """Two int32 words per device that kernels set and the host reads together: [0] the status of
+    the tcgen05 kernels' bounded waits (1 loads, 2 tensor-core issue, 4 epilogue), [1] the
+    non-finite flag of ``check_finite``."""
+    device = torch.device(device)
+    t = _status.get(device)
     if t is None:
-        t = torch.zeros(1, dtype=torch.int32, device=device)
-        _gemm_status[device] = t
+        t = torch.zeros(2, dtype=torch.int32, device=device)
+        _status[device] = t
     return t
 
 
-def check_gemm_status(device) -> None:
-    """Raise if a bounded wait inside the tcgen05 product ran out since the last check (one
-    4-byte read; call it where the host synchronises anyway)."""
-    t = _gemm_status.get(torch.device(device))
+def _status_word(device) -> torch.Tensor:
+    return status_words(device)[0:1]
+
+
+def finite_flag(device) -> torch.Tensor:
+    return status_words(device)[1:2]
+
+
+def wait_status_message(v: int) -> str:
+    return (f"a tcgen05 kernel gave up waiting (status {v}: 1 loads, 2 tensor-core issue, 4 epilogue); "
+            f"its result is not valid")
+
+
+def raise_on_status(device) -> None:
+    """Read both words (one 8-byte copy; it synchronises, so call it where the host waits anyway)
+    and raise if a bounded wait ran out or a checked tensor held NaN or Inf since the last call."""
+    t = _status.get(torch.device(device))
     if t is None:
         return
-    v = int(t.item())
-    if v:
+    wait, bad = t.tolist()
+    if wait or bad:
         t.zero_()
-        raise _lib.KernelError(f"the tcgen05 matrix product gave up waiting (status {v}: 1 loads, 2 tensor-core "
-                               f"issue, 4 epilogue); its result is not valid")
+    if wait:
+        raise _lib.KernelError(wait_status_message(wait))
+    if bad:
+        raise _lib.NonFiniteLogits("the model produced non-finite logits")
+
+
+check_gemm_status = raise_on_status
 
 
 GEMM_2CTA = os.environ.get("QNN_GEMM_2CTA", "1") != "0"
@@ -387,6 +427,26 @@ def linear(x: torch.Tensor, w: torch.Tensor, *, epilogue: int = EPI_NONE, cap: O
 ATTN_TCGEN05 = os.environ.get("QNN_ATTN", "tcgen05") != "mma"
 
 
+def attention_refusal(dtype: torch.dtype, n_heads: int, n_kv: int, head_dim: int) -> Optional[str]:
+    """None if the attention kernels take these head counts and this head size in ``dtype``, else the
+    reason in words.  Asked when a model is loaded."""
+    code = _lib.load().qnn_attn_supports(BF16 if dtype == torch.bfloat16 else F32, n_heads, n_kv, head_dim)
+    if code == 0:
+        return None
+    vec = 8 if dtype == torch.bfloat16 else 4
+    if code == _lib.ERR_ARGUMENT:
+        return f"{n_kv} key/value heads do not divide {n_heads} query heads"
+    return (f"head size {head_dim} in {dtype}: the attention kernels take multiples of {vec} up to {128 * vec} "
+            f"(less when four or more query heads share a key/value head)")
+
+
+def linear_refusal(dtype: torch.dtype, inner: int) -> Optional[str]:
+    """None if the matrix products take this inner size in ``dtype``, else the reason."""
+    if dtype == torch.bfloat16 and inner % 8:
+        return f"bfloat16 products need an inner size that is a multiple of 8 (got {inner})"
+    return None
+
+
 def attn_prefill(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, tok_pos: torch.Tensor,
                  tok_row0: torch.Tensor, scale: float, cap: Optional[float], window: Optional[int],
                  seq_row0: Optional[torch.Tensor] = None, seq_len: Optional[torch.Tensor] = None,
@@ -448,6 +508,33 @@ def attn_prefill_paged(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int
     return out
 
 
+def attn_extend(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, k_pool: torch.Tensor, v_pool: torch.Tensor,
+                page_table: torch.Tensor, page_size: int, ring: int, tok_pos: torch.Tensor, tok_row0: torch.Tensor,
+                tok_slot: torch.Tensor, scale: float, cap: Optional[float], window: Optional[int]):
+    """Attention of a step that continues sequences by several tokens: each row sees the cached
+    positions before its sequence's first row of this step (from the cache, as earlier steps left it)
+    and this step's own rows from there to itself (from ``qkv``, already rotated).  The caller appends
+    this step's keys and values to the cache afterwards."""
+    _req(qkv, "qkv", None, 2)
+    _req(k_pool, "k_pool", qkv.dtype, 4)
+    _req(v_pool, "v_pool", qkv.dtype, 4)
+    for n, t in (("tok_pos", tok_pos), ("tok_row0", tok_row0), ("tok_slot", tok_slot)):
+        _req(t, n, torch.int32, 1)
+    T = qkv.shape[0]
+    out = torch.empty((T, n_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
+    es = qkv.element_size()
+    q_ptr = qkv.data_ptr()
+    k_ptr = q_ptr + n_heads * head_dim * es
+    v_ptr = k_ptr + n_kv * head_dim * es
+    L = _lib.load()
+    _lib.check(L.qnn_attn_extend(
+        ctypes.c_void_p(q_ptr), ctypes.c_void_p(k_ptr), ctypes.c_void_p(v_ptr), qkv.shape[1], dt_code(qkv),
+        _p(k_pool), _p(v_pool), _p(page_table), page_table.shape[1], page_size, ring, _p(out), out.shape[1],
+        _p(tok_pos), _p(tok_row0), _p(tok_slot), T, n_heads, n_kv, head_dim, float(scale), float(cap or 0.0),
+        int(window or 0), _stream()), "attn_extend")
+    return out
+
+
 def attn_decode(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, k_pool: torch.Tensor,
                 v_pool: torch.Tensor, page_table: torch.Tensor, page_size: int, ring: int,
                 slots: torch.Tensor, slot_len: torch.Tensor, scale: float, cap: Optional[float],
@@ -482,7 +569,10 @@ def sample_scratch_bytes(rows: int, vocab: int, top_k: int) -> int:
 
 def sample(logits: torch.Tensor, top_k: int, temperature: float, top_p: float, penalty: float,
            rng_state: torch.Tensor, seen: Optional[torch.Tensor], seen_rows: Optional[torch.Tensor],
-           scratch: torch.Tensor, out_tokens: torch.Tensor, error_flag: Optional[torch.Tensor]):
+           scratch: torch.Tensor, out_tokens: torch.Tensor, error_flag: Optional[torch.Tensor],
+           status: Optional[torch.Tensor] = None):
+    """``status`` (one int32 on the device) is OR-ed into ``error_flag`` as bit 1 plus its value
+    from bit 8 up: what the step's kernels reported reaches the host with the ids."""
     _req(logits, "logits", torch.float32, 2)
     R, V = logits.shape
     _req(out_tokens, "out_tokens", torch.int32, 1)
@@ -494,7 +584,7 @@ def sample(logits: torch.Tensor, top_k: int, temperature: float, top_p: float, p
     L = _lib.load()
     _lib.check(L.qnn_sample(_p(logits), R, V, int(top_k), float(temperature), float(top_p), float(penalty),
                             _p(rng_state), _p(seen), _p(seen_rows), _p(scratch), _p(out_tokens), _p(error_flag),
-                            _stream()), "sample", 2)
+                            _p(status), _stream()), "sample", 2)
     return out_tokens
 
 

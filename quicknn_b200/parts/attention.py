@@ -5,8 +5,12 @@ Order of operations as in the reference's layer body
 (src/models/QuickNN.Models.Gemma2.pas:167-180): Q, K, V projections; rotation of Q and K;
 append K, V to the cache; attention with scale 1/sqrt(query_pre_attn_scalar), softcap
 and window; output projection.  The three projections are one product against the
-stacked matrix; rotation and append are one kernel, or, for the few rows of a decode
-step, the epilogue of that product.
+stacked matrix; rotation and append belong to the position part (one kernel, or, for the
+few rows of a decode step, the epilogue of that product).
+
+Decode attention cuts each sequence's keys into ranges that run as separate blocks and are
+merged afterwards; how many ranges, and the scratch that the partial results need, are
+decided here (``tuning["decode_splits"]`` fixes the number).
 """
 from __future__ import annotations
 
@@ -15,7 +19,7 @@ from typing import Dict, Optional, Tuple
 import torch
 
 from ..kernels import ops
-from .base import MIXERS, POSITIONS, CacheNeed, Mixer
+from .base import MIXERS, POSITIONS, CacheNeed, HeadShape, Mixer
 from .linear import project, stack_rows
 from .spec import PartSpec
 
@@ -34,10 +38,12 @@ class AttentionMixer(Mixer):
         self.window = p.get("window")
         if self.n_heads % self.n_kv:
             raise ValueError(f"{self.n_kv} kv heads do not divide {self.n_heads} heads")
+        self.heads = HeadShape(self.n_heads, self.n_kv, self.head_dim)
         pos: PartSpec = p["position"]
         self.position = POSITIONS.get(pos.kind)(pos)
         self.w_qkv: Optional[torch.Tensor] = None
         self.w_o: Optional[torch.Tensor] = None
+        self._resident = 148
 
     @classmethod
     def param_shapes(cls, spec: PartSpec) -> Dict[str, Tuple[Tuple[int, ...], str]]:
@@ -51,10 +57,17 @@ class AttentionMixer(Mixer):
         self.w_qkv = stack_rows([tensors["q_proj"], tensors["k_proj"], tensors["v_proj"]])
         self.w_o = tensors["o_proj"].contiguous()
         self.position.prepare(device)
-        elem = 4 if compute_dtype == torch.float32 else 2
-        if (self.head_dim * elem) % 16:
-            raise ValueError(f"head_dim {self.head_dim} is not a whole number of 16-byte vectors in "
-                             f"{compute_dtype}: the attention kernels refuse it")
+        # sizes that the kernels do not take are refused here, when the model is built, not at its first step
+        why = (ops.attention_refusal(compute_dtype, self.n_heads, self.n_kv, self.head_dim)
+               or ops.linear_refusal(self.w_qkv.dtype, self.hidden)
+               or ops.linear_refusal(self.w_o.dtype, self.n_heads * self.head_dim))
+        if why:
+            raise ValueError(f"attention mixer: {why}")
+        # blocks of the decode attention kernel that the device holds at once: its shared memory is
+        # 384 bytes per element of a head, so two fit on an SM at head size 256, four at 128, eight at 64
+        dev = torch.device(device)
+        sms = torch.cuda.get_device_properties(dev).multi_processor_count if dev.type == "cuda" else 148
+        self._resident = sms * max(1, min(8, 512 // max(1, self.head_dim)))
 
     def weight_bytes(self) -> int:
         return sum(w.numel() * w.element_size() for w in (self.w_qkv, self.w_o))
@@ -62,22 +75,44 @@ class AttentionMixer(Mixer):
     def cache_need(self) -> Optional[CacheNeed]:
         return CacheNeed(self.n_kv, self.head_dim, self.window)
 
+    def decode_splits(self, step) -> int:
+        """Key ranges per sequence in a decode step: a fixed number when the engine's owner gave one;
+        else as many as keep one wave of blocks on the device (measured at head size 256, context 8192:
+        batch 64 one range 9.48 ms against two 9.69; batch 32 two ranges; batch 16 four; batch 8 nine).
+        Results differ between batch sizes by rounding only: ranges are summed in a fixed order."""
+        fixed = step.tuning.get("decode_splits")
+        if fixed:
+            return int(fixed)
+        most = max(1, min(64, step.max_seq // 128))
+        return max(1, min(most, self._resident // max(1, step.n_seqs * self.n_kv)))
+
+    def scratch_need(self, step) -> int:
+        """Partial (maximum, sum, output) of every key range: float32, [rows, heads, ranges, head_dim + 2]."""
+        if step.mode != "decode":
+            return 0
+        return step.n_seqs * self.n_heads * self.decode_splits(step) * (self.head_dim + 2) * 4
+
     def forward(self, x: torch.Tensor, step, line) -> torch.Tensor:
-        if step.mode == "decode" and ops.qkv_rope_cache_fusable(x, self.w_qkv, self.head_dim,
-                                                                self.position.rotary_dim):
-            # few rows: rotation and append ride in the product's epilogue
-            qkv = ops.qkv_rope_cache(x, self.w_qkv, self.n_heads, self.n_kv, self.head_dim,
-                                     self.position.inv_freq, step.tok_pos, step.tok_slot, line.k, line.v,
-                                     line.page_table, line.page_size, line.ring, line.slot_len, line.writes)
-        else:
+        h = self.heads
+        extend = step.mode == "extend"
+        qkv = None if extend else self.position.project_and_place(x, self.w_qkv, h, step, line)
+        if qkv is None:
             qkv = project(x, self.w_qkv)
-            ops.rope_cache_write(qkv, self.n_heads, self.n_kv, self.head_dim, self.position.rotary_dim,
-                                 self.position.inv_freq, step.tok_pos, step.tok_slot, line.k, line.v,
-                                 line.page_table, line.page_size, line.ring, line.slot_len, line.writes)
-        if step.mode == "prefill" and not line.writes:
-            # the keys of this line were written by another layer earlier in this step
-            if line.ring and step.max_q_len > line.ring:
-                raise ValueError(f"a prompt of {step.max_q_len} tokens has overrun the ring of {line.ring} "
+            self.position.place(qkv, h, step, line, append=not extend)
+        if extend and line.writes:
+            # cached keys from before this step, this step's own rows from there on; the append comes last,
+            # so that the first rows still find the ring cells that the last rows overwrite
+            a = ops.attn_extend(qkv, h.n_heads, h.n_kv_heads, h.head_dim, line.k, line.v, line.page_table,
+                                line.page_size, line.ring, step.tok_pos, step.tok_row0, step.tok_slot, self.scale,
+                                self.softcap, self.window)
+            ops.cache_append(qkv, h.n_heads, h.n_kv_heads, h.head_dim, step.tok_pos, step.tok_slot, line)
+        elif step.mode != "decode" and not line.writes:
+            # the keys of this line were written by another layer earlier in this step; in a ring the last
+            # rows of the step have by then overwritten cells: whole prompts may fill the ring, a step that
+            # continues a sequence may bring only as many rows as the ring has cells beyond the window
+            room = line.ring - ((self.window or line.ring) - 1 if extend else 0)
+            if line.ring and step.max_q_len > room:
+                raise ValueError(f"a step of {step.max_q_len} tokens overruns the ring of {line.ring} "
                                  f"positions that this layer reads from another layer's cache line")
             a = ops.attn_prefill_paged(qkv, self.n_heads, self.n_kv, self.head_dim, line.k, line.v,
                                        line.page_table, line.page_size, line.ring, step.tok_pos, step.tok_slot,
@@ -86,7 +121,10 @@ class AttentionMixer(Mixer):
             a = ops.attn_prefill(qkv, self.n_heads, self.n_kv, self.head_dim, step.tok_pos, step.tok_row0,
                                  self.scale, self.softcap, self.window, step.seq_row0, step.seq_len, step.max_q_len)
         else:
+            splits = self.decode_splits(step)
+            n = step.n_seqs * self.n_heads * splits
+            part = step.scratch.view(torch.float32)
             a = ops.attn_decode(qkv, self.n_heads, self.n_kv, self.head_dim, line.k, line.v, line.page_table,
                                 line.page_size, line.ring, step.slots, line.slot_len, self.scale, self.softcap,
-                                self.window, step.decode_splits, step.part_o, step.part_ml)
+                                self.window, splits, part[:n * self.head_dim], part[n * self.head_dim:n * (self.head_dim + 2)])
         return project(a, self.w_o)

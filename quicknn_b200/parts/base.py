@@ -9,10 +9,14 @@ kind of part   interface
 =============  ==============================================================
 Norm           ``param_shapes(spec)``; ``load(tensors)``; ``__call__(x, out_dtype)``
 Positions      ``param_shapes`` (usually none); ``prepare(device)``;
-               ``tables()`` gives what the mixer's kernels need
+               ``place(qkv, heads, step, line, append)`` puts the step's
+               positions into its queries and keys and appends keys and
+               values to the cache line; ``project_and_place`` may fuse that
+               with the q|k|v product
 Mixer          ``param_shapes``; ``load``; ``cache_need()`` (growing keys/values,
                possibly windowed), ``state_need()`` (fixed-size per-sequence
-               state); ``forward(x, step, cache_line)``
+               state), ``scratch_need(step)`` (bytes of scratch for one step);
+               ``forward(x, step, cache_line)``
 FeedForward    ``param_shapes``; ``load``; ``forward(x, step)``
 Block          arrangement of the four above around the residual stream:
                ``forward(resid, step, cache_line)``
@@ -86,6 +90,20 @@ class StateNeed:
     dtype: str = "float32"
 
 
+@dataclasses.dataclass(frozen=True)
+class HeadShape:
+    """How the columns of a packed q|k|v row are cut: ``n_heads`` query heads, then ``n_kv_heads``
+    key heads, then as many value heads, ``head_dim`` columns each."""
+
+    n_heads: int
+    n_kv_heads: int
+    head_dim: int
+
+    @property
+    def width(self) -> int:
+        return (self.n_heads + 2 * self.n_kv_heads) * self.head_dim
+
+
 class Part:
     """Common base: parameters by local name."""
 
@@ -107,6 +125,14 @@ class Part:
     def weight_bytes(self) -> int:
         return 0
 
+    def scratch_need(self, step) -> int:
+        """Bytes of scratch (global memory beyond inputs and outputs) that this part wants for a
+        step of this shape: ``step.mode``, ``step.n_seqs``, ``step.n_tokens``, ``step.max_seq`` and
+        ``step.tuning`` are set when this is asked.  The engine allocates the largest need of all
+        parts once per shape and hands it to every part as ``step.scratch`` (uint8, 256-byte
+        aligned); parts run one after another, so they share it."""
+        return 0
+
 
 class Norm(Part):
     def __call__(self, x, out_dtype=None):  # pragma: no cover - interface
@@ -114,8 +140,22 @@ class Norm(Part):
 
 
 class Positions(Part):
+    """A position encoding owns what it does to queries and keys.  The mixer hands it the packed
+    q|k|v rows of the step and never looks inside."""
+
     def prepare(self, device) -> None:
         pass
+
+    def place(self, qkv, heads: HeadShape, step, line, append: bool = True) -> None:  # pragma: no cover - interface
+        """Put the positions ``step.tok_pos`` into the queries and keys of ``qkv``
+        ([tokens, heads.width], in place) and, with ``append``, write the keys and values of the
+        rows whose slot is not negative to the cache line (``line.writes`` permitting)."""
+        raise NotImplementedError
+
+    def project_and_place(self, x, w_qkv, heads: HeadShape, step, line):
+        """``x w_qkv^T`` with ``place(..., append=True)`` done in the same kernel, or None when this
+        encoding (or these sizes) has no such kernel; the mixer then projects and calls ``place``."""
+        return None
 
 
 class Mixer(Part):

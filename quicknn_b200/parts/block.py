@@ -58,6 +58,9 @@ class _LayerParts(Block):
     def weight_bytes(self) -> int:
         return self.mixer.weight_bytes() + self.ff.weight_bytes() + sum(n.weight_bytes() for n in self.norms.values())
 
+    def scratch_need(self, step) -> int:
+        return max(self.mixer.scratch_need(step), self.ff.scratch_need(step))
+
 
 @BLOCKS.register("sandwich")
 class SandwichBlock(_LayerParts):

@@ -38,6 +38,9 @@ class GatedMLP(FeedForward):
     def load(self, tensors, compute_dtype, device) -> None:
         self.w_gate_up = stack_rows([tensors["gate_proj"], tensors["up_proj"]])
         self.w_down = tensors["down_proj"].contiguous()
+        why = ops.linear_refusal(self.w_gate_up.dtype, self.hidden) or ops.linear_refusal(self.w_down.dtype, self.inter)
+        if why:
+            raise ValueError(f"gated feed-forward: {why}")
 
     def weight_bytes(self) -> int:
         return sum(w.numel() * w.element_size() for w in (self.w_gate_up, self.w_down))

@@ -1,5 +1,6 @@
-"""Position encodings.  A position part hands the mixer's kernels what they need to
-place a token: for ``rotary`` the table of frequencies and the rotated width.
+"""Position encodings.  A position part places a step's tokens: it changes the queries and keys
+of the packed q|k|v rows according to their positions and appends keys and values to the cache
+(one kernel does both, so the two belong to one call).
 
 Reference: GO_LLM_ROPE, angle = position * exp(-ln(theta) * 2j / head_dim), half-split
 rotation of the whole head (src/backends/vulkan/shaders/tensor.comp:318-327).  The
@@ -13,7 +14,8 @@ from typing import Optional
 
 import torch
 
-from .base import POSITIONS, Positions
+from ..kernels import ops
+from .base import POSITIONS, HeadShape, Positions
 from .spec import PartSpec
 
 
@@ -33,6 +35,19 @@ class Rotary(Positions):
         f = torch.exp(-math.log(self.theta) * 2.0 * j / self.rotary_dim)
         self.inv_freq = f.to(torch.float32).to(device)
 
+    def place(self, qkv, heads: HeadShape, step, line, append: bool = True) -> None:
+        ops.rope_cache_write(qkv, heads.n_heads, heads.n_kv_heads, heads.head_dim, self.rotary_dim, self.inv_freq,
+                             step.tok_pos, step.tok_slot, line.k, line.v, line.page_table, line.page_size, line.ring,
+                             line.slot_len, bool(append and line.writes))
+
+    def project_and_place(self, x, w_qkv, heads: HeadShape, step, line):
+        """For the few rows of a decode step, rotation and append ride in the product's epilogue."""
+        if step.mode != "decode" or not ops.qkv_rope_cache_fusable(x, w_qkv, heads.head_dim, self.rotary_dim):
+            return None
+        return ops.qkv_rope_cache(x, w_qkv, heads.n_heads, heads.n_kv_heads, heads.head_dim, self.inv_freq,
+                                  step.tok_pos, step.tok_slot, line.k, line.v, line.page_table, line.page_size,
+                                  line.ring, line.slot_len, line.writes)
+
 
 @POSITIONS.register("none")
 class NoPositions(Positions):
@@ -46,3 +61,7 @@ class NoPositions(Positions):
 
     def prepare(self, device) -> None:
         self.inv_freq = torch.zeros(0, dtype=torch.float32, device=device)
+
+    def place(self, qkv, heads: HeadShape, step, line, append: bool = True) -> None:
+        if append and line.writes:
+            ops.cache_append(qkv, heads.n_heads, heads.n_kv_heads, heads.head_dim, step.tok_pos, step.tok_slot, line)

@@ -7,12 +7,9 @@ import numpy as np
 import torch
 
 from ..kernels import ops
+from ..kernels.lib import KernelError, NonFiniteLogits
 from .options import GenerationOptions, seed_state
 
-
-class NonFiniteLogits(RuntimeError):
-    """NaN or Inf in the logits (the reference raises "non-finite values" at the next
-    readback, QuickNN.Vulkan.Context.Implementation.inc:732-756)."""
 
 
 class Sampler:
@@ -68,7 +65,7 @@ class Sampler:
         if self.seen is not None:
             seen_rows = torch.arange(R, dtype=torch.int32, device=self.device)
         ops.sample(logits, o.top_k, o.temperature, o.top_p, o.repetition_penalty, self.rng, self.seen,
-                   seen_rows, self.scratch, self.out, self.flag)
+                   seen_rows, self.scratch, self.out, self.flag, ops.status_words(self.device)[0:1])
         return self.out[:R]
 
     def read(self, tokens: torch.Tensor) -> np.ndarray:
@@ -93,7 +90,11 @@ class Sampler:
         """Wait for the read queued by ``post`` and return the ids."""
         self._event.synchronize()
         both = self._pinned[:self._posted + 1].numpy().copy()
-        if both[-1] != 0:
+        word = int(both[-1])
+        if word != 0:
             self.flag.zero_()
+            if word & 2:                      # a bounded wait of a tcgen05 kernel ran out during the step
+                ops.status_words(self.device)[0:1].zero_()
+                raise KernelError(ops.wait_status_message(word >> 8))
             raise NonFiniteLogits("the model produced non-finite logits")
         return both[:-1]

@@ -40,8 +40,11 @@ def random_tensors(arch: Architecture, cfg: ModelConfig, seed: int, dtype: torch
 
 
 def write_model_folder(path: str, arch: Architecture, cfg: ModelConfig, seed: int,
-                       dtype: torch.dtype = torch.bfloat16, norm_std: Optional[float] = None) -> str:
-    """Write ``config.json`` and ``model.safetensors`` for a random model."""
+                       dtype: torch.dtype = torch.bfloat16, norm_std: Optional[float] = None,
+                       device="cpu") -> str:
+    """Write ``config.json`` and ``model.safetensors`` for a random model.  ``device`` is where
+    the values are drawn (a CUDA device draws a large model in seconds; its generator gives
+    other values than the host's for the same seed)."""
     os.makedirs(path, exist_ok=True)
     raw = cfg.to_dict()
     if not raw.get("architectures"):
@@ -49,7 +52,7 @@ def write_model_folder(path: str, arch: Architecture, cfg: ModelConfig, seed: in
     raw["torch_dtype"] = "bfloat16" if dtype == torch.bfloat16 else "float32"
     with open(os.path.join(path, "config.json"), "w", encoding="utf-8") as fh:
         json.dump(raw, fh, indent=1)
-    tensors: Dict[str, torch.Tensor] = dict(random_tensors(arch, cfg, seed, dtype, norm_std))
+    tensors: Dict[str, torch.Tensor] = {n: t.cpu() for n, t in random_tensors(arch, cfg, seed, dtype, norm_std, device)}
     write_safetensors(os.path.join(path, "model.safetensors"), tensors,
                       metadata={"format": "pt", "seed": str(seed)})
     return path

@@ -244,13 +244,15 @@ def seed_state(seed: int) -> int:
 
 
 def sample(row: np.ndarray, temperature: float, top_k: int, top_p: float, penalty: float,
-           seen: Optional[np.ndarray], uniform: float) -> int:
+           seen: Optional[np.ndarray], uniform: float, info: Optional[dict] = None) -> int:
     """Top-k, temperature softmax over the kept, nucleus cut, inverse CDF
     (tensor.comp:164-197): repetition penalty s<0 ? s*pen : s/pen on seen ids (:172);
     k = 1 when temperature <= 0 (:168); candidates ordered by score, lowest id first on
     ties (:173); p_j = exp((s_j - s_0)/T); keep the shortest prefix whose mass reaches
     top_p * total (:190-191); draw target = u * retained, pick the first j whose running
-    sum exceeds it, else the last kept (:192-194).  Sums run in float32 as in the shader."""
+    sum exceeds it, else the last kept (:192-194).  Sums run in float32 as in the shader.
+    ``info`` (if given) receives ``margin``: the distance of the draw from the nearest boundary
+    between two candidates, as a fraction of the retained mass (1.0 for a greedy pick)."""
     s = row.astype(np.float32).copy()
     if seen is not None and penalty != 1.0:
         m = seen.astype(bool)
@@ -259,6 +261,8 @@ def sample(row: np.ndarray, temperature: float, top_k: int, top_p: float, penalt
     if temperature <= 0:
         k = 1
     order = np.lexsort((np.arange(len(s)), -s))[:k]
+    if info is not None:
+        info["margin"] = 1.0
     if k == 1:
         return int(order[0])
     vals = s[order]
@@ -281,4 +285,7 @@ def sample(row: np.ndarray, temperature: float, top_k: int, top_p: float, penalt
         if target < acc:
             chosen = int(order[j])
             break
+    if info is not None:
+        sums = np.cumsum(probs[:count].astype(np.float64))
+        info["margin"] = float(np.abs(sums - float(target)).min() / float(retained))
     return chosen

@@ -188,7 +188,11 @@ class TorchGemma2:
     def logits(self, ids: Sequence[int], rows: Optional[Sequence[int]] = None) -> np.ndarray:
         """Logits [rows, V] (every position when ``rows`` is None): final norm, tied head, final
         softcap (Gemma2.pas:192-195; the reference keeps only the last row)."""
-        x = self.hidden_states(ids)
+        return self.logits_of_hidden(self.hidden_states(ids), rows)
+
+    @torch.no_grad()
+    def logits_of_hidden(self, x: torch.Tensor, rows: Optional[Sequence[int]] = None) -> np.ndarray:
+        """The head alone, on rows of a residual stream that ``hidden_states`` returned."""
         if rows is not None:
             x = x[torch.as_tensor(list(rows), dtype=torch.long, device=self.device)]
         n = rmsnorm(x, self.w["model.norm.weight"], self.eps)

@@ -108,6 +108,10 @@ def test_random_walk_keeps_invariants():
             s = rnd.choice(list(live))
             c.free(s)
             del live[s]
+        elif r < 0.55 and live:
+            s = rnd.choice(list(live))                      # the undo of a step that was not launched
+            live[s] = max(0, live[s] - rnd.choice([1, 1, 17, 90]))
+            c.truncate([(s, live[s])])
         elif live:
             s = rnd.choice(list(live))
             n = live[s] + rnd.choice([1, 1, 1, 17, 90])
@@ -138,3 +142,31 @@ def test_state_region_zeroed_on_allocation():
     assert s2 == s and float(c.line(1).state[s2].abs().sum()) == 0.0
     empty = make()
     assert empty.state == {}                  # Gemma 2 asks for no state: zero lines
+
+
+def test_truncate_gives_back_what_extend_took():
+    c = make(max_tokens=512, max_slots=4, max_seq=256, window=100)
+    a = c.allocate()
+    c.extend([(a, 70)])
+    free = [g.pool.n_free for g in c.groups]
+    c.extend([(a, 200)])
+    c.truncate([(a, 70)])
+    assert c.length(a) == 70 and [g.pool.n_free for g in c.groups] == free
+    c.audit()
+    with pytest.raises(ValueError):
+        c.truncate([(a, 71)])
+    c.truncate([(a, 0)])
+    assert c.tokens_held() == 0
+    c.audit()
+
+
+def test_a_windowed_group_holds_a_ring_per_slot_at_most():
+    c = make(max_tokens=4096, max_slots=2, max_seq=2048, window=100)
+    ring_group = [g for g in c.groups if g.ring][0]
+    full_group = [g for g in c.groups if not g.ring][0]
+    assert ring_group.ring == 128 and ring_group.pool.n_pages == 2 * 2 + 1
+    assert full_group.pool.n_pages == 4096 // PAGE + 1
+    a, b = c.allocate(), c.allocate()
+    c.extend([(a, 2048), (b, 2048)])               # both rings full, the pool of the ring group exhausted
+    assert ring_group.pool.n_free == 0
+    c.audit()

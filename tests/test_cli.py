@@ -1,0 +1,92 @@
+"""The command line: ``python -m quicknn_b200 random | info | generate`` and its refusals."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+
+from conftest import ROOT, TINY, prompts_for
+
+
+def run(*argv, stdin=None):
+    env = dict(os.environ, PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    return subprocess.run([sys.executable, "-m", "quicknn_b200", *argv], input=stdin, capture_output=True, text=True,
+                          env=env, cwd=str(ROOT))
+
+
+def test_random_writes_a_folder_that_info_describes(tmp_path):
+    raw, seed, _ = TINY["B"]
+    cfg = tmp_path / "cfg.json"
+    cfg.write_text(json.dumps(raw))
+    out = tmp_path / "model"
+    p = run("random", "--config", str(cfg), "--seed", str(seed), "--out", str(out), "--dtype", "float32")
+    assert p.returncode == 0, p.stderr
+    assert p.stdout.strip() == str(out)
+    assert (out / "config.json").is_file() and (out / "model.safetensors").is_file()
+    p = run("info", "--model", str(out))
+    assert p.returncode == 0, p.stderr
+    info = json.loads(p.stdout)
+    H, I, V, L = raw["hidden_size"], raw["intermediate_size"], raw["vocab_size"], raw["num_hidden_layers"]
+    nq, nkv, hd = raw["num_attention_heads"], raw["num_key_value_heads"], raw["head_dim"]
+    per_layer = H * (nq + 2 * nkv) * hd + nq * hd * H + 3 * H * I + 4 * H
+    assert info["architecture"] == "Gemma2ForCausalLM" and info["layers"] == L
+    assert info["parameters"] == V * H + L * per_layer + H
+    assert info["config"]["sliding_window"] == raw["sliding_window"]
+    # the same seed gives the same file; another seed another
+    out2 = tmp_path / "again"
+    assert run("random", "--config", str(cfg), "--seed", str(seed), "--out", str(out2), "--dtype", "float32").returncode == 0
+    assert (out / "model.safetensors").read_bytes() == (out2 / "model.safetensors").read_bytes()
+
+
+def test_unknown_options_and_commands_are_errors(tmp_path):
+    p = run("info", "--model", str(tmp_path), "--verbose")
+    assert p.returncode == 2 and "unrecognized arguments" in p.stderr
+    p = run("info", "--mod", str(tmp_path))             # no abbreviations
+    assert p.returncode == 2
+    p = run("serve")
+    assert p.returncode == 2 and "invalid choice" in p.stderr
+    p = run("generate", "--model", str(tmp_path), "--top-k", "many")
+    assert p.returncode == 2
+    p = run("--help")
+    assert p.returncode == 0 and "generate" in p.stdout and "random" in p.stdout
+
+
+def test_generate_without_a_gpu_says_so_in_one_line(tmp_path):
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("this machine has a CUDA device")
+    p = run("generate", "--model", str(tmp_path), "--prompt-ids", "5,6")
+    assert p.returncode == 3 and "Traceback" not in p.stderr and "no CUDA device" in p.stderr
+
+
+@pytest.mark.gpu
+def test_generate_prints_what_the_plain_model_generates(folders, plain_models, tmp_path):
+    import torch
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    folder = folders("A", "float32")
+    plain = plain_models("A", "float32")
+    prompts = prompts_for("A", [5, 11, 17])
+    ids = ";".join(",".join(str(t) for t in p) for p in prompts)
+    p = run("generate", "--model", folder, "--prompt-ids", ids, "--max-new-tokens", "8", "--temperature", "0",
+            "--dtype", "float32", "--max-context", "64", "--stop-ids", "", "--stream")
+    assert p.returncode == 0, p.stderr
+    lines = [json.loads(l) for l in p.stdout.splitlines() if l.strip()]
+    results = [l for l in lines if "tokens" in l]
+    streamed = [l for l in lines if "token" in l]
+    assert len(results) == 3 and len(streamed) == 24
+    for r, pr in zip(results, prompts):
+        assert r["tokens"] == plain.greedy(pr, 8) and r["finish_reason"] == "max_tokens"
+        assert [s["token"] for s in streamed if s["request"] == r["request"]] == r["tokens"]
+    # prompts from a file, a stop id, and an option that the options' own rules refuse
+    f = tmp_path / "prompts.jsonl"
+    f.write_text(json.dumps(prompts[0]) + "\n" + json.dumps({"tokens": prompts[1]}) + "\n")
+    stop = plain.greedy(prompts[1], 8)[3]
+    p = run("generate", "--model", folder, "--prompt-file", str(f), "--max-new-tokens", "8", "--temperature", "0",
+            "--dtype", "float32", "--max-context", "64", "--stop-ids", str(stop))
+    assert p.returncode == 0, p.stderr
+    got = [json.loads(l) for l in p.stdout.splitlines() if l.strip()]
+    assert got[1]["tokens"] == plain.greedy(prompts[1], 8, stop_ids=[stop]) and got[1]["finish_reason"] == "eos"
+    p = run("generate", "--model", folder, "--prompt-ids", "5", "--top-p", "1.5")
+    assert p.returncode != 0

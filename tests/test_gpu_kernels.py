@@ -95,6 +95,14 @@ def test_gated_activation_softcap_gather_cast(ops, dtype):
     x = bf16_round(rng.normal(size=(3, 33)) * 40)
     assert_close(ops.softcap(T(x, dtype), 15.0), P.softcap(x, 15.0), torch.float32, "softcap")
     assert_close(ops.softcap(T(x, dtype), None), x, torch.float32, "softcap off")
+    bad = torch.tensor([float("nan"), float("inf"), -float("inf"), 1.0], dtype=dtype, device=DEV)
+    capped = ops.softcap(bad, 15.0).cpu().numpy()          # NaN must stay visible to the finite check; Inf saturates
+    assert np.isnan(capped[0]) and np.allclose(capped[1:3], [15.0, -15.0]) and np.isfinite(capped[3])
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops.check_finite(ops.softcap(bad[3:], 15.0), flag)
+    assert flag.item() == 0
+    ops.check_finite(ops.softcap(bad, 15.0), flag)
+    assert flag.item() != 0
     rows = T(np.array([2, 0, 2], dtype=np.int32), torch.int32)
     assert_close(ops.gather_rows(T(x, dtype), rows, torch.float32), x[[2, 0, 2]], torch.float32, "gather")
     assert ops.cast(T(x, torch.float32), torch.bfloat16).dtype == torch.bfloat16

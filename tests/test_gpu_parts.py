@@ -33,7 +33,7 @@ def rnd(shape, seed, scale=1.0):
     return (np.random.default_rng(seed).normal(size=shape) * scale).astype(np.float32)
 
 
-def make_step(lens, starts, slots, mode, dtype, cache, splits=2):
+def make_step(lens, starts, slots, mode, dtype, cache, splits=2, part=None):
     from quicknn_b200.engine.batch import StepBatch
     i32 = lambda a: torch.tensor(np.asarray(a), dtype=torch.int32, device=DEV)  # noqa: E731
     T = sum(lens)
@@ -42,10 +42,11 @@ def make_step(lens, starts, slots, mode, dtype, cache, splits=2):
     row0 = np.concatenate([np.full(n, r) for r, n in zip(np.cumsum([0] + lens[:-1]), lens)])
     cache.extend([(s, st + n) for s, st, n in zip(slots, starts, lens)])
     cache.sync()
-    po = torch.empty(len(lens) * 64 * splits * 64, device=DEV)
-    pm = torch.empty(len(lens) * 64 * splits * 2, device=DEV)
-    return StepBatch(mode, T, len(lens), i32(np.zeros(T)), i32(pos), i32(slot), i32(row0), i32(slots), i32([T - 1]),
-                     dtype, splits, po, pm, max(lens))
+    step = StepBatch(mode, T, len(lens), i32(np.zeros(T)), i32(pos), i32(slot), i32(row0), i32(slots), i32([T - 1]),
+                     dtype, max(lens), max_seq=cache.max_seq, tuning={"decode_splits": splits})
+    need = part.scratch_need(step) if part is not None else 0      # what the engine does for all parts of a model
+    step.scratch = torch.empty(need, dtype=torch.uint8, device=DEV) if need else None
+    return step
 
 
 def test_norm_part():
@@ -123,11 +124,13 @@ def test_attention_part_prefill_then_decode(window):
     ref = [plain(x) for x in xs]
     slots = [cache.allocate(), cache.allocate()]
     slots = slots[::-1]
-    step = make_step(lens, [0, 0], slots, "prefill", torch.float32, cache)
+    step = make_step(lens, [0, 0], slots, "prefill", torch.float32, cache, part=mixer)
+    assert step.scratch is None                                    # prompts need no scratch
     y = host(mixer.forward(dev(np.concatenate([x[:n] for x, n in zip(xs, lens)])), step, cache.line(0)))
     assert np.abs(y - np.concatenate([r[:n] for r, n in zip(ref, lens)])).max() < 2e-5
     for t in range(6):
-        step = make_step([1, 1], [n + t for n in lens], slots, "decode", torch.float32, cache)
+        step = make_step([1, 1], [n + t for n in lens], slots, "decode", torch.float32, cache, part=mixer)
+        assert step.scratch.numel() == 2 * nq * 2 * (hd + 2) * 4    # rows x heads x ranges x (head + 2) floats
         y = host(mixer.forward(dev(np.stack([x[n + t] for x, n in zip(xs, lens)])), step, cache.line(0)))
         assert np.abs(y - np.stack([r[n + t] for r, n in zip(ref, lens)])).max() < 2e-5
 
@@ -194,10 +197,14 @@ def _define_toy():
         def state_need(self):
             return StateNeed((self.hidden,), "float32")
 
+        def scratch_need(self, step):
+            return step.n_tokens * self.hidden * 4          # the running sums of the step's rows, float32
+
         def forward(self, x, step, line):
             slots = step.tok_slot.cpu().tolist()
             xf = x.float()
-            out = torch.empty_like(xf)
+            assert step.scratch is not None and step.scratch.numel() >= self.scratch_need(step)
+            out = step.scratch[:xf.numel() * 4].view(torch.float32).view(xf.shape)
             for t, s in enumerate(slots):                   # a toy: token by token
                 if s < 0:
                     out[t] = 0
@@ -305,7 +312,12 @@ def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
         want = np.concatenate([ref[0][:20], ref[1][:5]])
         assert np.abs(got - want).max() < 1e-4 * max(1.0, np.abs(want).max()), round_
         pos = [20, 5]
-        for _ in range(7):
+        if round_ == 1:           # several tokens onto started sequences: the state carries on, the attention
+            got = host(eng.step([(slots[0], seqs[0][20:23]), (slots[1], seqs[1][5:6])], "all"))   # layer reads cache + step
+            want = np.concatenate([ref[0][20:23], ref[1][5:6]])
+            assert np.abs(got - want).max() < 1e-4 * max(1.0, np.abs(want).max())
+            pos = [23, 6]
+        for _ in range(6):
             got = host(eng.step([(s, [q[p]]) for s, q, p in zip(slots, seqs, pos)]))
             for r in range(2):
                 assert np.abs(got[r] - ref[r][pos[r]]).max() < 1e-4 * max(1.0, np.abs(ref[r]).max())
@@ -379,6 +391,14 @@ def _define_toy2():
         def apply(self, x, tok_pos):
             return (x.float() + torch.sin(tok_pos.float().unsqueeze(1) * self.rates.unsqueeze(0))).to(x.dtype)
 
+        def place(self, qkv, heads, step, line, append=True):
+            """What the stock attention mixer calls: the same signal added to every query and key head
+            (``size`` = head size), values untouched, then the append."""
+            qk = qkv[:, :(heads.n_heads + heads.n_kv_heads) * heads.head_dim].view(qkv.shape[0], -1, heads.head_dim)
+            qk.add_(torch.sin(step.tok_pos.float().unsqueeze(1) * self.rates.unsqueeze(0)).unsqueeze(1).to(qkv.dtype))
+            if append and line.writes:
+                ops.cache_append(qkv, heads.n_heads, heads.n_kv_heads, heads.head_dim, step.tok_pos, step.tok_slot, line)
+
     @MIXERS.register("toy_posdecay", replace=True)
     class PosDecayMixer(Mixer):
         """The decaying sum of the first toy, over inputs that carry their position."""
@@ -444,15 +464,22 @@ def _define_toy2():
                                                                       "rotary_dim": c.rotary_dim})})
         posmix = PartSpec("toy_posdecay", {"hidden_size": H, "decay": c.decay,
                                            "position": PartSpec("toy_sinusoid", {"size": H, "base": 50.0})})
+        # the stock attention mixer with a position part that is not a rotation: nothing of the mixer changes
+        attn_abs = PartSpec("attention", {"hidden_size": H, "n_heads": c.n_heads, "n_kv_heads": c.n_kv_heads,
+                                          "head_dim": c.head_dim, "scale": c.head_dim ** -0.5, "softcap": None,
+                                          "window": None,
+                                          "position": PartSpec("toy_sinusoid", {"size": c.head_dim, "base": 30.0})})
         n4 = {k: norm for k in ("pre_mixer", "pre_ff")}
         l0 = {"mixer.mix": "a.mix", "ff.router": "a.router", "ff.w_in": "a.w_in", "ff.w_out": "a.w_out",
               "norms.pre_mixer.weight": "a.n1", "norms.pre_ff.weight": "a.n2"}
         l1 = {f"mixer.{x}_proj": f"b.{x}" for x in "qkvo"}
         l1.update({f"ff.{n}_proj": f"b.{n}" for n in ("gate", "up", "down")})
         l1.update({"norms.pre_mixer.weight": "b.n1", "norms.pre_ff.weight": "b.n2"})
+        l2 = {k.replace("b.", "c."): v.replace("b.", "c.") for k, v in l1.items()}
         layers = (LayerSpec(PartSpec("prenorm", {}), posmix, routed, n4, l0),
-                  LayerSpec(PartSpec("prenorm", {}), attn, dense, n4, l1))
-        schedule = (ScheduleEntry(0, 0), ScheduleEntry(1, 1))
+                  LayerSpec(PartSpec("prenorm", {}), attn, dense, n4, l1),
+                  LayerSpec(PartSpec("prenorm", {}), attn_abs, dense, n4, l2))
+        schedule = (ScheduleEntry(0, 0), ScheduleEntry(1, 1), ScheduleEntry(2, 2))
         return ModelSpec("Toy2ForTest", H, EmbeddingSpec(c.vocab_size, H, 1.0, "emb"), layers, schedule,
                          HeadSpec(c.vocab_size, H, True, None, None, norm, "nf"), c.max_position_embeddings,
                          init_std=0.3, init_norm_std=0.2)
@@ -499,6 +526,15 @@ def _toy2_plain(w, cfg, ids):
     x = x + a @ w["b.o"].T
     n = norm(x, w["b.n2"])
     x = x + (P.gelu_tanh(n @ w["b.gate"].T) * (n @ w["b.up"].T)) @ w["b.down"].T
+    # layer 2: full attention whose queries and keys carry an added position signal, dense feed-forward
+    n = norm(x, w["c.n1"])
+    sig = np.sin(pos[:, None] * np.exp(-math.log(30.0) * np.arange(hd) / hd).astype(np.float32).astype(np.float64)[None, :])
+    q = (n @ w["c.q"].T).reshape(T, nh, hd) + sig[:, None, :]
+    k = (n @ w["c.k"].T).reshape(T, nkv, hd) + sig[:, None, :]
+    v = (n @ w["c.v"].T).reshape(T, nkv, hd)
+    x = x + P.attention(q, k, v, hd ** -0.5, None, None).reshape(T, -1) @ w["c.o"].T
+    n = norm(x, w["c.n2"])
+    x = x + (P.gelu_tanh(n @ w["c.gate"].T) * (n @ w["c.up"].T)) @ w["c.down"].T
     return norm(x, w["nf"]) @ w["emb"].T, best
 
 

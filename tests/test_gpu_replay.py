@@ -150,3 +150,44 @@ def test_replay_refuses_more_tokens_than_it_was_sized_for(folders, tmp_path):
                        capture_output=True, text=True)
     assert p.returncode != 0 and "done 0" not in p.stdout
     assert "CacheFull" in p.stderr or "at most 64 tokens" in p.stderr
+
+
+@pytest.mark.parametrize("name,dtype,peaky", [("A", "float32", True), ("B", "float32", False), ("B", "bfloat16", False),
+                                              ("C", "float32", True), ("D", "bfloat16", False)])
+def test_prompts_cut_into_portions_and_requests_that_join_or_sit_out(folders, plain_models, tmp_path, name, dtype, peaky):
+    """Steps that are neither whole prompts nor one token each: a request goes on by several tokens
+    (portions of 2, portions that end on the 64-token page edge, portions longer than the window), sits
+    out a step, or starts while others go on.  Same logits at every position as the plain model."""
+    folder = folders(name, dtype, peaky)
+    plain = plain_models(name, dtype, peaky)
+    big = name in ("C", "D")
+    requests = prompts_for(name, [257, 170, 45] if big else [129, 70, 45], seed=11)
+    ref = [plain.logits(t) for t in requests]
+    replay = Replay(folder, dtype, tmp_path, max_tokens=576 if big else 384)
+    pos = [0, 0, 0]
+
+    def step(*parts, end=()):
+        """parts: (request, number of tokens); every position of every portion is checked."""
+        entries = [(f"r{i}", requests[i][pos[i]:pos[i] + n], range(n)) for i, n in parts]
+        got = replay.step(entries, end=[f"r{i}" for i in end])
+        r = 0
+        for i, n in parts:
+            ok, err, tol = close(got[r:r + n], ref[i][pos[i]:pos[i] + n], dtype)
+            assert ok, f"request {i} positions {pos[i]}..{pos[i] + n - 1}: error {err:.3g} > {tol:.3g}"
+            pos[i] += n
+            r += n
+    try:
+        a, b = len(requests[0]), len(requests[1])
+        step((0, 2), (1, 62))                    # two start together
+        step((0, 62))                            # request 1 sits out; request 0 reaches the page edge (64)
+        step((0, 2), (1, 2), (2, 40))            # portions of 2 across the edge; request 2 joins the batch
+        step((0, 1), (1, 1), (2, 1))             # an ordinary decode step in between
+        step((0, a - 67 - 3), (2, 4), end=[2])   # a portion longer than every window; request 2 ends
+        step((0, 3), (1, b - 65), end=[0, 1])
+        assert pos == [a, b, 45]
+        # what they held is free again: the longest request, whole
+        got = replay.step([("again", requests[0], [a - 1])], end=["again"])
+        ok, err, tol = close(got, ref[0][a - 1:a], dtype)
+        assert ok, (err, tol)
+    finally:
+        replay.close()
