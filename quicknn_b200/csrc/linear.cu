@@ -18,8 +18,12 @@
 // stacked, the CTA computes 8 columns of a head with their partners half a head away, rotates
 // the pairs by the token's position and writes K and V to the paged cache as well (what
 // rope_cache.cu does as a kernel of its own; reference: Gemma2.pas:167-175 runs three
-// projections, two rotations and a cache write as six dispatches).
+// projections, two rotations and a cache write as six dispatches); 4 arg-max: softcap, then only the
+// best (value, id) of the CTA's 16 output columns is stored for each row, out[row][CTA] as float2
+// (the head of a greedy decode step: the logits themselves are never written; the reference takes
+// the top-k of 512-wide tiles straight from the logits tensor, shaders/tensor.comp:121-155).
 #include "common.cuh"
+#include <float.h>
 
 using namespace qnn;
 
@@ -27,6 +31,7 @@ using namespace qnn;
 #define EPI_SOFTCAP 1
 #define EPI_GATED 2
 #define EPI_ROPE 3
+#define EPI_ARGMAX 4
 
 // What the rotate-and-append epilogue needs; the meaning of each field is that of the argument
 // of the same name of qnn_rope_cache_write.
@@ -73,7 +78,7 @@ __device__ __forceinline__ uint4 ldg16_early(const bf16* p) {
 template <int NT, int EPI, int NW>
 __global__ void __launch_bounds__(NW * 32) skinny_bf16_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W,
                                                           void* __restrict__ out, int out_dt, int M, int N, int K,
-                                                          float cap, int act, const RopeEpi rp) {
+                                                          float cap, int act, const RopeEpi rp, int* __restrict__ err) {
     constexpr int COLS = NT * 8;
     constexpr int THREADS = NW * 32;
     __shared__ float red[NW][16][COLS + 1];
@@ -291,10 +296,30 @@ __global__ void __launch_bounds__(NW * 32) skinny_bf16_kernel(const bf16* __rest
 #pragma unroll
             for (int w = 0; w < NW; ++w) u += red[w][row][col];
             v = activate_fast(v, act) * u;          // bfloat16 inputs and output: the fast activation
-        } else if (EPI == EPI_SOFTCAP) {
+        } else if (EPI == EPI_SOFTCAP || EPI == EPI_ARGMAX) {
             v = softcap(v, cap);
         }
-        if (n < Nout && m < M) store_out(out, out_dt, (size_t)m * Nout + n, v);
+        if constexpr (EPI == EPI_ARGMAX) {
+            // the 16 lanes of a half-warp hold the CTA's 16 columns of row m: the largest wins, the lowest
+            // column on ties; NaN and Inf set the error word and lose (whole warps get here: 16 * COLS is a
+            // multiple of 32)
+            unsigned id = (n < Nout && m < M) ? (unsigned)n : 0xffffffffu;
+            if (id != 0xffffffffu && (isnan(v) || isinf(v))) {
+                if (err != nullptr) atomicOr(err, 1);
+                v = -FLT_MAX;
+            }
+            if (id == 0xffffffffu) v = -FLT_MAX;
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, v, o, 16);
+                const unsigned oi = __shfl_xor_sync(0xffffffffu, id, o, 16);
+                if (ov > v || (ov == v && oi < id)) { v = ov; id = oi; }
+            }
+            if (row == 0 && m < M)
+                reinterpret_cast<float2*>(out)[(size_t)m * gridDim.x + blockIdx.x] = make_float2(v, __uint_as_float(id));
+        } else {
+            if (n < Nout && m < M) store_out(out, out_dt, (size_t)m * Nout + n, v);
+        }
     }
     }
 }
@@ -304,7 +329,7 @@ __global__ void __launch_bounds__(NW * 32) skinny_bf16_kernel(const bf16* __rest
 // least two 32-wide blocks and the partial tiles fit in shared memory.
 template <int EPI>
 static int launch_skinny(const bf16* x, const bf16* W, void* out, int out_dt, int M, int N, int K, float cap, int act,
-                         cudaStream_t st, const RopeEpi rp = RopeEpi()) {
+                         cudaStream_t st, const RopeEpi rp = RopeEpi(), int* err = nullptr) {
     const int Nout = (EPI == EPI_GATED) ? N / 2 : N;
     const unsigned blocks = (unsigned)((Nout + 15) / 16);
     const int nt = (M + 7) / 8;
@@ -314,11 +339,11 @@ static int launch_skinny(const bf16* x, const bf16* W, void* out, int out_dt, in
     if (nt == 1 && blocks * 16u < 3000u && kblocks >= 64) nw = 32;
 #define QNN_SK(NTV)                                                                                            \
     if (nw == 32 && NTV == 1)                                                                                  \
-        qnn::launch_pdl(skinny_bf16_kernel<1, EPI, 32>, dim3(blocks), dim3(1024), 0, st, x, W, out, out_dt, M, N, K, cap, act, rp);         \
+        qnn::launch_pdl(skinny_bf16_kernel<1, EPI, 32>, dim3(blocks), dim3(1024), 0, st, x, W, out, out_dt, M, N, K, cap, act, rp, err);         \
     else if (nw >= 16 && NTV <= 2)                                                                             \
-        qnn::launch_pdl(skinny_bf16_kernel<(NTV <= 2 ? NTV : 1), EPI, 16>, dim3(blocks), dim3(512), 0, st, x, W, out, out_dt, M, N, K, cap, act, rp); \
+        qnn::launch_pdl(skinny_bf16_kernel<(NTV <= 2 ? NTV : 1), EPI, 16>, dim3(blocks), dim3(512), 0, st, x, W, out, out_dt, M, N, K, cap, act, rp, err); \
     else                                                                                                       \
-        qnn::launch_pdl(skinny_bf16_kernel<NTV, EPI, 8>, dim3(blocks), dim3(256), 0, st, x, W, out, out_dt, M, N, K, cap, act, rp);         \
+        qnn::launch_pdl(skinny_bf16_kernel<NTV, EPI, 8>, dim3(blocks), dim3(256), 0, st, x, W, out, out_dt, M, N, K, cap, act, rp, err);         \
     break;
     switch (nt) {
         case 1: QNN_SK(1)
@@ -343,6 +368,17 @@ QNN_API int qnn_skinny_bf16(const void* x, const void* W, void* out, int out_dt,
         case EPI_GATED: return launch_skinny<EPI_GATED>((const bf16*)x, (const bf16*)W, out, out_dt, M, N, K, cap, act, st);
     }
     return QNN_ERR_ARGUMENT;
+}
+
+// The head of a greedy step: cand[m][c] = the best (softcapped value, column) among the 16 columns
+// of W that CTA c owns, for each of the M rows; ceil(N / 16) candidates per row, merged by
+// qnn_sample_candidates.  err (may be null) gets bit 0 set if a logit is NaN or Inf.
+QNN_API int qnn_skinny_argmax(const void* x, const void* W, void* cand, int M, int N, int K, float cap, int* err,
+                              cudaStream_t st) {
+    if (M <= 0 || N <= 0) return 0;
+    if (M > 64 || K % 8 != 0 || K <= 0) return QNN_ERR_UNSUPPORTED;
+    if (((uintptr_t)x | (uintptr_t)W) & 15 || ((uintptr_t)cand & 7)) return QNN_ERR_ARGUMENT;
+    return launch_skinny<EPI_ARGMAX>((const bf16*)x, (const bf16*)W, cand, QNN_DT_F32, M, N, K, cap, 0, st, RopeEpi(), err);
 }
 
 // qkv[M, (nq+2nkv)*hd] = x[M,K] W^T with Q and K rotated by each row's position and K, V appended to

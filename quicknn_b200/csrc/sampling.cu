@@ -174,6 +174,22 @@ QNN_API int qnn_sample(const float* logits, int R, int V, int top_k, float tempe
     QNN_LAUNCH_CHECK();
 }
 
+// The second half of qnn_sample alone, on candidates that another kernel produced (the arg-max
+// epilogue of the head product): cand[r][0..ncand) = (value, id), k best of them per row, then the
+// draw.  The candidates are consumed (overwritten).
+QNN_API int qnn_sample_candidates(void* cand, int R, int ncand, int V, int top_k, float temperature, float top_p,
+                                  unsigned* rng_state, unsigned char* seen, const int* seen_rows, int* out_tokens,
+                                  int* error_flag, const int* status_in, cudaStream_t st) {
+    if (R <= 0) return 0;
+    if (ncand <= 0 || top_k < 1 || !(temperature >= 0.f) || !(top_p > 0.f && top_p <= 1.f)) return QNN_ERR_ARGUMENT;
+    int k = top_k > SAMPLE_MAX_K ? SAMPLE_MAX_K : top_k;
+    if (k > ncand) k = ncand;
+    if (temperature <= 0.f) k = 1;
+    qnn::launch_pdl(sample_merge_kernel, dim3(R), dim3(SAMPLE_THREADS), 0, st, (float2*)cand, ncand, k, temperature, top_p,
+                    rng_state, out_tokens, seen, seen_rows, V, status_in, error_flag);
+    QNN_LAUNCH_CHECK();
+}
+
 QNN_API int qnn_sample_scratch_bytes(int R, int V, int top_k) {
     int k = top_k > SAMPLE_MAX_K ? SAMPLE_MAX_K : (top_k < 1 ? 1 : top_k);
     const long long tiles = (V + SAMPLE_TILE - 1) / SAMPLE_TILE;

@@ -41,3 +41,4 @@ class StepBatch:
     max_seq: int = 0
     tuning: Mapping[str, Any] = dataclasses.field(default_factory=dict)
     scratch: Optional[torch.Tensor] = None    # uint8
+    want_every_row: bool = False              # want_rows is 0, 1, ..., T-1: no gather is needed

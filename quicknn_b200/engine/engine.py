@@ -216,7 +216,7 @@ class Engine:
             ar = torch.arange(B, dtype=torch.int32, device=self.device)
             tokens = torch.zeros(B, dtype=torch.int32, device=self.device)
             step = StepBatch("decode", B, B, tokens, meta[:B], meta[B:], ar, meta[B:], ar, self.model.dtype,
-                             max_seq=self.max_seq, tuning=self.tuning)
+                             max_seq=self.max_seq, tuning=self.tuning, want_every_row=True)
             self._give_scratch(step)
             st = {"meta": meta, "step": step, "graph": None, "logits": None, "tail": tail}    # holds `tail` alive: its id is the key
             self._decode_state[key] = st
@@ -224,11 +224,11 @@ class Engine:
         st["step"].tokens.copy_(tokens_dev.reshape(-1))
         self.steps_run += 1
         def run():
+            if tail is not None:
+                return self.model.forward(st["step"], self.cache, reduce=tail)    # a sampler has its own error word
             logits = self.model.forward(st["step"], self.cache)
-            if tail is None:
-                _kops.check_finite(logits)            # read by check(); a sampler tail has its own word
-                return logits
-            return tail(logits)
+            _kops.check_finite(logits)                # read by check()
+            return logits
 
         if not use_graph:
             return run()

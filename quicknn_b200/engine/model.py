@@ -122,8 +122,11 @@ class Model:
         return n + sum(self.blocks[e.layer].weight_bytes() for e in self.spec.schedule)
 
     # ---- forward ----------------------------------------------------------------------
-    def forward(self, step: StepBatch, cache) -> torch.Tensor:
-        """Logits (float32, [wanted rows, vocab]) of the rows in ``step.want_rows``."""
+    def forward(self, step: StepBatch, cache, reduce=None):
+        """Logits (float32, [wanted rows, vocab]) of the rows in ``step.want_rows``; with ``reduce`` (a
+        callable on the logits that launches device work only, such as a sampler) what it returns.  If
+        ``reduce`` has a method ``head(rows, weight, softcap)`` it is offered the rows that go into the
+        output head first and may return its result without the logits ever being written."""
         spec = self.spec
         x = ops.embed(step.tokens, self.embedding, spec.embedding.scale)
         normed = None
@@ -135,12 +138,19 @@ class Model:
             nxt = self.blocks[sched[i + 1].layer].first_norm() if i + 1 < len(sched) else None
             out = self.blocks[e.layer].forward(x, step, line, normed=normed, next_norm=nxt)
             x, normed = out if nxt is not None else (out, None)
-        return self.logits_of_rows(x, step.want_rows, step.act_dtype)
+        return self.logits_of_rows(x, None if step.want_every_row else step.want_rows, step.act_dtype, reduce)
 
-    def logits_of_rows(self, x: torch.Tensor, rows: torch.Tensor, act_dtype: torch.dtype) -> torch.Tensor:
-        if rows.numel() == 0:
-            return torch.empty((0, self.spec.head.vocab_size), dtype=torch.float32, device=x.device)
-        picked = ops.gather_rows(x, rows, torch.float32)
+    def logits_of_rows(self, x: torch.Tensor, rows: Optional[torch.Tensor], act_dtype: torch.dtype, reduce=None):
+        """Final norm, head and softcap of the rows ``rows`` of the residual stream (None: every row)."""
+        if rows is not None and rows.numel() == 0:
+            empty = torch.empty((0, self.spec.head.vocab_size), dtype=torch.float32, device=x.device)
+            return empty if reduce is None else reduce(empty)
+        picked = x if rows is None else ops.gather_rows(x, rows, torch.float32)
         n = self.final_norm(picked, act_dtype)
         cap = self.spec.head.softcap
-        return project(n, self.head, epilogue=ops.EPI_SOFTCAP, cap=cap, out_dtype=torch.float32)
+        if reduce is not None and hasattr(reduce, "head"):
+            out = reduce.head(n, self.head, cap)
+            if out is not None:
+                return out
+        logits = project(n, self.head, epilogue=ops.EPI_SOFTCAP, cap=cap, out_dtype=torch.float32)
+        return logits if reduce is None else reduce(logits)

@@ -30,6 +30,7 @@ _SIGNATURES: Dict[str, list] = {
     "qnn_rope_cache_write": [c_vp, c_int, c_int, c_int, c_int, c_int, c_int, c_vp, c_vp, c_vp, c_vp, c_vp,
                              c_vp, c_int, c_int, c_int, c_vp, c_int, c_vp],
     "qnn_skinny_bf16": [c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_vp],
+    "qnn_skinny_argmax": [c_vp, c_vp, c_vp, c_int, c_int, c_int, c_float, c_vp, c_vp],
     "qnn_skinny_qkv_rope": [c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_int, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp,
                             c_int, c_int, c_int, c_vp, c_int, c_vp],
     "qnn_gemv_f32": [c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_float, c_int, c_vp],
@@ -52,6 +53,8 @@ _SIGNATURES: Dict[str, list] = {
                                c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_vp],
     "qnn_sample": [c_vp, c_int, c_int, c_int, c_float, c_float, c_float, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp,
                    c_vp, c_vp],
+    "qnn_sample_candidates": [c_vp, c_int, c_int, c_int, c_int, c_float, c_float, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp,
+                              c_vp],
     "qnn_sample_scratch_bytes": [c_int, c_int, c_int],
     "qnn_mark_seen": [c_vp, c_vp, c_vp, c_int, c_int, c_vp],
 }

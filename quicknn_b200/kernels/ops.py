@@ -588,6 +588,56 @@ def sample(logits: torch.Tensor, top_k: int, temperature: float, top_p: float, p
     return out_tokens
 
 
+def head_argmax_fusable(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether ``head_argmax`` takes this product: bfloat16 on both sides and so few rows that the
+    mma.sync small-M kernel would multiply them anyway."""
+    M, K = x.shape
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and M <= SKINNY_MAX_ROWS and K % 8 == 0
+            and not _takes_skinny_tcgen05(M, w.shape[0], K))
+
+
+def head_candidates(vocab: int) -> int:
+    """Candidates per row that ``head_argmax`` writes (one per 16 output columns)."""
+    return (vocab + 15) // 16
+
+
+def head_argmax(x: torch.Tensor, w: torch.Tensor, cap: Optional[float], cand: torch.Tensor,
+                error_flag: Optional[torch.Tensor]) -> torch.Tensor:
+    """softcap(x w^T) reduced in the product's epilogue to the best (value, id) of every 16 output
+    columns: ``cand`` (float32, at least rows * head_candidates(vocab) * 2) is filled, the logits are not
+    written.  NaN or Inf sets bit 0 of ``error_flag``."""
+    _req(x, "x", torch.bfloat16, 2)
+    _req(w, "w", torch.bfloat16, 2)
+    _req(cand, "cand", torch.float32)
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K:
+        raise ValueError(f"head_argmax: x is [*, {K}] but w is [*, {w.shape[1]}]")
+    if cand.numel() < M * head_candidates(N) * 2:
+        raise ValueError("head_argmax: the candidate buffer is too small")
+    L = _lib.load()
+    _lib.check(L.qnn_skinny_argmax(_p(x), _p(w), _p(cand), M, N, K, float(cap or 0.0), _p(error_flag), _stream()),
+               "skinny_argmax")
+    return cand
+
+
+def sample_candidates(cand: torch.Tensor, rows: int, ncand: int, vocab: int, top_k: int, temperature: float,
+                      top_p: float, rng_state: torch.Tensor, seen: Optional[torch.Tensor],
+                      seen_rows: Optional[torch.Tensor], out_tokens: torch.Tensor,
+                      error_flag: Optional[torch.Tensor], status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The merge-and-draw half of ``sample`` on candidates [rows, ncand] of (value, id) pairs."""
+    _req(cand, "cand", torch.float32)
+    _req(out_tokens, "out_tokens", torch.int32, 1)
+    _req(rng_state, "rng_state", torch.int32, 1)
+    if cand.numel() < rows * ncand * 2 or out_tokens.numel() < rows or rng_state.numel() < rows:
+        raise ValueError("sample_candidates: a buffer is shorter than the batch")
+    L = _lib.load()
+    _lib.check(L.qnn_sample_candidates(_p(cand), rows, ncand, vocab, int(top_k), float(temperature), float(top_p),
+                                       _p(rng_state), _p(seen), _p(seen_rows), _p(out_tokens), _p(error_flag),
+                                       _p(status), _stream()), "sample_candidates")
+    return out_tokens
+
+
 def mark_seen(tokens: torch.Tensor, rows: torch.Tensor, seen: torch.Tensor):
     _req(tokens, "tokens", torch.int32, 1)
     _req(rows, "rows", torch.int32, 1)

@@ -27,6 +27,9 @@ class Sampler:
         nbytes = ops.sample_scratch_bytes(max_rows, vocab_size, options.top_k)
         if nbytes < 0:
             raise ValueError("sampling scratch would exceed 2 GiB; lower the batch")
+        self.greedy_plain = options.temperature <= 0 and not (options.repetition_penalty != 1.0)
+        if self.greedy_plain:                # room for the candidates of the fused head as well
+            nbytes = max(nbytes, max_rows * ops.head_candidates(vocab_size) * 8)
         self.scratch = torch.empty(max(nbytes, 8), dtype=torch.uint8, device=device)
         self._pinned: Optional[torch.Tensor] = None
         self._event = None
@@ -66,6 +69,21 @@ class Sampler:
             seen_rows = torch.arange(R, dtype=torch.int32, device=self.device)
         ops.sample(logits, o.top_k, o.temperature, o.top_p, o.repetition_penalty, self.rng, self.seen,
                    seen_rows, self.scratch, self.out, self.flag, ops.status_words(self.device)[0:1])
+        return self.out[:R]
+
+    def head(self, hidden: torch.Tensor, weight: torch.Tensor, cap: Optional[float]) -> Optional[torch.Tensor]:
+        """Chosen ids straight from the rows that go into the output head (after the final norm),
+        without the logits in between: for greedy selection without a repetition penalty the head
+        product keeps only the best (value, id) of each group of 16 columns and the merge picks the
+        largest.  Returns None when that does not apply; the caller then forms the logits and calls
+        the sampler on them.  Same ids as that way (the same sums, compared in the same order)."""
+        if not self.greedy_plain or weight.shape[0] != self.vocab or not ops.head_argmax_fusable(hidden, weight):
+            return None
+        R = hidden.shape[0]
+        cand = self.scratch.view(torch.float32)
+        ops.head_argmax(hidden, weight, cap, cand, self.flag)
+        ops.sample_candidates(cand, R, ops.head_candidates(self.vocab), self.vocab, 1, 0.0, self.options.top_p, self.rng,
+                              None, None, self.out, self.flag, ops.status_words(self.device)[0:1])
         return self.out[:R]
 
     def read(self, tokens: torch.Tensor) -> np.ndarray:

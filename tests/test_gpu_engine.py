@@ -338,3 +338,31 @@ def test_a_step_that_cannot_be_launched_leaves_the_cache_as_it_was(folders, monk
     eng.step([(a, [5]), (b, [6])])
     assert (eng.length(a), eng.length(b)) == (70, 3)
     eng.cache.audit()
+
+
+def test_greedy_ids_without_logits_are_those_with_logits(folders, monkeypatch):
+    """bfloat16 greedy generation takes its ids from the head product's arg-max epilogue; with that
+    switched off (logits written, then the sampler's two kernels) the same ids come out."""
+    from quicknn_b200.engine import LLM
+    from quicknn_b200.sampling import GenerationOptions, Sampler
+    prompts = prompts_for("C", [40, 3, 77, 9, 120], seed=8)
+    llm = LLM(folders("C", "bfloat16"), max_context=160, max_batch=5, dtype="bfloat16")
+    used = []
+    real = Sampler.head
+
+    def spy(self, hidden, weight, cap):
+        out = real(self, hidden, weight, cap)
+        used.append(out is not None)
+        return out
+    monkeypatch.setattr(Sampler, "head", spy)
+    fused = [r.tokens for r in llm.generate(prompts, GenerationOptions.greedy(24), stop_ids=[])]
+    assert used and all(used)
+    monkeypatch.setattr(Sampler, "head", lambda self, hidden, weight, cap: None)
+    llm2 = LLM(model=llm.model, max_context=160, max_batch=5, dtype="bfloat16")
+    plain = [r.tokens for r in llm2.generate(prompts, GenerationOptions.greedy(24), stop_ids=[])]
+    assert fused == plain
+    monkeypatch.setattr(Sampler, "head", spy)
+    del used[:]
+    llm.generate(prompts[:2], GenerationOptions(max_new_tokens=4, temperature=0.5, seed=1), stop_ids=[])
+    llm.generate(prompts[:2], GenerationOptions(max_new_tokens=4, temperature=0.0, repetition_penalty=1.2), stop_ids=[])
+    assert used and not any(used)            # sampling and penalties need the logits
