@@ -5,7 +5,10 @@ end-to-end figures on the same JSON line.
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--layers L]
 
 A "step" is one decode step of a batch of 8 sequences whose cached context reaches the
-benchmark context length (8192) at the last timed step.  Weights are random (seeded,
+benchmark context length (8192) at the last timed step: from the ids that the step before chose
+(greedy, on the device) to the ids of the next.  ``vs_baseline`` is against the same steps written
+with plain PyTorch operations (``baseline/torch_ops_decode.py``): the reference publishes no
+Gemma 2 figure and cannot run here.  Weights are random (seeded,
 generated on the device); the cached history of the device-timed runs is random too
 (``fill_synthetic``), because a decode step's time does not depend on the values.
 Timing is by CUDA events on the launching stream after W warm-up steps; every step reads all
@@ -42,6 +45,7 @@ OTHER_SIZES = {
 CONTEXT = 8192
 BATCH = 8
 PREFILL_TOKENS = 2048
+RAMP_STEPS = 8
 SEED = 2
 FALLBACK_HBM_GBS, FALLBACK_BF16_TFLOPS = 6650.0, 1590.0
 
@@ -141,36 +145,118 @@ def fill_synthetic(engine, slots, lengths, torch, seed=0):
                 t[li].normal_(0.0, 1.0, generator=g)
 
 
-def timed_decode(engine, batch, steps, warmup, torch, with_clocks=False, context=CONTEXT, vocab=256000):
-    """Tokens per second of `steps` decode steps of `batch` sequences ending at `context` tokens."""
-    start_len = context - steps - warmup - 1
+def timed_decode(engine, batch, steps, warmup, torch, with_clocks=False, context=CONTEXT, lengths=None):
+    """Tokens per second of `steps` decode steps of `batch` sequences, each step from the ids that the
+    step before chose on the device (greedy) to the ids of the next.  The sequences end at `context`
+    tokens, or start from the given `lengths`."""
+    from quicknn_b200.sampling import GenerationOptions, Sampler
+    vocab = engine.model.spec.embedding.vocab_size
+    start = lengths if lengths is not None else [context - steps - warmup - RAMP_STEPS - 1] * batch
     slots = [engine.new_sequence() for _ in range(batch)]
-    fill_synthetic(engine, slots, [start_len] * batch, torch)
+    fill_synthetic(engine, slots, start, torch)
+    sampler = Sampler(vocab, batch, GenerationOptions.greedy(1), engine.device)
+    sampler.start(0, batch)
     tokens = torch.randint(1, vocab, (batch,), dtype=torch.int32, device=engine.device)
-    engine.decode(slots, tokens)          # eager pass, captures the graph
+    tokens = engine.decode(slots, tokens, tail=sampler)          # eager pass, captures the graph
     for _ in range(warmup):
-        engine.decode(slots, tokens)
+        tokens = engine.decode(slots, tokens, tail=sampler)
     torch.cuda.synchronize()
-    k0 = engine.kernels_launched()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     clocks = Clocks()
     ctx = clocks if with_clocks else open(os.devnull)
     with ctx:
-        if with_clocks:
-            time.sleep(0.25)
+        # untimed steps right before the timed ones, so that the SM clock that the sampler sees, and the
+        # timed steps run at, is the clock under load (the device idles while nvidia-smi starts)
+        for _ in range(RAMP_STEPS):
+            tokens = engine.decode(slots, tokens, tail=sampler)
         torch.cuda.synchronize()
+        k0 = engine.kernels_launched()
         e0.record()
         for _ in range(steps):
-            engine.decode(slots, tokens)
+            tokens = engine.decode(slots, tokens, tail=sampler)
         e1.record()
         torch.cuda.synchronize()
     ms = e0.elapsed_time(e1)
     launches = engine.kernels_launched() - k0
+    sampler.read(tokens)                                        # raises if a step gave NaN or a kernel gave up
     bytes_step = engine.model.step_weight_bytes() + engine.cache.bytes_read_per_step(slots)
     for s in slots:
         engine.release(s)
+    engine.forget_tail(sampler)
     return {"tok_s": batch * steps / (ms / 1e3), "ms_per_step": ms / steps, "bytes_per_step": bytes_step,
             "launches": launches, "clocks": clocks.summary() if with_clocks else None}
+
+
+def timed_baseline(cfg, steps, torch, context, batch):
+    """The same decode steps and the same prefill with plain PyTorch operations (baseline/torch_ops_decode.py,
+    tests/plain/gemma2_torch.py): bfloat16, cuBLAS products, a contiguous cache."""
+    sys.path.insert(0, os.path.join(ROOT, "baseline"))
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from torch_ops_decode import CachedTorchGemma2
+    from plain.gemma2_torch import TorchGemma2
+    from quicknn_b200.config.base import find_architecture
+    from quicknn_b200.weights.random_init import random_tensors
+    arch = find_architecture(cfg)
+    weights = dict(random_tensors(arch, arch.config_cls.from_dict(cfg), SEED, torch.bfloat16, device="cuda:0"))
+    steps = min(steps, 32)
+    model = CachedTorchGemma2(cfg, weights, batch, context, "cuda:0", torch.bfloat16)
+    model.fill_random(context - steps - 4)
+    tokens = torch.randint(1, cfg["vocab_size"], (batch,), device="cuda:0")
+    for _ in range(3):
+        tokens = model.decode(tokens)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        tokens = model.decode(tokens)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    del model
+    whole = TorchGemma2.from_tensors(cfg, weights, "cuda:0", torch.bfloat16)
+    ids = torch.randint(1, cfg["vocab_size"], (PREFILL_TOKENS,)).tolist()
+    times = []
+    for i in range(5):
+        torch.cuda.synchronize()
+        e0.record()
+        whole.logits(ids, [PREFILL_TOKENS - 1])
+        e1.record()
+        torch.cuda.synchronize()
+        if i >= 2:
+            times.append(e0.elapsed_time(e1))
+    del whole, weights
+    torch.cuda.empty_cache()
+    return {"impl": "plain PyTorch operations, bfloat16, cuBLAS products, contiguous cache", "value": round(batch / (ms / 1e3), 1),
+            "unit": "tokens/s", "ms_per_step": round(ms, 3), "steps": steps,
+            "prefill_ms": round(statistics.median(times), 3)}
+
+
+def timed_tiny(torch):
+    """BASELINE.json's two tiny workloads: the plain NumPy implementation on the CPU (whole sequence
+    recomputed for every token) and this library in float32 on the GPU, seconds for all requests."""
+    import tempfile
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from conftest import TINY, make_folder, prompts_for
+    from plain.gemma2_plain import PlainGemma2
+    from quicknn_b200.engine import LLM
+    from quicknn_b200.sampling import GenerationOptions
+    out = {}
+    with tempfile.TemporaryDirectory() as tmp:
+        for name, lens, new in (("A", [5, 11, 17], 8), ("B", [1, 6, 13, 29], 12)):
+            folder = make_folder(tmp, name, "float32")
+            prompts = prompts_for(name, lens)
+            plain = PlainGemma2(folder, dtype=__import__("numpy").float32)
+            t0 = time.perf_counter()
+            ref = [plain.greedy(p, new) for p in prompts]
+            out[f"{name.lower()}_plain_cpu_s"] = round(time.perf_counter() - t0, 4)
+            llm = LLM(folder, max_context=64, max_batch=len(prompts), dtype="float32")
+            llm.generate(prompts, GenerationOptions.greedy(new), stop_ids=[])       # warm-up: graphs, first launches
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            got = llm.generate(prompts, GenerationOptions.greedy(new), stop_ids=[])
+            out[f"{name.lower()}_ours_s"] = round(time.perf_counter() - t0, 4)
+            out[f"{name.lower()}_same_tokens"] = [r.tokens for r in got] == ref
+    return out
 
 
 def main():
@@ -189,6 +275,7 @@ def main():
     ap.add_argument("--skip-prefill", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-points", action="store_true")
+    ap.add_argument("--skip-baseline", action="store_true", help="do not time the plain PyTorch / NumPy baselines")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -228,14 +315,21 @@ def main():
     eng.use_graphs = not args.no_graph
 
     # ---- the headline: decode, batch 8 --------------------------------------------------
-    main_run = timed_decode(eng, args.batch, args.steps, args.warmup, torch, with_clocks=True, context=args.context,
-                            vocab=cfg["vocab_size"])
+    main_run = timed_decode(eng, args.batch, args.steps, args.warmup, torch, with_clocks=True, context=args.context)
     achieved = main_run["bytes_per_step"] / (main_run["ms_per_step"] / 1e3) / 1e9
 
-    points = {}
+    points, workload = {}, {}
     if not args.skip_points:
         for b in (1, big):
-            points[f"decode_b{b}"] = round(timed_decode(eng, b, min(args.steps, 128), args.warmup, torch)["tok_s"], 1)
+            points[f"decode_b{b}"] = round(timed_decode(eng, b, min(args.steps, 128), args.warmup, torch,
+                                                        context=args.context)["tok_s"], 1)
+        # BASELINE.json's workload as it is stated: prompts uniform in [512, 2048], then 256 decode steps
+        import numpy as np
+        rng = np.random.default_rng(SEED)
+        for b in (1, BATCH, big):
+            run = timed_decode(eng, b, 256, args.warmup, torch, lengths=rng.integers(512, 2049, b).tolist())
+            workload[f"decode_b{b}"] = round(run["tok_s"], 1)
+            workload[f"hbm_frac_b{b}"] = round(run["bytes_per_step"] / (run["ms_per_step"] / 1e3) / 1e9 / pk["hbm_gbs"], 3)
 
     # ---- prefill of 2,048 tokens -----------------------------------------------------------
     ids = torch.randint(1, cfg["vocab_size"], (PREFILL_TOKENS,)).tolist()
@@ -261,34 +355,52 @@ def main():
     if not args.skip_e2e:
         # as many steps as the device-timed run: the first 25 or so after the prompts run at a reduced SM clock
         # (the prefill of 8 x 8000 tokens hits the power cap; the clock takes about 80 ms to come back)
-        new = min(args.steps, 512)
+        # (so never fewer than 256 steps here, whatever the device-timed run was asked for)
+        new = max(256, min(args.steps, 512))
         plen = CONTEXT - new - 1
         prompts = [torch.randint(1, cfg["vocab_size"], (plen,)).tolist() for _ in range(BATCH)]
         llm.max_batch = BATCH
+        # a first call pays what is paid once (kernel attributes, the graphs of this sampler)
+        llm.generate([p[:2048] for p in prompts], GenerationOptions.greedy(4), stop_ids=[])
         res = llm.generate(prompts, GenerationOptions.greedy(new), stop_ids=[])
         dec = max(r.decode_seconds for r in res)
         gen = sum(r.generated_tokens - 1 for r in res)
+        ttft = max(r.time_to_first_token_seconds for r in res)
         e2e = {"value": round(gen / dec, 1), "unit": "tokens/s",
                "h2d_bytes_per_step": round(llm.last_io["h2d_bytes_per_step"], 1),
-               "d2h_bytes_per_step": round(llm.last_io["d2h_bytes_per_step"], 1), "prefill_seconds": round(max(r.time_to_first_token_seconds for r in res), 3)}
+               "d2h_bytes_per_step": round(llm.last_io["d2h_bytes_per_step"], 1), "steps": new, "prefill_seconds": round(ttft, 3),
+               "prefill_tokens_per_s": round(BATCH * plen / ttft, 1)}
+
+    # ---- the same steps with plain PyTorch operations; the tiny workloads with plain NumPy on the CPU --------
+    baseline = tiny = None
+    if not args.skip_baseline:
+        del llm, eng
+        import gc
+        gc.collect()
+        torch.cuda.empty_cache()
+        baseline = timed_baseline(cfg, args.steps, torch, args.context, args.batch)
+        tiny = timed_tiny(torch)
 
     out = {
         "metric": f"decode tokens/s, Gemma 2 {args.model.upper()} layer sizes, batch {args.batch}, context {args.context}", "value": round(main_run["tok_s"], 1),
         "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(main_run["ms_per_step"], 4), "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
+        "vs_baseline": round(main_run["tok_s"] / baseline["value"], 2) if baseline else None,
+        "dtype": "bf16", "data": "synthetic", "impl": "ours",
         "config": {"model": f"gemma2-{args.model}-sizes", "global_batch": args.batch, "seq_len": args.context, "parallelism": "none",
                    "layers": args.layers, "layers_of_config": base["num_hidden_layers"],
                    "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
                    "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
                    "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
                    "window": cfg["sliding_window"], "prefill_tokens": PREFILL_TOKENS, "weights": "random seed 2",
-                   "l2": "each step reads > 5 GB, larger than L2; no flush", "peaks": pk["source"]},
+                   "l2": "each step reads > 5 GB, larger than L2; no flush", "peaks": pk["source"],
+                   "step": "ids of one step to the ids of the next, greedy, on the device",
+                   "baseline": "plain PyTorch ops bf16 (the reference publishes no figure)"},
         "clocks": main_run["clocks"], "gpu_launches": main_run["launches"],
         "e2e": e2e, "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4)},
-        "points": points,
+        "points": points, "workload_u512_2048": workload, "baseline": baseline, "tiny": tiny,
     }
     print(json.dumps(out))
     return 0

@@ -141,10 +141,22 @@ class TorchGemma2:
     def __init__(self, model_dir: str, device="cpu", dtype: torch.dtype = torch.float64):
         with open(os.path.join(model_dir, "config.json"), "r", encoding="utf-8") as fh:
             c = json.load(fh)
+        self._setup(c, read_safetensors(os.path.join(model_dir, "model.safetensors"), torch.device(device), dtype),
+                    device, dtype)
+
+    @classmethod
+    def from_tensors(cls, config: Dict, weights: Dict[str, torch.Tensor], device, dtype: torch.dtype) -> "TorchGemma2":
+        """A model over tensors that are already in memory (checkpoint names -> tensors), for timing at
+        sizes whose files would take gigabytes."""
+        self = cls.__new__(cls)
+        self._setup(dict(config), {k: v.to(device=device, dtype=dtype) for k, v in weights.items()}, device, dtype)
+        return self
+
+    def _setup(self, c: Dict, weights: Dict[str, torch.Tensor], device, dtype: torch.dtype) -> None:
         self.cfg, self.device, self.dtype = c, torch.device(device), dtype
         torch.backends.cuda.matmul.allow_tf32 = False
         torch.backends.cudnn.allow_tf32 = False
-        self.w = read_safetensors(os.path.join(model_dir, "model.safetensors"), self.device, dtype)
+        self.w = weights
         self.H, self.L = c["hidden_size"], c["num_hidden_layers"]
         self.nq, self.nkv, self.hd = c["num_attention_heads"], c["num_key_value_heads"], c["head_dim"]
         self.V = c["vocab_size"]
@@ -196,7 +208,8 @@ class TorchGemma2:
         if rows is not None:
             x = x[torch.as_tensor(list(rows), dtype=torch.long, device=self.device)]
         n = rmsnorm(x, self.w["model.norm.weight"], self.eps)
-        return softcap(n @ self.w["model.embed_tokens.weight"].T, self.final_cap).cpu().numpy()
+        out = softcap(n @ self.w["model.embed_tokens.weight"].T, self.final_cap)
+        return (out.float() if out.dtype == torch.bfloat16 else out).cpu().numpy()    # NumPy has no bfloat16
 
     def greedy(self, ids: Sequence[int], steps: int, stop_ids: Sequence[int] = ()) -> List[int]:
         """Greedy continuation by recomputing the whole sequence each step; the largest score

@@ -133,3 +133,28 @@ def test_the_torch_plain_implementation_agrees_with_the_numpy_one(plain_models, 
     assert np.abs(t32.logits(ids) - ref).max() < 5e-5
     assert t64.greedy(ids[:7], 4) == plain_models(name).greedy(ids[:7], 4)
     assert [t64.layer_window(i) for i in range(2)] == [plain_models(name).layer_window(i) for i in range(2)]
+
+
+def test_the_timed_baseline_decodes_what_the_plain_model_computes(plain_models, folders):
+    """baseline/torch_ops_decode.py (torch operations with a contiguous cache; what the benchmark's
+    vs_baseline is measured against) fed a sequence token by token picks, at every position, the
+    plain model's best token: it is a correct implementation, not only a timed one."""
+    import json
+    import os
+    import sys
+    import torch
+    from conftest import ROOT
+    sys.path.insert(0, os.path.join(ROOT, "baseline"))
+    from torch_ops_decode import CachedTorchGemma2
+    from plain.gemma2_torch import read_safetensors
+    for name in ("A", "B"):
+        folder = folders(name)
+        with open(os.path.join(folder, "config.json")) as fh:
+            cfg = json.load(fh)
+        w = read_safetensors(os.path.join(folder, "model.safetensors"), "cpu", torch.float64)
+        seqs = prompts_for(name, [20, 20])
+        ref = [plain_models(name).logits(s) for s in seqs]
+        m = CachedTorchGemma2(cfg, w, batch=2, max_len=32, device="cpu", dtype=torch.float64)
+        for t in range(20):
+            got = m.decode(torch.tensor([s[t] for s in seqs])).tolist()
+            assert got == [int(np.argmax(r[t])) for r in ref], t
