@@ -509,21 +509,27 @@ __global__ void attn_combine_kernel(const float* __restrict__ part_o, const floa
     pdl_wait();
     extern __shared__ __align__(16) float comb[];  // [G][hd] partial sums, then [n_splits] weights and 1/sum
     const int lpg = hd / 4, G = max(1, min((int)blockDim.x / lpg, n_splits));
-    float* coef = comb + (size_t)G * hd;
+    float* coef = comb + max((size_t)G * hd, (size_t)n_splits);
     const int b = blockIdx.x / nq, h = blockIdx.x % nq;
     const size_t pbase = ((size_t)b * nq + h) * n_splits;
     if (threadIdx.x < 32) {
+        // every (maximum, sum) pair is loaded once, all loads of a lane in flight together; the weighted sums
+        // go through shared memory so that one thread can add them in ascending order without waiting for
+        // global memory at every term
+        float* wl = comb;                                   // [n_splits], before the partial sums take the space
         float mm = -CUDART_INF_F;
         for (int s = threadIdx.x; s < n_splits; s += 32) mm = fmaxf(mm, part_ml[(pbase + s) * 2]);
         mm = warp_max(mm);
         for (int s = threadIdx.x; s < n_splits; s += 32) {
-            const float ms = part_ml[(pbase + s) * 2];
-            coef[s] = (ms == -CUDART_INF_F) ? 0.f : expf(ms - mm);
+            const float2 ml = *reinterpret_cast<const float2*>(part_ml + (pbase + s) * 2);
+            const float w = (ml.x == -CUDART_INF_F) ? 0.f : expf(ml.x - mm);
+            coef[s] = w;
+            wl[s] = w * ml.y;
         }
         __syncwarp();
         if (threadIdx.x == 0) {
             float ll = 0.f;
-            for (int s = 0; s < n_splits; ++s) ll += coef[s] * part_ml[(pbase + s) * 2 + 1];   // ascending order
+            for (int s = 0; s < n_splits; ++s) ll += wl[s];   // ascending order
             coef[n_splits] = ll > 0.f ? 1.f / ll : 0.f;
         }
     }
@@ -730,10 +736,18 @@ extern "C" int qnn_attn_decode_mma_split(const void* q, long long q_stride, cons
                                          int n_splits, void* out, long long out_stride, int* combined,
                                          cudaStream_t st);
 
-// groups of the combine kernel's block of 256 threads (see attn_combine_kernel)
+// threads of the combine kernel's block: a group of hd/4 threads for every key range, up to 1024; and the
+// groups that such a block has (see attn_combine_kernel)
+static int combine_threads(int hd, int n_splits) {
+    const int lpg = hd / 4 > 0 ? hd / 4 : 1;
+    long long t = ((long long)lpg * n_splits + 31) / 32 * 32;
+    if (t < 64) t = 64;
+    const int most = lpg > 1024 ? lpg : 1024;      // at least one whole group
+    return (int)(t > most ? most : t);
+}
 static int combine_groups(int hd, int n_splits) {
     const int lpg = hd / 4;
-    int g = lpg > 0 ? 256 / lpg : 1;
+    int g = lpg > 0 ? combine_threads(hd, n_splits) / lpg : 1;
     if (g > n_splits) g = n_splits;
     return g < 1 ? 1 : g;
 }
@@ -794,7 +808,9 @@ static int decode_launch(const void* q, long long q_stride, const void* k_pool, 
 #undef QNN_DEC_ARGS
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
-    qnn::launch_pdl(attn_combine_kernel<T>, dim3(B * nq), dim3(256), ((size_t)combine_groups(hd, n_splits) * hd + n_splits + 1) * sizeof(float), st, part_o, part_ml, (T*)out, (size_t)out_stride, nq, hd, n_splits);
+    size_t comb_floats = (size_t)combine_groups(hd, n_splits) * hd;
+    if (comb_floats < (size_t)n_splits) comb_floats = (size_t)n_splits;      // the weighted sums pass through it first
+    qnn::launch_pdl(attn_combine_kernel<T>, dim3(B * nq), dim3(combine_threads(hd, n_splits)), (comb_floats + n_splits + 1) * sizeof(float), st, part_o, part_ml, (T*)out, (size_t)out_stride, nq, hd, n_splits);
     QNN_LAUNCH_CHECK();
 }
 

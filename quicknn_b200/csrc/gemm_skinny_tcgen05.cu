@@ -10,15 +10,19 @@
 // KS CTAs shares one 128-row tile of W and splits K:
 //   * each CTA streams its part of K and accumulates in tensor memory (lane = weight row, column =
 //     activation row);
-//   * its epilogue warps move the float32 accumulator to shared memory (over the ring, which is idle by
-//     then);
-//   * after a cluster barrier every CTA sums a slice of the weight rows over all CTAs of the cluster,
-//     reading the others' shared memory (distributed shared memory), always in rank order, applies
-//     the epilogue (none, softcap -> float32, or gated activation) and stores.
+//   * every rank finishes a slice of the tile's weight rows: the epilogue warps of each CTA move the float32
+//     accumulator to shared memory (over the ring, which is idle by then) and one thread sends each rank its
+//     slice with a bulk shared-to-shared copy (cp.async.bulk.shared::cluster into a receive buffer beside
+//     the ring, counted in bytes on the receiver's mbarrier).  Measured: loads from another CTA's shared
+//     memory cost a few hundred cycles each, and st.shared::cluster with one row per lane took 2.5 us for
+//     64 activation rows; the bulk copies take a few hundred nanoseconds;
+//   * when its mbarrier has counted all slices, every CTA sums them, from its own shared memory, always in
+//     rank order, applies the epilogue (none, softcap -> float32, or gated activation) and stores.
 // For the gated epilogue a tile is 64 gate rows and the 64 matching up rows.
 // Reference: the matvec shaders of src/backends/vulkan/shaders/tensor.comp:87-120 (one row).
-// Every mbarrier wait is bounded in time; on expiry a status word is set, and the CTA still takes
-// part in both cluster barriers, frees its tensor memory and returns.
+// Every mbarrier wait is bounded in time; on expiry a status word is set (1 loads, 2 tensor-core issue,
+// 4 accumulator, 8 hand-over), and the CTA still sends its (then zero) rows, takes part in the cluster
+// barriers, frees its tensor memory and returns.
 #include "common.cuh"
 #include <cuda.h>
 
@@ -33,7 +37,9 @@ namespace {
 constexpr int BW = 128, BK = 64, MAX_STAGES = 10, UMMA_K = 16;     // BW: weight rows of a tile
 constexpr int W_BYTES = BW * BK * 2;
 constexpr int THREADS = 192;
+constexpr int RECV_COLS = 64;              // activation rows that pass through the receive buffer in one round
 constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;
+constexpr unsigned WAIT_HINT_NS = 20u;    // longest sleep inside one try_wait: a waiter sees a completed phase no later than this
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
@@ -50,7 +56,7 @@ __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity) {
             "{\n\t.reg .pred p;\n\t"
             "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
             "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(done) : "r"(bar), "r"(parity), "r"(1000u) : "memory");
+            : "=r"(done) : "r"(bar), "r"(parity), "r"(WAIT_HINT_NS) : "memory");
         if (done) return true;
         if (clock64() - start > WAIT_LIMIT_CYCLES) return false;
     }
@@ -95,22 +101,28 @@ __device__ __forceinline__ unsigned cluster_rank() {
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
     return r;
 }
-__device__ __forceinline__ void cluster_sync() {
-    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ float4 ld_dsmem4(unsigned local_addr, unsigned rank) {
-    unsigned remote;
-    float4 v;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
-    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(remote) : "memory");
-    return v;
+// The cluster barrier in two halves.  Every thread arrives once at the start and waits before anything is sent
+// to a peer, by when the peers have long arrived: it makes sure that they run and that their barriers are set
+// up.  It is used again before a CTA leaves (arrive when everything this CTA is sent has come, wait at the end):
+// a CTA's shared memory is the source of copies until every receiver has them.
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+// `bytes` (a multiple of 16) from this CTA's shared memory to `dst_local` in the CTA of rank `rank`; completion
+// is counted in bytes on that CTA's mbarrier at `bar_local`.
+__device__ __forceinline__ void bulk_copy_to_rank(unsigned dst_local, unsigned src_local, unsigned bytes, unsigned bar_local,
+                                                  unsigned rank) {
+    unsigned dst, bar;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(dst) : "r"(dst_local), "r"(rank));
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(bar) : "r"(bar_local), "r"(rank));
+    asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "r"(src_local), "r"(bytes), "r"(bar) : "memory");
 }
 
 struct __align__(8) Barriers {
     uint64_t full[MAX_STAGES];
     uint64_t empty[MAX_STAGES];
     uint64_t acc_ready;
+    uint64_t recv_full;          // counts the bytes that the ranks send this CTA, one phase per round
     uint32_t tmem_base;
     uint32_t failed;
 };
@@ -125,9 +137,13 @@ gemm_skinny_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __gr
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const int x_bytes = NM * BK * 2, stage_bytes = W_BYTES + x_bytes;
-    const int PL = NM + 4;                                   // row pitch of the partial tile in floats
-    float* part = reinterpret_cast<float*>(smem);            // [BW][PL], over the ring once the products are done
-    Barriers* bars = reinterpret_cast<Barriers*>(smem + (size_t)stages * stage_bytes);
+    const int PL = min(NM, RECV_COLS) + 4;                   // row pitch of the partial tile in floats
+    const int RPB = BW / KS;                                 // weight rows of the tile that one rank finishes
+    float* part = reinterpret_cast<float*>(smem);            // [BW][PL]: this CTA's partial tile, over its idle ring
+    // [source rank][row of my slice][PL]: what the ranks send me; beside the ring, which is still in use then
+    // (a CTA that is alone on its tile finishes its own partial tile where it lies)
+    float* recv = KS > 1 ? reinterpret_cast<float*>(smem + (size_t)stages * stage_bytes) : part;
+    Barriers* bars = reinterpret_cast<Barriers*>(smem + (size_t)stages * stage_bytes + (KS > 1 ? (size_t)BW * PL * 4 : 0));
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const unsigned rank = cluster_rank();
     const int tile = blockIdx.x / KS;
@@ -144,6 +160,7 @@ gemm_skinny_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __gr
             mbar_init(smem_u32(&bars->empty[s]), 1);
         }
         mbar_init(smem_u32(&bars->acc_ready), 1);
+        mbar_init(smem_u32(&bars->recv_full), 1);
         bars->failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -155,6 +172,8 @@ gemm_skinny_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __gr
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (threadIdx.x == 0) mbar_expect_tx(smem_u32(&bars->recv_full), (unsigned)(BW * PL * 4));   // the first round
+    cluster_arrive();                                        // "this CTA runs, its barriers are set up"
     const unsigned tmem = bars->tmem_base;
     // Barriers and tensor memory are set up.  The weights do not depend on the kernel before this one: the
     // producer asks for the weight tiles of the first ring of stages, and only then waits for that kernel,
@@ -175,6 +194,7 @@ gemm_skinny_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __gr
     };
     for (int it = 0; it < ahead; ++it) load_weights(it);
     pdl_wait();
+    bool have_acc = false;     // epilogue warps: the accumulator is complete (else this CTA contributes zeros)
 
     if (warp == 0) {
         if (lane == 0) {
@@ -214,10 +234,7 @@ gemm_skinny_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __gr
             umma_commit(smem_u32(&bars->acc_ready));
         }
     } else {
-        // accumulator -> shared memory, float32, [weight row][activation row]; a CTA without slabs contributes
-        // zeros.  The ring is idle once acc_ready has come (every slab has been multiplied).
-        const int quarter = warp & 3;
-        const int wrow = quarter * 32 + lane;
+        // the accumulator is complete (a CTA without slabs contributes zeros)
         bool ok = true;
         if (kb1 > kb0) {
             ok = mbar_wait(smem_u32(&bars->acc_ready), 0);
@@ -227,55 +244,86 @@ gemm_skinny_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __gr
             }
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll 1
-        for (int c0 = 0; c0 < NM; c0 += 32) {
-            uint32_t v[32];
-            if (kb1 > kb0 && ok) {
-                tmem_ld32(tmem + ((unsigned)(quarter * 32) << 16) + c0, v);
-            } else {
-#pragma unroll
-                for (int j = 0; j < 32; ++j) v[j] = 0u;
-            }
-            float4* dst = reinterpret_cast<float4*>(part + (size_t)wrow * PL + c0);
-#pragma unroll
-            for (int j = 0; j < 32; j += 4)
-                if (c0 + j < NM)
-                    dst[j / 4] = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]), __uint_as_float(v[j + 2]),
-                                             __uint_as_float(v[j + 3]));
-        }
+        have_acc = kb1 > kb0 && ok;
     }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    if (warp == 1) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(tmem_cols) : "memory");
-    }
-    cluster_sync();      // every CTA's partial tile is complete and visible in the cluster
+    __syncwarp();
+    cluster_wait();            // the peers run and their barriers are set up: they may be sent to
 
-    // Rank r finishes weight rows [r * rpr, (r + 1) * rpr) of the tile, four activation rows at a time: sum
-    // over the ranks in ascending order, epilogue, store.  Consecutive threads take consecutive weight rows,
-    // i.e. consecutive elements of a row of C.
-    {
-        const int rpr = OUT_ROWS / KS;
-        const int r_lo = (int)rank * rpr;
-        const int mgroups = (M + 3) / 4;
-        const unsigned part_addr = smem_u32(part);
-        for (int idx = threadIdx.x; idx < rpr * mgroups; idx += THREADS) {
-            const int nn = r_lo + idx % rpr, m4 = (idx / rpr) * 4;
+    // Activation rows pass 64 at a time (one round for up to 64 rows).  In a round the epilogue warps move their
+    // accumulator rows to this CTA's partial tile [weight row][activation row], one thread sends every rank its
+    // rows of it, and when all ranks' rows have arrived rank r finishes weight rows [r * rpr, (r + 1) * rpr) of
+    // the tile, four activation rows at a time: sum over the ranks in ascending order, epilogue, store.
+    // Consecutive threads take consecutive weight rows, i.e. consecutive elements of a row of C.  A gated tile is
+    // 64 gate rows and their 64 up rows; a rank's slice is RPB / 2 of each.
+    const int rpr = OUT_ROWS / KS;
+    const int r_lo = (int)rank * rpr;
+    const unsigned recv_bar = smem_u32(&bars->recv_full);
+    bool arrived = true;
+    int round = 0;
+    for (int h = 0; h < NM; h += RECV_COLS, ++round) {
+        const int hcols = min(NM - h, RECV_COLS);
+        if (warp >= 2) {
+            const int quarter = warp & 3;
+            const int wrow = quarter * 32 + lane;
+#pragma unroll 1
+            for (int c0 = 0; c0 < hcols; c0 += 32) {
+                uint32_t v[32];
+                if (have_acc) {
+                    tmem_ld32(tmem + ((unsigned)(quarter * 32) << 16) + h + c0, v);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = 0u;
+                }
+                float4* dst = reinterpret_cast<float4*>(part + (size_t)wrow * PL + c0);
+#pragma unroll
+                for (int j = 0; j < 32; j += 4)
+                    if (c0 + j < hcols)
+                        dst[j / 4] = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]), __uint_as_float(v[j + 2]),
+                                                 __uint_as_float(v[j + 3]));
+            }
+            if (KS > 1) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // visible to the copy engine
+            asm volatile("bar.sync 1, 128;" ::: "memory");                   // the four epilogue warps
+            if (KS > 1 && warp == 2 && lane == 0) {
+                const unsigned part_addr = smem_u32(part), recv_addr = smem_u32(recv);
+                for (int q = 0; q < KS; ++q) {
+                    // rank q finishes rows [q * RPB, (q + 1) * RPB) of a plain tile; of a gated tile RPB / 2 gate rows
+                    // and the RPB / 2 up rows 64 further on
+                    if (EPI == EPI_GATED) {
+                        const unsigned half = (unsigned)(RPB / 2) * PL * 4u;
+                        bulk_copy_to_rank(recv_addr + (unsigned)rank * RPB * PL * 4u, part_addr + (unsigned)q * half, half, recv_bar, q);
+                        bulk_copy_to_rank(recv_addr + (unsigned)rank * RPB * PL * 4u + half,
+                                          part_addr + (unsigned)(BW / 2) * PL * 4u + (unsigned)q * half, half, recv_bar, q);
+                    } else {
+                        const unsigned bytes = (unsigned)RPB * PL * 4u;
+                        bulk_copy_to_rank(recv_addr + (unsigned)rank * bytes, part_addr + (unsigned)q * bytes, bytes, recv_bar, q);
+                    }
+                }
+            }
+        }
+        if (KS == 1) {
+            __syncthreads();                                     // the partial tile is complete
+        } else if (arrived && !mbar_wait(recv_bar, round & 1)) {  // every rank's rows have come
+            atomicOr(status, 8);
+            arrived = false;
+        }
+        const int mgroups = (min(M - h, hcols) + 3) / 4;
+        for (int idx = threadIdx.x; idx < rpr * mgroups && arrived; idx += THREADS) {
+            const int rr = idx % rpr, m4 = (idx / rpr) * 4;
             float4 acc = make_float4(0.f, 0.f, 0.f, 0.f), up = make_float4(0.f, 0.f, 0.f, 0.f);
             for (int q = 0; q < KS; ++q) {
-                const float4 v = ld_dsmem4(part_addr + ((unsigned)nn * PL + m4) * 4u, q);
+                const float4 v = *reinterpret_cast<const float4*>(recv + ((size_t)q * RPB + rr) * PL + m4);
                 acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
                 if (EPI == EPI_GATED) {
-                    const float4 w = ld_dsmem4(part_addr + ((unsigned)(nn + BW / 2) * PL + m4) * 4u, q);
+                    const float4 w = *reinterpret_cast<const float4*>(recv + ((size_t)q * RPB + rpr + rr) * PL + m4);
                     up.x += w.x; up.y += w.y; up.z += w.z; up.w += w.w;
                 }
             }
-            const int n = n0 + nn;
+            const int n = n0 + r_lo + rr;
             if (n >= Nout) continue;
             const float a4[4] = {acc.x, acc.y, acc.z, acc.w}, u4[4] = {up.x, up.y, up.z, up.w};
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                const int m = m4 + j;
+                const int m = h + m4 + j;
                 if (m >= M) continue;
                 if (EPI == EPI_GATED) {
                     reinterpret_cast<bf16*>(C)[(size_t)m * Nout + n] = __float2bfloat16_rn(activate_fast(a4[j], act) * u4[j]);
@@ -286,8 +334,26 @@ gemm_skinny_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __gr
                 }
             }
         }
+        if (h + RECV_COLS < NM) {
+            // Before the partial tiles and the receive buffers are written again, every CTA must have what it was
+            // sent (then the copies out of every partial tile are done) and must have read it.
+            __syncthreads();
+            if (KS > 1) {
+                if (threadIdx.x == 0) mbar_expect_tx(recv_bar, (unsigned)(BW * PL * 4));
+                cluster_arrive();
+                cluster_wait();
+            }
+        }
     }
-    cluster_sync();      // nobody leaves while its shared memory may still be read
+    // A CTA's partial tile is the source of copies until every receiver has them; each CTA arrives when it has
+    // everything it is sent (it waited for that above), so after this barrier nothing is in flight anywhere.
+    cluster_arrive();
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(tmem_cols) : "memory");
+    }
+    cluster_wait();
 }
 
 typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -323,7 +389,7 @@ template <int EPI>
 int launch(const CUtensorMap& map_x, const CUtensorMap& map_w, void* C, int M, int N, int K, int KS, int NM, int stages,
            float cap, int act, int* status, unsigned tiles, cudaStream_t st) {
     auto kern = gemm_skinny_tcgen05_kernel<EPI>;
-    const size_t smem = (size_t)stages * (W_BYTES + NM * BK * 2) + sizeof(Barriers) + 1024;
+    const size_t smem = (size_t)stages * (W_BYTES + NM * BK * 2) + (KS > 1 ? (size_t)BW * ((NM < RECV_COLS ? NM : RECV_COLS) + 4) * 4 : 0) + sizeof(Barriers) + 1024;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
@@ -381,22 +447,31 @@ QNN_API int qnn_gemm_skinny_tcgen05(const void* A, const void* B, void* C, int M
     const int nk = (K + 63) / 64;
     int KS = 1;
     while (KS < 8 && tiles * KS * 2 <= sm_count && nk / (KS * 2) >= 2) KS *= 2;      // the doubled grid still fits one round
-    // Depth of the ring: what fits beside the barriers, if the device then holds all clusters at once (clusters
-    // of 8 CTAs with 217 KB each do not: 15 of them fit); else, and with several rounds of CTAs anyway, half of
-    // that, so that two CTAs share an SM (and one's set-up and epilogue hide behind the other's main loop).
-    // The partial tile (128 x (NM + 4) floats) lies over the ring.
+    // Depth of the ring: what fits beside the receive buffer (128 x (min(NM, 64) + 4) floats) and the barriers, if the device
+    // then holds all clusters at once (clusters of 8 CTAs with 217 KB each do not: 15 of them fit); else, and
+    // with several rounds of CTAs anyway, half of that, so that two CTAs share an SM (and one's set-up and
+    // epilogue hide behind the other's main loop).
     const int stage_bytes = W_BYTES + NM * BK * 2;
-    const int part_bytes = BW * (NM + 4) * 4;
+    const int part_bytes = BW * ((NM < RECV_COLS ? NM : RECV_COLS) + 4) * 4;
+    const int recv_bytes = KS > 1 ? part_bytes : 0;
     const int per = (nk + KS - 1) / KS;
     auto depth = [&](int kib) {
-        int st = (int)(((long long)kib * 1024 - 1024 - (long long)sizeof(Barriers)) / stage_bytes);
+        int st = (int)(((long long)kib * 1024 - 1024 - recv_bytes - (long long)sizeof(Barriers)) / stage_bytes);
         if (st > MAX_STAGES) st = MAX_STAGES;
         if (st > per) st = per < 2 ? 2 : per;
-        while ((long long)st * stage_bytes < part_bytes) ++st;
+        if (st < 2) st = 2;
+        while ((long long)st * stage_bytes < part_bytes) ++st;      // the partial tile lies over the ring
         return st;
     };
+    static int force_kib = -1;
+    if (force_kib < 0) {
+        const char* e = getenv("QNN_SKINNY_KIB");
+        force_kib = e ? atoi(e) : 0;
+    }
     int stages = depth(227);
-    if (tiles * KS > 2ll * sm_count) {
+    if (force_kib > 0) {
+        stages = depth(force_kib);
+    } else if (tiles * KS > 2ll * sm_count) {
         stages = depth(113);
     } else if (KS > 1) {
         static int fits[4][MAX_STAGES + 1];                // clusters of 2^i CTAs that the device holds, by depth (0: not asked)
@@ -405,7 +480,7 @@ QNN_API int qnn_gemm_skinny_tcgen05(const void* A, const void* B, void* C, int M
             cudaLaunchConfig_t cfg = {};
             cfg.gridDim = dim3(KS * 64);
             cfg.blockDim = dim3(THREADS);
-            cfg.dynamicSmemBytes = (size_t)stages * stage_bytes + sizeof(Barriers) + 1024;
+            cfg.dynamicSmemBytes = (size_t)stages * stage_bytes + recv_bytes + sizeof(Barriers) + 1024;
             cudaLaunchAttribute attr[1];
             attr[0].id = cudaLaunchAttributeClusterDimension;
             attr[0].val.clusterDim.x = KS;
@@ -423,7 +498,7 @@ QNN_API int qnn_gemm_skinny_tcgen05(const void* A, const void* B, void* C, int M
         }
         if (fits[ki][stages] < tiles) stages = depth(113);
     }
-    if (stages > MAX_STAGES || (long long)stages * stage_bytes + (long long)sizeof(Barriers) + 1024 > 227 * 1024)
+    if (stages > MAX_STAGES || (long long)stages * stage_bytes + recv_bytes + (long long)sizeof(Barriers) + 1024 > 227 * 1024)
         return QNN_ERR_UNSUPPORTED;
     switch (epi) {
         case EPI_NONE: return launch<EPI_NONE>(map_x, map_w, C, M, N, K, KS, NM, stages, cap, act, status, (unsigned)tiles, st);

@@ -174,9 +174,45 @@ QNN_API int qnn_sample(const float* logits, int R, int V, int top_k, float tempe
     QNN_LAUNCH_CHECK();
 }
 
+// k = 1 over many candidates (the 16-column candidates of the head's arg-max epilogue: 16,000 per row at a
+// vocabulary of 256,000): one block of 1024 threads per row, every thread's loads independent of one another,
+// one block-wide arg-max.  Nothing is erased: the candidates stay as they were.
+__global__ void __launch_bounds__(1024)
+argmax_candidates_kernel(const float2* __restrict__ cand, int ncand, int* __restrict__ out_tokens,
+                         const int* __restrict__ status_in, int* __restrict__ error_flag) {
+    pdl_wait();
+    if (blockIdx.x == 0 && threadIdx.x == 0 && status_in != nullptr && error_flag != nullptr) {
+        const int s = *status_in;
+        if (s != 0) atomicOr(error_flag, 2 | (s << 8));
+    }
+    __shared__ float sv[32];
+    __shared__ unsigned si[32];
+    const float2* c = cand + (size_t)blockIdx.x * ncand;
+    float bv = -FLT_MAX;
+    unsigned bi = NO_ID;
+    int i = threadIdx.x;
+    for (; i + 3 * 1024 < ncand; i += 4 * 1024) {
+        float2 e[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) e[j] = __ldg(c + i + j * 1024);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const unsigned id = __float_as_uint(e[j].y);
+            if (better(e[j].x, id, bv, bi)) { bv = e[j].x; bi = id; }
+        }
+    }
+    for (; i < ncand; i += 1024) {
+        const float2 e = __ldg(c + i);
+        const unsigned id = __float_as_uint(e.y);
+        if (better(e.x, id, bv, bi)) { bv = e.x; bi = id; }
+    }
+    block_argmax(bv, bi, sv, si);
+    if (threadIdx.x == 0) out_tokens[blockIdx.x] = (bi == NO_ID) ? -1 : (int)bi;
+}
+
 // The second half of qnn_sample alone, on candidates that another kernel produced (the arg-max
 // epilogue of the head product): cand[r][0..ncand) = (value, id), k best of them per row, then the
-// draw.  The candidates are consumed (overwritten).
+// draw.  The candidates are consumed (overwritten), except for a plain arg-max (k = 1, no table of seen ids).
 QNN_API int qnn_sample_candidates(void* cand, int R, int ncand, int V, int top_k, float temperature, float top_p,
                                   unsigned* rng_state, unsigned char* seen, const int* seen_rows, int* out_tokens,
                                   int* error_flag, const int* status_in, cudaStream_t st) {
@@ -185,6 +221,11 @@ QNN_API int qnn_sample_candidates(void* cand, int R, int ncand, int V, int top_k
     int k = top_k > SAMPLE_MAX_K ? SAMPLE_MAX_K : top_k;
     if (k > ncand) k = ncand;
     if (temperature <= 0.f) k = 1;
+    if (k == 1 && seen == nullptr) {
+        qnn::launch_pdl(argmax_candidates_kernel, dim3(R), dim3(1024), 0, st, (const float2*)cand, ncand, out_tokens,
+                        status_in, error_flag);
+        QNN_LAUNCH_CHECK();
+    }
     qnn::launch_pdl(sample_merge_kernel, dim3(R), dim3(SAMPLE_THREADS), 0, st, (float2*)cand, ncand, k, temperature, top_p,
                     rng_state, out_tokens, seen, seen_rows, V, status_in, error_flag);
     QNN_LAUNCH_CHECK();
