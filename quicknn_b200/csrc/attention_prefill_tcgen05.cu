@@ -23,97 +23,31 @@
 // Keys of other sequences that a tile drags in are masked; rows beyond the sequence are never stored.
 // Every mbarrier wait is bounded in time; on expiry a status word is set and the CTA winds down.
 #include "common.cuh"
-#include <cuda.h>
+#include "tcgen05.cuh"
 #include <math_constants.h>
 
 using namespace qnn;
 
 namespace {
 
+using namespace qnn::tc;
+// this file's short names for the single-CTA forms
+__device__ __forceinline__ void umma_bf16(unsigned tmem_d, uint64_t adesc, uint64_t bdesc, unsigned idesc, unsigned accumulate) {
+    umma_bf16_cta1(tmem_d, adesc, bdesc, idesc, accumulate);
+}
+__device__ __forceinline__ void umma_commit(unsigned bar) { umma_commit_cta1(bar); }
+__device__ __forceinline__ void tmem_ld32(unsigned taddr, uint32_t (&r)[32]) { tmem_ld32_nowait(taddr, r); }
+inline int make_map(CUtensorMap* map, const void* base, long long rows, long long width, int box_rows) {
+    return make_map_bf16(map, base, rows, width, box_rows, CU_TENSOR_MAP_L2_PROMOTION_L2_128B);
+}
+
 constexpr int BM = 128, BN = 64, KV_STAGES = 2, UMMA_K = 16;
 constexpr int P_BYTES = BM * BN * 2;                 // 16 KB
 constexpr int THREADS = 192;
 constexpr int S_COL = 0, O_COL = 128;             // tensor-memory columns of S (two buffers of 64) and of O
-constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;
 constexpr float RESCALE_STEP = 8.f;
 constexpr int MERGE_ML_BYTES = BM * 8;               // (reference maximum, sum) per row that rank 1 of a pair hands to rank 0
 
-__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(unsigned bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity) {
-    const long long start = clock64();
-    for (;;) {
-        unsigned done;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(done) : "r"(bar), "r"(parity), "r"(1000u) : "memory");
-        if (done) return true;
-        if (clock64() - start > WAIT_LIMIT_CYCLES) return false;
-    }
-}
-// the same for a whole warp: either every lane goes on or none does (the tcgen05.ld / st and votes
-// that follow are warp-wide)
-__device__ __forceinline__ bool mbar_wait_warp(unsigned bar, unsigned parity) {
-    return __all_sync(0xffffffffu, mbar_wait(bar, parity));
-}
-__device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap* map, unsigned bar, int x, int y) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
-}
-// shared-memory operand descriptor, 128-byte swizzle; lbo/sbo in bytes
-__device__ __forceinline__ uint64_t umma_desc(unsigned smem_addr, unsigned lbo, unsigned sbo) {
-    uint64_t d = 0;
-    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
-    d |= (uint64_t)((lbo >> 4) & 0x3FFF) << 16;
-    d |= (uint64_t)((sbo >> 4) & 0x3FFF) << 32;
-    d |= (uint64_t)1 << 46;
-    d |= (uint64_t)2 << 61;
-    return d;
-}
-__device__ __forceinline__ void umma_bf16(unsigned tmem_d, uint64_t adesc, uint64_t bdesc, unsigned idesc, unsigned accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit(unsigned bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(unsigned taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr));
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void tmem_st32(unsigned taddr, const uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
-        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
-        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
-          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
-          "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
-          "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
-        : "memory");
-    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-}
 __device__ __forceinline__ float tanh_fast(float x) {
     float r;
     asm("tanh.approx.f32 %0, %1;" : "=f"(r) : "f"(x));
@@ -124,24 +58,7 @@ __device__ __forceinline__ float exp2_fast(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
     return r;
 }
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<uint32_t*>(&h);
-}
 
-__device__ __forceinline__ void cluster_barrier() {
-    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-// Copy `bytes` (a multiple of 16) from this CTA's shared memory to the same address in the CTA of rank
-// `rank`; completion is counted in bytes on that CTA's mbarrier at `bar_local`.
-__device__ __forceinline__ void bulk_copy_to_rank(unsigned local_addr, unsigned bytes, unsigned bar_local, unsigned rank) {
-    unsigned dst, bar;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(dst) : "r"(local_addr), "r"(rank));
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(bar) : "r"(bar_local), "r"(rank));
-    asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(dst), "r"(local_addr), "r"(bytes), "r"(bar) : "memory");
-}
 
 struct __align__(8) Barriers {
     uint64_t q_full;
@@ -509,8 +426,8 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         __syncthreads();
         cluster_barrier();                  // both CTAs are past their last product; rank 1's part is laid out
         if (rank == 1 && threadIdx.x == 64) {
-            bulk_copy_to_rank(smem_u32(sKV), MERGE_O_BYTES, smem_u32(&bars->merge_full), 0);
-            bulk_copy_to_rank(smem_u32(sP), MERGE_ML_BYTES, smem_u32(&bars->merge_full), 0);
+            bulk_copy_to_rank(smem_u32(sKV), smem_u32(sKV), MERGE_O_BYTES, smem_u32(&bars->merge_full), 0);    // to the same place in rank 0
+            bulk_copy_to_rank(smem_u32(sP), smem_u32(sP), MERGE_ML_BYTES, smem_u32(&bars->merge_full), 0);
         }
         if (warp >= 2 && rank == 0) {
             if (!mbar_wait_warp(smem_u32(&bars->merge_full), 0)) {
@@ -600,35 +517,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     }
 }
 
-typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-EncodeTiled encoder() {
-    static EncodeTiled fn = nullptr;
-    if (fn == nullptr) {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiled>(p);
-    }
-    return fn;
-}
-
-// the packed qkv buffer: rows x width bfloat16; box = 64 columns x box_rows rows
-int make_map(CUtensorMap* map, const void* base, long long rows, long long width, int box_rows) {
-    EncodeTiled enc = encoder();
-    if (enc == nullptr) return QNN_ERR_UNSUPPORTED;
-    const cuuint64_t dims[2] = {(cuuint64_t)width, (cuuint64_t)rows};
-    const cuuint64_t strides[1] = {(cuuint64_t)width * 2};
-    const cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
-    const cuuint32_t estr[2] = {1, 1};
-    const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? 0 : QNN_ERR_ARGUMENT;
-}
 
 template <int HD>
 int launch_attn(const void* qkv, long long total_rows, void* out, long long out_stride, const int* seq_row0,
@@ -667,7 +556,9 @@ int launch_attn(const void* qkv, long long total_rows, void* out, long long out_
     const long long singles = (long long)ntq * B * nq;
     const int reach = window > 0 ? (max_len < window + BM - 1 ? max_len : window + BM - 1) : max_len;
     const int key_tiles = (reach + BN - 1) / BN;   // of the heaviest query tile
-    const bool want_split = ntq >= 2 && !getenv("QNN_ATTN_NO_SPLIT") &&
+    static int no_split = -1;                       // QNN_ATTN_NO_SPLIT, read once
+    if (no_split < 0) no_split = getenv("QNN_ATTN_NO_SPLIT") ? 1 : 0;
+    const bool want_split = ntq >= 2 && !no_split &&
                             ((2 * singles <= sm_count && key_tiles >= 12) || (singles <= sm_count && key_tiles >= 24));
     cudaLaunchConfig_t cfg = {};
     cfg.blockDim = dim3(THREADS);

@@ -24,7 +24,7 @@
 // 4 accumulator, 8 hand-over), and the CTA still sends its (then zero) rows, takes part in the cluster
 // barriers, frees its tensor memory and returns.
 #include "common.cuh"
-#include <cuda.h>
+#include "tcgen05.cuh"
 
 using namespace qnn;
 
@@ -34,89 +34,22 @@ using namespace qnn;
 
 namespace {
 
+using namespace qnn::tc;
+// this file's short names for the single-CTA forms
+__device__ __forceinline__ void umma_bf16(unsigned tmem_d, uint64_t adesc, uint64_t bdesc, unsigned idesc, unsigned accumulate) {
+    umma_bf16_cta1(tmem_d, adesc, bdesc, idesc, accumulate);
+}
+__device__ __forceinline__ void umma_commit(unsigned bar) { umma_commit_cta1(bar); }
+__device__ __forceinline__ void tmem_ld32(unsigned taddr, uint32_t (&r)[32]) { tmem_ld32_sync(taddr, r); }
+inline int make_map(CUtensorMap* map, const void* base, long long rows, long long width, int box_rows) {
+    return make_map_bf16(map, base, rows, width, box_rows, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
+}
+
 constexpr int BW = 128, BK = 64, MAX_STAGES = 10, UMMA_K = 16;     // BW: weight rows of a tile
 constexpr int W_BYTES = BW * BK * 2;
 constexpr int THREADS = 192;
 constexpr int RECV_COLS = 64;              // activation rows that pass through the receive buffer in one round
-constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;
-constexpr unsigned WAIT_HINT_NS = 20u;    // longest sleep inside one try_wait: a waiter sees a completed phase no later than this
 
-__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity) {
-    const long long start = clock64();
-    for (;;) {
-        unsigned done;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(done) : "r"(bar), "r"(parity), "r"(WAIT_HINT_NS) : "memory");
-        if (done) return true;
-        if (clock64() - start > WAIT_LIMIT_CYCLES) return false;
-    }
-}
-__device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap* map, unsigned bar, int x, int y) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
-}
-__device__ __forceinline__ uint64_t umma_desc(unsigned smem_addr) {   // K-major, 128-byte swizzle
-    uint64_t d = 0;
-    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
-    d |= (uint64_t)1 << 16;
-    d |= (uint64_t)(1024 >> 4) << 32;
-    d |= (uint64_t)1 << 46;
-    d |= (uint64_t)2 << 61;
-    return d;
-}
-__device__ __forceinline__ void umma_bf16(unsigned tmem_d, uint64_t adesc, uint64_t bdesc, unsigned idesc, unsigned accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit(unsigned bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(unsigned taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ unsigned cluster_rank() {
-    unsigned r;
-    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-    return r;
-}
-// The cluster barrier in two halves.  Every thread arrives once at the start and waits before anything is sent
-// to a peer, by when the peers have long arrived: it makes sure that they run and that their barriers are set
-// up.  It is used again before a CTA leaves (arrive when everything this CTA is sent has come, wait at the end):
-// a CTA's shared memory is the source of copies until every receiver has them.
-__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
-__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
-// `bytes` (a multiple of 16) from this CTA's shared memory to `dst_local` in the CTA of rank `rank`; completion
-// is counted in bytes on that CTA's mbarrier at `bar_local`.
-__device__ __forceinline__ void bulk_copy_to_rank(unsigned dst_local, unsigned src_local, unsigned bytes, unsigned bar_local,
-                                                  unsigned rank) {
-    unsigned dst, bar;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(dst) : "r"(dst_local), "r"(rank));
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(bar) : "r"(bar_local), "r"(rank));
-    asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(dst), "r"(src_local), "r"(bytes), "r"(bar) : "memory");
-}
 
 struct __align__(8) Barriers {
     uint64_t full[MAX_STAGES];
@@ -173,7 +106,11 @@ gemm_skinny_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __gr
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     if (threadIdx.x == 0) mbar_expect_tx(smem_u32(&bars->recv_full), (unsigned)(BW * PL * 4));   // the first round
-    cluster_arrive();                                        // "this CTA runs, its barriers are set up"
+    // The cluster barrier is used in two halves.  Every thread arrives here and waits before anything is sent to
+    // a peer, by when the peers have long arrived: that makes sure that they run and that their barriers are
+    // set up.  It is used again before a CTA leaves (arrive when everything this CTA is sent has come, wait at
+    // the end): a CTA's shared memory is the source of copies until every receiver has them.
+    cluster_arrive();
     const unsigned tmem = bars->tmem_base;
     // Barriers and tensor memory are set up.  The weights do not depend on the kernel before this one: the
     // producer asks for the weight tiles of the first ring of stages, and only then waits for that kernel,
@@ -356,34 +293,7 @@ gemm_skinny_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __gr
     cluster_wait();
 }
 
-typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-EncodeTiled encoder() {
-    static EncodeTiled fn = nullptr;
-    if (fn == nullptr) {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiled>(p);
-    }
-    return fn;
-}
-
-int make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) {
-    EncodeTiled enc = encoder();
-    if (enc == nullptr) return QNN_ERR_UNSUPPORTED;
-    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-    const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-    const cuuint32_t estr[2] = {1, 1};
-    const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? 0 : QNN_ERR_ARGUMENT;
-}
 
 template <int EPI>
 int launch(const CUtensorMap& map_x, const CUtensorMap& map_w, void* C, int M, int N, int K, int KS, int NM, int stages,

@@ -18,6 +18,8 @@
 //   * It calls no cudaMalloc, cudaFree or any allocating library routine.  The first call on
 //     each device looks up the array's device address (cudaGetSymbolAddress) and remembers it;
 //     make that first call outside any stream capture.  Later calls on that device only launch.
+//     The address is the current device's: `stream` must be a stream of the device that is
+//     current when the function is called (cudaSetDevice first, as for any launch).
 //   * All calls share the one array, and it keeps the previous call's partial results.  Nothing
 //     in it has to start at zero: a call writes every element that it later reads.  Two calls
 //     that overlap on the GPU (different streams, or different host threads without ordering)
