@@ -3,8 +3,12 @@
 Each function checks devices, dtypes, shapes and contiguity on the host, then
 calls the C entry point on the current CUDA stream.  Outputs are allocated by the
 caller or here with ``torch.empty`` (the caching allocator, so that a step can be
-captured in a CUDA graph).  Library matrix products (cuBLAS through
-``torch.matmul``) are used for bfloat16 products of more than 64 rows only.
+captured in a CUDA graph).  Matrix products run on this library's own kernels:
+float32 on FFMA kernels, bfloat16 on the mma.sync small-M kernel (up to 64 rows), the
+cluster split-K tcgen05 kernel (9 to 128 rows) and the tcgen05/TMA GEMMs (whole
+prompts; sizes they refuse go through the small-M kernel 64 rows at a time).  A library
+product (cuBLAS through ``torch.matmul``) is used only when ``QNN_GEMM=cublas`` asks
+for it, for comparisons.
 """
 from __future__ import annotations
 
@@ -370,9 +374,9 @@ def linear(x: torch.Tensor, w: torch.Tensor, *, epilogue: int = EPI_NONE, cap: O
            activation: str = "gelu_tanh", out_dtype: Optional[torch.dtype] = None):
     """y = x w^T with an optional epilogue.  x: [M, K]; w: [N, K] (gated: [2*N_out, K]).
 
-    float32: FFMA kernels only.  bfloat16: the tensor-core small-M kernel up to 64 rows, the
-    tcgen05/TMA kernel above that (a library product, cuBLAS, only for the softcap epilogue of
-    many rows, for sizes the kernel refuses, or when QNN_GEMM=cublas is set)."""
+    float32: FFMA kernels only.  bfloat16: the tensor-core small-M kernel up to 64 rows (the cluster
+    split-K tcgen05 kernel from 9 rows on against big matrices), the tcgen05/TMA kernel above that; a
+    library product (cuBLAS) only when QNN_GEMM=cublas is set."""
     _req(x, "x", None, 2)
     _req(w, "w", None, 2)
     M, K = x.shape
@@ -407,16 +411,29 @@ def linear(x: torch.Tensor, w: torch.Tensor, *, epilogue: int = EPI_NONE, cap: O
         y = gemm_skinny_tcgen05(x, w, epilogue=epilogue, cap=cap, activation=activation)
         if y is not None:
             return y
+    def small(xr: torch.Tensor, out: torch.Tensor) -> None:
+        _lib.check(L.qnn_skinny_bf16(_p(xr), _p(w), _p(out), dt_code(out), xr.shape[0], N, K, epilogue, capv, act,
+                                     _stream()), "skinny_bf16")
+
     if M <= SKINNY_MAX_ROWS:
         out = torch.empty((M, n_out), dtype=out_dtype, device=x.device)
-        _lib.check(L.qnn_skinny_bf16(_p(x), _p(w), _p(out), dt_code(out), M, N, K, epilogue, capv, act, _stream()),
-                   "skinny_bf16")
+        small(x, out)
         return out
-    if USE_TCGEN05 and epilogue in (EPI_NONE, EPI_GATED) and out_dtype == torch.bfloat16:
-        y = gemm_tcgen05(x, w, epilogue=epilogue, activation=activation)
-        if y is not None:
-            return y
-    y = torch.matmul(x, w.t())
+    if USE_TCGEN05:
+        if epilogue in (EPI_NONE, EPI_GATED) and out_dtype == torch.bfloat16:
+            y = gemm_tcgen05(x, w, epilogue=epilogue, activation=activation)
+            if y is not None:
+                return y
+        elif epilogue == EPI_SOFTCAP:          # logits wanted at many places: the product, then the cap in float32
+            y = gemm_tcgen05(x, w)
+            if y is not None:
+                return softcap(y, cap)
+        # sizes that the tcgen05 kernels refuse: the small-M kernel, 64 rows at a time
+        out = torch.empty((M, n_out), dtype=out_dtype, device=x.device)
+        for r0 in range(0, M, SKINNY_MAX_ROWS):
+            small(x[r0:r0 + SKINNY_MAX_ROWS], out[r0:r0 + SKINNY_MAX_ROWS])
+        return out
+    y = torch.matmul(x, w.t())                 # QNN_GEMM=cublas: the library product, for comparisons
     if epilogue == EPI_GATED:
         return gated_act(y, activation)
     if epilogue == EPI_SOFTCAP:
