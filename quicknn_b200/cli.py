@@ -58,8 +58,14 @@ def cmd_generate(args) -> int:
         if args.stream:
             print(json.dumps({"request": i, "token": tok}), flush=True)
 
+    prof = None
     try:
-        results = llm.generate(prompts, opts, on_token=on_token, stop_ids=stops)
+        if args.profile:
+            from .engine.profile import StepProfiler
+            with StepProfiler(llm.engine) as prof:
+                results = llm.generate(prompts, opts, on_token=on_token, stop_ids=stops)
+        else:
+            results = llm.generate(prompts, opts, on_token=on_token, stop_ids=stops)
     except KeyboardInterrupt:
         print("cancelled", file=sys.stderr)
         return 130
@@ -69,6 +75,8 @@ def cmd_generate(args) -> int:
                           "time_to_first_token_seconds": round(r.time_to_first_token_seconds, 6),
                           "decode_seconds": round(r.decode_seconds, 6),
                           "decode_tokens_per_second": round(r.decode_tokens_per_second(), 3)}))
+    if prof is not None:
+        print(prof.table(), file=sys.stderr)
     return 0
 
 
@@ -125,6 +133,8 @@ def main(argv=None) -> int:
     g.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16")
     g.add_argument("--device", default="cuda:0")
     g.add_argument("--stream", action="store_true", help="print each token as it is produced")
+    g.add_argument("--profile", action="store_true",
+                   help="time every step and every kind of part with CUDA events (steps then run eagerly) and print a table")
     g.set_defaults(fn=cmd_generate)
 
     r = sub.add_parser("random", help="write a model folder with random weights", allow_abbrev=False)

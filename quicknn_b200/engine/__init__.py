@@ -5,6 +5,7 @@ from .generate import GenerationBackend, GenerationResult, PromptError, generate
 from .llm import LLM
 from .model import Model, as_dtype
 from ..kernels.lib import KernelError, NonFiniteLogits
+from .profile import StepProfiler
 
 __all__ = ["StepBatch", "Engine", "StepError", "GenerationBackend", "GenerationResult", "PromptError",
-           "generate", "plan_batches", "LLM", "Model", "as_dtype", "KernelError", "NonFiniteLogits"]
+           "generate", "plan_batches", "LLM", "Model", "as_dtype", "KernelError", "NonFiniteLogits", "StepProfiler"]

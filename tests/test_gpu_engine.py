@@ -366,3 +366,28 @@ def test_greedy_ids_without_logits_are_those_with_logits(folders, monkeypatch):
     llm.generate(prompts[:2], GenerationOptions(max_new_tokens=4, temperature=0.5, seed=1), stop_ids=[])
     llm.generate(prompts[:2], GenerationOptions(max_new_tokens=4, temperature=0.0, repetition_penalty=1.2), stop_ids=[])
     assert used and not any(used)            # sampling and penalties need the logits
+
+
+def test_the_profile_table_accounts_for_every_step_and_puts_everything_back(folders):
+    from quicknn_b200.engine import LLM, StepProfiler
+    from quicknn_b200.parts.norm import RMSNorm
+    from quicknn_b200.sampling import GenerationOptions
+    llm = LLM(folders("C", "bfloat16"), max_context=64, max_batch=2, dtype="bfloat16")
+    prompts = prompts_for("C", [20, 7])
+    opts = GenerationOptions.greedy(6)
+    before = [r.tokens for r in llm.generate(prompts, opts, stop_ids=[])]
+    norm_call = RMSNorm.__call__
+    with StepProfiler(llm.engine) as prof:
+        during = [r.tokens for r in llm.generate(prompts, opts, stop_ids=[])]
+    assert during == before and llm.engine.use_graphs and RMSNorm.__call__ is norm_call
+    assert "forward" not in vars(llm.model.blocks[0].mixer) and "step" not in vars(llm.engine)
+    steps = prof.steps()
+    assert steps["prompt"][:2] == (1, 27) and steps["decode"][0] >= 5 and steps["decode"][1] == 2 * steps["decode"][0]
+    kinds = prof.by_kind()
+    assert all(kinds[k] > 0 for k in ("embedding", "norms and residual", "mixer", "feed-forward", "head", "sampling"))
+    inside = sum(kinds.values())
+    outside = sum(ms for _, _, ms in steps.values())
+    assert 0.3 * outside < inside <= outside * 1.05            # the parts are most of a step and never more than it
+    table = prof.table()
+    assert "feed-forward" in table and "tokens/s" in table
+    assert [r.tokens for r in llm.generate(prompts, opts, stop_ids=[])] == before

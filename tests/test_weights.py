@@ -122,3 +122,32 @@ def test_shards_through_an_index(tmp_path):
     (tmp_path / "model.safetensors.index.json").write_text(json.dumps({"weight_map": {"z": "s1.safetensors"}}))
     with pytest.raises(SafetensorsError):
         TensorDirectory.open(str(tmp_path))
+
+
+def test_sizes_the_kernels_do_not_take_are_refused_when_the_model_is_built():
+    """A configuration may be valid and still ask for what the kernels refuse: a head size beyond the
+    attention kernels' reach, an inner size that is no multiple of 8 in bfloat16.  The model says so when
+    it is built, by name, and not at its first step (the checks are host functions of the kernel library)."""
+    import torch
+    from quicknn_b200.config import GEMMA2, Gemma2Config
+    from quicknn_b200.engine import Model
+    from quicknn_b200.weights import random_tensors
+    from conftest import TINY_A
+
+    def build(dtype, **over):
+        cfg = Gemma2Config.from_dict(dict(TINY_A, **over))
+        tensors = dict(random_tensors(GEMMA2, cfg, 0, dtype))
+        return Model(GEMMA2, cfg, tensors, dtype, "cpu")
+    build(torch.float32)                                                  # the sizes of tiny A are fine
+    with pytest.raises(ValueError, match="head size 1152"):
+        build(torch.bfloat16, head_dim=1152, num_attention_heads=1, num_key_value_heads=1)
+    with pytest.raises(ValueError, match="head size 516"):
+        build(torch.float32, head_dim=516, num_attention_heads=1, num_key_value_heads=1)
+    with pytest.raises(ValueError, match="head size 20"):
+        build(torch.bfloat16, head_dim=20)                                # 40 bytes: no whole 16-byte vectors
+    build(torch.float32, head_dim=20)                                     # 80 bytes in float32: fine
+    with pytest.raises(ValueError, match="multiple of 8"):
+        build(torch.bfloat16, hidden_size=68)
+    with pytest.raises(ValueError, match="multiple of 8"):
+        build(torch.bfloat16, intermediate_size=100)
+    build(torch.float32, hidden_size=68, intermediate_size=100)           # float32 products take any size
