@@ -15,6 +15,15 @@
 //                      O is rescaled in tensor memory only when a row maximum has grown by more than 8
 //                      since the value the row's exponentials are taken against (the stale maximum
 //                      cancels in the final division; P stays below e^8).
+//   warps 6..9         a second softmax group, with a softcap only (FIXED).  A capped score lies in
+//                      [-cap, cap], so exp(score) can neither overflow nor vanish in float32 and needs no
+//                      running maximum: p = exp(cap tanh(s / cap)) against the fixed reference 0, the same
+//                      softmax (it is invariant under the shift) with nothing carried from tile to tile but
+//                      a row's sum.  The tiles are then independent: warps 2..5 take the even key tiles,
+//                      warps 6..9 the odd ones, two tiles are in the softmax at any time (two warps per
+//                      scheduler hide each other's latencies), no maximum is tracked and O is never rescaled.
+//                      One warp per scheduler with the running maximum took 2350 cycles per tile against
+//                      1700 of tensor work.
 // With few CTAs (one short prompt: 16 query tiles x 8 heads on 148 SMs, the last tile walking 16 times as
 // many keys as the first) the grid is launched as clusters of two: the CTAs of a pair take alternate key
 // tiles of the same query tile; when both are done, rank 1 pushes its (reference maximum, sum, O) into
@@ -41,10 +50,20 @@ inline int make_map(CUtensorMap* map, const void* base, long long rows, long lon
     return make_map_bf16(map, base, rows, width, box_rows, CU_TENSOR_MAP_L2_PROMOTION_L2_128B);
 }
 
-constexpr int BM = 128, BN = 64, KV_STAGES = 2, UMMA_K = 16;
+constexpr int BM = 128, BN = 64, MAX_KV_STAGES = 6, UMMA_K = 16;
+// Depth of the K and V rings: what fits beside Q and P.  A tile's K and V are asked for about one ring ahead of their
+// use, and a load takes a few thousand cycles: two stages of 32 KB (head size 256) keep barely enough in flight.
+__host__ __device__ constexpr int kv_stages(int hd) { return hd >= 256 ? 2 : (hd >= 128 ? 4 : 6); }
 constexpr int P_BYTES = BM * BN * 2;                 // 16 KB
-constexpr int THREADS = 192;
-constexpr int S_COL = 0, O_COL = 128;             // tensor-memory columns of S (two buffers of 64) and of O
+constexpr int THREADS = 320;                       // producer, issue, two groups of four softmax warps
+constexpr int S_COL = 0, O_COL = 128;             // tensor-memory columns of S (two buffers of 64) and of O; Q follows O
+// D[tmem] (+)= A[tmem] B[smem]: the A operand (here Q: lane = row, two bfloat16 per column) read from tensor memory
+__device__ __forceinline__ void umma_bf16_a_tmem(unsigned tmem_d, unsigned tmem_a, uint64_t bdesc, unsigned idesc, unsigned accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
 constexpr float RESCALE_STEP = 8.f;
 constexpr int MERGE_ML_BYTES = BM * 8;               // (reference maximum, sum) per row that rank 1 of a pair hands to rank 0
 
@@ -62,10 +81,11 @@ __device__ __forceinline__ float exp2_fast(float x) {
 
 struct __align__(8) Barriers {
     uint64_t q_full;
-    uint64_t k_full[KV_STAGES];
-    uint64_t k_empty[KV_STAGES];   // S_j has read K_j
-    uint64_t v_full[KV_STAGES];
-    uint64_t v_empty[KV_STAGES];   // O += P_j V_j has read V_j
+    uint64_t q_tmem;          // the softmax warps have copied Q from shared to tensor memory
+    uint64_t k_full[MAX_KV_STAGES];
+    uint64_t k_empty[MAX_KV_STAGES];   // S_j has read K_j
+    uint64_t v_full[MAX_KV_STAGES];
+    uint64_t v_empty[MAX_KV_STAGES];   // O += P_j V_j has read V_j
     uint64_t s_ready[2];      // S_j is complete in tensor memory
     uint64_t p_ready[2];      // P_j is in shared memory and O has been corrected
     uint64_t pv_done[2];      // O += P_j V_j has completed
@@ -77,16 +97,20 @@ struct __align__(8) Barriers {
 __device__ __forceinline__ bool has_failed(Barriers* b) { return *reinterpret_cast<volatile uint32_t*>(&b->failed) != 0; }
 
 // HD: head size, 64, 128 or 256 (the operands are walked in blocks of 64 head elements = 128 bytes)
-template <int HD>
+// FIXED: softcap with a fixed reference, both softmax groups at work (see the head of this file); else the running
+// maximum, warps 2..5 only.
+template <int HD, bool FIXED>
 __global__ void __launch_bounds__(THREADS)
 attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
                             bf16* __restrict__ out, size_t out_stride, const int* __restrict__ seq_row0,
                             const int* __restrict__ seq_len, int nq, int nkv, float scale, float cap, int window,
                             int* __restrict__ status, int split) {
+    constexpr int KV_STAGES = kv_stages(HD);
     constexpr int Q_BYTES = BM * HD * 2;                             // HD / 64 blocks of [128 x 64]
     constexpr int K_BYTES = BN * HD * 2, V_BYTES = BN * HD * 2;      // HD / 64 blocks of [64 x 64] each
     constexpr int MERGE_O_BYTES = BM * HD * 4;                       // O of rank 1 of a pair, float32
-    constexpr int TMEM_COLS = HD > 128 ? 512 : 256;                  // 128 for S and HD for O, a power of two
+    constexpr int Q_COL = O_COL + HD;                                // Q: HD / 2 columns (two bfloat16 each)
+    constexpr int TMEM_COLS = HD > 64 ? 512 : 256;                   // 128 for S, HD for O, HD / 2 for Q; a power of two
     constexpr int CPR = HD / 8;                                      // 16-byte chunks of a bfloat16 output row
     static_assert(HD == 64 || HD == 128 || HD == 256, "head sizes 64, 128, 256");
     static_assert(MERGE_O_BYTES <= KV_STAGES * (K_BYTES + V_BYTES) && MERGE_ML_BYTES <= 2 * P_BYTES, "the pair's hand-over fits");
@@ -118,6 +142,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 
     if (threadIdx.x == 0) {
         mbar_init(smem_u32(&bars->q_full), 1);
+        mbar_init(smem_u32(&bars->q_tmem), 4);                       // one arrival per warp of the first softmax group
         for (int s = 0; s < KV_STAGES; ++s) {
             mbar_init(smem_u32(&bars->k_full[s]), 1);
             mbar_init(smem_u32(&bars->k_empty[s]), 1);
@@ -150,6 +175,8 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     // The softmax warps' view of their row (warps 2..5; thread = query row), kept past the role branches
     // for the merge of a pair and the output.
     const int quarter = warp & 3;
+    const int group = warp >= 6 ? 1 : 0;                  // softmax group (warps 2..5 / 6..9)
+    const bool grp0 = warp >= 2 && warp < 6;              // the group that also merges a pair and writes the output
     const int rloc = quarter * 32 + lane;                 // row within the tile = tensor-memory lane
     const int row = r0 + rloc;                            // position in the sequence
     const unsigned lane_base = tmem + ((unsigned)(quarter * 32) << 16);
@@ -221,18 +248,25 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             // S: M 128, N 64, both operands K-major.  O: M 128, N hd, A (P) K-major, B (V) MN-major.
             const unsigned idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(BN >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
             const unsigned idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((unsigned)(HD >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
-            bool ok = mbar_wait(smem_u32(&bars->q_full), 0);
+            bool ok = mbar_wait(smem_u32(&bars->q_tmem), 0);
             if (!ok) { atomicOr(status, 32); bars->failed = 1; }
+            // Operand descriptors differ only in their address field (bits 0..13, the address in 16-byte units; every
+            // operand lies below 256 KB, so adding an offset never carries out of the field): one descriptor per
+            // operand is formed here, and each product adds its offset, a single addition in front of the
+            // instruction.  Twenty products per key tile are issued by this one thread; with the descriptors
+            // assembled anew for each, issuing them took about as long as the tensor cores need to run them.
+            const uint64_t k_desc0 = umma_desc(smem_u32(sKV), 16, 1024);
+            const uint64_t v_desc0 = umma_desc(smem_u32(sKV + K_BYTES), BN * 128, 1024);
+            const uint64_t p_desc0 = umma_desc(smem_u32(sP), 16, 1024);
             auto issue_s = [&](int j) {       // S_j = Q K_j^T into S buffer j & 1
-                const unsigned kaddr = smem_u32(sKV + (j % KV_STAGES) * (K_BYTES + V_BYTES));
-                const unsigned qaddr = smem_u32(sQ);
+                const uint64_t k_desc = k_desc0 + (uint64_t)(((j % KV_STAGES) * (K_BYTES + V_BYTES)) >> 4);
                 const unsigned acc = tmem + S_COL + (j & 1) * BN;
 #pragma unroll
                 for (int d = 0; d < HD / 64; ++d)
 #pragma unroll
                     for (int k = 0; k < 64 / UMMA_K; ++k)
-                        umma_bf16(acc, umma_desc(qaddr + d * (BM * 128) + k * 32, 16, 1024),
-                                  umma_desc(kaddr + d * (BN * 128) + k * 32, 16, 1024), idesc_s, (d > 0 || k > 0) ? 1u : 0u);
+                        umma_bf16_a_tmem(acc, tmem + Q_COL + d * 32 + k * (UMMA_K / 2),
+                                         k_desc + (uint64_t)((d * (BN * 128) + k * 32) >> 4), idesc_s, (d > 0 || k > 0) ? 1u : 0u);
                 umma_commit(smem_u32(&bars->k_empty[j % KV_STAGES]));
                 umma_commit(smem_u32(&bars->s_ready[j & 1]));
             };
@@ -258,26 +292,52 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 ok = mbar_wait(smem_u32(&bars->v_full[j % KV_STAGES]), (j / KV_STAGES) & 1);
                 if (!ok) { atomicOr(status, 2); bars->failed = 1; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const unsigned vaddr = smem_u32(sKV + (j % KV_STAGES) * (K_BYTES + V_BYTES) + K_BYTES);
-                const unsigned paddr = smem_u32(sP + (j & 1) * P_BYTES);
+                const uint64_t v_desc = v_desc0 + (uint64_t)(((j % KV_STAGES) * (K_BYTES + V_BYTES)) >> 4);
+                const uint64_t p_desc = p_desc0 + (uint64_t)(((j & 1) * P_BYTES) >> 4);
 #pragma unroll
                 for (int k = 0; k < BN / UMMA_K; ++k)
                     // P: 16 keys further = 32 bytes in the swizzled row.  V (keys x dims, dims contiguous):
                     // 16 keys further = 16 rows of 128 bytes; the four 64-dim blocks are BN*128 bytes apart.
-                    umma_bf16(tmem + O_COL, umma_desc(paddr + k * 32, 16, 1024),
-                              umma_desc(vaddr + k * UMMA_K * 128, BN * 128, 1024), idesc_o, (j > 0 || k > 0) ? 1u : 0u);
+                    umma_bf16(tmem + O_COL, p_desc + (uint64_t)((k * 32) >> 4), v_desc + (uint64_t)((k * UMMA_K * 128) >> 4),
+                              idesc_o, (j > 0 || k > 0) ? 1u : 0u);
                 umma_commit(smem_u32(&bars->v_empty[j % KV_STAGES]));
                 umma_commit(smem_u32(&bars->pv_done[j & 1]));
             }
         }
     } else {
         // ---- softmax: thread = query row ---------------------------------------------------------------
+        // First, Q moves from shared to tensor memory, where S = Q K^T reads it as its A operand: 16 products per key
+        // tile no longer read 64 KB of Q from shared memory, whose bandwidth (with K, V, P and the TMA writes about
+        // 224 KB per tile) and not the tensor cores set the pace.  Thread = row; a row's 16-byte chunks are swizzled
+        // within each 64-column block, and eight of them fill 32 columns.
+        if (group == 0) {
+            if (!mbar_wait_warp(smem_u32(&bars->q_full), 0)) {
+                atomicOr(status, 32);
+                bars->failed = 1;
+                alive = false;
+            }
+#pragma unroll 1
+            for (int d = 0; d < HD / 64; ++d) {
+                uint32_t v[32];
+                const unsigned char* qrow = sQ + d * (BM * 128) + rloc * 128;
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    const uint4 w = *reinterpret_cast<const uint4*>(qrow + ((c ^ (rloc & 7)) << 4));
+                    v[c * 4 + 0] = w.x; v[c * 4 + 1] = w.y; v[c * 4 + 2] = w.z; v[c * 4 + 3] = w.w;
+                }
+                tmem_st32(lane_base + Q_COL + d * 32, v);
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bars->q_tmem));
+        }
         float m_run = -CUDART_INF_F;
         // the keys this row sees: key_lo .. key_hi (none when the row lies beyond the sequence)
         const int key_hi = min(row, len - 1);
         const int key_lo = (window > 0 && row - window + 1 > 0) ? row - window + 1 : 0;
         const unsigned key_span = key_hi >= key_lo ? (unsigned)(key_hi - key_lo) : 0u;
-        for (int j = 0; j < nt && alive; ++j) {
+        // FIXED: this group's tiles are group, group + 2, ...; else group 0 takes them all and group 1 none
+        for (int j = FIXED ? group : (group == 0 ? 0 : nt); j < nt && alive; j += FIXED ? 2 : 1) {
             const int bsel = j & 1;
             if (!mbar_wait_warp(smem_u32(&bars->s_ready[bsel]), (j >> 1) & 1)) {
                 atomicOr(status, 4);
@@ -304,6 +364,29 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             // skip the mask.
             const int col0 = (jt0 + j * stride) * BN;
             const bool interior = col0 + BN - 1 <= r0 && col0 + BN - 1 < len && (window <= 0 || col0 > r0 + BM - 1 - window);
+            float corr = 1.f;
+            bool rescale = false;
+            if (FIXED) {
+                // exp(capped score) against the reference 0: k2 = cap log2(e), the exponent stays within +-k2
+                float rs4[4] = {0.f, 0.f, 0.f, 0.f};
+                if (interior) {
+#pragma unroll
+                    for (int c = 0; c < BN; ++c) {
+                        const float pv = exp2_fast(tanh_fast(s[c] * k1) * k2);
+                        s[c] = pv;
+                        rs4[c & 3] += pv;
+                    }
+                } else {
+#pragma unroll
+                    for (int c = 0; c < BN; ++c) {
+                        const bool seen = (unsigned)(col0 + c - key_lo) <= key_span;      // key_lo <= column <= key_hi
+                        const float pv = seen ? exp2_fast(tanh_fast(s[c] * k1) * k2) : 0.f;
+                        s[c] = pv;
+                        rs4[c & 3] += pv;
+                    }
+                }
+                l_sum += (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
+            } else {
             float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
             if (interior) {
 #pragma unroll
@@ -324,8 +407,6 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             }
             const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             m_run = fmaxf(m_run, mx);
-            float corr = 1.f;
-            bool rescale = false;
             if (m_run != -CUDART_INF_F && (j == 0 || m_run > m_used + step || l_sum == 0.f)) {
                 // take the exponentials against the new maximum from here on
                 corr = (l_sum == 0.f) ? 0.f : exp2_fast((m_used - m_run) * k2);
@@ -342,6 +423,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             }
             const float rs = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
             l_sum = l_sum * corr + rs;
+            }
             // P_j overwrites the buffer that P_{j-2} V_{j-2} read.  That product was issued before S_j and
             // the commit behind S_j covers everything issued before it, so s_ready[j] already said that it
             // is done.  (O may only be touched once P_{j-1} V_{j-1} is done: see the rescale below.)
@@ -357,7 +439,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     *reinterpret_cast<uint4*>(prow + ((ch ^ (rloc & 7)) << 4)) = pk;
                 }
             }
-            if (__any_sync(0xffffffffu, rescale)) {
+            if (!FIXED && __any_sync(0xffffffffu, rescale)) {
                 if (j >= 1 && !mbar_wait_warp(smem_u32(&bars->pv_done[(j - 1) & 1]), ((j - 1) >> 1) & 1)) {
                     atomicOr(status, 64);
                     bars->failed = 1;
@@ -383,13 +465,32 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             if (lane == 0) mbar_arrive(smem_u32(&bars->p_ready[bsel]));
         }
         // the last product, then O / l -> bfloat16 -> global
+        // A waiter may only ask for a barrier's phase when it knows the phase before it to be over (a parity says
+        // nothing about a phase that has not begun).  A group knows that of the barrier of its own tiles: S_j was
+        // committed behind P_{j-2} V_{j-2}.  So each group waits for its own last product first; the products are
+        // done in order, so after that the one before the very last is over too, and the very last may be asked for.
         if (alive && nt > 0) {
             const int jl = nt - 1;
-            if (!mbar_wait_warp(smem_u32(&bars->pv_done[jl & 1]), (jl >> 1) & 1)) {
+            const int jmine = (FIXED && (jl & 1) != group) ? jl - 1 : jl;
+            if (jmine >= 0 && jmine != jl && !mbar_wait_warp(smem_u32(&bars->pv_done[jmine & 1]), (jmine >> 1) & 1)) {
                 atomicOr(status, 64);
                 bars->failed = 1;
                 alive = false;
             }
+            if (alive && !mbar_wait_warp(smem_u32(&bars->pv_done[jl & 1]), (jl >> 1) & 1)) {
+                atomicOr(status, 64);
+                bars->failed = 1;
+                alive = false;
+            }
+        }
+        if (FIXED) {
+            // a row's sum is the sum of its two groups' sums (both against the reference 0); the second group
+            // leaves its own at the end of the P buffers, which no product reads any more
+            float* l_second = reinterpret_cast<float*>(sP + 2 * P_BYTES - BM * 4);
+            if (group == 1) l_second[rloc] = alive ? l_sum : 0.f;
+            asm volatile("bar.sync 2, 256;" ::: "memory");       // the eight softmax warps
+            if (group == 0) l_sum += l_second[rloc];
+            if (__any_sync(0xffffffffu, has_failed(bars))) alive = false;
         }
     }
 
@@ -401,7 +502,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     // of its memory.
     float m_other = 0.f, l_other = 0.f;
     if (split) {
-        if (warp >= 2 && rank == 1) {
+        if (grp0 && rank == 1) {
             const bool have = alive && nt > 0 && !has_failed(bars);
             if (have) asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             unsigned char* orow = sKV + rloc * (HD * 4);
@@ -429,7 +530,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             bulk_copy_to_rank(smem_u32(sKV), smem_u32(sKV), MERGE_O_BYTES, smem_u32(&bars->merge_full), 0);    // to the same place in rank 0
             bulk_copy_to_rank(smem_u32(sP), smem_u32(sP), MERGE_ML_BYTES, smem_u32(&bars->merge_full), 0);
         }
-        if (warp >= 2 && rank == 0) {
+        if (grp0 && rank == 0) {
             if (!mbar_wait_warp(smem_u32(&bars->merge_full), 0)) {
                 atomicOr(status, 128);
                 bars->failed = 1;
@@ -444,7 +545,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         cluster_barrier();                  // the bytes have left rank 1's memory: it may go
     }
 
-    if (warp >= 2 && rank == 0) {
+    if (grp0 && rank == 0) {
         // Every product is done, so the Q tile's shared memory is free: each thread leaves its row there as
         // bfloat16 (16-byte chunks XOR-ed with the row number, so that neither side conflicts), and the
         // warps then write whole rows of the head to global memory.
@@ -519,7 +620,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 
 
 
-template <int HD>
+template <int HD, bool FIXED>
 int launch_attn(const void* qkv, long long total_rows, void* out, long long out_stride, const int* seq_row0,
                 const int* seq_len, int B, int max_len, int nq, int nkv, float scale, float cap, int window,
                 int* status, cudaStream_t st) {
@@ -529,8 +630,8 @@ int launch_attn(const void* qkv, long long total_rows, void* out, long long out_
     if (rc) return rc;
     rc = make_map(&map_kv, qkv, total_rows, width, BN);
     if (rc) return rc;
-    const size_t smem = (size_t)BM * HD * 2 + (size_t)KV_STAGES * 2 * BN * HD * 2 + 2 * P_BYTES + sizeof(Barriers) + 1024;
-    auto kern = attn_prefill_tcgen05_kernel<HD>;
+    const size_t smem = (size_t)BM * HD * 2 + (size_t)kv_stages(HD) * 2 * BN * HD * 2 + 2 * P_BYTES + sizeof(Barriers) + 1024;
+    auto kern = attn_prefill_tcgen05_kernel<HD, FIXED>;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -613,10 +714,19 @@ QNN_API int qnn_attn_prefill_tcgen05(const void* qkv, long long total_rows, void
     if (B > 65535 || nq > 32767 || (max_len + BM - 1) / BM > 65535) return QNN_ERR_UNSUPPORTED;
     if (((uintptr_t)qkv & 15) || ((uintptr_t)out & 15) || (out_stride * 2) % 16) return QNN_ERR_UNSUPPORTED;
 #define QNN_ATTN_ARGS qkv, total_rows, out, out_stride, seq_row0, seq_len, B, max_len, nq, nkv, scale, cap, window, status, st
+    // With a softcap up to 70 the exponent cap * log2(e) stays below 101, so that neither exp(score) nor a row's
+    // sum over a million keys leaves float32: the fixed-reference softmax with both groups of warps.  QNN_ATTN_FIXED=0
+    // keeps the running maximum (for comparisons).
+    static int fixed_ok = -1;
+    if (fixed_ok < 0) {
+        const char* e = getenv("QNN_ATTN_FIXED");
+        fixed_ok = (e && e[0] == '0') ? 0 : 1;
+    }
+    const bool fixed = fixed_ok && cap > 0.f && cap <= 70.f;
     switch (hd) {
-        case 64: return launch_attn<64>(QNN_ATTN_ARGS);
-        case 128: return launch_attn<128>(QNN_ATTN_ARGS);
-        default: return launch_attn<256>(QNN_ATTN_ARGS);
+        case 64: return fixed ? launch_attn<64, true>(QNN_ATTN_ARGS) : launch_attn<64, false>(QNN_ATTN_ARGS);
+        case 128: return fixed ? launch_attn<128, true>(QNN_ATTN_ARGS) : launch_attn<128, false>(QNN_ATTN_ARGS);
+        default: return fixed ? launch_attn<256, true>(QNN_ATTN_ARGS) : launch_attn<256, false>(QNN_ATTN_ARGS);
     }
 #undef QNN_ATTN_ARGS
 }
