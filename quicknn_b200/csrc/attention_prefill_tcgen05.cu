@@ -51,11 +51,11 @@ inline int make_map(CUtensorMap* map, const void* base, long long rows, long lon
 }
 
 constexpr int BM = 128, BN = 64, MAX_KV_STAGES = 6, UMMA_K = 16;
-// Depth of the K and V rings: what fits beside Q and P.  A tile's K and V are asked for about one ring ahead of their
-// use, and a load takes a few thousand cycles: two stages of 32 KB (head size 256) keep barely enough in flight.
-__host__ __device__ constexpr int kv_stages(int hd) { return hd >= 256 ? 2 : (hd >= 128 ? 4 : 6); }
+// Depth of the rings: K in pairs of key tiles (128 keys), V in tiles of 64 keys; what fits beside P in 227 KB.
+__host__ __device__ constexpr int k_stages(int hd) { return hd >= 256 ? 2 : (hd >= 128 ? 3 : 4); }
+__host__ __device__ constexpr int v_stages(int hd) { return hd >= 256 ? 2 : (hd >= 128 ? 4 : 6); }
 constexpr int P_BYTES = BM * BN * 2;                 // 16 KB
-constexpr int THREADS = 320;                       // producer, issue, two groups of four softmax warps
+constexpr int THREADS = 384;       // K producer, S issue, two groups of four softmax warps, V producer, P V issue
 constexpr int S_COL = 0, O_COL = 128;             // tensor-memory columns of S (two buffers of 64) and of O; Q follows O
 // D[tmem] (+)= A[tmem] B[smem]: the A operand (here Q: lane = row, two bfloat16 per column) read from tensor memory
 __device__ __forceinline__ void umma_bf16_a_tmem(unsigned tmem_d, unsigned tmem_a, uint64_t bdesc, unsigned idesc, unsigned accumulate) {
@@ -86,7 +86,8 @@ struct __align__(8) Barriers {
     uint64_t k_empty[MAX_KV_STAGES];   // S_j has read K_j
     uint64_t v_full[MAX_KV_STAGES];
     uint64_t v_empty[MAX_KV_STAGES];   // O += P_j V_j has read V_j
-    uint64_t s_ready[2];      // S_j is complete in tensor memory
+    uint64_t s_ready;         // S of a pair of key tiles is complete in tensor memory
+    uint64_t s_free;          // the softmax warps have read it (8 arrivals: 4 warps for each tile of the pair)
     uint64_t p_ready[2];      // P_j is in shared memory and O has been corrected
     uint64_t pv_done[2];      // O += P_j V_j has completed
     uint64_t merge_full;      // rank 0 of a pair: rank 1's partial result has arrived (bytes)
@@ -105,20 +106,25 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             bf16* __restrict__ out, size_t out_stride, const int* __restrict__ seq_row0,
                             const int* __restrict__ seq_len, int nq, int nkv, float scale, float cap, int window,
                             int* __restrict__ status, int split) {
-    constexpr int KV_STAGES = kv_stages(HD);
+    constexpr int KS = k_stages(HD), VS = v_stages(HD);
     constexpr int Q_BYTES = BM * HD * 2;                             // HD / 64 blocks of [128 x 64]
-    constexpr int K_BYTES = BN * HD * 2, V_BYTES = BN * HD * 2;      // HD / 64 blocks of [64 x 64] each
+    constexpr int KP_BYTES = 2 * BN * HD * 2;                        // a pair of key tiles: HD / 64 blocks of [128 x 64]
+    constexpr int V_BYTES = BN * HD * 2;                             // HD / 64 blocks of [64 x 64]
     constexpr int MERGE_O_BYTES = BM * HD * 4;                       // O of rank 1 of a pair, float32
     constexpr int Q_COL = O_COL + HD;                                // Q: HD / 2 columns (two bfloat16 each)
     constexpr int TMEM_COLS = HD > 64 ? 512 : 256;                   // 128 for S, HD for O, HD / 2 for Q; a power of two
     constexpr int CPR = HD / 8;                                      // 16-byte chunks of a bfloat16 output row
     static_assert(HD == 64 || HD == 128 || HD == 256, "head sizes 64, 128, 256");
-    static_assert(MERGE_O_BYTES <= KV_STAGES * (K_BYTES + V_BYTES) && MERGE_ML_BYTES <= 2 * P_BYTES, "the pair's hand-over fits");
+    static_assert(KS >= 2 && Q_BYTES == KP_BYTES, "Q is staged in the second stage of the K ring");
+    static_assert(MERGE_O_BYTES <= KS * KP_BYTES && MERGE_ML_BYTES <= 2 * P_BYTES, "the pair's hand-over fits");
+    static_assert(BM * HD * 2 <= VS * V_BYTES, "the output is staged in the V ring");
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    unsigned char* sQ = smem;
-    unsigned char* sKV = sQ + Q_BYTES;                              // [stage][K | V]
-    unsigned char* sP = sKV + KV_STAGES * (K_BYTES + V_BYTES);      // [2][P]
+    unsigned char* sK = smem;                                       // [KS] pairs of key tiles
+    unsigned char* sV = sK + KS * KP_BYTES;                         // [VS] value tiles
+    unsigned char* sP = sV + VS * V_BYTES;                          // [2][P]
+    unsigned char* sQ = sK + KP_BYTES;                              // Q on its way to tensor memory: K stage 1, before its first use
+    unsigned char* sOut = sV;                                       // the output rows, once every product is done
     Barriers* bars = reinterpret_cast<Barriers*>(sP + 2 * P_BYTES);
 
     // grid (heads [x 2 ranks], sequences, query tiles): the query tile is the slowest index, so that CTAs are
@@ -136,21 +142,29 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int last_row = min(r0 + BM, len) - 1;
     const int kv_lo = (window > 0 && r0 - window + 1 > 0) ? r0 - window + 1 : 0;
-    const int jt1 = last_row / BN;                                   // key tiles kv_lo / BN .. jt1 of the query tile,
-    const int jt0 = kv_lo / BN + rank;                               // of which this CTA takes jt0, jt0 + stride, ...
-    const int nt = jt1 >= jt0 ? (jt1 - jt0) / stride + 1 : 0;        // (none for rank 1 when there is a single tile)
+    // Keys are walked in pairs of 64-key tiles (S of a pair is one product of N = 128): pairs kv_lo / 128 ..
+    // last_row / 128 of the query tile, of which this CTA takes jp0, jp0 + stride, ...  Local tile j is half j & 1 of
+    // local pair j >> 1; a half outside the row range (the first pair's lower half under a window) is masked out
+    // like any other key that a row does not see.
+    const int jp1 = last_row / (2 * BN);
+    const int jp0 = kv_lo / (2 * BN) + rank;
+    const int np = jp1 >= jp0 ? (jp1 - jp0) / stride + 1 : 0;        // (none for rank 1 when there is a single pair)
+    const int nt = 2 * np;
 
     if (threadIdx.x == 0) {
         mbar_init(smem_u32(&bars->q_full), 1);
         mbar_init(smem_u32(&bars->q_tmem), 4);                       // one arrival per warp of the first softmax group
-        for (int s = 0; s < KV_STAGES; ++s) {
+        for (int s = 0; s < KS; ++s) {
             mbar_init(smem_u32(&bars->k_full[s]), 1);
             mbar_init(smem_u32(&bars->k_empty[s]), 1);
+        }
+        for (int s = 0; s < VS; ++s) {
             mbar_init(smem_u32(&bars->v_full[s]), 1);
             mbar_init(smem_u32(&bars->v_empty[s]), 1);
         }
+        mbar_init(smem_u32(&bars->s_ready), 1);
+        mbar_init(smem_u32(&bars->s_free), 8);                       // one arrival per softmax warp and tile of the pair
         for (int i = 0; i < 2; ++i) {
-            mbar_init(smem_u32(&bars->s_ready[i]), 1);
             mbar_init(smem_u32(&bars->p_ready[i]), 4);               // one arrival per softmax warp
             mbar_init(smem_u32(&bars->pv_done[i]), 1);
         }
@@ -172,10 +186,10 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     // loads below read (seq_row0 and seq_len, read above, come from the host before the step).
     pdl_wait();
 
-    // The softmax warps' view of their row (warps 2..5; thread = query row), kept past the role branches
+    // The softmax warps' view of their row (warps 2..9; thread = query row), kept past the role branches
     // for the merge of a pair and the output.
     const int quarter = warp & 3;
-    const int group = warp >= 6 ? 1 : 0;                  // softmax group (warps 2..5 / 6..9)
+    const int group = (warp >= 6 && warp < 10) ? 1 : 0;   // softmax group (warps 2..5 / 6..9)
     const bool grp0 = warp >= 2 && warp < 6;              // the group that also merges a pair and writes the output
     const int rloc = quarter * 32 + lane;                 // row within the tile = tensor-memory lane
     const int row = r0 + rloc;                            // position in the sequence
@@ -186,121 +200,108 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const float step = RESCALE_STEP / (cap > 0.f ? cap : 1.f);   // a growth of the maximum by 8 in the exponent
     float m_used = 0.f, l_sum = 0.f;                      // reference maximum of the exponentials, their sum
     bool alive = true;
+    const int kx = (nq + kh) * HD, vx = (nq + nkv + kh) * HD;     // columns of K and V in the qkv rows
 
     if (warp == 0) {
         if (lane == 0) {
-            // ---- producer -------------------------------------------------------------------------
+            // ---- producer of Q and K --------------------------------------------------------------------
+            // K of a pair of tiles is one operand of 128 rows; its stage is free again as soon as S of the pair has
+            // been formed.  (The boxes of 128 rows x 64 columns are those of Q: the same tensor map.)
             const unsigned qf = smem_u32(&bars->q_full);
             mbar_expect_tx(qf, Q_BYTES);
             for (int d = 0; d < HD / 64; ++d)
                 tma_load_2d(smem_u32(sQ + d * (BM * 128)), &map_q, qf, h * HD + d * 64, row0 + r0);
-            const int kx = (nq + kh) * HD, vx = (nq + nkv + kh) * HD;     // columns of K and V in the qkv rows
-            // K_j is free again as soon as S_j has been formed, V_j only after O += P_j V_j: two rings, so
-            // that the next keys are on their way while the softmax of this tile has not even begun
-            for (int j = 0; j < nt; ++j) {
-                const int s = j % KV_STAGES;
-                const unsigned par = ((j / KV_STAGES) - 1) & 1;
-                unsigned char* kdst = sKV + s * (K_BYTES + V_BYTES);
-                const int y = row0 + (jt0 + j * stride) * BN;
-                if (j >= KV_STAGES && !mbar_wait(smem_u32(&bars->k_empty[s]), par)) {
+            for (int J = 0; J < np; ++J) {
+                const int s = J % KS;
+                if (J >= KS && !mbar_wait(smem_u32(&bars->k_empty[s]), ((J / KS) - 1) & 1)) {
                     atomicOr(status, 16);
                     bars->failed = 1;
                     break;
                 }
-                const unsigned kfull = smem_u32(&bars->k_full[s]);
-                mbar_expect_tx(kfull, K_BYTES);
-                for (int d = 0; d < HD / 64; ++d)
-                    tma_load_2d(smem_u32(kdst + d * (BN * 128)), &map_kv, kfull, kx + d * 64, y);
-                // the values of the tile before: their stage was freed a product earlier
-                if (j >= 1) {
-                    const int jv = j - 1, sv = jv % KV_STAGES;
-                    if (jv >= KV_STAGES && !mbar_wait(smem_u32(&bars->v_empty[sv]), ((jv / KV_STAGES) - 1) & 1)) {
-                        atomicOr(status, 16);
-                        bars->failed = 1;
-                        break;
-                    }
-                    const unsigned vfull = smem_u32(&bars->v_full[sv]);
-                    unsigned char* vd = sKV + sv * (K_BYTES + V_BYTES) + K_BYTES;
-                    mbar_expect_tx(vfull, V_BYTES);
-                    for (int d = 0; d < HD / 64; ++d)
-                        tma_load_2d(smem_u32(vd + d * (BN * 128)), &map_kv, vfull, vx + d * 64, row0 + (jt0 + jv * stride) * BN);
+                if (J == 1 && !mbar_wait(smem_u32(&bars->q_tmem), 0)) {      // stage 1 held Q until now
+                    atomicOr(status, 32);
+                    bars->failed = 1;
+                    break;
                 }
+                const unsigned kfull = smem_u32(&bars->k_full[s]);
+                unsigned char* kdst = sK + s * KP_BYTES;
+                mbar_expect_tx(kfull, KP_BYTES);
+                for (int d = 0; d < HD / 64; ++d)
+                    tma_load_2d(smem_u32(kdst + d * (2 * BN * 128)), &map_q, kfull, kx + d * 64, row0 + (jp0 + J * stride) * 2 * BN);
             }
-            if (nt > 0 && !has_failed(bars)) {          // the values of the last tile
-                const int jv = nt - 1, sv = jv % KV_STAGES;
-                bool ok = true;
-                if (jv >= KV_STAGES) ok = mbar_wait(smem_u32(&bars->v_empty[sv]), ((jv / KV_STAGES) - 1) & 1);
-                if (!ok) {
+        }
+    } else if (warp == 10) {
+        if (lane == 0) {
+            // ---- producer of V: a stage is free only after O += P_j V_j ------------------------------------
+            for (int j = 0; j < nt; ++j) {
+                const int s = j % VS;
+                if (j >= VS && !mbar_wait(smem_u32(&bars->v_empty[s]), ((j / VS) - 1) & 1)) {
                     atomicOr(status, 16);
                     bars->failed = 1;
-                } else {
-                    const unsigned vfull = smem_u32(&bars->v_full[sv]);
-                    unsigned char* vd = sKV + sv * (K_BYTES + V_BYTES) + K_BYTES;
-                    mbar_expect_tx(vfull, V_BYTES);
-                    for (int d = 0; d < HD / 64; ++d)
-                        tma_load_2d(smem_u32(vd + d * (BN * 128)), &map_kv, vfull, vx + d * 64, row0 + (jt0 + jv * stride) * BN);
+                    break;
                 }
+                const unsigned vfull = smem_u32(&bars->v_full[s]);
+                unsigned char* vdst = sV + s * V_BYTES;
+                mbar_expect_tx(vfull, V_BYTES);
+                const int y = row0 + ((jp0 + (j >> 1) * stride) * 2 + (j & 1)) * BN;
+                for (int d = 0; d < HD / 64; ++d)
+                    tma_load_2d(smem_u32(vdst + d * (BN * 128)), &map_kv, vfull, vx + d * 64, y);
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            // ---- tensor-core issue -----------------------------------------------------------------
-            // S: M 128, N 64, both operands K-major.  O: M 128, N hd, A (P) K-major, B (V) MN-major.
-            const unsigned idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(BN >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
-            const unsigned idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((unsigned)(HD >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
-            bool ok = mbar_wait(smem_u32(&bars->q_tmem), 0);
-            if (!ok) { atomicOr(status, 32); bars->failed = 1; }
+            // ---- tensor-core issue of S ----------------------------------------------------------------
+            // Issuing one tcgen05.mma occupies its thread for about 100 cycles whatever its size (measured: N = 32,
+            // 64 and 128 alike, 138 at N = 256), so S is formed for two key tiles at once, 16 products of N = 128 with
+            // Q from tensor memory (M 128, B = K of the pair, K-major), and P V is issued by a thread of its own.
             // Operand descriptors differ only in their address field (bits 0..13, the address in 16-byte units; every
-            // operand lies below 256 KB, so adding an offset never carries out of the field): one descriptor per
-            // operand is formed here, and each product adds its offset, a single addition in front of the
-            // instruction.  Twenty products per key tile are issued by this one thread; with the descriptors
-            // assembled anew for each, issuing them took about as long as the tensor cores need to run them.
-            const uint64_t k_desc0 = umma_desc(smem_u32(sKV), 16, 1024);
-            const uint64_t v_desc0 = umma_desc(smem_u32(sKV + K_BYTES), BN * 128, 1024);
-            const uint64_t p_desc0 = umma_desc(smem_u32(sP), 16, 1024);
-            auto issue_s = [&](int j) {       // S_j = Q K_j^T into S buffer j & 1
-                const uint64_t k_desc = k_desc0 + (uint64_t)(((j % KV_STAGES) * (K_BYTES + V_BYTES)) >> 4);
-                const unsigned acc = tmem + S_COL + (j & 1) * BN;
+            // operand lies below 256 KB, so adding an offset never carries out of the field): one descriptor is
+            // formed once and each product adds its offset.
+            const unsigned idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)((2 * BN) >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
+            const uint64_t k_desc0 = umma_desc(smem_u32(sK), 16, 1024);
+            bool ok = np > 0;
+            if (ok && !mbar_wait(smem_u32(&bars->q_tmem), 0)) { atomicOr(status, 32); bars->failed = 1; ok = false; }
+            for (int J = 0; J < np && ok; ++J) {
+                ok = mbar_wait(smem_u32(&bars->k_full[J % KS]), (J / KS) & 1);
+                if (!ok) { atomicOr(status, 2); bars->failed = 1; break; }
+                // the S columns are free once the softmax warps have taken the pair before into their registers
+                if (J >= 1 && !mbar_wait(smem_u32(&bars->s_free), (J - 1) & 1)) { atomicOr(status, 8); bars->failed = 1; break; }
+                if (has_failed(bars)) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint64_t k_desc = k_desc0 + (uint64_t)(((J % KS) * KP_BYTES) >> 4);
 #pragma unroll
                 for (int d = 0; d < HD / 64; ++d)
 #pragma unroll
                     for (int k = 0; k < 64 / UMMA_K; ++k)
-                        umma_bf16_a_tmem(acc, tmem + Q_COL + d * 32 + k * (UMMA_K / 2),
-                                         k_desc + (uint64_t)((d * (BN * 128) + k * 32) >> 4), idesc_s, (d > 0 || k > 0) ? 1u : 0u);
-                umma_commit(smem_u32(&bars->k_empty[j % KV_STAGES]));
-                umma_commit(smem_u32(&bars->s_ready[j & 1]));
-            };
-            if (nt == 0) ok = false;                      // nothing to multiply (and nobody waits for it)
-            if (ok) {
-                ok = mbar_wait(smem_u32(&bars->k_full[0]), 0);
-                if (!ok) { atomicOr(status, 2); bars->failed = 1; }
+                        umma_bf16_a_tmem(tmem + S_COL, tmem + Q_COL + d * 32 + k * (UMMA_K / 2),
+                                         k_desc + (uint64_t)((d * (2 * BN * 128) + k * 32) >> 4), idesc_s, (d > 0 || k > 0) ? 1u : 0u);
+                umma_commit(smem_u32(&bars->k_empty[J % KS]));
+                umma_commit(smem_u32(&bars->s_ready));
             }
-            if (ok) {
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                issue_s(0);
-            }
+        }
+    } else if (warp == 11) {
+        if (lane == 0) {
+            // ---- tensor-core issue of O += P_j V_j: M 128, N hd, A (P) K-major, B (V) MN-major -----------------
+            const unsigned idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((unsigned)(HD >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
+            const uint64_t v_desc0 = umma_desc(smem_u32(sV), BN * 128, 1024);
+            const uint64_t p_desc0 = umma_desc(smem_u32(sP), 16, 1024);
+            bool ok = true;
             for (int j = 0; j < nt && ok; ++j) {
-                if (j + 1 < nt) {
-                    ok = mbar_wait(smem_u32(&bars->k_full[(j + 1) % KV_STAGES]), ((j + 1) / KV_STAGES) & 1);
-                    if (!ok) { atomicOr(status, 2); bars->failed = 1; break; }
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    issue_s(j + 1);
-                }
                 ok = mbar_wait(smem_u32(&bars->p_ready[j & 1]), (j >> 1) & 1);
                 if (!ok) { atomicOr(status, 8); bars->failed = 1; break; }
                 if (has_failed(bars)) break;
-                ok = mbar_wait(smem_u32(&bars->v_full[j % KV_STAGES]), (j / KV_STAGES) & 1);
+                ok = mbar_wait(smem_u32(&bars->v_full[j % VS]), (j / VS) & 1);
                 if (!ok) { atomicOr(status, 2); bars->failed = 1; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint64_t v_desc = v_desc0 + (uint64_t)(((j % KV_STAGES) * (K_BYTES + V_BYTES)) >> 4);
+                const uint64_t v_desc = v_desc0 + (uint64_t)(((j % VS) * V_BYTES) >> 4);
                 const uint64_t p_desc = p_desc0 + (uint64_t)(((j & 1) * P_BYTES) >> 4);
 #pragma unroll
                 for (int k = 0; k < BN / UMMA_K; ++k)
                     // P: 16 keys further = 32 bytes in the swizzled row.  V (keys x dims, dims contiguous):
-                    // 16 keys further = 16 rows of 128 bytes; the four 64-dim blocks are BN*128 bytes apart.
+                    // 16 keys further = 16 rows of 128 bytes; the 64-dim blocks are BN*128 bytes apart.
                     umma_bf16(tmem + O_COL, p_desc + (uint64_t)((k * 32) >> 4), v_desc + (uint64_t)((k * UMMA_K * 128) >> 4),
                               idesc_o, (j > 0 || k > 0) ? 1u : 0u);
-                umma_commit(smem_u32(&bars->v_empty[j % KV_STAGES]));
+                umma_commit(smem_u32(&bars->v_empty[j % VS]));
                 umma_commit(smem_u32(&bars->pv_done[j & 1]));
             }
         }
@@ -338,8 +339,8 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const unsigned key_span = key_hi >= key_lo ? (unsigned)(key_hi - key_lo) : 0u;
         // FIXED: this group's tiles are group, group + 2, ...; else group 0 takes them all and group 1 none
         for (int j = FIXED ? group : (group == 0 ? 0 : nt); j < nt && alive; j += FIXED ? 2 : 1) {
-            const int bsel = j & 1;
-            if (!mbar_wait_warp(smem_u32(&bars->s_ready[bsel]), (j >> 1) & 1)) {
+            const int bsel = j & 1;                      // half of the pair = S columns = P buffer
+            if (!mbar_wait_warp(smem_u32(&bars->s_ready), (j >> 1) & 1)) {
                 atomicOr(status, 4);
                 bars->failed = 1;
                 alive = false;
@@ -353,6 +354,10 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 tmem_ld32(lane_base + S_COL + bsel * BN, v0);
                 tmem_ld32(lane_base + S_COL + bsel * BN + 32, v1);
                 tmem_ld_wait();
+                // the scores are in registers: the S columns may take the next pair
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&bars->s_free));
 #pragma unroll
                 for (int c = 0; c < 32; ++c) s[c] = __uint_as_float(v0[c]);
 #pragma unroll
@@ -362,7 +367,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             // its argument to +-20 changes nothing: tanh.approx saturates), the scaled score without;
             // either times k2 is the exponent to base 2.  Tiles wholly inside every row's range of keys
             // skip the mask.
-            const int col0 = (jt0 + j * stride) * BN;
+            const int col0 = ((jp0 + (j >> 1) * stride) * 2 + bsel) * BN;
             const bool interior = col0 + BN - 1 <= r0 && col0 + BN - 1 < len && (window <= 0 || col0 > r0 + BM - 1 - window);
             float corr = 1.f;
             bool rescale = false;
@@ -424,9 +429,15 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             const float rs = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
             l_sum = l_sum * corr + rs;
             }
-            // P_j overwrites the buffer that P_{j-2} V_{j-2} read.  That product was issued before S_j and
-            // the commit behind S_j covers everything issued before it, so s_ready[j] already said that it
-            // is done.  (O may only be touched once P_{j-1} V_{j-1} is done: see the rescale below.)
+            // P_j overwrites the buffer that P_{j-2} V_{j-2} read: that product (issued by another thread than S, so
+            // s_ready says nothing about it) has to be done.  Whoever writes P_j has seen every earlier phase of this
+            // barrier, tile by tile.  (O may only be touched once P_{j-1} V_{j-1} is done: see the rescale below.)
+            if (j >= 2 && !mbar_wait_warp(smem_u32(&bars->pv_done[bsel]), ((j - 2) >> 1) & 1)) {
+                atomicOr(status, 64);
+                bars->failed = 1;
+                alive = false;
+                break;
+            }
             {
                 unsigned char* prow = sP + bsel * P_BYTES + rloc * 128;
 #pragma unroll
@@ -505,7 +516,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         if (grp0 && rank == 1) {
             const bool have = alive && nt > 0 && !has_failed(bars);
             if (have) asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            unsigned char* orow = sKV + rloc * (HD * 4);
+            unsigned char* orow = sK + rloc * (HD * 4);
 #pragma unroll 1
             for (int c0 = 0; c0 < HD; c0 += 32) {
                 uint32_t v[32];
@@ -527,7 +538,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         __syncthreads();
         cluster_barrier();                  // both CTAs are past their last product; rank 1's part is laid out
         if (rank == 1 && threadIdx.x == 64) {
-            bulk_copy_to_rank(smem_u32(sKV), smem_u32(sKV), MERGE_O_BYTES, smem_u32(&bars->merge_full), 0);    // to the same place in rank 0
+            bulk_copy_to_rank(smem_u32(sK), smem_u32(sK), MERGE_O_BYTES, smem_u32(&bars->merge_full), 0);    // to the same place in rank 0
             bulk_copy_to_rank(smem_u32(sP), smem_u32(sP), MERGE_ML_BYTES, smem_u32(&bars->merge_full), 0);
         }
         if (grp0 && rank == 0) {
@@ -560,8 +571,8 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             const float l_row = l_sum * w0 + l_other * w1;
             const float inv = l_row > 0.f ? 1.f / l_row : 0.f;
             const float f0 = w0 * inv, f1 = w1 * inv;
-            unsigned char* orow = sQ + rloc * (HD * 2);
-            const unsigned char* prow = sKV + rloc * (HD * 4);
+            unsigned char* orow = sOut + rloc * (HD * 2);
+            const unsigned char* prow = sK + rloc * (HD * 4);
 #pragma unroll 1
             for (int c0 = 0; c0 < HD; c0 += 64) {
                 uint32_t v0[32], v1[32];
@@ -605,7 +616,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             for (int rr = 0; rr < 32; rr += RPI) {
                 const int rl = quarter * 32 + rr + lane / CPR, pos = lane % CPR;
                 if (r0 + rl >= len) continue;
-                const uint4 pk = *reinterpret_cast<const uint4*>(sQ + rl * (HD * 2) + (pos << 4));
+                const uint4 pk = *reinterpret_cast<const uint4*>(sOut + rl * (HD * 2) + (pos << 4));
                 bf16* dst = out + (size_t)(row0 + r0 + rl) * out_stride + (size_t)h * HD + ((pos ^ (rl & (CPR - 1))) << 3);
                 *reinterpret_cast<uint4*>(dst) = pk;
             }
@@ -630,7 +641,7 @@ int launch_attn(const void* qkv, long long total_rows, void* out, long long out_
     if (rc) return rc;
     rc = make_map(&map_kv, qkv, total_rows, width, BN);
     if (rc) return rc;
-    const size_t smem = (size_t)BM * HD * 2 + (size_t)kv_stages(HD) * 2 * BN * HD * 2 + 2 * P_BYTES + sizeof(Barriers) + 1024;
+    const size_t smem = (size_t)k_stages(HD) * 2 * BN * HD * 2 + (size_t)v_stages(HD) * BN * HD * 2 + 2 * P_BYTES + sizeof(Barriers) + 1024;
     auto kern = attn_prefill_tcgen05_kernel<HD, FIXED>;
     static bool configured = false;
     if (!configured) {
