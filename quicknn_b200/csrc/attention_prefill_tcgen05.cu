@@ -2,33 +2,38 @@
 // packed one after another, causal, optional sliding window, optional tanh softcap, grouped
 // query heads.  Formulas: attention.cu (reference: src/backends/vulkan/shaders/attention.comp:18-38).
 //
-// A CTA owns 128 query rows of one sequence and one query head and walks over 64-key tiles:
-//   warp 0 (one lane)  TMA producer: Q once (hd/64 boxes of 128 x 64), then K and V tiles (hd/64 boxes of 64 x 64
-//                      boxes each) into two 2-stage rings (a K stage is free once S has been formed, a V
-//                      stage only after the second product); everything 128-byte swizzled.
-//   warp 1 (one lane)  tensor-core issue:  S_j[128 x 64] = Q K_j^T   (hd/16 tcgen05.mma, K-major operands)
-//                                           O[128 x hd]  += P_j V_j   ( 4 tcgen05.mma, V as MN-major operand)
-//                      S_{j+1} is issued before P_j V_j, so it runs while the softmax of tile j does.
-//   warps 2..5         softmax, one thread per query row (tensor-memory lane = row, so row maxima and
-//                      sums need no shuffles): tcgen05.ld of S, scale, softcap, mask, exp; P_j goes to
-//                      shared memory as bfloat16 in the swizzled K-major layout the next product reads;
-//                      O is rescaled in tensor memory only when a row maximum has grown by more than 8
-//                      since the value the row's exponentials are taken against (the stale maximum
-//                      cancels in the final division; P stays below e^8).
-//   warps 6..9         a second softmax group, with a softcap only (FIXED).  A capped score lies in
-//                      [-cap, cap], so exp(score) can neither overflow nor vanish in float32 and needs no
-//                      running maximum: p = exp(cap tanh(s / cap)) against the fixed reference 0, the same
-//                      softmax (it is invariant under the shift) with nothing carried from tile to tile but
-//                      a row's sum.  The tiles are then independent: warps 2..5 take the even key tiles,
-//                      warps 6..9 the odd ones, two tiles are in the softmax at any time (two warps per
-//                      scheduler hide each other's latencies), no maximum is tracked and O is never rescaled.
-//                      One warp per scheduler with the running maximum took 2350 cycles per tile against
-//                      1700 of tensor work.
-// With few CTAs (one short prompt: 16 query tiles x 8 heads on 148 SMs, the last tile walking 16 times as
-// many keys as the first) the grid is launched as clusters of two: the CTAs of a pair take alternate key
-// tiles of the same query tile; when both are done, rank 1 pushes its (reference maximum, sum, O) into
-// rank 0's shared memory through the cluster's distributed shared memory and rank 0 merges and writes.
-// Tensor memory: S double-buffered (2 x 64 columns), O one column per head element.  All softmax arithmetic is float32.
+// A CTA owns 128 query rows of one sequence and one query head and walks over its keys in tiles of 64, two tiles
+// (a pair) at a time.  Twelve warps:
+//   warp 0  (one lane)  TMA producer of Q (once, into the second stage of the K ring) and of K: a pair of key
+//                       tiles is one operand of 128 rows (hd/64 boxes of 128 x 64), free again once S is formed.
+//   warp 10 (one lane)  TMA producer of V, tiles of 64 keys, free only after O += P V.  128-byte swizzle throughout.
+//   warp 1  (one lane)  issues S[128 x 128] = Q K^T for a pair of tiles: hd/16 tcgen05.mma of N = 128 whose A operand,
+//                       Q, is read from tensor memory.  Issuing one tcgen05.mma occupies its thread for about 100
+//                       cycles whatever its size (N = 32, 64, 128 alike; 138 at N = 256 with A from tensor memory,
+//                       171 with A from shared memory), so products of N = 64 cost their issue, not their work.
+//   warp 11 (one lane)  issues O[128 x hd] += P_j V_j (4 tcgen05.mma of N = hd, V as MN-major operand) for every tile.
+//   warps 2..5          softmax, one thread per query row (tensor-memory lane = row, so row maxima and sums need no
+//                       shuffles): first they copy Q from shared to tensor memory; then per tile tcgen05.ld of S
+//                       (the S columns are handed back as soon as the scores are in registers), scale, softcap,
+//                       mask, exp; P_j goes to shared memory as bfloat16 in the swizzled K-major layout the next
+//                       product reads.  Without a softcap: a running maximum, and O is rescaled in tensor memory only
+//                       when a row maximum has grown by more than 8 since the value the row's exponentials are taken
+//                       against (the stale maximum cancels in the final division; P stays below e^8).
+//   warps 6..9          a second softmax group, with a softcap only (FIXED).  A capped score lies in [-cap, cap], so
+//                       exp(score) can neither overflow nor vanish in float32 and needs no running maximum:
+//                       p = exp(cap tanh(s / cap)) against the fixed reference 0, the same softmax (it is invariant
+//                       under the shift) with nothing carried from tile to tile but a row's sum.  The tiles are then
+//                       independent: warps 2..5 take the lower tile of each pair, warps 6..9 the upper one, two tiles
+//                       are in the softmax at any time, no maximum is tracked and O is never rescaled.
+// What set the pace, in the order in which it was found (clock64 around the waits of each role): the softmax chain of
+// one warp per scheduler (2350 cycles per tile); the issue of 16 + 4 products per tile by one thread (1850); shared
+// memory bandwidth (Q, K, V, P and the TMA writes: 224 KB per tile, 160 with Q in tensor memory).  One prompt of 8192
+// tokens, 8 heads of 256: 316 us with the running maximum and S of N = 64, 297 us with the fixed reference, two softmax
+// groups and Q in tensor memory, 242 us (1.13 PFLOP/s) with S of N = 128 and P V issued by a thread of its own.
+// With few CTAs the grid may be launched as clusters of two (the policy is in launch_attn): the CTAs of a pair take
+// alternate pairs of key tiles of the same query tile; when both are done, rank 1 pushes its (reference maximum, sum,
+// O) into rank 0's shared memory through the cluster's distributed shared memory and rank 0 merges and writes.
+// Tensor memory: S 128 columns, O one column per head element, Q hd / 2 columns.  All softmax arithmetic is float32.
 // Keys of other sequences that a tile drags in are masked; rows beyond the sequence are never stored.
 // Every mbarrier wait is bounded in time; on expiry a status word is set and the CTA winds down.
 #include "common.cuh"
@@ -105,7 +110,7 @@ __global__ void __launch_bounds__(THREADS)
 attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
                             bf16* __restrict__ out, size_t out_stride, const int* __restrict__ seq_row0,
                             const int* __restrict__ seq_len, int nq, int nkv, float scale, float cap, int window,
-                            int* __restrict__ status, int split) {
+                            int* __restrict__ status, int split_levels) {
     constexpr int KS = k_stages(HD), VS = v_stages(HD);
     constexpr int Q_BYTES = BM * HD * 2;                             // HD / 64 blocks of [128 x 64]
     constexpr int KP_BYTES = 2 * BN * HD * 2;                        // a pair of key tiles: HD / 64 blocks of [128 x 64]
@@ -129,13 +134,17 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 
     // grid (heads [x 2 ranks], sequences, query tiles): the query tile is the slowest index, so that CTAs are
     // handed out from the heaviest tiles of all heads down to the lightest
-    const int b = blockIdx.y, h = split ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+    const int b = blockIdx.y, h = split_levels ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
     const int len = seq_len[b];
     const int ntiles_q = (len + BM - 1) / BM;
-    // split: blockIdx.x = 2 * head + rank in the pair (both CTAs of a pair return here or neither)
-    const int rank = split ? (int)(blockIdx.x & 1) : 0, stride = split ? 2 : 1;
     const int qx = (int)blockIdx.z;
     if (qx >= ntiles_q) return;                                      // before any barrier or tensor memory
+    // split_levels > 0: the grid is clusters of two, blockIdx.x = 2 * head + rank.  The heaviest query tiles of a
+    // sequence (the split_levels last ones) are shared by the pair; of every other tile rank 0 walks all keys and
+    // rank 1 leaves at once (both CTAs of a pair agree on this, and an unshared tile uses nothing of the cluster).
+    const bool split = qx < split_levels;
+    if (split_levels && !split && (blockIdx.x & 1)) return;
+    const int rank = split ? (int)(blockIdx.x & 1) : 0, stride = split ? 2 : 1;
     const int qt = ntiles_q - 1 - qx;                                // the longest rows first
     const int r0 = qt * BM, row0 = seq_row0[b];
     const int kh = h / (nq / nkv);
@@ -658,20 +667,23 @@ int launch_attn(const void* qkv, long long total_rows, void* out, long long out_
             sm_count = 148;
     }
     // Few CTAs with long key walks: pairs of CTAs share a query tile's keys (see the head of this file).  A pair
-    // pays for the hand-over and doubles the CTAs, so it needs enough key tiles in the heaviest query tile: 12
-    // when the pairs still fit the device at once, 24 when they need a second round.  With more CTAs than SMs
-    // the heavy ones are started first and the rest fills in behind them.  Measured inside a CUDA graph, head
-    // size 256, pairs against single CTAs: 8 heads, 1024 tokens 22.0 / 25.5 us, 2048 tokens 42.7 / 46.6 us;
-    // 4 heads, 2048 tokens 31.9 / 45.7 us; but 8 heads, 512 tokens 16.6 / 15.3 us; 16 heads, 1024 tokens
-    // 33.9 / 26.5 us; 8 heads, 2048 tokens with a window of 512: 37.0 / 20.0 us.
+    // pays for the cluster launch and the hand-over; the policy and its measurements are below.
     static int split_ok = -1;                      // the device holds a pair of these CTAs (asked once)
     const long long singles = (long long)ntq * B * nq;
     const int reach = window > 0 ? (max_len < window + BM - 1 ? max_len : window + BM - 1) : max_len;
     const int key_tiles = (reach + BN - 1) / BN;   // of the heaviest query tile
     static int no_split = -1;                       // QNN_ATTN_NO_SPLIT, read once
     if (no_split < 0) no_split = getenv("QNN_ATTN_NO_SPLIT") ? 1 : 0;
-    const bool want_split = ntq >= 2 && !no_split &&
-                            ((2 * singles <= sm_count && key_tiles >= 12) || (singles <= sm_count && key_tiles >= 24));
+    // How many of the heaviest query tiles (counted from a sequence's last) are shared by pairs: all of them, when
+    // both CTAs of every pair fit the device at once and the heaviest tile walks at least 12 key tiles; else none.
+    // Measured inside a CUDA graph, head size 256, one prompt, pairs against single CTAs: 4 heads, 2048 tokens 28.6 /
+    // 36.0 us; 2 heads, 2048 tokens 27.6 / 36.0; 4 heads, 1024 tokens 20.3 / 21.4.  With 8 heads and 2048 tokens (128
+    // tiles on 148 SMs) pairs for every tile need a second round of CTAs (41.0 us), pairs for the two heaviest levels
+    // only, so that everything still starts together, took 41.7 us, single CTAs 37.7 us: the cluster launch and the
+    // hand-over cost more than the shorter key walk saves, so such a grid runs single CTAs.
+    int levels = 0;
+    if (ntq >= 2 && !no_split && 2 * singles <= sm_count && key_tiles >= 12) levels = ntq;
+    const bool want_split = levels > 0;
     cudaLaunchConfig_t cfg = {};
     cfg.blockDim = dim3(THREADS);
     cfg.dynamicSmemBytes = smem;
@@ -693,7 +705,7 @@ int launch_attn(const void* qkv, long long total_rows, void* out, long long out_
         if (!split_ok) (void)cudaGetLastError();
         cfg.attrs = attr;
     }
-    const int split = (want_split && split_ok == 1) ? 1 : 0;
+    const int split = (want_split && split_ok == 1) ? levels : 0;
     cfg.gridDim = dim3((unsigned)(split ? 2 * nq : nq), B, ntq);
     const long long ctas = (long long)cfg.gridDim.x * B * ntq;
     const bool pdl = qnn::pdl_enabled() && ctas <= qnn::pdl_max_grid();
