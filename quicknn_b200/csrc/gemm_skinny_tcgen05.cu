@@ -31,6 +31,7 @@ using namespace qnn;
 #define EPI_NONE 0
 #define EPI_SOFTCAP 1
 #define EPI_GATED 2
+#define EPI_ARGMAX 3      // softcap, then only the best (value, column) of the CTA's 128 columns per row: cand[row][tile]
 
 namespace {
 
@@ -66,7 +67,7 @@ template <int EPI>
 __global__ void __launch_bounds__(THREADS)
 gemm_skinny_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                            void* __restrict__ C, int M, int N, int K, int KS, int NM, int stages, int tmem_cols,
-                           float cap, int act, int* __restrict__ status) {
+                           float cap, int act, int* __restrict__ status, int* __restrict__ err) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const int x_bytes = NM * BK * 2, stage_bytes = W_BYTES + x_bytes;
@@ -243,7 +244,28 @@ gemm_skinny_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __gr
             atomicOr(status, 8);
             arrived = false;
         }
-        const int mgroups = (min(M - h, hcols) + 3) / 4;
+        if (EPI == EPI_ARGMAX) {
+            // The head of a greedy step for 9 to 128 rows (always a tile of its own: KS = 1): a thread per activation
+            // row walks the tile's 128 weight rows in ascending order (the lowest column wins a tie), the cap is
+            // monotonic and is applied to the winner only; NaN and Inf set the error word and lose.  The logits are
+            // not written: one (value, column) per row and tile.
+            const int m = h + (int)threadIdx.x;
+            if ((int)threadIdx.x < hcols && m < M) {
+                float best = -3.402823466e38f;
+                int best_n = -1;
+                bool bad = false;
+                const int rows = min(OUT_ROWS, Nout - n0);
+                for (int rr = 0; rr < rows; ++rr) {
+                    const float v = recv[(size_t)rr * PL + threadIdx.x];
+                    if (!(fabsf(v) <= 3.402823466e38f)) { bad = true; continue; }
+                    if (v > best) { best = v; best_n = n0 + rr; }
+                }
+                if (bad && err != nullptr) atomicOr(err, 1);
+                reinterpret_cast<float2*>(C)[(size_t)m * gridDim.x + tile] =
+                    make_float2(best_n >= 0 ? softcap(best, cap) : -3.402823466e38f, __uint_as_float(best_n >= 0 ? (unsigned)best_n : 0xffffffffu));
+            }
+        }
+        const int mgroups = EPI == EPI_ARGMAX ? 0 : (min(M - h, hcols) + 3) / 4;
         for (int idx = threadIdx.x; idx < rpr * mgroups && arrived; idx += THREADS) {
             const int rr = idx % rpr, m4 = (idx / rpr) * 4;
             float4 acc = make_float4(0.f, 0.f, 0.f, 0.f), up = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -297,7 +319,7 @@ gemm_skinny_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __gr
 
 template <int EPI>
 int launch(const CUtensorMap& map_x, const CUtensorMap& map_w, void* C, int M, int N, int K, int KS, int NM, int stages,
-           float cap, int act, int* status, unsigned tiles, cudaStream_t st) {
+           float cap, int act, int* status, unsigned tiles, cudaStream_t st, int* err = nullptr) {
     auto kern = gemm_skinny_tcgen05_kernel<EPI>;
     const size_t smem = (size_t)stages * (W_BYTES + NM * BK * 2) + (KS > 1 ? (size_t)BW * ((NM < RECV_COLS ? NM : RECV_COLS) + 4) * 4 : 0) + sizeof(Barriers) + 1024;
     static bool configured = false;
@@ -322,7 +344,7 @@ int launch(const CUtensorMap& map_x, const CUtensorMap& map_w, void* C, int M, i
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = (qnn::pdl_enabled() && (long long)tiles * KS <= qnn::pdl_max_grid()) ? 2 : 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, map_x, map_w, C, M, N, K, KS, NM, stages, tmem_cols, cap, act, status);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, map_x, map_w, C, M, N, K, KS, NM, stages, tmem_cols, cap, act, status, err);
     return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }
 
@@ -331,8 +353,8 @@ int launch(const CUtensorMap& map_x, const CUtensorMap& map_w, void* C, int M, i
 // C = X W^T for M <= 128 rows.  epi 0: bfloat16 out; 1: softcap, float32 out; 2: gated (W = [gate; up],
 // C is [M, N/2], bfloat16).  `status` as in qnn_gemm_tcgen05.  Returns QNN_ERR_UNSUPPORTED for sizes it
 // does not take.
-QNN_API int qnn_gemm_skinny_tcgen05(const void* A, const void* B, void* C, int M, int N, int K, int epi, float cap,
-                                    int act, int* status, cudaStream_t st) {
+static int skinny_tcgen05(const void* A, const void* B, void* C, int M, int N, int K, int epi, float cap, int act,
+                         int* status, int* err, cudaStream_t st) {
     if (M <= 0 || N <= 0) return 0;
     if (M > 128 || K <= 0 || (K & 7) || ((((uintptr_t)A | (uintptr_t)B | (uintptr_t)C) & 15) != 0)) return QNN_ERR_UNSUPPORTED;
     if (epi == EPI_GATED && (N & 1)) return QNN_ERR_ARGUMENT;
@@ -410,10 +432,30 @@ QNN_API int qnn_gemm_skinny_tcgen05(const void* A, const void* B, void* C, int M
     }
     if (stages > MAX_STAGES || (long long)stages * stage_bytes + recv_bytes + (long long)sizeof(Barriers) + 1024 > 227 * 1024)
         return QNN_ERR_UNSUPPORTED;
+    if (epi == EPI_ARGMAX) {
+        if (KS != 1) return QNN_ERR_UNSUPPORTED;        // so few columns that tiles share K: the caller writes logits
+        return launch<EPI_ARGMAX>(map_x, map_w, C, M, N, K, KS, NM, stages, cap, act, status, (unsigned)tiles, st, err);
+    }
     switch (epi) {
         case EPI_NONE: return launch<EPI_NONE>(map_x, map_w, C, M, N, K, KS, NM, stages, cap, act, status, (unsigned)tiles, st);
         case EPI_SOFTCAP: return launch<EPI_SOFTCAP>(map_x, map_w, C, M, N, K, KS, NM, stages, cap, act, status, (unsigned)tiles, st);
         case EPI_GATED: return launch<EPI_GATED>(map_x, map_w, C, M, N, K, KS, NM, stages, cap, act, status, (unsigned)tiles, st);
     }
     return QNN_ERR_ARGUMENT;
+}
+
+QNN_API int qnn_gemm_skinny_tcgen05(const void* A, const void* B, void* C, int M, int N, int K, int epi, float cap,
+                                    int act, int* status, cudaStream_t st) {
+    if (epi != EPI_NONE && epi != EPI_SOFTCAP && epi != EPI_GATED) return QNN_ERR_ARGUMENT;
+    return skinny_tcgen05(A, B, C, M, N, K, epi, cap, act, status, nullptr, st);
+}
+
+// The head of a greedy step for up to 128 rows: cand[m][t] = the best (softcapped value, column) among the 128
+// columns of W that tile t covers; ceil(N / 128) candidates per row, merged by qnn_sample_candidates.  err (may be
+// null) gets bit 0 set if a logit is NaN or Inf.  QNN_ERR_UNSUPPORTED for a matrix of so few rows that its tiles
+// would share K.
+QNN_API int qnn_gemm_skinny_tcgen05_argmax(const void* A, const void* B, void* cand, int M, int N, int K, float cap,
+                                           int* err, int* status, cudaStream_t st) {
+    if ((uintptr_t)cand & 7) return QNN_ERR_ARGUMENT;
+    return skinny_tcgen05(A, B, cand, M, N, K, EPI_ARGMAX, cap, 0, status, err, st);
 }

@@ -38,6 +38,7 @@ _SIGNATURES: Dict[str, list] = {
     "qnn_gemm_tcgen05": [c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_int, c_vp, c_vp],
     "qnn_gemm_tcgen05_2cta": [c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_int, c_vp, c_vp],
     "qnn_gemm_skinny_tcgen05": [c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_float, c_int, c_vp, c_vp],
+    "qnn_gemm_skinny_tcgen05_argmax": [c_vp, c_vp, c_vp, c_int, c_int, c_int, c_float, c_vp, c_vp, c_vp],
     "qnn_attn_decode": [c_vp, c_ll, c_int, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_vp, c_vp, c_int, c_int,
                         c_int, c_int, c_float, c_float, c_int, c_vp, c_vp, c_int, c_vp, c_ll, c_vp],
     "qnn_attn_extend": [c_vp, c_vp, c_vp, c_ll, c_int, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_vp, c_ll, c_vp, c_vp,

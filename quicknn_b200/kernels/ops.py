@@ -606,23 +606,25 @@ def sample(logits: torch.Tensor, top_k: int, temperature: float, top_p: float, p
 
 
 def head_argmax_fusable(x: torch.Tensor, w: torch.Tensor) -> bool:
-    """Whether ``head_argmax`` takes this product: bfloat16 on both sides and so few rows that the
-    mma.sync small-M kernel would multiply them anyway."""
+    """Whether ``head_argmax`` takes this product: bfloat16 on both sides, an inner size in whole 16-byte
+    vectors, and at most 128 rows."""
     M, K = x.shape
-    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and M <= SKINNY_MAX_ROWS and K % 8 == 0
-            and not _takes_skinny_tcgen05(M, w.shape[0], K))
+    return x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and K % 8 == 0 and 1 <= M <= 128
 
 
 def head_candidates(vocab: int) -> int:
-    """Candidates per row that ``head_argmax`` writes (one per 16 output columns)."""
+    """The most candidates per row that ``head_argmax`` writes (one per 16 output columns)."""
     return (vocab + 15) // 16
 
 
 def head_argmax(x: torch.Tensor, w: torch.Tensor, cap: Optional[float], cand: torch.Tensor,
-                error_flag: Optional[torch.Tensor]) -> torch.Tensor:
-    """softcap(x w^T) reduced in the product's epilogue to the best (value, id) of every 16 output
+                error_flag: Optional[torch.Tensor]) -> Optional[int]:
+    """softcap(x w^T) reduced in the product's epilogue to the best (value, id) of every group of output
     columns: ``cand`` (float32, at least rows * head_candidates(vocab) * 2) is filled, the logits are not
-    written.  NaN or Inf sets bit 0 of ``error_flag``."""
+    written.  The product is the one that ``linear`` would run for these sizes: the mma.sync small-M kernel
+    (a candidate per 16 columns) or, from 9 rows on against a big matrix, the tcgen05 kernel (a candidate
+    per 128 columns).  Returns the number of candidates per row, or None when the sizes are refused (the
+    caller then forms the logits).  NaN or Inf sets bit 0 of ``error_flag``."""
     _req(x, "x", torch.bfloat16, 2)
     _req(w, "w", torch.bfloat16, 2)
     _req(cand, "cand", torch.float32)
@@ -633,9 +635,17 @@ def head_argmax(x: torch.Tensor, w: torch.Tensor, cap: Optional[float], cand: to
     if cand.numel() < M * head_candidates(N) * 2:
         raise ValueError("head_argmax: the candidate buffer is too small")
     L = _lib.load()
+    if _takes_skinny_tcgen05(M, N, K):
+        code = L.qnn_gemm_skinny_tcgen05_argmax(_p(x), _p(w), _p(cand), M, N, K, float(cap or 0.0), _p(error_flag),
+                                                _p(_status_word(x.device)), _stream())
+        if code != _lib.ERR_UNSUPPORTED:
+            _lib.check(code, "gemm_skinny_tcgen05_argmax")
+            return (N + 127) // 128
+    if M > SKINNY_MAX_ROWS:
+        return None
     _lib.check(L.qnn_skinny_argmax(_p(x), _p(w), _p(cand), M, N, K, float(cap or 0.0), _p(error_flag), _stream()),
                "skinny_argmax")
-    return cand
+    return (N + 15) // 16
 
 
 def sample_candidates(cand: torch.Tensor, rows: int, ncand: int, vocab: int, top_k: int, temperature: float,

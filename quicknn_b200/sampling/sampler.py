@@ -81,9 +81,11 @@ class Sampler:
             return None
         R = hidden.shape[0]
         cand = self.scratch.view(torch.float32)
-        ops.head_argmax(hidden, weight, cap, cand, self.flag)
-        ops.sample_candidates(cand, R, ops.head_candidates(self.vocab), self.vocab, 1, 0.0, self.options.top_p, self.rng,
-                              None, None, self.out, self.flag, ops.status_words(self.device)[0:1])
+        ncand = ops.head_argmax(hidden, weight, cap, cand, self.flag)
+        if ncand is None:
+            return None
+        ops.sample_candidates(cand, R, ncand, self.vocab, 1, 0.0, self.options.top_p, self.rng, None, None, self.out,
+                              self.flag, ops.status_words(self.device)[0:1])
         return self.out[:R]
 
     def read(self, tokens: torch.Tensor) -> np.ndarray:

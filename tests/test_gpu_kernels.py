@@ -653,33 +653,34 @@ def test_sampling_follows_the_plain_sampler(ops, V):
     assert int(flag) == 0
 
 
-@pytest.mark.parametrize("M,V,K", [(1, 256000, 2304), (8, 256000, 2304), (5, 1000, 96), (20, 1000, 200), (30, 3001, 64)])
+@pytest.mark.parametrize("M,V,K", [(1, 256000, 2304), (8, 256000, 2304), (5, 1000, 96), (20, 1000, 200), (30, 3001, 64),
+                                   (12, 256000, 2304), (40, 3001, 64), (100, 30000, 256), (64, 20000, 128)])
 def test_head_with_the_arg_max_in_its_epilogue(ops, M, V, K):
-    """The greedy head: only the best (value, id) of every 16 columns leaves the product.  The chosen ids
-    are those of the largest logit as the ordinary head product writes it, the lowest id on ties; a
-    vocabulary that is no multiple of 16; NaN sets the error word."""
+    """The greedy head: only the best (value, id) of every group of columns leaves the product (16 columns in
+    the mma.sync kernel, 128 in the tcgen05 kernel that takes 9 rows and more against a big matrix).  The chosen
+    ids are those of the largest logit as the ordinary head product writes it, the lowest id on ties; a
+    vocabulary that is no multiple of the group; more than 64 rows (two rounds); NaN sets the error word."""
     g = torch.Generator(device=DEV)
     g.manual_seed(M * 1000 + K)
     x = torch.randn((M, K), generator=g, device=DEV).to(torch.bfloat16)
     w = (torch.randn((V, K), generator=g, device=DEV) * 0.05).to(torch.bfloat16)
-    w[V - 3] = w[7]                                   # two columns with the same logit in every row
     big = (x[0].float() / x[0].float().norm()).to(torch.bfloat16)
-    w[7] = big
-    w[V - 3] = big                                    # ... which is row 0's largest: id 7 must win
+    w[7] = big                                        # two columns with the same logit in every row,
+    w[V - 3] = big                                    # row 0's largest: id 7 must win
     logits = ops.linear(x, w, epilogue=ops.EPI_SOFTCAP, cap=30.0).cpu().numpy()
     want = [P.argmax_lowest(r) for r in logits]
     assert want[0] == 7
     flag = torch.zeros(1, dtype=torch.int32, device=DEV)
-    ncand = ops.head_candidates(V)
-    cand = torch.empty(M * ncand * 2, device=DEV)
+    cand = torch.full((M * ops.head_candidates(V) * 2,), float("nan"), device=DEV)
     assert ops.head_argmax_fusable(x, w)
-    ops.head_argmax(x, w, 30.0, cand, flag)
-    c = cand.cpu().numpy().reshape(M, ncand, 2)
+    ncand = ops.head_argmax(x, w, 30.0, cand, flag)
+    group = {(V + 15) // 16: 16, (V + 127) // 128: 128}[ncand]
+    c = cand[:M * ncand * 2].cpu().numpy().reshape(M, ncand, 2)
     ids = c[:, :, 1].copy().view(np.uint32)
-    for m in range(M):                                # every candidate is the best of its 16 columns
+    for m in range(M):                                # every candidate is the best of its group of columns
         for blk in (0, ncand // 2, ncand - 1):
-            cols = logits[m, blk * 16:(blk + 1) * 16]
-            assert c[m, blk, 0] == cols.max() and ids[m, blk] == blk * 16 + int(np.argmax(cols))
+            cols = logits[m, blk * group:(blk + 1) * group]
+            assert c[m, blk, 0] == cols.max() and ids[m, blk] == blk * group + int(np.argmax(cols)), (m, blk)
     out = torch.zeros(M, dtype=torch.int32, device=DEV)
     rng_state = torch.ones(M, dtype=torch.int32, device=DEV)
     ops.sample_candidates(cand, M, ncand, V, 1, 0.0, 1.0, rng_state, None, None, out, flag)
@@ -687,6 +688,7 @@ def test_head_with_the_arg_max_in_its_epilogue(ops, M, V, K):
     x[M - 1, 3] = float("nan")
     ops.head_argmax(x, w, 30.0, cand, flag)
     assert int(flag) == 1
+    ops.raise_on_status(DEV)
 
 
 def test_sampling_flags_non_finite_logits_and_marks_prompts(ops):
