@@ -512,19 +512,46 @@ __global__ void attn_combine_kernel(const float* __restrict__ part_o, const floa
     float* coef = comb + max((size_t)G * hd, (size_t)n_splits);
     const int b = blockIdx.x / nq, h = blockIdx.x % nq;
     const size_t pbase = ((size_t)b * nq + h) * n_splits;
+    // A thread's first partial outputs do not depend on the ranges' weights: they are asked for first, and
+    // the (maximum, sum) pairs right after, so that the kernel waits for global memory once.
+    constexpr int AHEAD = 4;
+    const int g = threadIdx.x / lpg, c = (threadIdx.x % lpg) * 4;
+    float4 first[AHEAD];
+#pragma unroll
+    for (int i = 0; i < AHEAD; ++i) {
+        const int s = g + i * G;
+        first[i] = (g < G && s < n_splits) ? *reinterpret_cast<const float4*>(part_o + (pbase + s) * hd + c)
+                                           : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
     if (threadIdx.x < 32) {
-        // every (maximum, sum) pair is loaded once, all loads of a lane in flight together; the weighted sums
-        // go through shared memory so that one thread can add them in ascending order without waiting for
-        // global memory at every term
+        // every (maximum, sum) pair is loaded once (up to 128 ranges stay in registers between the two passes);
+        // the weighted sums go through shared memory so that one thread can add them in ascending order
+        // without waiting for global memory at every term
         float* wl = comb;                                   // [n_splits], before the partial sums take the space
+        float2 ml[4];
         float mm = -CUDART_INF_F;
-        for (int s = threadIdx.x; s < n_splits; s += 32) mm = fmaxf(mm, part_ml[(pbase + s) * 2]);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int s = threadIdx.x + i * 32;
+            ml[i] = s < n_splits ? *reinterpret_cast<const float2*>(part_ml + (pbase + s) * 2) : make_float2(-CUDART_INF_F, 0.f);
+            mm = fmaxf(mm, ml[i].x);
+        }
+        for (int s = threadIdx.x + 128; s < n_splits; s += 32) mm = fmaxf(mm, part_ml[(pbase + s) * 2]);
         mm = warp_max(mm);
-        for (int s = threadIdx.x; s < n_splits; s += 32) {
-            const float2 ml = *reinterpret_cast<const float2*>(part_ml + (pbase + s) * 2);
-            const float w = (ml.x == -CUDART_INF_F) ? 0.f : expf(ml.x - mm);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int s = threadIdx.x + i * 32;
+            if (s < n_splits) {
+                const float w = (ml[i].x == -CUDART_INF_F) ? 0.f : expf(ml[i].x - mm);
+                coef[s] = w;
+                wl[s] = w * ml[i].y;
+            }
+        }
+        for (int s = threadIdx.x + 128; s < n_splits; s += 32) {
+            const float2 v = *reinterpret_cast<const float2*>(part_ml + (pbase + s) * 2);
+            const float w = (v.x == -CUDART_INF_F) ? 0.f : expf(v.x - mm);
             coef[s] = w;
-            wl[s] = w * ml.y;
+            wl[s] = w * v.y;
         }
         __syncwarp();
         if (threadIdx.x == 0) {
@@ -534,11 +561,21 @@ __global__ void attn_combine_kernel(const float* __restrict__ part_o, const floa
         }
     }
     __syncthreads();
-    const int g = threadIdx.x / lpg, c = (threadIdx.x % lpg) * 4;
     if (g < G) {
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int i = 0; i < AHEAD; ++i) {
+            const int s = g + i * G;
+            if (s < n_splits) {
+                const float w = coef[s];
+                acc.x += w * first[i].x;
+                acc.y += w * first[i].y;
+                acc.z += w * first[i].z;
+                acc.w += w * first[i].w;
+            }
+        }
 #pragma unroll 4
-        for (int s = g; s < n_splits; s += G) {
+        for (int s = g + AHEAD * G; s < n_splits; s += G) {
             const float w = coef[s];
             const float4 v = *reinterpret_cast<const float4*>(part_o + (pbase + s) * hd + c);
             acc.x += w * v.x;
