@@ -22,168 +22,9 @@
 //   prefill: one warp per (token, kv head, head tile); K and V come from this step's own
 //            packed projections (rows of the qkv buffer), which is what makes a prompt
 //            longer than the window independent of the ring in the cache.
-#include "common.cuh"
-#include <math_constants.h>
-
-using namespace qnn;
+#include "attention_generic.cuh"
 
 namespace {
-
-// expf in the float32 path, the fast exponential where the data are bfloat16 anyway
-template <typename T> __device__ __forceinline__ float fexp(float x);
-template <> __device__ __forceinline__ float fexp<float>(float x) { return expf(x); }
-template <> __device__ __forceinline__ float fexp<bf16>(float x) { return __expf(x); }
-
-// softcap with the exact tanhf in the float32 path and the hardware tanh where the data are
-// bfloat16 (its error, about 2^-11, is below bfloat16's own rounding)
-template <typename T> __device__ __forceinline__ float softcap_t(float x, float cap);
-template <> __device__ __forceinline__ float softcap_t<float>(float x, float cap) { return softcap(x, cap); }
-template <> __device__ __forceinline__ float softcap_t<bf16>(float x, float cap) {
-    if (cap > 0.f) {
-        float t = fminf(fmaxf(__fdividef(x, cap), -20.f), 20.f), r;
-        asm("tanh.approx.f32 %0, %1;" : "=f"(r) : "f"(t));
-        return cap * r;
-    }
-    return x;
-}
-
-template <typename T>
-struct PagedKV {
-    const T* k_pool;
-    const T* v_pool;
-    const int* page_row;  // page table row of this sequence
-    int page_size, nkv, hd, ring, kh;
-    __device__ __forceinline__ size_t off(int p) const {
-        const int r = ring > 0 ? p % ring : p;
-        const int page = page_row[r / page_size];
-        return (((size_t)page * nkv + kh) * page_size + (r % page_size)) * hd;
-    }
-    __device__ __forceinline__ const T* k(int p) const { return k_pool + off(p); }
-    __device__ __forceinline__ const T* v(int p) const { return v_pool + off(p); }
-};
-
-template <typename T>
-struct PackedKV {
-    const T* kbase;  // already offset to this kv head
-    const T* vbase;
-    size_t row_stride;
-    int row0;
-    __device__ __forceinline__ const T* k(int p) const { return kbase + (size_t)(row0 + p) * row_stride; }
-    __device__ __forceinline__ const T* v(int p) const { return vbase + (size_t)(row0 + p) * row_stride; }
-};
-
-// One warp over the keys [begin, end), taking keys begin + first + i*stride + group.
-template <typename T, int CPL, int GT, typename KV>
-__device__ __forceinline__ void attend_range(const float (&q)[GT][CPL][Vec16<T>::N], const KV& kv, int begin, int end,
-                                             int first, int stride, int LPT, int chunks, float cap,
-                                             float (&m)[GT], float (&l)[GT], float (&o)[GT][CPL][Vec16<T>::N]) {
-    constexpr int VEC = Vec16<T>::N;
-    const int lane = threadIdx.x & 31;
-    const int sl = lane % LPT, ti = lane / LPT;
-    for (int base = begin + first; base < end; base += stride) {
-        const int p = base + ti;
-        const bool valid = p < end;
-        float s[GT];
-#pragma unroll
-        for (int g = 0; g < GT; ++g) s[g] = 0.f;
-        float vv[CPL][VEC];
-        if (valid) {
-            const T* kp = kv.k(p);
-            const T* vp = kv.v(p);
-            Vec16<T> kvec[CPL], vvec[CPL];
-#pragma unroll
-            for (int i = 0; i < CPL; ++i) {
-                const int c = sl + i * LPT;
-                if (c < chunks) {
-                    kvec[i].load(kp + c * VEC);
-                    vvec[i].load(vp + c * VEC);
-                }
-            }
-#pragma unroll
-            for (int i = 0; i < CPL; ++i) {
-                const int c = sl + i * LPT;
-                if (c < chunks) {
-                    float kk[VEC];
-                    kvec[i].unpack(kk);
-                    vvec[i].unpack(vv[i]);
-#pragma unroll
-                    for (int g = 0; g < GT; ++g)
-#pragma unroll
-                        for (int e = 0; e < VEC; ++e) s[g] = fmaf(q[g][i][e], kk[e], s[g]);
-                } else {
-#pragma unroll
-                    for (int e = 0; e < VEC; ++e) vv[i][e] = 0.f;
-                }
-            }
-        }
-#pragma unroll
-        for (int g = 0; g < GT; ++g)
-            for (int off = LPT >> 1; off > 0; off >>= 1) s[g] += __shfl_xor_sync(0xffffffffu, s[g], off);
-        if (valid) {
-#pragma unroll
-            for (int g = 0; g < GT; ++g) {
-                const float sc = softcap(s[g], cap);
-                const float mn = fmaxf(m[g], sc);
-                const float corr = fexp<T>(m[g] - mn);  // m = -inf on the first key gives 0
-                const float w = fexp<T>(sc - mn);
-                l[g] = l[g] * corr + w;
-#pragma unroll
-                for (int i = 0; i < CPL; ++i)
-#pragma unroll
-                    for (int e = 0; e < VEC; ++e) o[g][i][e] = o[g][i][e] * corr + w * vv[i][e];
-                m[g] = mn;
-            }
-        }
-    }
-}
-
-// Merge the states of the 32/LPT lane groups of a warp; afterwards every lane holds the
-// merged state for its own chunks.
-template <int CPL, int GT, int VEC>
-__device__ __forceinline__ void merge_groups(int LPT, float (&m)[GT], float (&l)[GT], float (&o)[GT][CPL][VEC]) {
-    for (int off = LPT; off < 32; off <<= 1) {
-#pragma unroll
-        for (int g = 0; g < GT; ++g) {
-            const float mo = __shfl_xor_sync(0xffffffffu, m[g], off);
-            const float lo = __shfl_xor_sync(0xffffffffu, l[g], off);
-            const float mn = fmaxf(m[g], mo);
-            const float ca = (m[g] == -CUDART_INF_F) ? 0.f : expf(m[g] - mn);
-            const float cb = (mo == -CUDART_INF_F) ? 0.f : expf(mo - mn);
-            l[g] = l[g] * ca + lo * cb;
-#pragma unroll
-            for (int i = 0; i < CPL; ++i)
-#pragma unroll
-                for (int e = 0; e < VEC; ++e) {
-                    const float oo = __shfl_xor_sync(0xffffffffu, o[g][i][e], off);
-                    o[g][i][e] = o[g][i][e] * ca + oo * cb;
-                }
-            m[g] = mn;
-        }
-    }
-}
-
-template <typename T, int CPL, int GT>
-__device__ __forceinline__ void load_query(const T* qrow0, int hd, int G, int gt0, int LPT, int chunks, float scale,
-                                           float (&q)[GT][CPL][Vec16<T>::N]) {
-    constexpr int VEC = Vec16<T>::N;
-    const int sl = (threadIdx.x & 31) % LPT;
-#pragma unroll
-    for (int g = 0; g < GT; ++g)
-#pragma unroll
-        for (int i = 0; i < CPL; ++i) {
-            const int c = sl + i * LPT;
-            if (gt0 + g < G && c < chunks) {
-                Vec16<T> v;
-                v.load(qrow0 + (size_t)(gt0 + g) * hd + c * VEC);
-                v.unpack(q[g][i]);
-#pragma unroll
-                for (int e = 0; e < VEC; ++e) q[g][i][e] *= scale;
-            } else {
-#pragma unroll
-                for (int e = 0; e < VEC; ++e) q[g][i][e] = 0.f;
-            }
-        }
-}
 
 constexpr int DEC_WARPS = 4;
 
@@ -594,177 +435,7 @@ __global__ void attn_combine_kernel(const float* __restrict__ part_o, const floa
     }
 }
 
-constexpr int PRE_WARPS = 4;
-
-// After the lane groups of a warp have been merged: group 0 normalises and stores the rows of
-// the head tile.
-template <typename T, int CPL, int GT>
-__device__ __forceinline__ void store_rows(T* __restrict__ out_row, int kh, int G, int gt0, int hd, int LPT, int chunks,
-                                           const float (&l)[GT], const float (&o)[GT][CPL][Vec16<T>::N]) {
-    constexpr int VEC = Vec16<T>::N;
-    const int lane = threadIdx.x & 31, sl = lane % LPT, ti = lane / LPT;
-    if (ti != 0) return;
-#pragma unroll
-    for (int g = 0; g < GT; ++g) {
-        if (gt0 + g >= G) continue;
-        const float inv = l[g] > 0.f ? 1.f / l[g] : 0.f;
-        T* dst = out_row + (size_t)(kh * G + gt0 + g) * hd;
-#pragma unroll
-        for (int i = 0; i < CPL; ++i) {
-            const int c = sl + i * LPT;
-            if (c < chunks) {
-                float r[VEC];
-#pragma unroll
-                for (int e = 0; e < VEC; ++e) r[e] = o[g][i][e] * inv;
-                Vec16<T>::store(dst + c * VEC, r);
-            }
-        }
-    }
-}
-
-
-// One warp per (token, kv head, head tile).  PAGED = false: keys are rows of this step's
-// packed projections (k, v, row_stride, tok_row0).  PAGED = true: keys come from the paged
-// cache of the token's sequence (k = K pool, v = V pool, tok_row0 = slot per token); used
-// by a layer that reads a cache line which another layer wrote.
-template <typename T, int CPL, int GT, bool PAGED>
-__global__ void __launch_bounds__(PRE_WARPS * 32)
-attn_prefill_generic_kernel(const T* __restrict__ q, size_t q_stride, const T* __restrict__ k, const T* __restrict__ v,
-                            size_t row_stride, T* __restrict__ out, size_t out_stride, const int* __restrict__ tok_pos,
-                            const int* __restrict__ tok_row0, int n_tokens, int nq, int nkv, int hd, int LPT,
-                            float scale, float cap, int window, const int* __restrict__ page_table, int max_pages,
-                            int page_size, int ring) {
-    pdl_wait();
-    constexpr int VEC = Vec16<T>::N;
-    const int warp = threadIdx.x >> 5;
-    const int t = blockIdx.x * PRE_WARPS + warp;
-    if (t >= n_tokens) return;
-    const int G = nq / nkv, gtiles = (G + GT - 1) / GT;
-    const int kh = blockIdx.y / gtiles, gt0 = (blockIdx.y % gtiles) * GT;
-    const int chunks = hd / VEC;
-    const int TPW = 32 / LPT;
-    const int row0 = tok_row0[t];
-
-    float m[GT], l[GT], o[GT][CPL][VEC];
-#pragma unroll
-    for (int g = 0; g < GT; ++g) {
-        m[g] = -CUDART_INF_F;
-        l[g] = 0.f;
-#pragma unroll
-        for (int i = 0; i < CPL; ++i)
-#pragma unroll
-            for (int e = 0; e < VEC; ++e) o[g][i][e] = 0.f;
-    }
-    if (row0 >= 0) {
-        const int p = tok_pos[t];
-        const int end = p + 1;
-        const int begin = (window > 0 && end > window) ? end - window : 0;
-        float qr[GT][CPL][VEC];
-        load_query<T, CPL, GT>(q + (size_t)t * q_stride + (size_t)kh * G * hd, hd, G, gt0, LPT, chunks, scale, qr);
-        if (PAGED) {
-            PagedKV<T> kv{k, v, page_table + (size_t)row0 * max_pages, page_size, nkv, hd, ring, kh};
-            attend_range<T, CPL, GT>(qr, kv, begin, end, 0, TPW, LPT, chunks, cap, m, l, o);
-        } else {
-            PackedKV<T> kv{k + (size_t)kh * hd, v + (size_t)kh * hd, row_stride, row0};
-            attend_range<T, CPL, GT>(qr, kv, begin, end, 0, TPW, LPT, chunks, cap, m, l, o);
-        }
-    }
-    merge_groups<CPL, GT, VEC>(LPT, m, l, o);
-    store_rows<T, CPL, GT>(out + (size_t)t * out_stride, kh, G, gt0, hd, LPT, chunks, l, o);
-}
-
-// A step that continues sequences by several tokens (or starts some and continues others): token t
-// of the sequence in slot tok_slot[t] at position tok_pos[t] sees the cached positions before its
-// sequence's first token of this step from the paged cache (k_pool, v_pool: what earlier steps wrote;
-// this step's keys are appended only after this kernel, so that a ring may be as short as the window)
-// and the positions from there up to its own from this step's packed projections (k, v).  The first
-// packed row of the token's sequence is tok_row0[t]; that row's position is the sequence's length
-// before the step.
-template <typename T, int CPL, int GT>
-__global__ void __launch_bounds__(PRE_WARPS * 32)
-attn_extend_generic_kernel(const T* __restrict__ q, size_t q_stride, const T* __restrict__ k, const T* __restrict__ v,
-                           size_t row_stride, const T* __restrict__ k_pool, const T* __restrict__ v_pool,
-                           T* __restrict__ out, size_t out_stride, const int* __restrict__ tok_pos,
-                           const int* __restrict__ tok_row0, const int* __restrict__ tok_slot, int n_tokens, int nq,
-                           int nkv, int hd, int LPT, float scale, float cap, int window,
-                           const int* __restrict__ page_table, int max_pages, int page_size, int ring) {
-    pdl_wait();
-    constexpr int VEC = Vec16<T>::N;
-    const int warp = threadIdx.x >> 5;
-    const int t = blockIdx.x * PRE_WARPS + warp;
-    if (t >= n_tokens) return;
-    const int G = nq / nkv, gtiles = (G + GT - 1) / GT;
-    const int kh = blockIdx.y / gtiles, gt0 = (blockIdx.y % gtiles) * GT;
-    const int chunks = hd / VEC;
-    const int TPW = 32 / LPT;
-    const int slot = tok_slot[t];
-
-    float m[GT], l[GT], o[GT][CPL][VEC];
-#pragma unroll
-    for (int g = 0; g < GT; ++g) {
-        m[g] = -CUDART_INF_F;
-        l[g] = 0.f;
-#pragma unroll
-        for (int i = 0; i < CPL; ++i)
-#pragma unroll
-            for (int e = 0; e < VEC; ++e) o[g][i][e] = 0.f;
-    }
-    if (slot >= 0) {
-        const int p = tok_pos[t], row0 = tok_row0[t];
-        const int first = p - (t - row0);                 // position of the sequence's first token of this step
-        const int end = p + 1;
-        const int begin = (window > 0 && end > window) ? end - window : 0;
-        float qr[GT][CPL][VEC];
-        load_query<T, CPL, GT>(q + (size_t)t * q_stride + (size_t)kh * G * hd, hd, G, gt0, LPT, chunks, scale, qr);
-        if (begin < first) {
-            PagedKV<T> kv{k_pool, v_pool, page_table + (size_t)slot * max_pages, page_size, nkv, hd, ring, kh};
-            attend_range<T, CPL, GT>(qr, kv, begin, first, 0, TPW, LPT, chunks, cap, m, l, o);
-        }
-        PackedKV<T> kv{k + (size_t)kh * hd, v + (size_t)kh * hd, row_stride, row0 - first};
-        attend_range<T, CPL, GT>(qr, kv, begin > first ? begin : first, end, 0, TPW, LPT, chunks, cap, m, l, o);
-    }
-    merge_groups<CPL, GT, VEC>(LPT, m, l, o);
-    store_rows<T, CPL, GT>(out + (size_t)t * out_stride, kh, G, gt0, hd, LPT, chunks, l, o);
-}
-
-struct Geometry {
-    int cpl, lpt, gt;
-    bool ok;
-};
-
-template <typename T>
-Geometry geometry(int hd, int G) {
-    constexpr int VEC = 16 / sizeof(T);
-    Geometry g{0, 0, 0, false};
-    if (hd <= 0 || hd % VEC) return g;
-    const int chunks = hd / VEC;
-    int cpl = (chunks + 31) / 32;
-    cpl = cpl <= 1 ? 1 : (cpl <= 2 ? 2 : 4);
-    if (chunks > 32 * 4) return g;
-    const int per = (chunks + cpl - 1) / cpl;
-    int lpt = 1;
-    while (lpt < per) lpt <<= 1;
-    g.cpl = cpl;
-    g.lpt = lpt;
-    g.gt = G <= 1 ? 1 : (G <= 2 ? 2 : 4);
-    g.ok = true;
-    return g;
-}
-
 }  // namespace
-
-#define QNN_DISPATCH_CPL_GT(CPLV, GTV, ...)                                   \
-    if (geo.cpl == CPLV && geo.gt == GTV) {                                    \
-        constexpr int CPL = CPLV;                                              \
-        constexpr int GT = GTV;                                                \
-        __VA_ARGS__                                                            \
-    }
-#define QNN_DISPATCH_ALL(...)                                                                       \
-    QNN_DISPATCH_CPL_GT(1, 1, __VA_ARGS__) QNN_DISPATCH_CPL_GT(1, 2, __VA_ARGS__)                    \
-    QNN_DISPATCH_CPL_GT(1, 4, __VA_ARGS__) QNN_DISPATCH_CPL_GT(2, 1, __VA_ARGS__)                    \
-    QNN_DISPATCH_CPL_GT(2, 2, __VA_ARGS__) QNN_DISPATCH_CPL_GT(2, 4, __VA_ARGS__)                    \
-    QNN_DISPATCH_CPL_GT(4, 1, __VA_ARGS__) QNN_DISPATCH_CPL_GT(4, 2, __VA_ARGS__)                    \
-    QNN_DISPATCH_CPL_GT(4, 4, __VA_ARGS__)
 
 extern "C" int qnn_attn_decode_mma_split(const void* q, long long q_stride, const void* k_pool, const void* v_pool,
                                          const int* page_table, int max_pages, int page_size, int ring,
@@ -879,98 +550,4 @@ QNN_API int qnn_attn_decode(const void* q, long long q_stride, int dtype, const 
                                    B, nq, nkv, hd, scale, cap, window, part_o, part_ml, n_splits, out, out_stride, st);
     return decode_launch<float>(q, q_stride, k_pool, v_pool, page_table, max_pages, page_size, ring, slots, slot_len, B,
                                 nq, nkv, hd, scale, cap, window, part_o, part_ml, n_splits, out, out_stride, st);
-}
-
-template <typename T>
-static int prefill_launch(const void* q, long long q_stride, const void* k, const void* v, long long row_stride,
-                          void* out, long long out_stride, const int* tok_pos, const int* tok_row0, int n_tokens,
-                          int nq, int nkv, int hd, float scale, float cap, int window, const int* page_table,
-                          int max_pages, int page_size, int ring, bool paged, cudaStream_t st) {
-    if (nkv <= 0 || nq % nkv) return QNN_ERR_ARGUMENT;
-    const Geometry geo = geometry<T>(hd, nq / nkv);
-    if (!geo.ok) return QNN_ERR_UNSUPPORTED;
-    if ((q_stride * sizeof(T)) % 16 || (row_stride * sizeof(T)) % 16 || (out_stride * sizeof(T)) % 16 ||
-        (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)out) & 15))
-        return QNN_ERR_ARGUMENT;
-    const int gtiles = (nq / nkv + geo.gt - 1) / geo.gt;
-    dim3 grid((n_tokens + PRE_WARPS - 1) / PRE_WARPS, nkv * gtiles);
-    QNN_DISPATCH_ALL({
-        if (paged)
-            qnn::launch_pdl(attn_prefill_generic_kernel<T, CPL, GT, true>, dim3(grid), dim3(PRE_WARPS * 32), 0, st, 
-                (const T*)q, (size_t)q_stride, (const T*)k, (const T*)v, (size_t)row_stride, (T*)out,
-                (size_t)out_stride, tok_pos, tok_row0, n_tokens, nq, nkv, hd, geo.lpt, scale, cap, window, page_table,
-                max_pages, page_size, ring);
-        else
-            qnn::launch_pdl(attn_prefill_generic_kernel<T, CPL, GT, false>, dim3(grid), dim3(PRE_WARPS * 32), 0, st, 
-                (const T*)q, (size_t)q_stride, (const T*)k, (const T*)v, (size_t)row_stride, (T*)out,
-                (size_t)out_stride, tok_pos, tok_row0, n_tokens, nq, nkv, hd, geo.lpt, scale, cap, window, page_table,
-                max_pages, page_size, ring);
-    })
-    QNN_LAUNCH_CHECK();
-}
-
-// q, k, v: rows of this step's projections (row_stride elements apart); key p of the
-// sequence of token t is row tok_row0[t] + p.  tok_row0[t] < 0 marks padding (zeros out).
-QNN_API int qnn_attn_prefill_generic(const void* q, const void* k, const void* v, long long row_stride, int dtype,
-                                     void* out, long long out_stride, const int* tok_pos, const int* tok_row0,
-                                     int n_tokens, int nq, int nkv, int hd, float scale, float cap, int window,
-                                     cudaStream_t st) {
-    if (n_tokens <= 0) return 0;
-    if (dtype == QNN_DT_BF16)
-        return prefill_launch<bf16>(q, row_stride, k, v, row_stride, out, out_stride, tok_pos, tok_row0, n_tokens, nq,
-                                    nkv, hd, scale, cap, window, nullptr, 0, 1, 0, false, st);
-    return prefill_launch<float>(q, row_stride, k, v, row_stride, out, out_stride, tok_pos, tok_row0, n_tokens, nq, nkv,
-                                 hd, scale, cap, window, nullptr, 0, 1, 0, false, st);
-}
-
-// Cached keys before this step's tokens, this step's own rows from there on (see
-// attn_extend_generic_kernel).  q, k, v: this step's packed, already rotated projections.
-template <typename T>
-static int extend_launch(const void* q, const void* k, const void* v, long long row_stride, const void* k_pool,
-                         const void* v_pool, const int* page_table, int max_pages, int page_size, int ring, void* out,
-                         long long out_stride, const int* tok_pos, const int* tok_row0, const int* tok_slot, int n_tokens,
-                         int nq, int nkv, int hd, float scale, float cap, int window, cudaStream_t st) {
-    if (nkv <= 0 || nq % nkv) return QNN_ERR_ARGUMENT;
-    const Geometry geo = geometry<T>(hd, nq / nkv);
-    if (!geo.ok) return QNN_ERR_UNSUPPORTED;
-    if ((row_stride * sizeof(T)) % 16 || (out_stride * sizeof(T)) % 16 ||
-        (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)out) & 15))
-        return QNN_ERR_ARGUMENT;
-    const int gtiles = (nq / nkv + geo.gt - 1) / geo.gt;
-    dim3 grid((n_tokens + PRE_WARPS - 1) / PRE_WARPS, nkv * gtiles);
-    QNN_DISPATCH_ALL({
-        qnn::launch_pdl(attn_extend_generic_kernel<T, CPL, GT>, dim3(grid), dim3(PRE_WARPS * 32), 0, st, (const T*)q,
-                        (size_t)row_stride, (const T*)k, (const T*)v, (size_t)row_stride, (const T*)k_pool,
-                        (const T*)v_pool, (T*)out, (size_t)out_stride, tok_pos, tok_row0, tok_slot, n_tokens, nq, nkv, hd,
-                        geo.lpt, scale, cap, window, page_table, max_pages, page_size, ring);
-    })
-    QNN_LAUNCH_CHECK();
-}
-
-QNN_API int qnn_attn_extend(const void* q, const void* k, const void* v, long long row_stride, int dtype,
-                            const void* k_pool, const void* v_pool, const int* page_table, int max_pages, int page_size,
-                            int ring, void* out, long long out_stride, const int* tok_pos, const int* tok_row0,
-                            const int* tok_slot, int n_tokens, int nq, int nkv, int hd, float scale, float cap,
-                            int window, cudaStream_t st) {
-    if (n_tokens <= 0) return 0;
-    if (dtype == QNN_DT_BF16)
-        return extend_launch<bf16>(q, k, v, row_stride, k_pool, v_pool, page_table, max_pages, page_size, ring, out,
-                                   out_stride, tok_pos, tok_row0, tok_slot, n_tokens, nq, nkv, hd, scale, cap, window, st);
-    return extend_launch<float>(q, k, v, row_stride, k_pool, v_pool, page_table, max_pages, page_size, ring, out,
-                                out_stride, tok_pos, tok_row0, tok_slot, n_tokens, nq, nkv, hd, scale, cap, window, st);
-}
-
-// Several query rows per sequence against the paged cache: token t of the sequence in slot
-// tok_slot[t] at position tok_pos[t] sees the cached positions up to its own.  With a ring
-// the caller must make sure that no needed position has been overwritten.
-QNN_API int qnn_attn_prefill_paged(const void* q, long long q_stride, int dtype, const void* k_pool, const void* v_pool,
-                                   const int* page_table, int max_pages, int page_size, int ring, void* out,
-                                   long long out_stride, const int* tok_pos, const int* tok_slot, int n_tokens, int nq,
-                                   int nkv, int hd, float scale, float cap, int window, cudaStream_t st) {
-    if (n_tokens <= 0) return 0;
-    if (dtype == QNN_DT_BF16)
-        return prefill_launch<bf16>(q, q_stride, k_pool, v_pool, 0, out, out_stride, tok_pos, tok_slot, n_tokens, nq,
-                                    nkv, hd, scale, cap, window, page_table, max_pages, page_size, ring, true, st);
-    return prefill_launch<float>(q, q_stride, k_pool, v_pool, 0, out, out_stride, tok_pos, tok_slot, n_tokens, nq, nkv,
-                                 hd, scale, cap, window, page_table, max_pages, page_size, ring, true, st);
 }
