@@ -23,6 +23,10 @@ class StepBatch:
     that the engine's owner set and that parts may look up by name, for instance
     ``decode_splits``) let a part choose its schedule; ``scratch`` is the scratch
     memory that the parts asked for with ``scratch_need`` (bytes; None if none did).
+    ``longest`` and ``spread`` describe the lengths of a decode step's sequences in coarse
+    classes (an upper bound of the longest sequence; a typical ratio of the longest to the
+    mean), 0 when unknown: a schedule that a part derives from them holds for every step
+    of the same classes, which is what the engine captures a decode graph for.
     """
 
     mode: str
@@ -42,3 +46,5 @@ class StepBatch:
     tuning: Mapping[str, Any] = dataclasses.field(default_factory=dict)
     scratch: Optional[torch.Tensor] = None    # uint8
     want_every_row: bool = False              # want_rows is 0, 1, ..., T-1: no gather is needed
+    longest: int = 0                          # decode: class of the longest sequence (an upper bound), 0 = unknown
+    spread: float = 0.0                       # decode: class of longest / mean length (1.0, 1.25, 1.6 or 2.2), 0 = unknown

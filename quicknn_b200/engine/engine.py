@@ -22,6 +22,8 @@ from ..kernels import ops as _kops
 from .batch import StepBatch
 from .model import Model
 
+MAX_DECODE_GRAPHS = 48        # decode states (graph, buffers, scratch) kept at a time, over batch sizes and length classes
+
 
 class StepError(ValueError):
     pass
@@ -50,8 +52,7 @@ class Engine:
         self.tuning: Dict[str, Any] = dict(tuning or {})
         if decode_splits:
             self.tuning["decode_splits"] = int(decode_splits)
-        self._scratch: Dict[int, torch.Tensor] = {}         # decode steps: per batch size (their graphs keep the address)
-        self._scratch_other: Optional[torch.Tensor] = None   # every other step: one buffer that grows
+        self._scratch_other: Optional[torch.Tensor] = None   # steps outside decode graphs: one buffer that grows
         self._decode_state: Dict[tuple, dict] = {}
         self.use_graphs = True
         self.graph_kernels_replayed = 0
@@ -73,11 +74,9 @@ class Engine:
         need = (int(self.model.scratch_need(step)) + 255) // 256 * 256
         if need <= 0:
             step.scratch = None
-        elif step.mode == "decode":
-            buf = self._scratch.get(step.n_seqs)
-            if buf is None or buf.numel() < need:
-                buf = self._scratch[step.n_seqs] = torch.empty(need, dtype=torch.uint8, device=self.device)
-            step.scratch = buf
+        elif step.mode == "decode" and step.want_every_row:
+            # a decode state of its own (its graph keeps the address): never shared, never replaced
+            step.scratch = torch.empty(need, dtype=torch.uint8, device=self.device)
         else:
             if self._scratch_other is None or self._scratch_other.numel() < need:
                 self._scratch_other = torch.empty(need, dtype=torch.uint8, device=self.device)
@@ -158,9 +157,10 @@ class Engine:
         for a in arrays:
             views.append(dev[o:o + a.size])
             o += a.size
+        longest, spread = self.length_classes((arrays[1] + 1).tolist()) if mode == "decode" else (0, 0.0)
         step = StepBatch(mode, T, B, views[0], views[1], views[2], views[3], views[4], views[5],
                          self.model.dtype, max_q_len=int(arrays[7].max()), seq_row0=views[6], seq_len=views[7],
-                         max_seq=self.max_seq, tuning=self.tuning)
+                         max_seq=self.max_seq, tuning=self.tuning, longest=longest, spread=spread)
         self._give_scratch(step)
         logits = self.model.forward(step, self.cache)
         if logits.numel():
@@ -205,18 +205,34 @@ class Engine:
             self.cache.truncate(list(zip(slots, starts)))
             raise
 
+    @staticmethod
+    def length_classes(lengths: Sequence[int]) -> Tuple[int, float]:
+        """(longest, spread) of ``StepBatch`` for sequences of these lengths: the longest rounded up to a power
+        of two (at least 256), and longest / mean as one of four classes.  Coarse on purpose: a decode graph is
+        captured per class, and a batch changes class a few times in its life."""
+        longest = max(lengths)
+        bound = 256
+        while bound < longest:
+            bound *= 2
+        ratio = longest * len(lengths) / max(1, sum(lengths))
+        return bound, (1.0 if ratio < 1.1 else (1.25 if ratio < 1.4 else (1.6 if ratio < 1.9 else 2.2)))
+
     def _decode(self, slots, starts, tokens_dev, use_graph, tail):
         B = len(slots)
         self.cache.sync()
         use_graph = self.use_graphs if use_graph is None else use_graph
-        key = (B, id(tail) if tail is not None else None)
+        longest, spread = self.length_classes([p + 1 for p in starts])
+        key = (B, id(tail) if tail is not None else None, longest, spread)
         st = self._decode_state.get(key)
         if st is None:
+            if len(self._decode_state) >= MAX_DECODE_GRAPHS:     # the oldest goes (its graph, buffers and scratch with it)
+                del self._decode_state[next(iter(self._decode_state))]
             meta = torch.zeros(2 * B, dtype=torch.int32, device=self.device)
             ar = torch.arange(B, dtype=torch.int32, device=self.device)
             tokens = torch.zeros(B, dtype=torch.int32, device=self.device)
             step = StepBatch("decode", B, B, tokens, meta[:B], meta[B:], ar, meta[B:], ar, self.model.dtype,
-                             max_seq=self.max_seq, tuning=self.tuning, want_every_row=True)
+                             max_seq=self.max_seq, tuning=self.tuning, want_every_row=True, longest=longest,
+                             spread=spread)
             self._give_scratch(step)
             st = {"meta": meta, "step": step, "graph": None, "logits": None, "tail": tail}    # holds `tail` alive: its id is the key
             self._decode_state[key] = st

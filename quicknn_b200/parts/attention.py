@@ -24,6 +24,10 @@ from .linear import project, stack_rows
 from .spec import PartSpec
 
 
+BLOCK_COST = 64.0        # a decode-attention block's fixed cost, in keys of its walk
+MERGE_COST = 100.0       # the kernel that merges more than four ranges, in the same unit
+
+
 @MIXERS.register("attention")
 class AttentionMixer(Mixer):
     def __init__(self, spec: PartSpec):
@@ -76,15 +80,37 @@ class AttentionMixer(Mixer):
         return CacheNeed(self.n_kv, self.head_dim, self.window)
 
     def decode_splits(self, step) -> int:
-        """Key ranges per sequence in a decode step: a fixed number when the engine's owner gave one;
-        else as many as keep one wave of blocks on the device (measured at head size 256, context 8192:
-        batch 64 one range 9.48 ms against two 9.69; batch 32 two ranges; batch 16 four; batch 8 nine).
-        Results differ between batch sizes by rounding only: ranges are summed in a fixed order."""
+        """Key ranges per sequence in a decode step: a fixed number when the engine's owner gave one, else the
+        number with the shortest estimated time for the step's length classes (``step.longest``, ``step.spread``).
+
+        A sequence's keys are cut into equal ranges, a block per (range, kv head, sequence).  While all blocks
+        fit the device at once the step takes as long as the longest sequence's range; with more blocks than
+        that they run in turns, and the time is the work of all blocks spread over the device plus about half a
+        block at the end.  A block costs about as much as 64 keys before its first key, and more than four
+        ranges are merged by a kernel of its own, which costs about as much as a hundred.  Measured at head size 256: context 8192, equal lengths, batch 64 one range 9.48 ms
+        against two 9.69, batch 32 two ranges, batch 16 four, batch 8 nine; batch 64 with prompts of 512 to
+        2048 tokens one range 4.20 ms, four 4.03, six 3.90, nine 4.12 (the longest sequence no longer sets the
+        pace).  Results differ between these choices by rounding only: ranges are summed in a fixed order."""
         fixed = step.tuning.get("decode_splits")
         if fixed:
             return int(fixed)
-        most = max(1, min(64, step.max_seq // 128))
-        return max(1, min(most, self._resident // max(1, step.n_seqs * self.n_kv)))
+        tiles = max(1, step.n_seqs * self.n_kv)
+        longest = step.longest or step.max_seq
+        if self.window:
+            longest = min(longest, self.window)
+        most = max(1, min(64, longest // 32))
+        mean = longest / (step.spread or 1.0)
+        best, best_time = 1, float("inf")
+        for s in range(1, most + 1):                 # times in keys of one block's walk
+            if s * tiles <= self._resident:
+                t = longest / s + BLOCK_COST
+            else:
+                t = tiles * (mean + s * BLOCK_COST) / self._resident + longest / (2 * s)
+            if s > 4:
+                t += MERGE_COST
+            if t < best_time * 0.999:
+                best, best_time = s, t
+        return best
 
     def scratch_need(self, step) -> int:
         """Partial (maximum, sum, output) of every key range: float32, [rows, heads, ranges, head_dim + 2]."""

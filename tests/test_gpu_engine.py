@@ -142,6 +142,26 @@ def test_more_requests_than_slots_reuse_them(folders, plain_models):
     assert llm.memory_status()["live_sequences"] == 0
 
 
+def test_decode_graphs_are_kept_per_length_class_and_the_oldest_goes(folders, plain_models, monkeypatch):
+    """A decode graph belongs to a batch size and to classes of the sequences' lengths (they decide the number of
+    key ranges).  A batch that grows from 250 to 270 tokens changes class on the way, batches of other sizes and
+    spreads bring more states than the engine keeps (2 here): generation goes on with the same tokens as the
+    plain implementation, and graphs that were dropped are captured again when their class comes back."""
+    from quicknn_b200.engine import LLM
+    from quicknn_b200.engine import engine as engine_module
+    from quicknn_b200.sampling import GenerationOptions
+    monkeypatch.setattr(engine_module, "MAX_DECODE_GRAPHS", 2)
+    plain = plain_models("B", "float32")
+    llm = LLM(folders("B", "float32"), max_context=300, max_batch=3, dtype="float32")
+    for lens in ([250, 40, 3], [250, 245], [30], [250, 40, 3]):
+        prompts = prompts_for("B", lens, seed=sum(lens))
+        res = llm.generate(prompts, GenerationOptions.greedy(20), stop_ids=[])
+        for r, p in zip(res, prompts):
+            assert r.tokens == plain.greedy(p, 20)
+        assert len(llm.engine._decode_state) <= 2
+    assert llm.memory_status()["live_sequences"] == 0
+
+
 def test_running_one_step_ahead_changes_no_token(folders, plain_models):
     """The entry point queues each decode step before it reads the ids of the one before; rows
     that end (stop token, budget, full context) are dropped a step late and their extra token is

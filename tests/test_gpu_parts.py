@@ -130,7 +130,8 @@ def test_attention_part_prefill_then_decode(window):
     assert np.abs(y - np.concatenate([r[:n] for r, n in zip(ref, lens)])).max() < 2e-5
     for t in range(6):
         step = make_step([1, 1], [n + t for n in lens], slots, "decode", torch.float32, cache, part=mixer)
-        assert step.scratch.numel() == 2 * nq * 2 * (hd + 2) * 4    # rows x heads x ranges x (head + 2) floats
+        ranges = mixer.decode_splits(step)
+        assert ranges > 1 and step.scratch.numel() == 2 * nq * ranges * (hd + 2) * 4    # rows x heads x ranges x (head + 2) floats
         y = host(mixer.forward(dev(np.stack([x[n + t] for x, n in zip(xs, lens)])), step, cache.line(0)))
         assert np.abs(y - np.stack([r[n + t] for r, n in zip(ref, lens)])).max() < 2e-5
 

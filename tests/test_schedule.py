@@ -1,0 +1,72 @@
+"""Decisions that the engine and the attention mixer make on the host about a decode step: the classes of
+sequence lengths that a decode graph is captured for, and the number of key ranges per sequence."""
+from types import SimpleNamespace
+
+import pytest
+
+from quicknn_b200.engine.engine import Engine
+from quicknn_b200.parts import MIXERS, PartSpec
+
+
+def mixer(n_kv=4, head_dim=256, window=None, resident=296):
+    pos = PartSpec("rotary", {"head_dim": head_dim, "theta": 1e4, "rotary_dim": head_dim})
+    m = MIXERS.get("attention")(PartSpec("attention", {
+        "hidden_size": 64, "n_heads": 2 * n_kv, "n_kv_heads": n_kv, "head_dim": head_dim, "scale": 0.1,
+        "softcap": None, "window": window, "position": pos}))
+    m._resident = resident
+    return m
+
+
+def step(n_seqs, longest, spread, max_seq=8192, tuning=None):
+    return SimpleNamespace(n_seqs=n_seqs, longest=longest, spread=spread, max_seq=max_seq, tuning=tuning or {},
+                           mode="decode")
+
+
+def test_length_classes_are_coarse_and_bound_the_longest_sequence():
+    assert Engine.length_classes([1]) == (256, 1.0)
+    assert Engine.length_classes([256, 250]) == (256, 1.0)
+    assert Engine.length_classes([257, 250]) == (512, 1.0)
+    assert Engine.length_classes([8192] * 8) == (8192, 1.0)
+    assert Engine.length_classes([2048, 1024, 1024, 1024]) == (2048, 1.6)       # 2048 / 1280
+    assert Engine.length_classes([1000, 800, 700]) == (1024, 1.25)
+    assert Engine.length_classes([4000] + [100] * 15) == (4096, 2.2)
+    # a batch that decodes 300 tokens from prompts of 600..900 changes class once
+    seen = {Engine.length_classes([600 + t, 750 + t, 900 + t]) for t in range(300)}
+    assert len(seen) == 2
+
+
+def test_key_ranges_at_equal_lengths_keep_one_round_of_blocks():
+    """What was measured at context 8192 with equal lengths: batch 1 takes 64 ranges, 8 nine, 16 four, 32 two."""
+    m = mixer()
+    got = {b: m.decode_splits(step(b, 8192, 1.0)) for b in (1, 2, 4, 8, 12, 16, 32)}
+    assert got == {1: 64, 2: 37, 4: 18, 8: 9, 12: 6, 16: 4, 32: 2}
+    # all blocks fit the device at once in each of these
+    assert all(s * b * 4 <= 296 for b, s in got.items())
+    # a windowed layer sees at most its window
+    assert mixer(window=4096).decode_splits(step(8, 8192, 1.0)) == 9
+    assert mixer(window=128).decode_splits(step(8, 8192, 1.0)) == 4
+    # short sequences: no range shorter than 32 keys
+    assert m.decode_splits(step(1, 256, 1.0)) <= 8
+
+
+def test_key_ranges_with_unequal_lengths_take_more_than_one_round():
+    """64 sequences of very unequal lengths: one range each would let the longest set the pace; equal lengths
+    at the same batch stay with few, long blocks."""
+    m = mixer()
+    assert m.decode_splits(step(64, 2048, 1.6)) == 4
+    assert m.decode_splits(step(64, 2048, 1.0)) == 1
+    assert m.decode_splits(step(32, 2048, 1.6)) == 4
+    # the caller's fixed number wins
+    assert m.decode_splits(step(64, 2048, 1.6, tuning={"decode_splits": 7})) == 7
+    # lengths unknown (a step built by hand): the cache's longest sequence stands in
+    assert m.decode_splits(step(8, 0, 0.0, max_seq=8192)) == 9
+
+
+@pytest.mark.parametrize("n_kv,hd,resident", [(1, 64, 1184), (16, 128, 592), (8, 256, 296)])
+def test_key_ranges_stay_within_what_the_kernels_take(n_kv, hd, resident):
+    m = mixer(n_kv=n_kv, head_dim=hd, resident=resident)
+    for b in (1, 3, 8, 40, 128, 256):
+        for longest in (256, 1024, 8192):
+            for spread in (1.0, 1.25, 1.6, 2.2):
+                s = m.decode_splits(step(b, longest, spread))
+                assert 1 <= s <= 64 and s <= max(1, longest // 32)
