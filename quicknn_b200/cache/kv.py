@@ -104,6 +104,7 @@ class KVCache:
             self.groups.append(g)
         self.uploader = PinnedUploader(device, entries=32)
         self.lengths_host = np.zeros(max_slots, dtype=np.int32)
+        self.longest_host = np.zeros(max_slots, dtype=np.int32)    # the longest that a slot's sequence has been: what its rings have overwritten
         self.lengths_dev = torch.zeros(max_slots, dtype=torch.int32, device=device)
         self._lengths_dirty = False
         self.state: Dict[int, torch.Tensor] = {}
@@ -116,6 +117,7 @@ class KVCache:
     def allocate(self) -> int:
         slot = self.slots.take()
         self.lengths_host[slot] = 0
+        self.longest_host[slot] = 0
         self._lengths_dirty = True
         for t in self.state.values():
             t[slot].zero_()
@@ -129,6 +131,7 @@ class KVCache:
             g.table_host[slot, :] = 0
             g.dirty.add(slot)
         self.lengths_host[slot] = 0
+        self.longest_host[slot] = 0
         self._lengths_dirty = True
 
     def length(self, slot: int) -> int:
@@ -168,6 +171,7 @@ class KVCache:
                 g.dirty.add(slot)
         for slot, new_len in slot_lengths:
             self.lengths_host[slot] = new_len
+            self.longest_host[slot] = max(int(self.longest_host[slot]), new_len)
         self._lengths_dirty = True
 
     def truncate(self, slot_lengths: Sequence[Tuple[int, int]]) -> None:
@@ -188,6 +192,21 @@ class KVCache:
                     g.dirty.add(slot)
             self.lengths_host[slot] = new_len
         self._lengths_dirty = True
+
+    def rewind_limit(self, slot: int) -> int:
+        """The shortest length that ``truncate`` may bring the sequence in ``slot`` to with everything still
+        there that the next token needs: any length for groups that keep every position; for a ring the
+        positions that later tokens have overwritten are gone, so a sequence that has been L tokens long can go
+        back to ``L - (ring - window + 1)`` at most; fixed-size state describes the whole sequence and cannot go back at all
+        (the reference rebuilds recurrent state on a changed prefix, src/models/QuickNN.Models.LLM.pas:725-733)."""
+        length, longest = int(self.lengths_host[slot]), int(self.longest_host[slot])
+        if self.state:
+            return length
+        limit = 0
+        for g in self.groups:
+            if g.ring and longest > g.ring:
+                limit = max(limit, longest - (g.ring - int(g.need.window) + 1))
+        return max(0, min(limit, length))
 
     def sync(self) -> None:
         """Bring the device copies of the page tables and lengths up to date."""

@@ -43,6 +43,7 @@ class GenerationResult:
     time_to_first_token_seconds: float = 0.0
     decode_seconds: float = 0.0
     total_seconds: float = 0.0
+    reused_tokens: int = 0          # tokens of the prompt that a conversation found in its cache (ReusedTokens)
 
     @property
     def generated_tokens(self) -> int:

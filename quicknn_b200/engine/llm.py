@@ -104,6 +104,113 @@ class _Backend(GenerationBackend):
         self.ahead = None
 
 
+class _ConversationBackend(_Backend):
+    """The backend of a ``Conversation``: one sequence whose slot outlives the call.  ``begin`` keeps what
+    the cache holds of the new prompt and runs only the rest; ``finish`` releases nothing."""
+
+    def __init__(self, engine: Engine, sampler: Sampler, run_ahead: bool, conv: "Conversation"):
+        super().__init__(engine, sampler, 1, run_ahead)
+        self.conv = conv
+
+    def begin(self, first_index: int, prompts: Sequence[Sequence[int]]) -> np.ndarray:
+        eng, conv = self.engine, self.conv
+        prompt = list(prompts[0])
+        common = conv.keep_common_prefix(prompt)
+        self.slots = [conv.slot]
+        self.sampler.start(first_index, 1)
+        if self.sampler.penalised:                 # the whole prompt counts as seen, reused or not (LLM.pas:737-744)
+            toks = torch.tensor(prompt, dtype=torch.int32, device=eng.device)
+            self.sampler.mark_prompt(toks, torch.zeros(len(prompt), dtype=torch.int32, device=eng.device))
+        logits = eng.step([(conv.slot, prompt[common:])], "last")
+        self.cur = self.sampler(logits).clone()
+        self.sampler.post(self.cur)
+        self.ahead = self._launch_ahead()
+        return self.sampler.collect()
+
+    def finish(self) -> None:
+        self.slots = []
+        self.cur = None
+        self.ahead = None
+
+
+class Conversation:
+    """One sequence that keeps its cache between calls, as the reference's engine keeps its history
+    (``FHistory``, src/models/QuickNN.Models.LLM.pas:24,715-745): a call whose prompt begins with what the cache
+    already holds (the usual next turn: old prompt + old reply + new text) runs only the new tokens, and
+    ``GenerationResult.reused_tokens`` says how many were found.  Where the prompt departs from the history the
+    cache is shortened to the common part, if the model can go back that far (rings of windowed layers have
+    lost what later tokens overwrote, fixed-size state cannot go back at all: ``KVCache.rewind_limit``);
+    otherwise the sequence starts again from its first token.  A conversation holds one of the engine's
+    ``max_batch`` slots until ``close`` (or the ``with`` block's end)."""
+
+    def __init__(self, llm: "LLM"):
+        self.llm = llm
+        self.slot: Optional[int] = None
+        self.history: List[int] = []               # the tokens whose keys and values the cache holds
+        self.reused = 0
+
+    def __enter__(self) -> "Conversation":
+        return self
+
+    def __exit__(self, *exc) -> None:
+        self.close()
+
+    def reset(self) -> None:
+        """Forget the history (``ResetContext``, LLM.pas:436-449); the next call starts at the first token."""
+        if self.slot is not None:
+            self.llm.engine.release(self.slot)
+        self.slot, self.history = None, []
+
+    close = reset
+
+    def keep_common_prefix(self, prompt: Sequence[int]) -> int:
+        """Shorten the cache to what it shares with ``prompt`` and return that many tokens; the last token of
+        the prompt is never taken from the cache, since its logits are wanted (LLM.pas:719-721)."""
+        eng = self.llm.engine
+        common = 0
+        while common < len(prompt) and common < len(self.history) and prompt[common] == self.history[common]:
+            common += 1
+        if common == len(prompt):
+            common -= 1
+        if self.slot is not None and (common <= 0 or common < eng.cache.rewind_limit(self.slot)):
+            self.reset()
+        if self.slot is None:
+            self.slot, common = eng.new_sequence(), 0
+        elif common < eng.length(self.slot):
+            eng.cache.truncate([(self.slot, common)])
+        self.history = list(prompt[:common])
+        self.reused = common
+        return common
+
+    def generate(self, prompt: Sequence[int], options: Optional[GenerationOptions] = None,
+                 on_token: Optional[Callable[[int, int], Optional[bool]]] = None,
+                 stop_ids: Optional[Sequence[int]] = None,
+                 should_cancel: Optional[Callable[[], bool]] = None) -> GenerationResult:
+        llm = self.llm
+        options = options or GenerationOptions()
+        options.validate()
+        backend = _ConversationBackend(llm.engine, llm._sampler(options), llm.run_ahead, self)
+        stops = llm.stop_ids if stop_ids is None else list(stop_ids)
+        self.reused = 0
+        try:
+            res = generate(backend, [list(prompt)], options, stops, on_token, should_cancel)[0]
+        except Exception:
+            self.reset()                           # what the cache holds is no longer known
+            raise
+        res.reused_tokens = self.reused
+        if self.slot is not None:
+            # the cache holds the prompt and every generated token that was fed back (the step that runs ahead
+            # may have fed one that the loop then dropped: a stop token)
+            known = list(prompt) + list(res.tokens)
+            held = llm.engine.length(self.slot)
+            if held > len(known) and llm.engine.cache.rewind_limit(self.slot) <= len(known):
+                llm.engine.cache.truncate([(self.slot, len(known))])
+                held = len(known)
+            # (state that cannot go back keeps the dropped token: no later prompt matches beyond it)
+            self.history = (known + [-1] * max(0, held - len(known)))[:held]
+        return res
+
+
 class LLM:
     """A loaded model with its cache, ready to generate.
 
@@ -174,6 +281,10 @@ class LLM:
             n = max(backend.decode_steps, 1)
             self.last_io = {"decode_steps": backend.decode_steps, "h2d_bytes_per_step": backend.h2d_bytes / n,
                             "d2h_bytes_per_step": backend.d2h_bytes / n}
+
+    def conversation(self) -> Conversation:
+        """A sequence that keeps its cache between calls and reuses the common prefix of successive prompts."""
+        return Conversation(self)
 
     def evaluate_tokens(self, ids: Sequence[int]) -> np.ndarray:
         """Logits after the last of ``ids`` as a host array (``EvaluateTokens``, LLM.pas:1064-1088)."""

@@ -170,3 +170,35 @@ def test_a_windowed_group_holds_a_ring_per_slot_at_most():
     c.extend([(a, 2048), (b, 2048)])               # both rings full, the pool of the ring group exhausted
     assert ring_group.pool.n_free == 0
     c.audit()
+
+
+def test_how_far_a_sequence_can_go_back():
+    """A ring of 128 positions for a window of 100: once later tokens have overwritten earlier ones, a sequence of L
+    tokens can be shortened by 128 - 100 + 1 at most; before that, and in groups that keep everything, to any length;
+    with fixed-size state not at all."""
+    c = make(max_tokens=4096, max_slots=2, max_seq=2048, window=100)
+    a = c.allocate()
+    c.extend([(a, 90)])
+    assert c.rewind_limit(a) == 0
+    c.extend([(a, 128)])
+    assert c.rewind_limit(a) == 0                  # nothing overwritten yet
+    c.extend([(a, 129)])
+    assert c.rewind_limit(a) == 129 - 29           # position 0 is gone: the next query needs positions >= P - 99
+    c.extend([(a, 1000)])
+    assert c.rewind_limit(a) == 971
+    c.truncate([(a, 971)])
+    assert c.rewind_limit(a) == 971                # what the ring lost when the sequence was 1000 long stays lost
+    c.extend([(a, 990)])
+    assert c.rewind_limit(a) == 971
+    c.free(a)
+    a = c.allocate()
+    c.extend([(a, 50)])
+    assert c.rewind_limit(a) == 0                  # a new sequence in the slot starts over
+    full = KVCache([CacheNeed(2, 16, None)], [None], 512, 2, 256, torch.float32, "cpu")
+    b = full.allocate()
+    full.extend([(b, 200)])
+    assert full.rewind_limit(b) == 0
+    st = KVCache([CacheNeed(1, 8, None), None], [None, StateNeed((3, 2), "float32")], 128, 2, 128, torch.float32, "cpu")
+    s = st.allocate()
+    st.extend([(s, 40)])
+    assert st.rewind_limit(s) == 40

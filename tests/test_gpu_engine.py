@@ -162,6 +162,74 @@ def test_decode_graphs_are_kept_per_length_class_and_the_oldest_goes(folders, pl
     assert llm.memory_status()["live_sequences"] == 0
 
 
+@pytest.mark.parametrize("name,dtype,ahead", [("A", "float32", True), ("B", "float32", False), ("A", "bfloat16", True)])
+def test_a_conversation_reuses_the_common_prefix(folders, plain_models, name, dtype, ahead):
+    """Successive prompts through one ``Conversation``: a next turn (old prompt + reply + new text) runs only the new
+    tokens; a prompt that departs a little way back shortens the cache; one that departs further back than the ring
+    of the windowed layers still has, or at once, starts over; a repeated prompt recomputes its last token.  Every
+    reply is what the plain implementation generates for the whole prompt."""
+    from quicknn_b200.engine import LLM
+    from quicknn_b200.sampling import GenerationOptions
+    plain = plain_models(name, dtype)
+    llm = LLM(folders(name, dtype), max_context=400, max_batch=2, dtype=dtype)
+    llm.run_ahead = ahead
+    window = TINY[name][0]["sliding_window"]
+    greedy = GenerationOptions.greedy(6)
+
+    def same(res, prompt, n=6):
+        if dtype == "float32":
+            assert res.tokens == plain.greedy(prompt, n)
+            return
+        seq = list(prompt)                        # bfloat16: a near tie may fall the other way
+        for t in res.tokens:
+            row = plain.logits(seq)[-1]
+            assert row[t] >= row.max() - 0.06 * max(1.0, np.abs(row).max()), len(seq)
+            seq.append(t)
+
+    with llm.conversation() as conv:
+        p1 = prompts_for(name, [20], seed=5)[0]
+        r1 = conv.generate(p1, greedy, stop_ids=[])
+        assert r1.reused_tokens == 0
+        same(r1, p1)
+        # the next turn
+        p2 = p1 + r1.tokens + prompts_for(name, [5], seed=6)[0]
+        r2 = conv.generate(p2, greedy, stop_ids=[])
+        assert r2.reused_tokens in (len(p1) + 5, len(p1) + 6)           # the last reply token was fed only by a step ahead
+        same(r2, p2)
+        # the same prompt again: everything but its last token is there
+        r2b = conv.generate(p2, greedy, stop_ids=[])
+        assert r2b.reused_tokens == len(p2) - 1 and r2b.tokens == r2.tokens
+        # departs 4 tokens back: the ring (64 positions) still holds what the window needs
+        p3 = p2[:-4] + prompts_for(name, [7], seed=7)[0]
+        r3 = conv.generate(p3, greedy, stop_ids=[])
+        assert r3.reused_tokens == len(p2) - 4
+        same(r3, p3)
+        # a long turn, so that the rings have wrapped; then a prompt that departs further back than they reach
+        p4 = p3 + r3.tokens[:5] + prompts_for(name, [150], seed=8)[0]
+        r4 = conv.generate(p4, greedy, stop_ids=[])
+        assert r4.reused_tokens >= len(p3)
+        same(r4, p4)
+        back = 64 - window + 10
+        p5 = p4[:-back] + prompts_for(name, [3], seed=9)[0]
+        r5 = conv.generate(p5, greedy, stop_ids=[])
+        assert r5.reused_tokens == 0
+        same(r5, p5)
+        # within reach of the rings: kept
+        p6 = p5[:-3] + prompts_for(name, [2], seed=10)[0]
+        r6 = conv.generate(p6, greedy, stop_ids=[])
+        assert r6.reused_tokens == len(p5) - 3
+        same(r6, p6)
+        # an unrelated prompt starts over; and a batch beside the conversation leaves it alone
+        p7 = prompts_for(name, [9], seed=11)[0]
+        others = llm.generate([p1], greedy, stop_ids=[])
+        same(others[0], p1)
+        r7 = conv.generate(p7, greedy, stop_ids=[])
+        assert r7.reused_tokens == 0
+        same(r7, p7)
+        assert llm.memory_status()["live_sequences"] == 1
+    assert llm.memory_status()["live_sequences"] == 0
+
+
 def test_running_one_step_ahead_changes_no_token(folders, plain_models):
     """The entry point queues each decode step before it reads the ids of the one before; rows
     that end (stop token, budget, full context) are dropped a step late and their extra token is
