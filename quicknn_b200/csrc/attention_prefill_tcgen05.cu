@@ -125,8 +125,8 @@ template <int HD, bool FIXED>
 __global__ void __launch_bounds__(THREADS)
 attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
                             bf16* __restrict__ out, size_t out_stride, const int* __restrict__ seq_row0,
-                            const int* __restrict__ seq_len, int nq, int nkv, float scale, float cap, int window,
-                            int* __restrict__ status, int split_levels) {
+                            const int* __restrict__ seq_len, const int* __restrict__ seq_q0, int nq, int nkv,
+                            float scale, float cap, int window, int* __restrict__ status, int split_levels) {
     constexpr int KS = k_stages(HD), VS = v_stages(HD);
     constexpr int Q_BYTES = BM * HD * 2;                             // HD / 64 blocks of [128 x 64]
     constexpr int KP_BYTES = 2 * BN * HD * 2;                        // a pair of key tiles: HD / 64 blocks of [128 x 64]
@@ -162,6 +162,9 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     if (split_levels && !split && (blockIdx.x & 1)) return;
     const int rank = split ? (int)(blockIdx.x & 1) : 0, stride = split ? 2 : 1;
     const int qt = ntiles_q - 1 - qx;                                // the longest rows first
+    // seq_q0: the first rows of a sequence may be there for their keys and values only (a sequence that goes on from
+    // cached tokens); query tiles that end before row seq_q0[b] are left out (both CTAs of a pair agree on this)
+    if (seq_q0 != nullptr && (qt + 1) * BM <= seq_q0[b]) return;
     const int r0 = qt * BM, row0 = seq_row0[b];
     const int kh = h / (nq / nkv);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -660,8 +663,8 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 
 template <int HD, bool FIXED>
 int launch_attn(const void* qkv, long long total_rows, void* out, long long out_stride, const int* seq_row0,
-                const int* seq_len, int B, int max_len, int nq, int nkv, float scale, float cap, int window,
-                int* status, cudaStream_t st) {
+                const int* seq_len, const int* seq_q0, int B, int max_len, int nq, int nkv, float scale, float cap,
+                int window, int* status, cudaStream_t st) {
     const long long width = (long long)(nq + 2 * nkv) * HD;
     CUtensorMap map_q, map_kv;
     int rc = make_map(&map_q, qkv, total_rows, width, BM);
@@ -733,7 +736,7 @@ int launch_attn(const void* qkv, long long total_rows, void* out, long long out_
     } else {
         cfg.numAttrs = pdl ? 1 : 0;
     }
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, map_q, map_kv, (bf16*)out, (size_t)out_stride, seq_row0, seq_len, nq,
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, map_q, map_kv, (bf16*)out, (size_t)out_stride, seq_row0, seq_len, seq_q0, nq,
                                        nkv, scale, cap, window, status, split);
     return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }
@@ -741,20 +744,23 @@ int launch_attn(const void* qkv, long long total_rows, void* out, long long out_
 }  // namespace
 
 // qkv: this step's projections, [T rows, (nq + 2 nkv) * hd] bfloat16, rotated; sequence b occupies rows
-// seq_row0[b] .. + seq_len[b] - 1.  Head sizes 64, 128 and 256; QNN_ERR_UNSUPPORTED for others.  `status` as in
+// seq_row0[b] .. + seq_len[b] - 1.  seq_q0 (may be null): row seq_q0[b] of sequence b is the first whose output is
+// wanted; the rows before it bring keys and values only (qnn_attn_extend_gather lays cached tokens out that way) and
+// their output rows hold nothing of use.  Head sizes 64, 128 and 256; QNN_ERR_UNSUPPORTED for others.  `status` as in
 // qnn_gemm_tcgen05 (bits: 2 K/V wait, 4 S wait, 8 P wait, 16 ring wait, 32 Q wait, 64 product wait, 128 wait for
 // the other half of a pair).  seq_row0 and seq_len are read before the kernel waits for the kernel launched
 // in front of it on the stream: that kernel must not be the one that writes them (copies from the host and
 // kernels further back are complete by then).
 QNN_API int qnn_attn_prefill_tcgen05(const void* qkv, long long total_rows, void* out, long long out_stride,
-                                     const int* seq_row0, const int* seq_len, int B, int max_len, int nq, int nkv,
-                                     int hd, float scale, float cap, int window, int* status, cudaStream_t st) {
+                                     const int* seq_row0, const int* seq_len, const int* seq_q0, int B, int max_len,
+                                     int nq, int nkv, int hd, float scale, float cap, int window, int* status,
+                                     cudaStream_t st) {
     if (B <= 0 || max_len <= 0) return 0;
     if (hd != 64 && hd != 128 && hd != 256) return QNN_ERR_UNSUPPORTED;
     if (nkv <= 0 || nq % nkv) return QNN_ERR_ARGUMENT;
     if (B > 65535 || nq > 32767 || (max_len + BM - 1) / BM > 65535) return QNN_ERR_UNSUPPORTED;
     if (((uintptr_t)qkv & 15) || ((uintptr_t)out & 15) || (out_stride * 2) % 16) return QNN_ERR_UNSUPPORTED;
-#define QNN_ATTN_ARGS qkv, total_rows, out, out_stride, seq_row0, seq_len, B, max_len, nq, nkv, scale, cap, window, status, st
+#define QNN_ATTN_ARGS qkv, total_rows, out, out_stride, seq_row0, seq_len, seq_q0, B, max_len, nq, nkv, scale, cap, window, status, st
     // With a softcap up to 70 the exponent cap * log2(e) stays below 101, so that neither exp(score) nor a row's
     // sum over a million keys leaves float32: the fixed-reference softmax with both groups of warps.  QNN_ATTN_FIXED=0
     // keeps the running maximum (for comparisons).

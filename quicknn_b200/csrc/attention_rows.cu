@@ -235,3 +235,64 @@ QNN_API int qnn_attn_prefill_paged(const void* q, long long q_stride, int dtype,
     return prefill_launch<float>(q, q_stride, k_pool, v_pool, 0, out, out_stride, tok_pos, tok_slot, n_tokens, nq, nkv,
                                  hd, scale, cap, window, page_table, max_pages, page_size, ring, true, st);
 }
+
+// ---------------------------------------------------------------------------------
+// Whole sequences laid out as rows, for the tensor-core prompt kernel: sequence b, whose first seq_start[b]
+// tokens are cached and which brings seq_len[b] new rows in `qkv`, gets rows whole_row0[b] .. of `whole`
+// ([rows, (nq + 2 nkv) * hd] bfloat16): a cached position carries its keys and values from the paged cache (zeros
+// where a ring no longer holds it, and in the query columns), a new position the step's own projections.
+// qnn_attn_prefill_tcgen05 with seq_q0 = seq_start then computes the new rows against everything before them.
+// grid (longest whole sequence, sequences).
+// ---------------------------------------------------------------------------------
+__global__ void extend_gather_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ k_pool,
+                                     const bf16* __restrict__ v_pool, const int* __restrict__ page_table, int max_pages,
+                                     int page_size, int ring, const int* __restrict__ slots,
+                                     const int* __restrict__ seq_start, const int* __restrict__ seq_row0,
+                                     const int* __restrict__ seq_len, const int* __restrict__ whole_row0,
+                                     bf16* __restrict__ whole, int nq, int nkv, int hd) {
+    pdl_wait();
+    const int p = blockIdx.x, b = blockIdx.y;
+    const int start = seq_start[b], n = seq_len[b];
+    if (p >= start + n) return;
+    const int width = (nq + 2 * nkv) * hd, chunks = width / 8;
+    uint4* dst = reinterpret_cast<uint4*>(whole + ((size_t)whole_row0[b] + p) * width);
+    if (p >= start) {
+        const uint4* src = reinterpret_cast<const uint4*>(qkv + ((size_t)seq_row0[b] + (p - start)) * width);
+        for (int c = threadIdx.x; c < chunks; c += blockDim.x) dst[c] = src[c];
+        return;
+    }
+    const int slot = slots[b];
+    const bool held = slot >= 0 && (ring <= 0 || p >= start - ring);
+    const int r = ring > 0 ? p % ring : p;
+    size_t base = 0;
+    if (held) {
+        const int page = page_table[(size_t)slot * max_pages + r / page_size];
+        base = ((size_t)page * nkv * page_size + (r % page_size)) * hd;
+    }
+    const int qc = nq * hd / 8, hc = hd / 8, kvc = nkv * hc;
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+    for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
+        uint4 v = zero;
+        if (held && c >= qc) {
+            const int e = c - qc;
+            const bf16* pool = e < kvc ? k_pool : v_pool;
+            const int e2 = e < kvc ? e : e - kvc;
+            const int kh = e2 / hc, d = (e2 % hc) * 8;
+            v = *reinterpret_cast<const uint4*>(pool + base + (size_t)kh * page_size * hd + d);
+        }
+        dst[c] = v;
+    }
+}
+
+QNN_API int qnn_attn_extend_gather(const void* qkv, const void* k_pool, const void* v_pool, const int* page_table,
+                                   int max_pages, int page_size, int ring, const int* slots, const int* seq_start,
+                                   const int* seq_row0, const int* seq_len, const int* whole_row0, void* whole, int B,
+                                   int longest, int nq, int nkv, int hd, cudaStream_t st) {
+    if (B <= 0 || longest <= 0) return 0;
+    if (hd <= 0 || (hd & 7) || page_size <= 0 || B > 65535) return QNN_ERR_UNSUPPORTED;
+    if ((((uintptr_t)qkv | (uintptr_t)k_pool | (uintptr_t)v_pool | (uintptr_t)whole) & 15)) return QNN_ERR_ARGUMENT;
+    qnn::launch_pdl(extend_gather_kernel, dim3((unsigned)longest, (unsigned)B), dim3(128), 0, st, (const bf16*)qkv,
+                    (const bf16*)k_pool, (const bf16*)v_pool, page_table, max_pages, page_size, ring, slots, seq_start,
+                    seq_row0, seq_len, whole_row0, (bf16*)whole, nq, nkv, hd);
+    QNN_LAUNCH_CHECK();
+}

@@ -8,6 +8,25 @@ import torch
 
 
 @dataclasses.dataclass
+class WholeSequences:
+    """The sequences of a step that goes on from cached tokens, as if each were laid out whole, cached tokens
+    first: sequence b has ``start[b]`` cached tokens and brings ``new_len[b]`` rows (rows ``new_row0[b]``.. of the
+    packed batch); in the whole layout it owns rows ``row0[b]`` .. ``row0[b] + length[b] - 1`` and token t of the
+    packed batch is row ``tok_row[t]``.  Device arrays are int32; the counts are host integers."""
+
+    slots: torch.Tensor             # [B]
+    start: torch.Tensor             # [B]
+    new_row0: torch.Tensor          # [B]
+    new_len: torch.Tensor           # [B]
+    row0: torch.Tensor              # [B]
+    length: torch.Tensor            # [B] = start + new_len
+    tok_row: torch.Tensor           # [T]
+    total: int                      # rows of the whole layout
+    longest: int                    # longest whole sequence
+    most_new: int                   # most rows that one sequence brings
+
+
+@dataclasses.dataclass
 class StepBatch:
     """Device-side description of one step.
 
@@ -46,5 +65,6 @@ class StepBatch:
     tuning: Mapping[str, Any] = dataclasses.field(default_factory=dict)
     scratch: Optional[torch.Tensor] = None    # uint8
     want_every_row: bool = False              # want_rows is 0, 1, ..., T-1: no gather is needed
+    whole: Optional[WholeSequences] = None    # extend steps: the sequences with their cached tokens in front
     longest: int = 0                          # decode: class of the longest sequence (an upper bound), 0 = unknown
     spread: float = 0.0                       # decode: class of longest / mean length (1.0, 1.25, 1.6 or 2.2), 0 = unknown

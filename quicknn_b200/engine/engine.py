@@ -19,7 +19,7 @@ import torch
 from ..cache import PAGE, CacheFull, KVCache
 from ..kernels import lib as _klib
 from ..kernels import ops as _kops
-from .batch import StepBatch
+from .batch import StepBatch, WholeSequences
 from .model import Model
 
 MAX_DECODE_GRAPHS = 48        # decode states (graph, buffers, scratch) kept at a time, over batch sizes and length classes
@@ -149,6 +149,15 @@ class Engine:
 
     def _launch_step(self, mode, T, B, arrays) -> torch.Tensor:
         self.cache.sync()
+        extra = ()
+        if mode == "extend":
+            tok_pos, row0, lens = arrays[1], arrays[6], arrays[7]
+            start = tok_pos[row0]                                   # a sequence's first row stands at its cached length
+            length = start + lens
+            whole_row0 = (np.cumsum(length) - length).astype(np.int32)
+            tok_row = (np.repeat(whole_row0, lens) + tok_pos).astype(np.int32)  # position p of sequence b is row whole_row0[b] + p
+            extra = (start.astype(np.int32), whole_row0, length.astype(np.int32), tok_row)
+            arrays = tuple(arrays) + extra
         packed = np.concatenate(arrays).astype(np.int32, copy=False)
         dev = torch.empty(packed.size, dtype=torch.int32, device=self.device)
         self.cache.uploader.send(dev, packed)
@@ -158,9 +167,13 @@ class Engine:
             views.append(dev[o:o + a.size])
             o += a.size
         longest, spread = self.length_classes((arrays[1] + 1).tolist()) if mode == "decode" else (0, 0.0)
+        whole = None
+        if extra:
+            whole = WholeSequences(views[4], views[8], views[6], views[7], views[9], views[10], views[11],
+                                   total=int(extra[2].sum()), longest=int(extra[2].max()), most_new=int(arrays[7].max()))
         step = StepBatch(mode, T, B, views[0], views[1], views[2], views[3], views[4], views[5],
                          self.model.dtype, max_q_len=int(arrays[7].max()), seq_row0=views[6], seq_len=views[7],
-                         max_seq=self.max_seq, tuning=self.tuning, longest=longest, spread=spread)
+                         max_seq=self.max_seq, tuning=self.tuning, longest=longest, spread=spread, whole=whole)
         self._give_scratch(step)
         logits = self.model.forward(step, self.cache)
         if logits.numel():

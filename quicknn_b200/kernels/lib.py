@@ -48,8 +48,10 @@ _SIGNATURES: Dict[str, list] = {
                                  c_int, c_float, c_float, c_int, c_vp],
     "qnn_attn_prefill_mma": [c_vp, c_vp, c_vp, c_ll, c_vp, c_ll, c_vp, c_vp, c_int, c_int, c_int, c_int, c_int,
                              c_float, c_float, c_int, c_vp],
-    "qnn_attn_prefill_tcgen05": [c_vp, c_ll, c_vp, c_ll, c_vp, c_vp, c_int, c_int, c_int, c_int, c_int, c_float,
+    "qnn_attn_prefill_tcgen05": [c_vp, c_ll, c_vp, c_ll, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_int, c_float,
                                  c_float, c_int, c_vp, c_vp],
+    "qnn_attn_extend_gather": [c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_int,
+                               c_int, c_int, c_int, c_int, c_vp],
     "qnn_attn_prefill_paged": [c_vp, c_ll, c_int, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_vp, c_ll, c_vp, c_vp,
                                c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_vp],
     "qnn_sample": [c_vp, c_int, c_int, c_int, c_float, c_float, c_float, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp,

@@ -442,6 +442,11 @@ def linear(x: torch.Tensor, w: torch.Tensor, *, epilogue: int = EPI_NONE, cap: O
 
 
 ATTN_TCGEN05 = os.environ.get("QNN_ATTN", "tcgen05") != "mma"
+# A step that continues sequences takes the tensor-core prompt kernel from this many rows of a sequence on.  Measured
+# at 8 heads of 256, one sequence, launched eagerly: 8 new rows on 4000 cached tokens 108 us against 3776 us of the
+# generic kernel (a warp per row and kv head that walks the keys one after the other), 512 rows on 7000: 152 us against
+# 8477; so always, where the sizes allow.
+EXTEND_TENSOR_CORE_FROM = int(os.environ.get("QNN_EXTEND_TC_FROM", "1"))
 
 
 def attention_refusal(dtype: torch.dtype, n_heads: int, n_kv: int, head_dim: int) -> Optional[str]:
@@ -486,7 +491,7 @@ def attn_prefill(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, tok_
         _req(seq_len, "seq_len", torch.int32, 1)
         if ATTN_TCGEN05:
             code = L.qnn_attn_prefill_tcgen05(
-                _p(qkv), T, _p(out), out.shape[1], _p(seq_row0), _p(seq_len), seq_row0.numel(), int(max_len),
+                _p(qkv), T, _p(out), out.shape[1], _p(seq_row0), _p(seq_len), None, seq_row0.numel(), int(max_len),
                 n_heads, n_kv, head_dim, float(scale), float(cap or 0.0), int(window or 0),
                 _p(_status_word(qkv.device)), _stream())
             if code != _lib.ERR_UNSUPPORTED:
@@ -527,17 +532,40 @@ def attn_prefill_paged(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int
 
 def attn_extend(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, k_pool: torch.Tensor, v_pool: torch.Tensor,
                 page_table: torch.Tensor, page_size: int, ring: int, tok_pos: torch.Tensor, tok_row0: torch.Tensor,
-                tok_slot: torch.Tensor, scale: float, cap: Optional[float], window: Optional[int]):
+                tok_slot: torch.Tensor, scale: float, cap: Optional[float], window: Optional[int], whole=None):
     """Attention of a step that continues sequences by several tokens: each row sees the cached
     positions before its sequence's first row of this step (from the cache, as earlier steps left it)
     and this step's own rows from there to itself (from ``qkv``, already rotated).  The caller appends
-    this step's keys and values to the cache afterwards."""
+    this step's keys and values to the cache afterwards.
+
+    ``whole`` (a ``WholeSequences``, optional) describes the step's sequences laid out with their cached
+    tokens in front; with it, bfloat16 rows of head size 64, 128 or 256 go through the tensor-core prompt
+    kernel: the cached keys and values are copied out of the pages into that layout, the kernel leaves out
+    the query tiles that lie before each sequence's new rows, and the new rows' outputs are picked out.
+    The generic kernel walks the keys once per row and kv head: it serves float32 and the other head sizes."""
     _req(qkv, "qkv", None, 2)
     _req(k_pool, "k_pool", qkv.dtype, 4)
     _req(v_pool, "v_pool", qkv.dtype, 4)
     for n, t in (("tok_pos", tok_pos), ("tok_row0", tok_row0), ("tok_slot", tok_slot)):
         _req(t, n, torch.int32, 1)
     T = qkv.shape[0]
+    if (whole is not None and ATTN_TCGEN05 and qkv.dtype == torch.bfloat16 and head_dim in (64, 128, 256)
+            and whole.most_new >= EXTEND_TENSOR_CORE_FROM):
+        L = _lib.load()
+        B = whole.row0.numel()
+        rows = torch.empty((whole.total, qkv.shape[1]), dtype=qkv.dtype, device=qkv.device)
+        _lib.check(L.qnn_attn_extend_gather(
+            _p(qkv), _p(k_pool), _p(v_pool), _p(page_table), page_table.shape[1], page_size, ring, _p(whole.slots),
+            _p(whole.start), _p(whole.new_row0), _p(whole.new_len), _p(whole.row0), _p(rows), B, whole.longest,
+            n_heads, n_kv, head_dim, _stream()), "attn_extend_gather")
+        out_rows = torch.empty((whole.total, n_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
+        code = L.qnn_attn_prefill_tcgen05(
+            _p(rows), whole.total, _p(out_rows), out_rows.shape[1], _p(whole.row0), _p(whole.length), _p(whole.start), B,
+            whole.longest, n_heads, n_kv, head_dim, float(scale), float(cap or 0.0), int(window or 0),
+            _p(_status_word(qkv.device)), _stream())
+        if code != _lib.ERR_UNSUPPORTED:
+            _lib.check(code, "attn_prefill_tcgen05")
+            return gather_rows(out_rows, whole.tok_row, qkv.dtype)
     out = torch.empty((T, n_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
     es = qkv.element_size()
     q_ptr = qkv.data_ptr()

@@ -130,7 +130,7 @@ class AttentionMixer(Mixer):
             # so that the first rows still find the ring cells that the last rows overwrite
             a = ops.attn_extend(qkv, h.n_heads, h.n_kv_heads, h.head_dim, line.k, line.v, line.page_table,
                                 line.page_size, line.ring, step.tok_pos, step.tok_row0, step.tok_slot, self.scale,
-                                self.softcap, self.window)
+                                self.softcap, self.window, whole=getattr(step, "whole", None))
             ops.cache_append(qkv, h.n_heads, h.n_kv_heads, h.head_dim, step.tok_pos, step.tok_slot, line)
         elif step.mode != "decode" and not line.writes:
             # the keys of this line were written by another layer earlier in this step; in a ring the last

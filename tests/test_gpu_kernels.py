@@ -542,6 +542,56 @@ def test_attention_decode(ops, dtype, nq, nkv, hd, window, cap, splits):
     assert float(out[-1].abs().sum()) == 0.0                                  # the padding row attends to nothing
 
 
+@pytest.mark.parametrize("dtype,nq,nkv,hd,tensor_cores", [
+    (torch.float32, 4, 2, 16, False), (torch.bfloat16, 6, 1, 24, False), (torch.bfloat16, 8, 4, 64, True),
+    (torch.bfloat16, 4, 2, 128, True), (torch.bfloat16, 8, 4, 256, True), (torch.bfloat16, 8, 4, 256, False)])
+@pytest.mark.parametrize("window,cap", [(None, 50.0), (128, None), (100, 30.0)])
+def test_attention_of_steps_that_continue_sequences(ops, dtype, nq, nkv, hd, tensor_cores, window, cap):
+    """attn_extend: cached keys from the pages (a ring of 128 positions under a window, wrapped for the long
+    sequence), the step's own rows from the packed projections; one sequence starts in this step, one brings a
+    single row.  With the whole-sequence layout the bfloat16 rows of head size 64 / 128 / 256 go through the
+    tensor-core prompt kernel, which leaves out the query tiles before the new rows."""
+    from quicknn_b200.engine.batch import WholeSequences
+    rng = np.random.default_rng(nq + hd + (window or 0))
+    seqs = [(300, 40), (0, 70), (130, 1), (1000, 200)]                      # (cached, new)
+    ring = 128 if window else 0
+    per = 2 if ring else 19
+    tables = (1 + rng.permutation(len(seqs) * per)).reshape(len(seqs), per).tolist()
+    k = [bf16_round(rng.normal(size=(c + n, nkv, hd))) for c, n in seqs]
+    v = [bf16_round(rng.normal(size=(c + n, nkv, hd))) for c, n in seqs]
+    q = [bf16_round(rng.normal(size=(c + n, nq, hd))) for c, n in seqs]
+    k_pool, v_pool = _fill_cache([kk[:c] for kk, (c, n) in zip(k, seqs)], [vv[:c] for vv, (c, n) in zip(v, seqs)],
+                                 tables, dtype, 1 + len(seqs) * per, ring)
+    packed = np.concatenate([np.concatenate([qq[c:].reshape(n, -1), kk[c:].reshape(n, -1), vv[c:].reshape(n, -1)], axis=1)
+                             for qq, kk, vv, (c, n) in zip(q, k, v, seqs)])
+    new = np.array([n for c, n in seqs], np.int32)
+    start = np.array([c for c, n in seqs], np.int32)
+    new_row0 = (np.cumsum(new) - new).astype(np.int32)
+    tok_pos = np.concatenate([np.arange(c, c + n) for c, n in seqs]).astype(np.int32)
+    tok_row0 = np.repeat(new_row0, new)
+    slots = np.arange(len(seqs), dtype=np.int32)[::-1].copy()               # rows are not in slot order
+    table = np.zeros((len(seqs), per), np.int32)
+    for s_, tb in zip(slots, tables):
+        table[s_] = tb
+    tok_slot = np.repeat(slots, new)
+    i32 = lambda a: T(np.asarray(a, np.int32), torch.int32)  # noqa: E731
+    whole = None
+    if tensor_cores:
+        length = start + new
+        row0 = (np.cumsum(length) - length).astype(np.int32)
+        tok_row = (np.repeat(row0, new) + tok_pos).astype(np.int32)
+        whole = WholeSequences(i32(slots), i32(start), i32(new_row0), i32(new), i32(row0), i32(length), i32(tok_row),
+                               total=int(length.sum()), longest=int(length.max()), most_new=int(new.max()))
+    scale = 1.0 / math.sqrt(hd)
+    out = ops.attn_extend(T(packed, dtype), nq, nkv, hd, k_pool, v_pool, i32(table), 64, ring, i32(tok_pos), i32(tok_row0),
+                          i32(tok_slot), scale, cap, window, whole=whole)
+    ops.raise_on_status(DEV)
+    assert tuple(out.shape) == (int(new.sum()), nq * hd)
+    for b, (c, n) in enumerate(seqs):
+        ref = P.attention(q[b], k[b], v[b], scale, cap, window)[c:].reshape(n, -1)
+        assert_close(out[new_row0[b]:new_row0[b] + n], ref, dtype, f"sequence {b}", mult=4)
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_decode_attention_finds_one_far_key_among_hundreds(ops, dtype):
     """Random keys would hide a skipped key: here one key per test scores far above the rest and
