@@ -58,20 +58,34 @@ def cmd_generate(args) -> int:
         if args.stream:
             print(json.dumps({"request": i, "token": tok}), flush=True)
 
+    def run():
+        if not args.turns:
+            return llm.generate(prompts, opts, on_token=on_token, stop_ids=stops)
+        # the prompts are the turns of one conversation: each is appended to what was said so far, and only
+        # what the cache does not hold yet is run
+        out, said = [], []
+        with llm.conversation() as chat:
+            for i, turn in enumerate(prompts):
+                r = chat.generate(said + turn, opts, on_token=lambda _, tok, i=i: on_token(i, tok), stop_ids=stops)
+                r.index = i
+                said = said + turn + r.tokens
+                out.append(r)
+        return out
+
     prof = None
     try:
         if args.profile:
             from .engine.profile import StepProfiler
             with StepProfiler(llm.engine) as prof:
-                results = llm.generate(prompts, opts, on_token=on_token, stop_ids=stops)
+                results = run()
         else:
-            results = llm.generate(prompts, opts, on_token=on_token, stop_ids=stops)
+            results = run()
     except KeyboardInterrupt:
         print("cancelled", file=sys.stderr)
         return 130
     for r in results:
         print(json.dumps({"request": r.index, "prompt_tokens": r.prompt_tokens, "tokens": r.tokens,
-                          "finish_reason": r.finish_reason,
+                          "finish_reason": r.finish_reason, "reused_tokens": r.reused_tokens,
                           "time_to_first_token_seconds": round(r.time_to_first_token_seconds, 6),
                           "decode_seconds": round(r.decode_seconds, 6),
                           "decode_tokens_per_second": round(r.decode_tokens_per_second(), 3)}))
@@ -133,6 +147,9 @@ def main(argv=None) -> int:
     g.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16")
     g.add_argument("--device", default="cuda:0")
     g.add_argument("--stream", action="store_true", help="print each token as it is produced")
+    g.add_argument("--turns", action="store_true",
+                   help="the prompts are successive turns of one conversation that keeps its cache (reused_tokens "
+                        "says how much of each turn's prompt was found there)")
     g.add_argument("--profile", action="store_true",
                    help="time every step and every kind of part with CUDA events (steps then run eagerly) and print a table")
     g.set_defaults(fn=cmd_generate)

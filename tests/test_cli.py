@@ -90,3 +90,14 @@ def test_generate_prints_what_the_plain_model_generates(folders, plain_models, t
     assert got[1]["tokens"] == plain.greedy(prompts[1], 8, stop_ids=[stop]) and got[1]["finish_reason"] == "eos"
     p = run("generate", "--model", folder, "--prompt-ids", "5", "--top-p", "1.5")
     assert p.returncode != 0
+    # the same prompts as the turns of one conversation: each reply is the plain model's for everything said so far
+    p = run("generate", "--model", folder, "--prompt-ids", ids, "--max-new-tokens", "4", "--temperature", "0",
+            "--dtype", "float32", "--max-context", "128", "--stop-ids", "", "--turns")
+    assert p.returncode == 0, p.stderr
+    got = [json.loads(l) for l in p.stdout.splitlines() if l.strip()]
+    said = []
+    for r, turn in zip(got, prompts):
+        assert r["tokens"] == plain.greedy(said + turn, 4)
+        assert r["reused_tokens"] in (max(0, len(said) - 1), len(said))       # all that was said, but for a reply's last token
+        said = said + turn + r["tokens"]
+
