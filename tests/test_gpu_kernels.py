@@ -724,6 +724,9 @@ def test_head_with_the_arg_max_in_its_epilogue(ops, M, V, K):
     cand = torch.full((M * ops.head_candidates(V) * 2,), float("nan"), device=DEV)
     assert ops.head_argmax_fusable(x, w)
     ncand = ops.head_argmax(x, w, 30.0, cand, flag)
+    if ncand is None:                                 # more than 64 rows with the tcgen05 decode product switched off:
+        assert M > 64 and not ops._takes_skinny_tcgen05(M, V, K)     # the caller forms the logits, as documented
+        return
     group = {(V + 15) // 16: 16, (V + 127) // 128: 128}[ncand]
     c = cand[:M * ncand * 2].cpu().numpy().reshape(M, ncand, 2)
     ids = c[:, :, 1].copy().view(np.uint32)
