@@ -629,7 +629,7 @@ def sample(logits: torch.Tensor, top_k: int, temperature: float, top_p: float, p
     L = _lib.load()
     _lib.check(L.qnn_sample(_p(logits), R, V, int(top_k), float(temperature), float(top_p), float(penalty),
                             _p(rng_state), _p(seen), _p(seen_rows), _p(scratch), _p(out_tokens), _p(error_flag),
-                            _p(status), _stream()), "sample", 2)
+                            _p(status), _stream()), "sample", 4 if (temperature > 0 and top_k > 1 and V > 1) else 2)
     return out_tokens
 
 

@@ -703,6 +703,41 @@ def test_sampling_follows_the_plain_sampler(ops, V):
     assert int(flag) == 0
 
 
+@pytest.mark.parametrize("V", [3000, 40000, 256000])
+def test_sampling_when_many_values_crowd_the_top(ops, V):
+    """The k best are looked for among the values at or above the k-th largest tile maximum, kept in a list of 4096;
+    rows that overflow it take k rounds over everything instead: a row of equal logits (the lowest ids win), a row
+    whose best thirty tiles are all outliers, a row of two values in halves; beside an ordinary row and one with
+    fewer finite values than k."""
+    rng = np.random.default_rng(V)
+    R = 5
+    logits = rng.normal(size=(R, V)).astype(np.float32)
+    logits[0, :] = 1.25
+    width = min(V, 31000)
+    logits[1, V - width:] = 50.0 + rng.normal(size=width).astype(np.float32)
+    logits[2, :] = np.where(np.arange(V) % 2 == 0, 3.0, -3.0)
+    logits[4, :] = -np.inf
+    logits[4, [7, V - 1, V // 2]] = [0.5, 0.25, 0.5]
+    lg = T(logits, torch.float32)
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    for temp, k, p in [(0.9, 20, 0.95), (1.3, 64, 1.0), (0.5, 2, 0.9)]:
+        states = np.array([P.seed_state(7 + i) for i in range(R)], dtype=np.uint32)
+        rng_state = T(states.view(np.int32), torch.int32)
+        scratch = torch.empty(ops.sample_scratch_bytes(R, V, k), dtype=torch.uint8, device=DEV)
+        out = torch.zeros(R, dtype=torch.int32, device=DEV)
+        st = states.copy()
+        for draw in range(6):
+            ops.sample(lg, k, temp, p, 1.0, rng_state, None, None, scratch, out, flag)
+            got = out.cpu().numpy()
+            for r in range(R):
+                s_, u = P.xorshift32(int(st[r]))
+                st[r] = s_
+                row = np.where(np.isfinite(logits[r]), logits[r], -3.0e38)        # non-finite values lose
+                ref = P.sample(row, temp, min(k, 3) if r == 4 else k, p, 1.0, None, u)
+                assert got[r] == ref, (temp, k, p, draw, r, got[r], ref)
+    assert int(flag) == 1                                       # the infinities were seen
+
+
 @pytest.mark.parametrize("M,V,K", [(1, 256000, 2304), (8, 256000, 2304), (5, 1000, 96), (20, 1000, 200), (30, 3001, 64),
                                    (12, 256000, 2304), (40, 3001, 64), (100, 30000, 256), (64, 20000, 128)])
 def test_head_with_the_arg_max_in_its_epilogue(ops, M, V, K):
