@@ -145,16 +145,16 @@ def fill_synthetic(engine, slots, lengths, torch, seed=0):
                 t[li].normal_(0.0, 1.0, generator=g)
 
 
-def timed_decode(engine, batch, steps, warmup, torch, with_clocks=False, context=CONTEXT, lengths=None):
+def timed_decode(engine, batch, steps, warmup, torch, with_clocks=False, context=CONTEXT, lengths=None, options=None):
     """Tokens per second of `steps` decode steps of `batch` sequences, each step from the ids that the
-    step before chose on the device (greedy) to the ids of the next.  The sequences end at `context`
-    tokens, or start from the given `lengths`."""
+    step before chose on the device (greedy, or sampled with `options`) to the ids of the next.  The
+    sequences end at `context` tokens, or start from the given `lengths`."""
     from quicknn_b200.sampling import GenerationOptions, Sampler
     vocab = engine.model.spec.embedding.vocab_size
     start = lengths if lengths is not None else [context - steps - warmup - RAMP_STEPS - 1] * batch
     slots = [engine.new_sequence() for _ in range(batch)]
     fill_synthetic(engine, slots, start, torch)
-    sampler = Sampler(vocab, batch, GenerationOptions.greedy(1), engine.device)
+    sampler = Sampler(vocab, batch, options or GenerationOptions.greedy(1), engine.device)
     sampler.start(0, batch)
     tokens = torch.randint(1, vocab, (batch,), dtype=torch.int32, device=engine.device)
     tokens = engine.decode(slots, tokens, tail=sampler)          # eager pass, captures the graph
@@ -347,6 +347,11 @@ def main():
         for b in (1, big):
             points[f"decode_b{b}"] = round(timed_decode(eng, b, min(args.steps, 128), args.warmup, torch,
                                                         context=args.context)["tok_s"], 1)
+        # the headline's steps with the reference's default sampling (temperature 0.6, top-k 20, top-p 0.95) instead
+        # of the arg-max: the head writes its logits and the sampler's kernels run inside the step
+        points[f"decode_b{args.batch}_sampled"] = round(timed_decode(
+            eng, args.batch, min(args.steps, 128), args.warmup, torch, context=args.context,
+            options=GenerationOptions(max_new_tokens=1))["tok_s"], 1)
         # BASELINE.json's workload as it is stated: prompts uniform in [512, 2048], then 256 decode steps
         import numpy as np
         rng = np.random.default_rng(SEED)
