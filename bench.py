@@ -359,6 +359,14 @@ def main():
             run = timed_decode(eng, b, 256, args.warmup, torch, lengths=rng.integers(512, 2049, b).tolist())
             workload[f"decode_b{b}"] = round(run["tok_s"], 1)
             workload[f"hbm_frac_b{b}"] = round(run["bytes_per_step"] / (run["ms_per_step"] / 1e3) / 1e9 / pk["hbm_gbs"], 3)
+        # the workloads that are stated for the two larger sizes: 8 prompts uniform in [100, 6000] and 128 steps;
+        # 16 prompts uniform in [256, 4096] and 64 steps
+        stated = {"9b": (8, 100, 6000, 128), "27b": (16, 256, 4096, 64)}.get(args.model)
+        if stated is not None and stated[0] <= max_b:
+            n, lo, hi, steps_ = stated
+            run = timed_decode(eng, n, steps_, args.warmup, torch, lengths=rng.integers(lo, hi + 1, n).tolist())
+            workload[f"stated_b{n}_u{lo}_{hi}"] = round(run["tok_s"], 1)
+            workload[f"stated_hbm_frac"] = round(run["bytes_per_step"] / (run["ms_per_step"] / 1e3) / 1e9 / pk["hbm_gbs"], 3)
 
     # ---- end to end through the Python entry point ------------------------------------------
     e2e = None
