@@ -22,7 +22,7 @@ from ..kernels import ops as _kops
 from .batch import StepBatch, WholeSequences
 from .model import Model
 
-MAX_DECODE_GRAPHS = 48        # decode states (graph, buffers, scratch) kept at a time, over batch sizes and length classes
+MAX_DECODE_GRAPHS = 256       # decode states (graph, buffers, scratch) kept at a time, over batch sizes, samplers and schedules
 
 
 class StepError(ValueError):
@@ -54,6 +54,7 @@ class Engine:
             self.tuning["decode_splits"] = int(decode_splits)
         self._scratch_other: Optional[torch.Tensor] = None   # steps outside decode graphs: one buffer that grows
         self._decode_state: Dict[tuple, dict] = {}
+        self._schedules: Dict[tuple, int] = {}               # (batch, longest, spread) -> hash of the model's schedule
         self.use_graphs = True
         self.graph_kernels_replayed = 0
         self.steps_run = 0
@@ -235,10 +236,20 @@ class Engine:
         self.cache.sync()
         use_graph = self.use_graphs if use_graph is None else use_graph
         longest, spread = self.length_classes([p + 1 for p in starts])
-        key = (B, id(tail) if tail is not None else None, longest, spread)
-        st = self._decode_state.get(key)
-        if st is None:
-            if len(self._decode_state) >= MAX_DECODE_GRAPHS:     # the oldest goes (its graph, buffers and scratch with it)
+        # a graph per batch size, sampler and schedule that the parts derive from the length classes (classes
+        # that lead to the same decisions share one); the schedule of a class is asked once
+        shape = (B, longest, spread, tuple(sorted(self.tuning.items())))
+        sched = self._schedules.get(shape)
+        if sched is None:
+            probe = StepBatch("decode", B, B, None, None, None, None, None, None, self.model.dtype, max_seq=self.max_seq,
+                              tuning=self.tuning, want_every_row=True, longest=longest, spread=spread)
+            sched = self._schedules[shape] = hash(self.model.schedule(probe))
+        key = (B, id(tail) if tail is not None else None, sched)
+        st = self._decode_state.pop(key, None)
+        if st is not None:
+            self._decode_state[key] = st                          # most recently used last
+        else:
+            if len(self._decode_state) >= MAX_DECODE_GRAPHS:     # the least recently used goes (graph, buffers, scratch)
                 del self._decode_state[next(iter(self._decode_state))]
             meta = torch.zeros(2 * B, dtype=torch.int32, device=self.device)
             ar = torch.arange(B, dtype=torch.int32, device=self.device)

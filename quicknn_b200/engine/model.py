@@ -109,6 +109,10 @@ class Model:
         (they run one after another and share it)."""
         return max([self.blocks[e.layer].scratch_need(step) for e in self.spec.schedule] or [0])
 
+    def schedule(self, step) -> tuple:
+        """The decisions of the layers that run, in order (see ``Part.schedule``)."""
+        return tuple(self.blocks[e.layer].schedule(step) for e in self.spec.schedule)
+
     def weight_bytes(self) -> int:
         n = self.embedding.numel() * self.embedding.element_size()
         if self.head is not self.embedding:

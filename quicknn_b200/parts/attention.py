@@ -112,6 +112,9 @@ class AttentionMixer(Mixer):
                 best, best_time = s, t
         return best
 
+    def schedule(self, step) -> tuple:
+        return (self.decode_splits(step),) if step.mode == "decode" else ()
+
     def scratch_need(self, step) -> int:
         """Partial (maximum, sum, output) of every key range: float32, [rows, heads, ranges, head_dim + 2]."""
         if step.mode != "decode":

@@ -15,8 +15,9 @@ Positions      ``param_shapes`` (usually none); ``prepare(device)``;
                with the q|k|v product
 Mixer          ``param_shapes``; ``load``; ``cache_need()`` (growing keys/values,
                possibly windowed), ``state_need()`` (fixed-size per-sequence
-               state), ``scratch_need(step)`` (bytes of scratch for one step);
-               ``forward(x, step, cache_line)``
+               state), ``scratch_need(step)`` (bytes of scratch for one step),
+               ``schedule(step)`` (what it decides from a step's shape that a
+               captured decode graph bakes in); ``forward(x, step, cache_line)``
 FeedForward    ``param_shapes``; ``load``; ``forward(x, step)``
 Block          arrangement of the four above around the residual stream:
                ``forward(resid, step, cache_line)``
@@ -124,6 +125,13 @@ class Part:
 
     def weight_bytes(self) -> int:
         return 0
+
+    def schedule(self, step) -> tuple:
+        """What this part decides from the step's shape and length classes that a captured launch sequence
+        would bake in (grid sizes, kernels chosen), as a hashable value; ``()`` when nothing.  The engine keeps
+        one decode graph per batch size and distinct schedule of the model, so two length classes that lead to
+        the same decisions share a graph."""
+        return ()
 
     def scratch_need(self, step) -> int:
         """Bytes of scratch (global memory beyond inputs and outputs) that this part wants for a

@@ -61,6 +61,9 @@ class _LayerParts(Block):
     def scratch_need(self, step) -> int:
         return max(self.mixer.scratch_need(step), self.ff.scratch_need(step))
 
+    def schedule(self, step) -> tuple:
+        return self.mixer.schedule(step) + self.ff.schedule(step)
+
 
 @BLOCKS.register("sandwich")
 class SandwichBlock(_LayerParts):
