@@ -191,7 +191,7 @@ class Engine:
 
     # ---- decode with ids that are already on the device -------------------------------
     def decode(self, slots: Sequence[int], tokens_dev: torch.Tensor, use_graph: Optional[bool] = None,
-               tail=None) -> torch.Tensor:
+               tail=None, pad: bool = False) -> torch.Tensor:
         """One token for each sequence in ``slots``; ``tokens_dev`` ([B] int32) stays on the
         device (the reference feeds the sampled id from device memory too,
         src/models/QuickNN.Models.LLM.pas:802-807).  Returns the logits of every row, or, with
@@ -201,7 +201,12 @@ class Engine:
 
         The launch sequence of a batch size is captured in a CUDA graph the first time it
         runs and replayed afterwards; lengths, page tables and ids are read from device
-        memory by the kernels, so one graph serves every step of that batch size."""
+        memory by the kernels, so one graph serves every step of that batch size.
+
+        ``pad``: run the step with a few more rows than sequences (rows of no sequence, which attend to nothing
+        and write nothing) so that a batch that shrinks one sequence at a time passes through few row counts
+        (``decode_rows``) and so needs few graphs, each of which takes about 10 ms to capture; the result is
+        that of the sequences' rows.  ``tail`` then sees the padded rows too and must have room for them."""
         B = len(slots)
         if B < 1:
             raise StepError("a step needs at least one sequence")
@@ -214,10 +219,16 @@ class Engine:
             raise StepError("decode needs one int32 id per sequence on the device")
         self.cache.extend([(s, p + 1) for s, p in zip(slots, starts)])
         try:
-            return self._decode(slots, starts, tokens_dev, use_graph, tail)
+            return self._decode(slots, starts, tokens_dev, use_graph, tail, self.decode_rows(B) if pad else B)
         except Exception:
             self.cache.truncate(list(zip(slots, starts)))
             raise
+
+    def decode_rows(self, n_seqs: int) -> int:
+        """Rows of a padded decode step for this many sequences: every count up to 8, then steps of 2 up to 16,
+        of 4 up to 32, of 8 up to 64, of 16 beyond; never more than the cache has slots."""
+        step = 1 if n_seqs <= 8 else (2 if n_seqs <= 16 else (4 if n_seqs <= 32 else (8 if n_seqs <= 64 else 16)))
+        return max(n_seqs, min((n_seqs + step - 1) // step * step, self.max_slots))
 
     @staticmethod
     def length_classes(lengths: Sequence[int]) -> Tuple[int, float]:
@@ -231,8 +242,8 @@ class Engine:
         ratio = longest * len(lengths) / max(1, sum(lengths))
         return bound, (1.0 if ratio < 1.1 else (1.25 if ratio < 1.4 else (1.6 if ratio < 1.9 else 2.2)))
 
-    def _decode(self, slots, starts, tokens_dev, use_graph, tail):
-        B = len(slots)
+    def _decode(self, slots, starts, tokens_dev, use_graph, tail, rows):
+        n_seqs, B = len(slots), rows                 # B rows, of which the last B - n_seqs belong to no sequence
         self.cache.sync()
         use_graph = self.use_graphs if use_graph is None else use_graph
         longest, spread = self.length_classes([p + 1 for p in starts])
@@ -260,9 +271,17 @@ class Engine:
             self._give_scratch(step)
             st = {"meta": meta, "step": step, "graph": None, "logits": None, "tail": tail}    # holds `tail` alive: its id is the key
             self._decode_state[key] = st
-        self.cache.uploader.send(st["meta"], np.concatenate([np.asarray(starts, np.int32), np.asarray(slots, np.int32)]))
-        st["step"].tokens.copy_(tokens_dev.reshape(-1))
+        pad_rows = B - n_seqs
+        self.cache.uploader.send(st["meta"], np.concatenate([np.asarray(list(starts) + [0] * pad_rows, np.int32),
+                                                             np.asarray(list(slots) + [-1] * pad_rows, np.int32)]))
+        st["step"].tokens[:n_seqs].copy_(tokens_dev.reshape(-1))
         self.steps_run += 1
+        if pad_rows:
+            inner = self._replay_or_capture(st, tail, use_graph)
+            return inner[:n_seqs]
+        return self._replay_or_capture(st, tail, use_graph)
+
+    def _replay_or_capture(self, st, tail, use_graph):
         def run():
             if tail is not None:
                 return self.model.forward(st["step"], self.cache, reduce=tail)    # a sampler has its own error word

@@ -47,7 +47,7 @@ class _Backend(GenerationBackend):
         before = up.bytes_sent
         # the sampler runs inside the step's graph; its ids stay valid until the next step of this batch
         # size is launched, and everything that reads them is queued before that
-        ids = self.engine.decode(self.slots, tokens, tail=self.sampler)
+        ids = self.engine.decode(self.slots, tokens, tail=self.sampler, pad=True)    # few row counts, few graphs
         self.h2d_bytes += up.bytes_sent - before
         self.d2h_bytes += 4 * (len(self.slots) + 1)
         self.decode_steps += 1

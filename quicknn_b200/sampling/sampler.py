@@ -63,6 +63,8 @@ class Sampler:
     def __call__(self, logits: torch.Tensor) -> torch.Tensor:
         """logits [R, V] float32 -> chosen ids [R] int32 (device)."""
         R = logits.shape[0]
+        if R > self.max_rows:
+            raise ValueError(f"the sampler was built for {self.max_rows} rows, the step has {R}")
         o = self.options
         seen_rows = None
         if self.seen is not None:
@@ -80,6 +82,8 @@ class Sampler:
         if not self.greedy_plain or weight.shape[0] != self.vocab or not ops.head_argmax_fusable(hidden, weight):
             return None
         R = hidden.shape[0]
+        if R > self.max_rows:
+            raise ValueError(f"the sampler was built for {self.max_rows} rows, the step has {R}")
         cand = self.scratch.view(torch.float32)
         ncand = ops.head_argmax(hidden, weight, cap, cand, self.flag)
         if ncand is None:

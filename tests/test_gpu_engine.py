@@ -230,6 +230,34 @@ def test_a_conversation_reuses_the_common_prefix(folders, plain_models, name, dt
     assert llm.memory_status()["live_sequences"] == 0
 
 
+@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("D", "bfloat16")])
+def test_padded_decode_steps_give_the_sequences_rows(folders, name, dtype):
+    """``Engine.decode(..., pad=True)`` runs 9 sequences as 10 rows and 13 as 14 (rows of no sequence at the end);
+    the logits of the sequences' rows are those of the unpadded step, and the cache holds what it would."""
+    eng_a = build(folders(name, dtype), dtype, max_tokens=64 * 24, max_slots=16, max_seq=64)
+    eng_b = build(folders(name, dtype), dtype, max_tokens=64 * 24, max_slots=16, max_seq=64)
+    assert [eng_a.decode_rows(n) for n in (1, 7, 8, 9, 10, 13, 15, 16)] == [1, 7, 8, 10, 10, 14, 16, 16]
+    for n in (9, 13):
+        prompts = prompts_for(name, [3 + (5 * i) % 11 for i in range(n)], seed=n)
+        slots_a = [eng_a.new_sequence() for _ in prompts]
+        slots_b = [eng_b.new_sequence() for _ in prompts]
+        eng_a.step(list(zip(slots_a, prompts)), "last")
+        eng_b.step(list(zip(slots_b, prompts)), "last")
+        tok = torch.tensor([p[0] for p in prompts], dtype=torch.int32, device=DEV)
+        for t in range(4):
+            la = eng_a.decode(slots_a, tok, pad=True)
+            lb = eng_b.decode(slots_b, tok)
+            assert la.shape == lb.shape == (n, TINY[name][0]["vocab_size"])
+            close(la.cpu().numpy(), lb.cpu().numpy(), dtype)
+            tok = lb.argmax(dim=-1).to(torch.int32)
+        assert [eng_a.length(s) for s in slots_a] == [eng_b.length(s) for s in slots_b]
+        for s in slots_a:
+            eng_a.release(s)
+        for s in slots_b:
+            eng_b.release(s)
+    assert sorted({k[0] for k in eng_a._decode_state}) == [10, 14] and sorted({k[0] for k in eng_b._decode_state}) == [9, 13]
+
+
 def test_running_one_step_ahead_changes_no_token(folders, plain_models):
     """The entry point queues each decode step before it reads the ids of the one before; rows
     that end (stop token, budget, full context) are dropped a step late and their extra token is
