@@ -230,6 +230,55 @@ def test_a_conversation_reuses_the_common_prefix(folders, plain_models, name, dt
     assert llm.memory_status()["live_sequences"] == 0
 
 
+@pytest.mark.parametrize("name,dtype,seed", [("A", "float32", 1), ("B", "float32", 2), ("C", "bfloat16", 3),
+                                             ("D", "bfloat16", 4), ("A", "float32", 5)])
+def test_random_schedules_of_steps_give_the_plain_logits(folders, plain_models, name, dtype, seed):
+    """Sequences of random lengths fed in random portions: in every step a random subset of the live sequences goes
+    on by a random number of tokens (one token each, several, whole prompts of sequences that start, all mixed),
+    logits are wanted at random places, finished sequences give their slots and pages back and new ones take
+    them.  Every logit equals the plain model's for the whole sequence, whatever the cutting and the company."""
+    rng = np.random.default_rng(seed)
+    plain = plain_models(name, dtype)
+    eng = build(folders(name, dtype), dtype, max_tokens=64 * 16, max_slots=5, max_seq=200)
+    todo = [rng.integers(1, TINY[name][0]["vocab_size"], int(n)).tolist() for n in rng.integers(1, 190, 14)]
+    ref = {}
+    live = {}                                          # slot -> [tokens, fed]
+    steps = checked = 0
+    modes = set()
+    while todo or live:
+        while todo and len(live) < 5 and (not live or rng.random() < 0.5):
+            live[eng.new_sequence()] = [todo.pop(), 0]
+        chosen = [s for s in live if rng.random() < 0.7] or [next(iter(live))]
+        kind = rng.integers(0, 3)
+        entries, want = [], []
+        for s in chosen:
+            toks, fed = live[s]
+            n = 1 if kind == 0 else int(rng.integers(1, 1 + min(len(toks) - fed, 3 if kind == 1 else 80)))
+            entries.append((s, toks[fed:fed + n]))
+            want.append(sorted(set(rng.integers(0, n, int(rng.integers(0, 3))).tolist())))
+        starts = [live[s][1] for s in chosen]
+        modes.add("prefill" if all(p == 0 for p in starts) else ("decode" if all(len(t) == 1 for _, t in entries) else "extend"))
+        logits = eng.step(entries, want).cpu().numpy()
+        row = 0
+        for (s, t), w in zip(entries, want):
+            toks, fed = live[s]
+            if id(toks) not in ref:
+                ref[id(toks)] = plain.logits(toks)
+            for place in w:
+                close(logits[row], ref[id(toks)][fed + place], dtype)
+                row += 1
+                checked += 1
+            live[s][1] = fed + len(t)
+            if live[s][1] == len(toks):
+                eng.release(s)
+                del live[s]
+        assert row == logits.shape[0]
+        steps += 1
+    assert modes == {"prefill", "decode", "extend"} and checked > 50 and steps > 30
+    assert eng.cache.slots.live() == []
+    eng.cache.audit()
+
+
 @pytest.mark.parametrize("name,dtype", [("A", "float32"), ("D", "bfloat16")])
 def test_padded_decode_steps_give_the_sequences_rows(folders, name, dtype):
     """``Engine.decode(..., pad=True)`` runs 9 sequences as 10 rows and 13 as 14 (rows of no sequence at the end);
