@@ -31,6 +31,48 @@ __global__ void embed_kernel(const int* __restrict__ tokens, const W* __restrict
     for (int j = threadIdx.x; j < H; j += blockDim.x) o[j] = to_f(row[j]) * scale;
 }
 
+// The same with the first norm of the first layer in the same kernel: out[t] as above, and
+// normed[t] = rmsnorm(out[t]; w) in `normed_dt` (one kernel less at the head of every step).
+template <typename W>
+__global__ void embed_rmsnorm_kernel(const int* __restrict__ tokens, const W* __restrict__ table, float scale,
+                                     float* __restrict__ out, int H, int V, const void* __restrict__ w, int w_dt,
+                                     float eps, float offset, void* __restrict__ normed, int normed_dt) {
+    pdl_wait();
+    __shared__ float red[32];
+    const int t = blockIdx.x;
+    const int tok = tokens[t];
+    const bool valid = tok >= 0 && tok < V;
+    const W* row = table + (size_t)(valid ? tok : 0) * H;
+    float* o = out + (size_t)t * H;
+    float ss = 0.f;
+    for (int j = threadIdx.x; j < H; j += blockDim.x) {
+        const float v = valid ? to_f(row[j]) * scale : 0.f;
+        o[j] = v;
+        ss += v * v;
+    }
+    ss = block_sum(ss, red);
+    const float inv = rsqrtf(ss / (float)H + eps);
+    for (int j = threadIdx.x; j < H; j += blockDim.x) {       // each thread re-reads what it wrote itself
+        const float g = load_as_f(w, w_dt, j) + offset;
+        store_from_f(normed, normed_dt, (size_t)t * H + j, o[j] * inv * g);
+    }
+}
+
+QNN_API int qnn_embed_rmsnorm(const int* tokens, const void* table, int table_dtype, float scale, float* out,
+                              const void* w, int w_dt, float eps, int unit_offset, void* normed, int normed_dt,
+                              int T, int H, int V, cudaStream_t st) {
+    if (T <= 0) return 0;
+    const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+    const float off = unit_offset ? 1.f : 0.f;
+    if (table_dtype == QNN_DT_BF16)
+        qnn::launch_pdl(embed_rmsnorm_kernel<bf16>, dim3(T), dim3(threads), 0, st, tokens, (const bf16*)table, scale, out, H,
+                        V, w, w_dt, eps, off, normed, normed_dt);
+    else
+        qnn::launch_pdl(embed_rmsnorm_kernel<float>, dim3(T), dim3(threads), 0, st, tokens, (const float*)table, scale, out,
+                        H, V, w, w_dt, eps, off, normed, normed_dt);
+    QNN_LAUNCH_CHECK();
+}
+
 QNN_API int qnn_embed(const int* tokens, const void* table, int table_dtype, float scale, float* out,
                       int T, int H, int V, cudaStream_t st) {
     if (T <= 0) return 0;

@@ -132,9 +132,13 @@ class Model:
         ``reduce`` has a method ``head(rows, weight, softcap)`` it is offered the rows that go into the
         output head first and may return its result without the logits ever being written."""
         spec = self.spec
-        x = ops.embed(step.tokens, self.embedding, spec.embedding.scale)
-        normed = None
         sched = spec.schedule
+        first = self.blocks[sched[0].layer].first_norm() if sched else None
+        if hasattr(first, "of_embedding"):
+            # the first layer's first norm in the embedding's kernel; the layer is handed its input normed
+            x, normed = first.of_embedding(step.tokens, self.embedding, spec.embedding.scale, step.act_dtype)
+        else:
+            x, normed = ops.embed(step.tokens, self.embedding, spec.embedding.scale), None
         for i, e in enumerate(sched):
             line = cache.line(e.cache, writes=e.writes_cache)
             # the first norm of the layer that runs next is applied by this one, in the kernel

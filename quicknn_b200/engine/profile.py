@@ -67,6 +67,7 @@ class StepProfiler:
         self._patch(RMSNorm, "add_to", "norms and residual")
         self._patch(ops, "add_", "norms and residual")
         self._patch(ops, "embed", "embedding")
+        self._patch(ops, "embed_rmsnorm", "embedding")
         self._patch(model, "logits_of_rows", "head")
         self._patch(Sampler, "__call__", "sampling")
         self._patch(Sampler, "head", "sampling")

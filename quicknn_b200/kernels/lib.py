@@ -18,6 +18,8 @@ c_int, c_float, c_ll, c_vp = ctypes.c_int, ctypes.c_float, ctypes.c_longlong, ct
 # name -> argument types (all return int)
 _SIGNATURES: Dict[str, list] = {
     "qnn_embed": [c_vp, c_vp, c_int, c_float, c_vp, c_int, c_int, c_int, c_vp],
+    "qnn_embed_rmsnorm": [c_vp, c_vp, c_int, c_float, c_vp, c_vp, c_int, c_float, c_int, c_vp, c_int, c_int, c_int, c_int,
+                          c_vp],
     "qnn_rmsnorm": [c_vp, c_int, c_vp, c_int, c_float, c_int, c_vp, c_int, c_int, c_int, c_vp],
     "qnn_add_rmsnorm": [c_vp, c_vp, c_int, c_vp, c_int, c_float, c_int, c_vp, c_int, c_float, c_int,
                         c_vp, c_int, c_int, c_int, c_vp],

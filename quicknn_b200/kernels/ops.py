@@ -75,6 +75,23 @@ def embed(tokens: torch.Tensor, table: torch.Tensor, scale: float, out: Optional
     return out
 
 
+def embed_rmsnorm(tokens: torch.Tensor, table: torch.Tensor, scale: float, weight: torch.Tensor, eps: float,
+                  unit_offset: bool, out_dtype: torch.dtype):
+    """``embed`` and the first norm of what it gives in one kernel: (rows [T, H] float32, rmsnorm(rows))."""
+    _req(tokens, "tokens", torch.int32, 1)
+    _req(table, "table", None, 2)
+    _req(weight, "weight", None, 1)
+    T, (V, H) = tokens.numel(), table.shape
+    if weight.numel() != H:
+        raise ValueError(f"norm weight has {weight.numel()} elements for width {H}")
+    out = torch.empty((T, H), dtype=torch.float32, device=tokens.device)
+    normed = torch.empty((T, H), dtype=out_dtype, device=tokens.device)
+    _lib.check(_lib.load().qnn_embed_rmsnorm(_p(tokens), _p(table), dt_code(table), float(scale), _p(out), _p(weight),
+                                             dt_code(weight), float(eps), int(unit_offset), _p(normed), dt_code(normed),
+                                             T, H, V, _stream()), "embed_rmsnorm")
+    return out, normed
+
+
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, unit_offset: bool, out_dtype: torch.dtype,
             out: Optional[torch.Tensor] = None):
     _req(x, "x", None, 2)

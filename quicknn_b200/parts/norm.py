@@ -37,6 +37,10 @@ class RMSNorm(Norm):
     def __call__(self, x: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
         return ops.rmsnorm(x, self.weight, self.eps, self.unit_offset, out_dtype)
 
+    def of_embedding(self, tokens: torch.Tensor, table: torch.Tensor, scale: float, out_dtype: torch.dtype):
+        """(embedded rows, self(embedded rows)) in one kernel: the first norm of a model's first layer."""
+        return ops.embed_rmsnorm(tokens, table, scale, self.weight, self.eps, self.unit_offset, out_dtype)
+
     def add_to(self, resid: torch.Tensor, y: torch.Tensor, then: Optional["RMSNorm"] = None,
                out_dtype: Optional[torch.dtype] = None) -> Optional[torch.Tensor]:
         """resid += self(y); returns then(resid) when ``then`` is given, in one kernel."""

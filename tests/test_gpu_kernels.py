@@ -56,6 +56,12 @@ def test_embed(ops, dtype):
     assert out.dtype == torch.float32
     assert_close(out, ref, torch.float32, "embed")
     assert float(out[3].abs().sum()) == 0.0 and float(out[4].abs().sum()) == 0.0   # ids outside the table
+    # the same rows with their first norm from the same kernel
+    w = bf16_round(rng.normal(size=100) * 0.2)
+    for act in (torch.float32, torch.bfloat16):
+        rows, normed = ops.embed_rmsnorm(T(ids, torch.int32), T(table, dtype), math.sqrt(100), T(w, dtype), 1e-6, True, act)
+        assert torch.equal(rows, out) and normed.dtype == act
+        assert_close(normed, P.rmsnorm(N(out), w, 1e-6), act, "embed + norm")
 
 
 @pytest.mark.parametrize("H", [8, 100, 2304])
