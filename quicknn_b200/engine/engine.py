@@ -197,11 +197,12 @@ class Engine:
         src/models/QuickNN.Models.LLM.pas:802-807).  Returns the logits of every row, or, with
         ``tail`` (a callable on the logits that launches device work only, such as a sampler),
         what ``tail`` returns: it then runs as part of the same graph, and its result lives in a
-        buffer that the next step of this batch size overwrites.
+        buffer that the next step replayed from the same graph overwrites.
 
-        The launch sequence of a batch size is captured in a CUDA graph the first time it
-        runs and replayed afterwards; lengths, page tables and ids are read from device
-        memory by the kernels, so one graph serves every step of that batch size.
+        The launch sequence is captured in a CUDA graph the first time it runs and replayed
+        afterwards; lengths, page tables and ids are read from device memory by the kernels, so
+        one graph serves every step of the same row count, ``tail`` and schedule (what the parts
+        decide from the lengths' classes, ``Part.schedule``).
 
         ``pad``: run the step with a few more rows than sequences (rows of no sequence, which attend to nothing
         and write nothing) so that a batch that shrinks one sequence at a time passes through few row counts
