@@ -148,6 +148,7 @@ class Conversation:
         self.slot: Optional[int] = None
         self.history: List[int] = []               # the tokens whose keys and values the cache holds
         self.reused = 0
+        self.said: List[int] = []                  # the last call's prompt and reply
 
     def __enter__(self) -> "Conversation":
         return self
@@ -198,6 +199,7 @@ class Conversation:
             self.reset()                           # what the cache holds is no longer known
             raise
         res.reused_tokens = self.reused
+        self.said = list(prompt) + list(res.tokens)
         if self.slot is not None:
             # the cache holds the prompt and every generated token that was fed back (the step that runs ahead
             # may have fed one that the loop then dropped: a stop token)
@@ -209,6 +211,15 @@ class Conversation:
             # (state that cannot go back keeps the dropped token: no later prompt matches beyond it)
             self.history = (known + [-1] * max(0, held - len(known)))[:held]
         return res
+
+
+    def continue_generation(self, options: Optional[GenerationOptions] = None, **kw) -> GenerationResult:
+        """Go on from where the last call stopped (``ContinueGeneration``, LLM.pas:1029-1047): the prompt is
+        everything said so far, all of which but the last token the cache still holds.  Greedy replies continue
+        as if they had never stopped; sampled ones draw from freshly seeded generators."""
+        if not self.said:
+            raise ValueError("nothing to continue: generate first")
+        return self.generate(self.said, options, **kw)
 
 
 class LLM:

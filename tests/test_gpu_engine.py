@@ -219,6 +219,12 @@ def test_a_conversation_reuses_the_common_prefix(folders, plain_models, name, dt
         r6 = conv.generate(p6, greedy, stop_ids=[])
         assert r6.reused_tokens == len(p5) - 3
         same(r6, p6)
+        # a reply continued after it stopped is the reply that never stopped
+        r6b = conv.continue_generation(greedy, stop_ids=[])
+        assert r6b.reused_tokens == len(p6) + len(r6.tokens) - 1
+        same(r6b, p6 + r6.tokens)
+        if dtype == "float32":
+            assert r6.tokens + r6b.tokens == plain.greedy(p6, 12)
         # an unrelated prompt starts over; and a batch beside the conversation leaves it alone
         p7 = prompts_for(name, [9], seed=11)[0]
         others = llm.generate([p1], greedy, stop_ids=[])
