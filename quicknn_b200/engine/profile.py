@@ -12,6 +12,8 @@ eager launches; the shares between the kinds of part are what the table is for.
     with StepProfiler(llm.engine) as prof:
         llm.generate(prompts, options)
     print(prof.table())
+
+``StepProfiler(engine, nvtx=True)`` also opens an NVTX range of the part's kind around every call.
 """
 from __future__ import annotations
 
@@ -27,8 +29,9 @@ KINDS = ("embedding", "norms and residual", "mixer", "feed-forward", "head", "sa
 
 
 class StepProfiler:
-    def __init__(self, engine):
+    def __init__(self, engine, nvtx: bool = False):
         self.engine = engine
+        self.nvtx = nvtx                         # also an NVTX range around every call of a part, for a timeline tool
         self._undo: List[Tuple[object, str, object]] = []
         self._open: List[list] = []            # the calls that are running: [kind, start, stop, time of the calls inside]
         self._calls: List[list] = []
@@ -44,11 +47,15 @@ class StepProfiler:
             else:
                 self._calls.append(rec)
             self._open.append(rec)
+            if self.nvtx:
+                torch.cuda.nvtx.range_push(kind)
             rec[1].record()
             try:
                 return fn(*a, **kw)
             finally:
                 rec[2].record()
+                if self.nvtx:
+                    torch.cuda.nvtx.range_pop()
                 self._open.pop()
         return call
 
