@@ -562,3 +562,6 @@ def test_the_profile_table_accounts_for_every_step_and_puts_everything_back(fold
     table = prof.table()
     assert "feed-forward" in table and "tokens/s" in table
     assert [r.tokens for r in llm.generate(prompts, opts, stop_ids=[])] == before
+    with StepProfiler(llm.engine, nvtx=True) as prof2:           # NVTX ranges around the same calls change nothing
+        assert [r.tokens for r in llm.generate(prompts, opts, stop_ids=[])] == before
+    assert prof2.by_kind()["mixer"] > 0
