@@ -249,6 +249,20 @@ class KVCache:
                 total += n * per_tok
         return total
 
+    def verify_device(self) -> None:
+        """The device copies of the page tables and lengths are what the host holds (after ``sync``, with the
+        copies complete: this waits for the device).  A check for tests and for hunting a fault: a page table that
+        reached the device late or from a reused staging buffer shows here, not as a wrong token somewhere."""
+        self.sync()
+        if torch.device(self.device).type == "cuda":
+            torch.cuda.synchronize(self.device)
+        for i, g in enumerate(self.groups):
+            if not np.array_equal(g.table_dev.cpu().numpy(), g.table_host):
+                bad = np.argwhere(g.table_dev.cpu().numpy() != g.table_host)[0]
+                raise AssertionError(f"group {i}: page table on the device differs at slot {bad[0]}, entry {bad[1]}")
+        if not np.array_equal(self.lengths_dev.cpu().numpy(), self.lengths_host):
+            raise AssertionError("the lengths on the device differ from the host's")
+
     def audit(self) -> None:
         """No page lost, held twice or freed twice; tables agree with what slots hold."""
         for g in self.groups:

@@ -202,3 +202,14 @@ def test_how_far_a_sequence_can_go_back():
     s = st.allocate()
     st.extend([(s, 40)])
     assert st.rewind_limit(s) == 40
+
+
+def test_the_device_copies_can_be_checked_against_the_host():
+    c = make()
+    a = c.allocate()
+    c.extend([(a, 100)])
+    c.verify_device()                              # on the CPU the "device" copies are plain tensors
+    c.groups[0].table_dev[a, 0] += 1
+    with pytest.raises(AssertionError):
+        c.verify_device()
+
