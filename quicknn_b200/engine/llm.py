@@ -11,6 +11,7 @@ import numpy as np
 import torch
 
 from ..config.base import Architecture, ModelConfig, find_architecture
+from ..config.generation import stop_ids_of_folder
 from ..cache.pages import PAGE, CacheFull
 from ..sampling import GenerationOptions, Sampler
 from ..weights.random_init import random_tensors
@@ -238,6 +239,10 @@ class LLM:
                 raise ValueError("give a model folder or a Model")
             model = Model.from_folder(model_dir, dtype, device)
         self.model = model
+        stops = list(model.spec.stop_ids)
+        if model_dir is not None:              # the folder's generation_config.json may add stop ids (LLM.pas:260-271)
+            stops = stop_ids_of_folder(model_dir, model.spec.embedding.vocab_size, stops)
+        self._stop_ids = stops
         if max_context > model.spec.max_positions:
             raise ValueError(f"max_context {max_context} exceeds max_position_embeddings {model.spec.max_positions}")
         if max_tokens is None:
@@ -261,8 +266,9 @@ class LLM:
 
     @property
     def stop_ids(self) -> List[int]:
-        """Stop ids from the configuration's ``eos_token_id`` (LLM.pas:166)."""
-        return list(self.model.spec.stop_ids)
+        """Stop ids from the configuration's ``eos_token_id`` (LLM.pas:166) and, for a model folder, from its
+        generation_config.json as well."""
+        return list(self._stop_ids)
 
     def _sampler(self, options: GenerationOptions) -> Sampler:
         key = (options.top_k, options.temperature, options.top_p, options.repetition_penalty, options.seed)

@@ -76,3 +76,26 @@ def test_round_trip_through_a_file(tmp_path):
     p.write_text(json.dumps(c.to_dict()))
     arch, c2 = load_config(str(tmp_path))
     assert arch.name == "Gemma2ForCausalLM" and c2 == c
+
+
+def test_stop_ids_of_a_folder(tmp_path):
+    """eos_token_id of generation_config.json joins the ids of config.json: an integer or a list, each id once,
+    an id outside the vocabulary or a file that is no JSON object is an error."""
+    import json
+    from quicknn_b200.config.generation import stop_ids_of_folder
+    d = str(tmp_path)
+    assert stop_ids_of_folder(d, 100, [1]) == [1]                     # no file: the configuration's ids
+    (tmp_path / "generation_config.json").write_text(json.dumps({"eos_token_id": [1, 7, [9, 7]], "top_k": 5}))
+    assert stop_ids_of_folder(d, 100, [1, 3, 1]) == [1, 3, 7, 9]
+    (tmp_path / "generation_config.json").write_text(json.dumps({"eos_token_id": 42}))
+    assert stop_ids_of_folder(d, 100, []) == [42]
+    (tmp_path / "generation_config.json").write_text(json.dumps({"temperature": 1.0}))
+    assert stop_ids_of_folder(d, 100, [2]) == [2]
+    for bad in ({"eos_token_id": 100}, {"eos_token_id": -1}, {"eos_token_id": "1"}, {"eos_token_id": True}, [1]):
+        (tmp_path / "generation_config.json").write_text(json.dumps(bad))
+        with pytest.raises(ValueError):
+            stop_ids_of_folder(d, 100, [1])
+    (tmp_path / "generation_config.json").write_text("{not json")
+    with pytest.raises(ValueError):
+        stop_ids_of_folder(d, 100, [1])
+

@@ -130,6 +130,25 @@ def test_greedy_generation_through_the_entry_point(folders, plain_models, name, 
     assert np.abs(llm.evaluate_tokens(prompts[1]) - plain.logits(prompts[1])[-1]).max() < (1e-4 if dtype == "float32" else 0.1)
 
 
+def test_stop_ids_of_generation_config_json_end_a_request(folders, plain_models, tmp_path):
+    """A folder's generation_config.json adds its eos_token_id to the stop ids of config.json (LLM.pas:260-271)."""
+    import json
+    import shutil
+    from quicknn_b200.engine import LLM
+    from quicknn_b200.sampling import GenerationOptions
+    plain = plain_models("A", "float32")
+    prompt = prompts_for("A", [9], seed=3)[0]
+    ref = plain.greedy(prompt, 8)
+    stop = next(t for t in ref[2:] if t not in ref[:2])
+    folder = tmp_path / "model"
+    shutil.copytree(folders("A", "float32"), folder)
+    (folder / "generation_config.json").write_text(json.dumps({"eos_token_id": [stop]}))
+    llm = LLM(str(folder), max_context=64, max_batch=1, dtype="float32")
+    assert stop in llm.stop_ids and set(llm.model.spec.stop_ids) <= set(llm.stop_ids)
+    res = llm.generate([prompt], GenerationOptions.greedy(8))[0]
+    assert res.finish_reason == "eos" and res.tokens == ref[:ref.index(stop)]
+
+
 def test_more_requests_than_slots_reuse_them(folders, plain_models):
     from quicknn_b200.engine import LLM
     from quicknn_b200.sampling import GenerationOptions
