@@ -29,8 +29,10 @@ class _Backend(GenerationBackend):
     is thrown away with the row's slot, and the other rows' ids do not depend on it.  A step
     runs ahead only if every row has room for one more token."""
 
-    def __init__(self, engine: Engine, sampler: Sampler, max_batch: int, run_ahead: bool = True):
+    def __init__(self, engine: Engine, sampler: Sampler, max_batch: int, run_ahead: bool = True,
+                 seed: Optional[int] = None):
         self.engine, self.sampler = engine, sampler
+        self.seed = seed
         self.max_batch = max_batch
         self.max_tokens = engine.cache.max_tokens
         self.max_seq = engine.max_seq
@@ -66,7 +68,7 @@ class _Backend(GenerationBackend):
     def begin(self, first_index: int, prompts: Sequence[Sequence[int]]) -> np.ndarray:
         eng = self.engine
         self.slots = [eng.new_sequence() for _ in prompts]
-        self.sampler.start(first_index, len(prompts))
+        self.sampler.start(first_index, len(prompts), self.seed)
         if self.sampler.penalised:
             toks = torch.tensor([t for p in prompts for t in p], dtype=torch.int32, device=eng.device)
             rows = torch.tensor([r for r, p in enumerate(prompts) for _ in p], dtype=torch.int32, device=eng.device)
@@ -109,8 +111,8 @@ class _ConversationBackend(_Backend):
     """The backend of a ``Conversation``: one sequence whose slot outlives the call.  ``begin`` keeps what
     the cache holds of the new prompt and runs only the rest; ``finish`` releases nothing."""
 
-    def __init__(self, engine: Engine, sampler: Sampler, run_ahead: bool, conv: "Conversation"):
-        super().__init__(engine, sampler, 1, run_ahead)
+    def __init__(self, engine: Engine, sampler: Sampler, run_ahead: bool, conv: "Conversation", seed: Optional[int] = None):
+        super().__init__(engine, sampler, 1, run_ahead, seed)
         self.conv = conv
 
     def begin(self, first_index: int, prompts: Sequence[Sequence[int]]) -> np.ndarray:
@@ -118,7 +120,7 @@ class _ConversationBackend(_Backend):
         prompt = list(prompts[0])
         common = conv.keep_common_prefix(prompt)
         self.slots = [conv.slot]
-        self.sampler.start(first_index, 1)
+        self.sampler.start(first_index, 1, self.seed)
         if self.sampler.penalised:                 # the whole prompt counts as seen, reused or not (LLM.pas:737-744)
             toks = torch.tensor(prompt, dtype=torch.int32, device=eng.device)
             self.sampler.mark_prompt(toks, torch.zeros(len(prompt), dtype=torch.int32, device=eng.device))
@@ -191,7 +193,7 @@ class Conversation:
         llm = self.llm
         options = options or GenerationOptions()
         options.validate()
-        backend = _ConversationBackend(llm.engine, llm._sampler(options), llm.run_ahead, self)
+        backend = _ConversationBackend(llm.engine, llm._sampler(options), llm.run_ahead, self, options.seed)
         stops = llm.stop_ids if stop_ids is None else list(stop_ids)
         self.reused = 0
         try:
@@ -271,7 +273,10 @@ class LLM:
         return list(self._stop_ids)
 
     def _sampler(self, options: GenerationOptions) -> Sampler:
-        key = (options.top_k, options.temperature, options.top_p, options.repetition_penalty, options.seed)
+        # what the captured decode steps bake in; the seed is not part of it (it only sets the generators' states)
+        key = (options.top_k, options.temperature, options.top_p, options.repetition_penalty)
+        if options.temperature <= 0:
+            key = ("greedy", options.repetition_penalty)          # an arg-max whatever top_k and top_p say
         s = self._samplers.get(key)
         if s is None:
             if len(self._samplers) > 4:
@@ -290,7 +295,7 @@ class LLM:
         up to ``max_batch``, one batch after another."""
         options = options or GenerationOptions()
         options.validate()
-        backend = _Backend(self.engine, self._sampler(options), self.max_batch, self.run_ahead)
+        backend = _Backend(self.engine, self._sampler(options), self.max_batch, self.run_ahead, options.seed)
         stops = self.stop_ids if stop_ids is None else list(stop_ids)
         try:
             return generate(backend, prompts, options, stops, on_token, should_cancel)

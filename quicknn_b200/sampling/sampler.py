@@ -40,9 +40,12 @@ class Sampler:
         if self.penalised:
             self.seen = torch.zeros((max_rows, vocab_size), dtype=torch.uint8, device=device)
 
-    def start(self, first_index: int, n_rows: int) -> None:
-        """Seed rows 0..n_rows-1 for the requests first_index, first_index+1, ..."""
-        states = np.array([seed_state(self.options.seed, first_index + i) for i in range(n_rows)], dtype=np.uint32)
+    def start(self, first_index: int, n_rows: int, seed: Optional[int] = None) -> None:
+        """Seed rows 0..n_rows-1 for the requests first_index, first_index+1, ... (``seed``: instead of the
+        options' own, so that one sampler, and the decode graphs that embed it, serve calls that differ in
+        nothing but the seed)."""
+        seed = self.options.seed if seed is None else seed
+        states = np.array([seed_state(seed, first_index + i) for i in range(n_rows)], dtype=np.uint32)
         self.rng[:n_rows].copy_(torch.from_numpy(states.view(np.int32)))
         if self.seen is not None:
             self.seen[:n_rows].zero_()

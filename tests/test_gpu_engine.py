@@ -438,6 +438,13 @@ def test_many_option_sets_do_not_pile_up_graphs(folders):
         assert len({k[1] for k in llm.engine._decode_state}) <= 5
     again = llm.generate(prompts, GenerationOptions(max_new_tokens=4, temperature=0.7, seed=0), stop_ids=[])
     assert [r.tokens for r in again] == first
+    assert len(llm._samplers) == 1                      # calls that differ in the seed alone share a sampler and its graphs
+    for k in (3, 5, 7, 9, 11, 13):
+        llm.generate(prompts, GenerationOptions(max_new_tokens=2, temperature=0.7, top_k=k), stop_ids=[])
+        assert len(llm._samplers) <= 5 and len({key[1] for key in llm.engine._decode_state}) <= 5
+    for k in (3, 5, 7):                                 # greedy is greedy whatever top_k says
+        llm.generate(prompts, GenerationOptions(max_new_tokens=2, temperature=0.0, top_k=k), stop_ids=[])
+    assert sum(1 for key in llm._samplers if key[0] == "greedy") == 1
     assert llm.engine.cache.slots.live() == []
 
 
