@@ -304,6 +304,40 @@ class LLM:
             self.last_io = {"decode_steps": backend.decode_steps, "h2d_bytes_per_step": backend.h2d_bytes / n,
                             "d2h_bytes_per_step": backend.d2h_bytes / n}
 
+    def warm_up(self, options: Optional[GenerationOptions] = None, batch_sizes: Optional[Sequence[int]] = None,
+                context: Optional[int] = None) -> int:
+        """Capture the decode graphs that ``generate`` with these options would otherwise capture on the way (about
+        10 ms each, in the middle of a reply): for every row count that batches of ``batch_sizes`` (default: all up
+        to ``max_batch``) pass through, at sequences of ``context`` tokens (default: the longest allowed; the
+        schedule of a step depends on the lengths' class).  The cache contents of the dummy sequences are whatever
+        the pages held; their tokens are thrown away.  Returns the number of decode states held afterwards."""
+        opts = options or GenerationOptions()
+        opts.validate()
+        eng, sampler = self.engine, self._sampler(opts)
+        sizes = sorted({b for b in (batch_sizes or range(1, self.max_batch + 1)) if 1 <= b <= self.max_batch})
+        length = max(1, min(context or eng.max_seq, eng.max_seq) - 3)
+        done = set()
+        for b in sizes:
+            rows = eng.decode_rows(b)
+            if rows in done or b * (length + 3) > eng.cache.max_tokens:
+                continue
+            done.add(rows)
+            slots = [eng.new_sequence() for _ in range(b)]
+            try:
+                eng.cache.extend([(s, length) for s in slots])
+                sampler.start(0, b, opts.seed)
+                tok = torch.ones(b, dtype=torch.int32, device=eng.device)
+                for _ in range(2):                                  # the eager pass with the capture, then a replay
+                    tok = eng.decode(slots, tok, tail=sampler, pad=True)
+                try:
+                    sampler.read(tok)
+                except Exception:                                   # whatever the stale pages gave: nothing is kept
+                    pass
+            finally:
+                for s in slots:
+                    eng.release(s)
+        return len(eng._decode_state)
+
     def conversation(self) -> Conversation:
         """A sequence that keeps its cache between calls and reuses the common prefix of successive prompts."""
         return Conversation(self)

@@ -149,6 +149,24 @@ def test_stop_ids_of_generation_config_json_end_a_request(folders, plain_models,
     assert res.finish_reason == "eos" and res.tokens == ref[:ref.index(stop)]
 
 
+def test_warm_up_captures_the_graphs_that_generation_then_finds(folders, plain_models):
+    from quicknn_b200.engine import LLM
+    from quicknn_b200.sampling import GenerationOptions
+    plain = plain_models("A", "float32")
+    llm = LLM(folders("A", "float32"), max_context=64, max_batch=6, dtype="float32")
+    opts = GenerationOptions.greedy(5)
+    states = llm.warm_up(opts, context=40)
+    assert states == 6 and sorted({k[0] for k in llm.engine._decode_state}) == [1, 2, 3, 4, 5, 6]
+    assert llm.memory_status()["live_sequences"] == 0
+    llm.engine.cache.audit()
+    prompts = prompts_for("A", [30, 12, 33, 20], seed=4)
+    res = llm.generate(prompts, opts, stop_ids=[])
+    for r, p in zip(res, prompts):
+        assert r.tokens == plain.greedy(p, 5)
+    assert len(llm.engine._decode_state) == states                    # nothing new had to be captured
+    assert llm.warm_up(opts, batch_sizes=[2, 3], context=40) == states
+
+
 def test_more_requests_than_slots_reuse_them(folders, plain_models):
     from quicknn_b200.engine import LLM
     from quicknn_b200.sampling import GenerationOptions
