@@ -308,7 +308,8 @@ def test_random_schedules_of_steps_give_the_plain_logits(folders, plain_models, 
             if id(toks) not in ref:
                 ref[id(toks)] = plain.logits(toks)
             for place in w:
-                close(logits[row], ref[id(toks)][fed + place], dtype)
+                ok, err, tol = close(logits[row], ref[id(toks)][fed + place], dtype)
+                assert ok, f"step {steps}, place {fed + place} of {len(toks)}: error {err:.3g} above {tol:.3g}"
                 row += 1
                 checked += 1
             live[s][1] = fed + len(t)
@@ -342,7 +343,8 @@ def test_padded_decode_steps_give_the_sequences_rows(folders, name, dtype):
             la = eng_a.decode(slots_a, tok, pad=True)
             lb = eng_b.decode(slots_b, tok)
             assert la.shape == lb.shape == (n, TINY[name][0]["vocab_size"])
-            close(la.cpu().numpy(), lb.cpu().numpy(), dtype)
+            ok, err, tol = close(la.cpu().numpy(), lb.cpu().numpy(), dtype)
+            assert ok, f"{n} sequences, token {t}: error {err:.3g} above {tol:.3g}"
             tok = lb.argmax(dim=-1).to(torch.int32)
         assert [eng_a.length(s) for s in slots_a] == [eng_b.length(s) for s in slots_b]
         for s in slots_a:
