@@ -557,3 +557,72 @@ QNN_API int qnn_sgemm_f32(const float* A, const float* B, float* C, int M, int N
     else return QNN_ERR_ARGUMENT;
     QNN_LAUNCH_CHECK();
 }
+
+// ---------------------------------------------------------------------------------
+// bfloat16 product for inner sizes that are no multiple of 8 (rows that do not start on 16 bytes, so
+// neither the vector loads of the small-M kernel nor a TMA map can be used): one warp per output
+// column, 8 rows at a time, lanes stride K with 2-byte loads, float32 sums.  Slow and only there so
+// that such a width is served rather than refused; the order of additions depends on K only.
+// ---------------------------------------------------------------------------------
+template <int EPI>
+__global__ void linear_bf16_any_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, void* __restrict__ out,
+                                       int out_f32, int M, int N, int K, float cap, int act) {
+    pdl_wait();
+    constexpr int MT = 8;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int Nout = (EPI == EPI_GATED) ? N / 2 : N;
+    const int n = blockIdx.x * (blockDim.x >> 5) + warp;
+    const int m0 = blockIdx.y * MT;
+    if (n >= Nout) return;
+    float acc[MT], accu[MT];
+#pragma unroll
+    for (int m = 0; m < MT; ++m) acc[m] = accu[m] = 0.f;
+    const bf16* w = W + (size_t)n * K;
+    const bf16* u = W + (size_t)(Nout + n) * K;
+    for (int k = lane; k < K; k += 32) {
+        const float wv = __bfloat162float(w[k]);
+        const float uv = (EPI == EPI_GATED) ? __bfloat162float(u[k]) : 0.f;
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+            if (m0 + m < M) {
+                const float xv = __bfloat162float(x[(size_t)(m0 + m) * K + k]);
+                acc[m] += xv * wv;
+                if (EPI == EPI_GATED) accu[m] += xv * uv;
+            }
+        }
+    }
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+        float v = warp_sum(acc[m]);
+        const float uu = (EPI == EPI_GATED) ? warp_sum(accu[m]) : 0.f;
+        if (lane == 0 && m0 + m < M) {
+            if (EPI == EPI_GATED) v = activate(v, act) * uu;
+            else if (EPI == EPI_SOFTCAP) v = softcap(v, cap);
+            const size_t at = (size_t)(m0 + m) * Nout + n;
+            if (out_f32) reinterpret_cast<float*>(out)[at] = v;
+            else reinterpret_cast<bf16*>(out)[at] = __float2bfloat16_rn(v);
+        }
+    }
+}
+
+QNN_API int qnn_linear_bf16_any(const void* x, const void* W, void* out, int out_dt, int M, int N, int K, int epi,
+                                float cap, int act, cudaStream_t st) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0) return QNN_ERR_ARGUMENT;
+    if (epi == EPI_GATED && (N % 2)) return QNN_ERR_ARGUMENT;
+    if (out_dt != QNN_DT_BF16 && out_dt != QNN_DT_F32) return QNN_ERR_ARGUMENT;
+    const int Nout = epi == EPI_GATED ? N / 2 : N;
+    const int warps = 4;
+    const dim3 grid((unsigned)((Nout + warps - 1) / warps), (unsigned)((M + 7) / 8));
+    if (grid.y > 65535) return QNN_ERR_UNSUPPORTED;
+    const bf16* xp = (const bf16*)x;
+    const bf16* wp = (const bf16*)W;
+    const int f32 = out_dt == QNN_DT_F32;
+    switch (epi) {
+        case EPI_NONE: qnn::launch_pdl(linear_bf16_any_kernel<EPI_NONE>, grid, dim3(warps * 32), 0, st, xp, wp, out, f32, M, N, K, cap, act); break;
+        case EPI_SOFTCAP: qnn::launch_pdl(linear_bf16_any_kernel<EPI_SOFTCAP>, grid, dim3(warps * 32), 0, st, xp, wp, out, f32, M, N, K, cap, act); break;
+        case EPI_GATED: qnn::launch_pdl(linear_bf16_any_kernel<EPI_GATED>, grid, dim3(warps * 32), 0, st, xp, wp, out, f32, M, N, K, cap, act); break;
+        default: return QNN_ERR_ARGUMENT;
+    }
+    QNN_LAUNCH_CHECK();
+}

@@ -35,6 +35,7 @@ _SIGNATURES: Dict[str, list] = {
     "qnn_skinny_argmax": [c_vp, c_vp, c_vp, c_int, c_int, c_int, c_float, c_vp, c_vp],
     "qnn_skinny_qkv_rope": [c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_int, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp,
                             c_int, c_int, c_int, c_vp, c_int, c_vp],
+    "qnn_linear_bf16_any": [c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_vp],
     "qnn_gemv_f32": [c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_float, c_int, c_vp],
     "qnn_sgemm_f32": [c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_float, c_vp],
     "qnn_gemm_tcgen05": [c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_int, c_vp, c_vp],

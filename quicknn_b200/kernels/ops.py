@@ -431,8 +431,11 @@ def linear(x: torch.Tensor, w: torch.Tensor, *, epilogue: int = EPI_NONE, cap: O
             _lib.check(L.qnn_sgemm_f32(_p(x), _p(w), _p(out), M, N, K, epilogue, capv, _stream()), "sgemm_f32")
         return out
     # bfloat16
-    if K % 8:
-        raise _lib.KernelError(f"bfloat16 products need an inner size that is a multiple of 8 (got {K})")
+    if K % 8:                                  # rows that do not start on 16 bytes: the plain kernel for any inner size
+        out = torch.empty((M, n_out), dtype=out_dtype, device=x.device)
+        _lib.check(L.qnn_linear_bf16_any(_p(x), _p(w), _p(out), dt_code(out), M, N, K, epilogue, capv, act, _stream()),
+                   "linear_bf16_any")
+        return out
     if _takes_skinny_tcgen05(M, N, K) and out_dtype == (torch.float32 if epilogue == EPI_SOFTCAP else torch.bfloat16):
         y = gemm_skinny_tcgen05(x, w, epilogue=epilogue, cap=cap, activation=activation)
         if y is not None:
@@ -489,9 +492,10 @@ def attention_refusal(dtype: torch.dtype, n_heads: int, n_kv: int, head_dim: int
 
 
 def linear_refusal(dtype: torch.dtype, inner: int) -> Optional[str]:
-    """None if the matrix products take this inner size in ``dtype``, else the reason."""
-    if dtype == torch.bfloat16 and inner % 8:
-        return f"bfloat16 products need an inner size that is a multiple of 8 (got {inner})"
+    """None if the matrix products take this inner size in ``dtype``, else the reason.  Every size is taken:
+    bfloat16 rows of whole 16-byte pieces (a multiple of 8) by the tensor-core kernels, others by a plain one."""
+    if inner <= 0:
+        return f"an inner size of {inner}"
     return None
 
 

@@ -61,7 +61,17 @@ TINY_D = dict(
     query_pre_attn_scalar=256, eos_token_id=1, bos_token_id=2, initializer_range=0.03,
     hidden_activation="gelu_pytorch_tanh", tie_word_embeddings=True)
 
-TINY = {"A": (TINY_A, TINY_A_SEED, TINY_A_NORM_STD), "B": (TINY_B, TINY_B_SEED, TINY_B_NORM_STD),
+# Tiny E: a width, a feed-forward width and a vocabulary that are no multiple of 8 (bfloat16 rows that do not
+# start on 16 bytes), five query heads on five kv heads, one layer more than a local/global pair.
+TINY_E = dict(
+    architectures=["Gemma2ForCausalLM"], model_type="gemma2",
+    hidden_size=100, intermediate_size=70, num_attention_heads=5, num_key_value_heads=5, head_dim=16,
+    vocab_size=301, num_hidden_layers=3, max_position_embeddings=1024, rope_theta=20000.0,
+    rms_norm_eps=1e-4, sliding_window=11, attn_logit_softcapping=40.0, final_logit_softcapping=None,
+    query_pre_attn_scalar=20, eos_token_id=1, bos_token_id=2, initializer_range=0.05,
+    hidden_activation="gelu_pytorch_tanh", tie_word_embeddings=True)
+
+TINY = {"E": (TINY_E, 4, 0.15), "A": (TINY_A, TINY_A_SEED, TINY_A_NORM_STD), "B": (TINY_B, TINY_B_SEED, TINY_B_NORM_STD),
         "C": (TINY_C, 2, 0.15), "D": (TINY_D, 3, 0.1)}
 
 

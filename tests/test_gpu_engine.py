@@ -93,7 +93,7 @@ def test_padding_rows_change_no_result(folders, dtype):
     assert np.array_equal(again, base)
 
 
-@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("B", "float32"), ("A", "bfloat16")])
+@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("B", "float32"), ("A", "bfloat16"), ("E", "bfloat16")])
 def test_greedy_generation_through_the_entry_point(folders, plain_models, name, dtype):
     from quicknn_b200.engine import LLM
     from quicknn_b200.sampling import GenerationOptions

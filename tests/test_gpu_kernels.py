@@ -140,10 +140,26 @@ def test_skinny_bf16(ops, M, N_, K):
     assert_close(y, P.gelu_tanh(ref[:, :h]) * ref[:, h:], torch.bfloat16, "skinny geglu")
 
 
-def test_bf16_products_refuse_odd_inner_sizes(ops):
-    from quicknn_b200.kernels.lib import KernelError
-    with pytest.raises(KernelError):
-        ops.linear(torch.zeros(2, 12, dtype=torch.bfloat16, device=DEV), torch.zeros(4, 12, dtype=torch.bfloat16, device=DEV))
+@pytest.mark.parametrize("M", [1, 7, 9, 70])
+@pytest.mark.parametrize("N_,K", [(50, 100), (130, 50), (36, 7), (1001, 36)])
+def test_bf16_products_of_inner_sizes_that_are_no_multiple_of_8(ops, M, N_, K):
+    """Rows that do not start on 16 bytes go to the plain kernel: same roundings (bfloat16 in, float32 sums)."""
+    rng = np.random.default_rng(M * 1000 + N_)
+    x, w = bf16_round(rng.normal(size=(M, K))), bf16_round(rng.normal(size=(N_ & ~1, K)) / math.sqrt(K))
+    ref = x @ w.T
+    y = ops.linear(T(x, torch.bfloat16), T(w, torch.bfloat16))
+    assert y.dtype == torch.bfloat16 and tuple(y.shape) == (M, N_ & ~1)
+    assert_close(y, ref, torch.bfloat16, "any inner size")
+    y = ops.linear(T(x, torch.bfloat16), T(w, torch.bfloat16), epilogue=ops.EPI_SOFTCAP, cap=2.0)
+    assert y.dtype == torch.float32
+    assert_close(y, P.softcap(ref, 2.0), torch.float32, "any inner size, softcap", mult=50)
+    y = ops.linear(T(x, torch.bfloat16), T(w, torch.bfloat16), epilogue=ops.EPI_GATED, activation="gelu_tanh")
+    h = (N_ & ~1) // 2
+    assert tuple(y.shape) == (M, h)
+    assert_close(y, P.gelu_tanh(ref[:, :h]) * ref[:, h:], torch.bfloat16, "any inner size, geglu")
+
+
+def test_products_refuse_mixed_precisions(ops):
     with pytest.raises(TypeError):
         ops.linear(torch.zeros(2, 16, dtype=torch.bfloat16, device=DEV), torch.zeros(4, 16, device=DEV))
 

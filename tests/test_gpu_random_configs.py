@@ -24,10 +24,10 @@ def random_config(rng, dtype):
     hd = int(rng.choice([16, 32, 48, 64, 80, 128] if dtype == "bfloat16" else [8, 16, 24, 40, 64]))
     nkv = int(rng.choice([1, 2, 3, 4]))
     group = int(rng.choice([1, 2, 3, 4, 8]))
-    hidden = int(rng.choice([40, 72, 96, 136, 200]))
+    hidden = int(rng.choice([36, 40, 50, 72, 96, 100, 136, 200]))
     return dict(
         architectures=["Gemma2ForCausalLM"], model_type="gemma2", hidden_size=hidden,
-        intermediate_size=int(rng.choice([64, 88, 160, 264])), num_attention_heads=nkv * group, num_key_value_heads=nkv,
+        intermediate_size=int(rng.choice([64, 70, 88, 100, 160, 264])), num_attention_heads=nkv * group, num_key_value_heads=nkv,
         head_dim=hd, vocab_size=int(rng.integers(100, 1200)), num_hidden_layers=int(rng.integers(1, 5)),
         max_position_embeddings=512, rope_theta=float(rng.choice([1e4, 5e4, 1e6])),
         rms_norm_eps=float(rng.choice([1e-6, 1e-5, 1e-4])), sliding_window=int(rng.choice([4, 9, 33, 64, 100, 400])),

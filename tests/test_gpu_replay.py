@@ -107,7 +107,8 @@ def run_all_cuttings(replay, requests, ref, dtype):
                                               ("B", "float32", False), ("B", "bfloat16", False),
                                               ("B", "float32", True), ("A", "bfloat16", True),
                                               ("C", "bfloat16", False), ("C", "float32", True),
-                                              ("D", "bfloat16", False), ("D", "float32", False)])
+                                              ("D", "bfloat16", False), ("D", "float32", False),
+                                              ("E", "bfloat16", False), ("E", "float32", True)])
 def test_every_cutting_gives_the_plain_logits(folders, plain_models, tmp_path, name, dtype, peaky):
     # The peaky variant of C is run in float32 only: with its head size and depth the bfloat16
     # rounding of the activations alone (whatever kernels compute the attention) moves the logits
@@ -153,11 +154,15 @@ def test_replay_refuses_more_tokens_than_it_was_sized_for(folders, tmp_path):
 
 
 @pytest.mark.parametrize("name,dtype,peaky", [("A", "float32", True), ("B", "float32", False), ("B", "bfloat16", False),
-                                              ("C", "float32", True), ("D", "bfloat16", False)])
+                                              ("C", "float32", True), ("D", "bfloat16", False),
+                                              ("E", "bfloat16", False), ("E", "float32", True)])
 def test_prompts_cut_into_portions_and_requests_that_join_or_sit_out(folders, plain_models, tmp_path, name, dtype, peaky):
     """Steps that are neither whole prompts nor one token each: a request goes on by several tokens
     (portions of 2, portions that end on the 64-token page edge, portions longer than the window), sits
-    out a step, or starts while others go on.  Same logits at every position as the plain model."""
+    out a step, or starts while others go on.  Same logits at every position as the plain model.
+    (Tiny E with scaled queries and keys runs in float32 only: in bfloat16 the rounding of its activations alone
+    moves the logits by 8 % of their size, in whole prompts as in portions, while float32 on the same weights is
+    exact.)"""
     folder = folders(name, dtype, peaky)
     plain = plain_models(name, dtype, peaky)
     big = name in ("C", "D")
