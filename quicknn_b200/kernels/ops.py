@@ -401,8 +401,9 @@ def linear(x: torch.Tensor, w: torch.Tensor, *, epilogue: int = EPI_NONE, cap: O
     """y = x w^T with an optional epilogue.  x: [M, K]; w: [N, K] (gated: [2*N_out, K]).
 
     float32: FFMA kernels only.  bfloat16: the tensor-core small-M kernel up to 64 rows (the cluster
-    split-K tcgen05 kernel from 9 rows on against big matrices), the tcgen05/TMA kernel above that; a
-    library product (cuBLAS) only when QNN_GEMM=cublas is set."""
+    split-K tcgen05 kernel from 9 rows on against big matrices), the tcgen05/TMA kernel above that; an inner
+    size that is no multiple of 8 (rows that do not start on 16 bytes) goes to a plain kernel; a library
+    product (cuBLAS) only when QNN_GEMM=cublas is set."""
     _req(x, "x", None, 2)
     _req(w, "w", None, 2)
     M, K = x.shape
