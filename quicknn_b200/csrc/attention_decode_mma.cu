@@ -368,34 +368,68 @@ size_t smem_bytes(int max_pages) {
     return smem + ((size_t)max_pages + 2) * sizeof(int);
 }
 
-// Whether the device can hold a cluster of CLUSTER_MAX CTAs of this kernel (asked once).
+// How many clusters of `size` CTAs of this kernel the device holds at once (asked once per size; 0: none, or
+// clusters are switched off).  Clusters are placed inside a GPC, so fewer CTAs may fit than as a plain grid.
 template <int HD, int MMA_WARPS>
-bool cluster_fits(size_t smem) {
+int clusters_at_once(size_t smem, int size) {
     constexpr int ST = stages<HD, true>();
-    static int fits = -1;
-    if (fits < 0) {
+    static int known[CLUSTER_MAX + 1] = {-1, -1, -1, -1, -1};
+    if (size < 1 || size > CLUSTER_MAX) return 0;
+    if (known[size] < 0) {
         const char* e = getenv("QNN_ATTN_CLUSTER");
-        fits = 0;
+        known[size] = 0;
         if (!(e && e[0] == '0')) {
             cudaLaunchConfig_t cfg = {};
-            cfg.gridDim = dim3(CLUSTER_MAX, 1, 1);
+            cfg.gridDim = dim3(size, 1, 1);
             cfg.blockDim = dim3(MMA_WARPS * 32);
             cfg.dynamicSmemBytes = smem;
             cudaLaunchAttribute attr[1];
             attr[0].id = cudaLaunchAttributeClusterDimension;
-            attr[0].val.clusterDim.x = CLUSTER_MAX;
+            attr[0].val.clusterDim.x = size;
             attr[0].val.clusterDim.y = 1;
             attr[0].val.clusterDim.z = 1;
             cfg.attrs = attr;
             cfg.numAttrs = 1;
             int n = 0;
             if (cudaOccupancyMaxActiveClusters(&n, attn_decode_mma_kernel<HD, MMA_WARPS, ST>, &cfg) == cudaSuccess && n > 0)
-                fits = 1;
+                known[size] = n;
             else
                 (void)cudaGetLastError();
         }
     }
-    return fits == 1;
+    return known[size];
+}
+
+// CTAs of this kernel that the device holds at once as a plain grid (asked once).
+template <int HD, int MMA_WARPS>
+int ctas_at_once(size_t smem) {
+    constexpr int ST = stages<HD, false>();
+    static int known = -1;
+    if (known < 0) {
+        int per_sm = 0, dev = 0, sms = 0;
+        known = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attn_decode_mma_kernel<HD, MMA_WARPS, ST>,
+                                                          MMA_WARPS * 32, smem) == cudaSuccess &&
+            cudaGetDevice(&dev) == cudaSuccess &&
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess)
+            known = per_sm * sms;
+        else
+            (void)cudaGetLastError();
+    }
+    return known;
+}
+
+// Whether a grid of `clusters` clusters of `size` CTAs merges its key ranges inside the clusters.  Yes if
+// they all fit the device at once, or if the device holds nearly as many CTAs in clusters of this size as
+// it holds plain ones (a grid of several rounds loses little then).  Measured at head size 256, 24
+// sequences x 4 kv heads x 3 ranges at context 8192: 96 clusters of 3 do not fit at once where 288 plain
+// CTAs do, and a step of 6 layers took 1.58 ms against 1.08 ms with the combine kernel.
+template <int HD, int MMA_WARPS>
+bool merge_in_clusters(size_t smem_plain, size_t smem_cluster, int size, long long clusters) {
+    const int at_once = clusters_at_once<HD, MMA_WARPS>(smem_cluster, size);
+    if (at_once <= 0) return false;
+    if (clusters <= at_once) return true;
+    return (long long)at_once * size * 100 >= (long long)ctas_at_once<HD, MMA_WARPS>(smem_plain) * 95;
 }
 
 template <int HD, int MMA_WARPS>
@@ -420,7 +454,8 @@ int launch(const void* q, long long q_stride, const void* k_pool, const void* v_
     const int G = nq / nkv;
     dim3 grid(n_splits, nkv * ((G + 7) / 8), B);
     *combined = 0;
-    if (out != nullptr && n_splits <= CLUSTER_MAX && cluster_fits<HD, MMA_WARPS>(smem_c)) {
+    if (out != nullptr && n_splits <= CLUSTER_MAX &&
+        merge_in_clusters<HD, MMA_WARPS>(smem, smem_c, n_splits, (long long)grid.y * grid.z)) {
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = grid;
         cfg.blockDim = dim3(MMA_WARPS * 32);

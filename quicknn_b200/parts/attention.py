@@ -84,13 +84,17 @@ class AttentionMixer(Mixer):
         number with the shortest estimated time for the step's length classes (``step.longest``, ``step.spread``).
 
         A sequence's keys are cut into equal ranges, a block per (range, kv head, sequence).  While all blocks
-        fit the device at once the step takes as long as the longest sequence's range; with more blocks than
-        that they run in turns, and the time is the work of all blocks spread over the device plus about half a
-        block at the end.  A block costs about as much as 64 keys before its first key, and more than four
-        ranges are merged by a kernel of its own, which costs about as much as a hundred.  Measured at head size 256: context 8192, equal lengths, batch 64 one range 9.48 ms
-        against two 9.69, batch 32 two ranges, batch 16 four, batch 8 nine; batch 64 with prompts of 512 to
-        2048 tokens one range 4.20 ms, four 4.03, six 3.90, nine 4.12 (the longest sequence no longer sets the
-        pace).  Results differ between these choices by rounding only: ranges are summed in a fixed order."""
+        fit the device at once the step takes as long as the longest sequence's range.  With more blocks than
+        that they run in turns: blocks of one length (sequences of nearly equal lengths) in whole rounds, each as
+        long as a block; blocks of unequal lengths fill the device evenly, and the time is the work of all blocks
+        spread over the device plus about half a block at the end.  A block costs about as much as 64 keys before
+        its first key, and more than four ranges are merged by a kernel of its own, which costs about as much as a
+        hundred.  Measured at head size 256, context 8192, equal lengths, 6 layers, ms per step by ranges: batch 24:
+        2: 1.32, 3: 1.08, 4: 1.34, 5: 1.20, 6: 1.11, 8: 1.18 (one round of 288 blocks, then 2, 2, 2 and 3 rounds);
+        batch 28: 2: 1.34, 3: 1.60, 5: 1.23, 6: 1.39; batch 12: 4: 0.91, 5: 0.85, 6: 0.81, 8: 0.94; batch 64 one
+        range 9.48 ms (26 layers) against two 9.69 and eight 8.42; batch 64 with prompts of 512 to 2048 tokens one
+        range 4.20 ms, four 4.03, six 3.90, nine 4.12 (the longest sequence no longer sets the pace).  Results
+        differ between these choices by rounding only: ranges are summed in a fixed order."""
         fixed = step.tuning.get("decode_splits")
         if fixed:
             return int(fixed)
@@ -101,9 +105,12 @@ class AttentionMixer(Mixer):
         most = max(1, min(64, longest // 32))
         mean = longest / (step.spread or 1.0)
         best, best_time = 1, float("inf")
+        equal = (step.spread or 1.0) <= 1.0
         for s in range(1, most + 1):                 # times in keys of one block's walk
             if s * tiles <= self._resident:
                 t = longest / s + BLOCK_COST
+            elif equal:                              # blocks of one length run in rounds
+                t = -(-s * tiles // self._resident) * (longest / s + BLOCK_COST)
             else:
                 t = tiles * (mean + s * BLOCK_COST) / self._resident + longest / (2 * s)
             if s > 4:

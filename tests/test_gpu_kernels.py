@@ -564,6 +564,33 @@ def test_attention_decode(ops, dtype, nq, nkv, hd, window, cap, splits):
     assert float(out[-1].abs().sum()) == 0.0                                  # the padding row attends to nothing
 
 
+@pytest.mark.parametrize("splits", [2, 3, 4])
+def test_attention_decode_with_more_clusters_than_the_device_holds(ops, splits):
+    """30 sequences x 4 kv heads at head size 256: 120 clusters of 3 CTAs do not fit the device at once, so the
+    key ranges go through the scratch and the merge kernel; with 2 and 4 ranges they merge inside the clusters.
+    The same numbers either way."""
+    rng = np.random.default_rng(splits)
+    nq, nkv, hd, B = 8, 4, 256, 30
+    lens = [int(n) for n in rng.integers(1, 190, B)]
+    k = [bf16_round(rng.normal(size=(n, nkv, hd))) for n in lens]
+    v = [bf16_round(rng.normal(size=(n, nkv, hd))) for n in lens]
+    q = bf16_round(rng.normal(size=(B, nq, hd)))
+    tables = [[3 * b + 2, 3 * b, 3 * b + 1] for b in range(B)]
+    k_pool, v_pool = _fill_cache(k, v, tables, torch.bfloat16, 3 * B, 0)
+    qkv = np.zeros((B, (nq + 2 * nkv) * hd))
+    qkv[:, :nq * hd] = q.reshape(B, -1)
+    part_o = torch.empty(B * nq * splits * hd, device=DEV)
+    part_ml = torch.empty(B * nq * splits * 2, device=DEV)
+    out = ops.attn_decode(T(qkv, torch.bfloat16), nq, nkv, hd, k_pool, v_pool, T(np.array(tables, np.int32), torch.int32),
+                          64, 0, T(np.arange(B, dtype=np.int32), torch.int32), T(np.array(lens, np.int32), torch.int32),
+                          1.0 / 16, 50.0, None, splits, part_o, part_ml)
+    for b, n in enumerate(lens):
+        qq = np.zeros((n, nq, hd))
+        qq[-1] = q[b]
+        ref = P.attention(qq, k[b], v[b], 1.0 / 16, 50.0, None)[-1].reshape(-1)
+        assert_close(out[b], ref, torch.bfloat16, f"decode attention row {b}", mult=4)
+
+
 @pytest.mark.parametrize("dtype,nq,nkv,hd,tensor_cores", [
     (torch.float32, 4, 2, 16, False), (torch.bfloat16, 6, 1, 24, False), (torch.bfloat16, 8, 4, 64, True),
     (torch.bfloat16, 4, 2, 128, True), (torch.bfloat16, 8, 4, 256, True), (torch.bfloat16, 8, 4, 256, False)])

@@ -35,13 +35,18 @@ def test_length_classes_are_coarse_and_bound_the_longest_sequence():
     assert len(seen) == 2
 
 
-def test_key_ranges_at_equal_lengths_keep_one_round_of_blocks():
-    """What was measured at context 8192 with equal lengths: batch 1 takes 64 ranges, 8 nine, 16 four, 32 two."""
+def test_key_ranges_at_equal_lengths_fill_whole_rounds_of_blocks():
+    """What was measured at context 8192 with equal lengths: batch 1 takes 64 ranges, 8 nine, 12 six, 24 three (one
+    round of blocks each); 28 sequences take five ranges (two rounds of 560 blocks on 296 places: faster than
+    one round of two long ranges, while six ranges would need a third round)."""
     m = mixer()
-    got = {b: m.decode_splits(step(b, 8192, 1.0)) for b in (1, 2, 4, 8, 12, 16, 32)}
-    assert got == {1: 64, 2: 37, 4: 18, 8: 9, 12: 6, 16: 4, 32: 2}
-    # all blocks fit the device at once in each of these
-    assert all(s * b * 4 <= 296 for b, s in got.items())
+    got = {b: m.decode_splits(step(b, 8192, 1.0)) for b in (1, 2, 4, 8, 12, 16, 24, 28, 32)}
+    assert got == {1: 64, 2: 37, 4: 18, 8: 9, 12: 6, 16: 9, 24: 3, 28: 5, 32: 9}
+    # all blocks fit the device at once up to 12 sequences and at 24
+    assert all(got[b] * b * 4 <= 296 for b in (1, 2, 4, 8, 12, 24))
+    # whole rounds: 16 x 4 x 9 = 576 blocks are two rounds of 296 places, 32 x 4 x 9 four
+    assert -(-16 * 4 * 9 // 296) == 2 and -(-32 * 4 * 9 // 296) == 4
+    assert {b: m.decode_splits(step(b, 2048, 1.0)) for b in (16, 32, 64)} == {16: 4, 32: 2, 64: 1}
     # a windowed layer sees at most its window
     assert mixer(window=4096).decode_splits(step(8, 8192, 1.0)) == 9
     assert mixer(window=128).decode_splits(step(8, 8192, 1.0)) == 4
