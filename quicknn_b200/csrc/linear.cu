@@ -75,8 +75,16 @@ __device__ __forceinline__ uint4 ldg16_early(const bf16* p) {
     return v;
 }
 
+// Blocks per SM that the compiler has to leave room for.  The 16-warp kernels for 9 to 16 rows took 70 to 79
+// registers, so one block of 512 threads filled an SM and the 256 blocks of a q|k|v product ran in two rounds (its
+// share of a decode step of 10 rows: 10.4 us, with two blocks per SM 6.3); the kernels for 17 rows and more measured
+// 2 us a layer faster when told that one block per SM is enough; the others are fastest left to the compiler (an
+// explicit 1 cost the 8-row step 9 %).
+template <int NT, int NW>
+constexpr int skinny_min_blocks() { return (NW == 16 && NT >= 2) ? 2 : (NT >= 4 ? 1 : 0); }
+
 template <int NT, int EPI, int NW>
-__global__ void __launch_bounds__(NW * 32) skinny_bf16_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W,
+__global__ void __launch_bounds__(NW * 32, skinny_min_blocks<NT, NW>()) skinny_bf16_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W,
                                                           void* __restrict__ out, int out_dt, int M, int N, int K,
                                                           float cap, int act, const RopeEpi rp, int* __restrict__ err) {
     constexpr int COLS = NT * 8;
