@@ -329,7 +329,7 @@ GEMM_2CTA = os.environ.get("QNN_GEMM_2CTA", "1") != "0"
 
 
 def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, *, epilogue: int = EPI_NONE, activation: str = "gelu_tanh",
-                 pair: Optional[bool] = None):
+                 pair: Optional[bool] = None, out: Optional[torch.Tensor] = None):
     """x w^T for whole prompts on the 5th-generation tensor cores (bfloat16, any M; K a multiple of 8).
     Epilogues: none, or gated (w = [gate; up] stacked).  With more than 128 rows pairs of CTAs
     compute 256 x 256 tiles (``pair``; QNN_GEMM_2CTA=0 keeps one CTA per tile).  Returns None when
@@ -341,7 +341,12 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, *, epilogue: int = EPI_NONE, 
     if epilogue not in (EPI_NONE, EPI_GATED) or K % 8 or w.shape[1] != K:
         return None
     n_out = N // 2 if epilogue == EPI_GATED else N
-    out = torch.empty((M, n_out), dtype=torch.bfloat16, device=x.device)
+    if out is None:
+        out = torch.empty((M, n_out), dtype=torch.bfloat16, device=x.device)
+    else:
+        _req(out, "out", torch.bfloat16, 2)
+        if tuple(out.shape) != (M, n_out):
+            raise ValueError(f"gemm_tcgen05: out is {tuple(out.shape)}, the product [{M}, {n_out}]")
     L = _lib.load()
     if pair is None:
         pair = GEMM_2CTA and M > 128
@@ -360,7 +365,7 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, *, epilogue: int = EPI_NONE, 
 
 
 def gemm_skinny_tcgen05(x: torch.Tensor, w: torch.Tensor, *, epilogue: int = EPI_NONE, cap: Optional[float] = None,
-                        activation: str = "gelu_tanh"):
+                        activation: str = "gelu_tanh", out: Optional[torch.Tensor] = None):
     """x w^T for up to 128 rows: TMA + tcgen05 with K split over a thread-block cluster and summed
     through distributed shared memory.  Epilogues: none (bfloat16), softcap (float32), gated.
     Returns None when the sizes are refused."""
@@ -371,7 +376,13 @@ def gemm_skinny_tcgen05(x: torch.Tensor, w: torch.Tensor, *, epilogue: int = EPI
     if M > 128 or K % 8 or w.shape[1] != K:
         return None
     n_out = N // 2 if epilogue == EPI_GATED else N
-    out = torch.empty((M, n_out), dtype=torch.float32 if epilogue == EPI_SOFTCAP else torch.bfloat16, device=x.device)
+    out_dtype = torch.float32 if epilogue == EPI_SOFTCAP else torch.bfloat16
+    if out is None:
+        out = torch.empty((M, n_out), dtype=out_dtype, device=x.device)
+    else:
+        _req(out, "out", out_dtype, 2)
+        if tuple(out.shape) != (M, n_out):
+            raise ValueError(f"gemm_skinny_tcgen05: out is {tuple(out.shape)}, the product [{M}, {n_out}]")
     L = _lib.load()
     code = L.qnn_gemm_skinny_tcgen05(_p(x), _p(w), _p(out), M, N, K, epilogue, float(cap or 0.0),
                                      ACT_CODES[activation], _p(_status_word(x.device)), _stream())
@@ -394,6 +405,39 @@ SKINNY_TCGEN05_ANY_FROM = 32          # from this many rows on, the small matric
 def _takes_skinny_tcgen05(M: int, N: int, K: int) -> bool:
     return USE_TCGEN05 and SKINNY_TCGEN05_FROM <= M <= 128 and (M >= SKINNY_TCGEN05_ANY_FROM or
                                                                 N * K >= SKINNY_TCGEN05_MIN_WEIGHTS)
+
+
+_SM_COUNT: dict = {}
+
+
+def _rows_for_the_small_kernel(M: int, n_out: int, K: int, epilogue: int, device) -> int:
+    """How many of the last rows of a whole-prompt product go to the kernel for few rows instead (0: none).
+
+    The prompt kernel works in 256 x 256 tiles (256 x 128 outputs when gated), a pair of SMs per tile, so its time
+    goes up by a round of tiles when the tile count passes a multiple of the pairs.  Measured for the down product
+    (2304 x 9216): 2048 rows (72 tiles on 74 pairs) 58 us, 2049 rows 92 us, 4096 / 4097 rows 114 / 140 us, 6144 /
+    6145 rows 175 / 212 us: a round that only a few tiles open costs about 0.6 of a tile's time.  The kernel for few
+    rows takes the weights' bytes once more plus 5 us up to 32 rows and 9 us up to 64 (2049 rows: 66 us together, 4097:
+    123, 6145: 179); with more rows it costs what the round does (2200 rows in two launches: 90 against 92 us), and
+    for the matrices with a short inner size the round is cheap, so only up to 64 rows are cut off, and only where
+    the round costs well more than they do."""
+    if not GEMM_2CTA or M <= 256:
+        return 0
+    tail = M % 256
+    if tail == 0 or tail > 64:
+        return 0
+    key = str(device)
+    if key not in _SM_COUNT:
+        _SM_COUNT[key] = torch.cuda.get_device_properties(device).multi_processor_count if device.type == "cuda" else 148
+    pairs = max(1, _SM_COUNT[key] // 2)
+    per_row_tile = -(-n_out // (128 if epilogue == EPI_GATED else 256))
+    rounds = lambda m_tiles: -(-m_tiles * per_row_tile // pairs)          # noqa: E731
+    if rounds(-(-M // 256)) == rounds(M // 256):
+        return 0
+    weights = n_out * (2 if epilogue == EPI_GATED else 1) * K
+    round_us = 0.6 * 2.0 * 256 * 256 * K / 22.0e6                # a tile at a pair's share of 1.6 PFLOP/s
+    small_us = 2.0 * weights / 6.5e6 + (5.0 if tail <= 32 else 9.0)
+    return tail if round_us > 1.5 * small_us else 0
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, *, epilogue: int = EPI_NONE, cap: Optional[float] = None,
@@ -451,6 +495,16 @@ def linear(x: torch.Tensor, w: torch.Tensor, *, epilogue: int = EPI_NONE, cap: O
         return out
     if USE_TCGEN05:
         if epilogue in (EPI_NONE, EPI_GATED) and out_dtype == torch.bfloat16:
+            tail = _rows_for_the_small_kernel(M, n_out, K, epilogue, x.device)
+            if tail:
+                # the last rows would open one more round of 256 x 256 tiles: they go to the kernel for few rows
+                head = M - tail
+                out = torch.empty((M, n_out), dtype=out_dtype, device=x.device)
+                ok = (gemm_tcgen05(x[:head], w, epilogue=epilogue, activation=activation, out=out[:head]) is not None
+                      and gemm_skinny_tcgen05(x[head:], w, epilogue=epilogue, activation=activation,
+                                              out=out[head:]) is not None)
+                if ok:
+                    return out
             y = gemm_tcgen05(x, w, epilogue=epilogue, activation=activation)
             if y is not None:
                 return y

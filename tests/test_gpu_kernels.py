@@ -208,6 +208,29 @@ def test_tcgen05_product(ops, M, N_, K, pair):
                             torch.zeros(8, 12, dtype=torch.bfloat16, device=DEV)) is None      # refused, not wrong
 
 
+@pytest.mark.parametrize("M", [2049, 2110])
+def test_rows_that_would_open_another_round_of_tiles_go_to_the_small_kernel(ops, M):
+    """A product of 2049 or 2110 rows against [2304, 9216] is 81 tiles of 256 x 256 on 74 pairs of SMs: the rows
+    beyond 2048 are computed by the kernel for few rows, into the same output."""
+    N_, K = 2304, 9216
+    assert ops._rows_for_the_small_kernel(M, N_, K, ops.EPI_NONE, torch.device(DEV)) == M - 2048
+    assert ops._rows_for_the_small_kernel(2048, N_, K, ops.EPI_NONE, torch.device(DEV)) == 0
+    assert ops._rows_for_the_small_kernel(2200, N_, K, ops.EPI_NONE, torch.device(DEV)) == 0      # too many rows to gain
+    assert ops._rows_for_the_small_kernel(M, 4096, 2304, ops.EPI_NONE, torch.device(DEV)) == 0    # a cheap round stays
+    g = torch.Generator(device=DEV).manual_seed(M)
+    x = torch.randn(M, K, generator=g, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(N_, K, generator=g, device=DEV) / math.sqrt(K)).to(torch.bfloat16)
+    y = ops.linear(x, w)
+    torch.cuda.synchronize()
+    ops.check_gemm_status(DEV)
+    rows = [0, 1000, 2047, 2048, M - 1]
+    ref = N(x[rows].float()) @ N(w.float()).T
+    assert_close(y[rows], ref, torch.bfloat16, "rows on either side of the cut")
+    whole = ops.gemm_tcgen05(x, w)                               # the same product by the prompt kernel alone
+    assert float((y.float() - whole.float()).abs().max()) <= 0.02 * float(whole.float().abs().max())
+    assert torch.equal(y[:2048], whole[:2048])
+
+
 @pytest.mark.parametrize("M,N_,K", [(1, 128, 64), (17, 300, 96), (64, 256, 512), (128, 1000, 200), (33, 2304, 2048),
                                      (64, 130, 4160), (9, 24, 8)])
 def test_cluster_split_k_tcgen05_product(ops, M, N_, K):
