@@ -381,8 +381,9 @@ static int skinny_tcgen05(const void* A, const void* B, void* C, int M, int N, i
     while (KS < 8 && tiles * KS * 2 <= sm_count && nk / (KS * 2) >= 2) KS *= 2;      // the doubled grid still fits one round
     // Depth of the ring: what fits beside the receive buffer (128 x (min(NM, 64) + 4) floats) and the barriers, if the device
     // then holds all clusters at once (clusters of 8 CTAs with 217 KB each do not: 15 of them fit); else, and
-    // with several rounds of CTAs anyway, half of that, so that two CTAs share an SM (and one's set-up and
-    // epilogue hide behind the other's main loop).
+    // with more CTAs than SMs anyway, half of that, so that two CTAs share an SM (and one's set-up and
+    // epilogue hide behind the other's main loop).  The gate|up product of the 9B sizes is 224 tiles: with an SM
+    // to each CTA they ran in two rounds, 49.6 us in a step of 10 rows where the weights' traffic needs 31.6.
     const int stage_bytes = W_BYTES + NM * BK * 2;
     const int part_bytes = BW * ((NM < RECV_COLS ? NM : RECV_COLS) + 4) * 4;
     const int recv_bytes = KS > 1 ? part_bytes : 0;
@@ -403,7 +404,7 @@ static int skinny_tcgen05(const void* A, const void* B, void* C, int M, int N, i
     int stages = depth(227);
     if (force_kib > 0) {
         stages = depth(force_kib);
-    } else if (tiles * KS > 2ll * sm_count) {
+    } else if (tiles * KS > (long long)sm_count) {
         stages = depth(113);
     } else if (KS > 1) {
         static int fits[4][MAX_STAGES + 1];                // clusters of 2^i CTAs that the device holds, by depth (0: not asked)
