@@ -75,3 +75,15 @@ def test_key_ranges_stay_within_what_the_kernels_take(n_kv, hd, resident):
             for spread in (1.0, 1.25, 1.6, 2.2):
                 s = m.decode_splits(step(b, longest, spread))
                 assert 1 <= s <= 64 and s <= max(1, longest // 32)
+
+
+def test_rows_cut_off_a_prompt_product_only_where_a_round_of_tiles_is_saved():
+    """The decision is a host function of the sizes: at the 2B layer sizes only the down product (inner size 9216),
+    only just beyond a multiple of 2048 rows (72 -> 81 tiles of 256 x 256 on 74 pairs of SMs), and only up to 64 rows."""
+    import torch
+    from quicknn_b200.kernels import ops
+    cpu = torch.device("cpu")                         # stands for 148 SMs
+    down = lambda m: ops._rows_for_the_small_kernel(m, 2304, 9216, ops.EPI_NONE, cpu)            # noqa: E731
+    assert [down(m) for m in (2048, 2049, 2112, 2113, 2304, 4096, 4097, 6145, 257, 100)] == [0, 1, 64, 0, 0, 0, 1, 1, 0, 0]
+    for n_out, k, epi in ((4096, 2304, ops.EPI_NONE), (2304, 2048, ops.EPI_NONE), (9216, 2304, ops.EPI_GATED)):
+        assert all(ops._rows_for_the_small_kernel(m, n_out, k, epi, cpu) == 0 for m in (2049, 4097, 6145, 8193))
