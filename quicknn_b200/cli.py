@@ -8,6 +8,7 @@ Examples/LLMChat/QuickNN.LLMChat.Settings.pas:38).
     python -m quicknn_b200 random   --config config.json --seed 0 --out DIR
     python -m quicknn_b200 replay   --model DIR --dtype float32 --out DIR --max-tokens 4096 < trace.jsonl
     python -m quicknn_b200 info     --model DIR
+    python -m quicknn_b200 chat     --model DIR          # a conversation over token ids: /new /memory /help /exit
 """
 from __future__ import annotations
 
@@ -94,6 +95,109 @@ def cmd_generate(args) -> int:
     return 0
 
 
+CHAT_HELP = ("/new: a new conversation, /memory: what the device holds, /help: this text, /exit: leave.  "
+             "A line of token ids (\"5, 17, 3\") is a turn; Ctrl+C stops the reply that is being written; "
+             "the history is cleared by /new only.")
+
+
+class ChatSession:
+    """The loop of the reference's chat console (Examples/LLMChat/QuickNNChat.dpr:126-205) over token ids instead
+    of text: a line is a command or a turn; a turn is appended to what was said so far and answered, the answer's
+    ids are written as they come, then a line of figures as the reference prints it (tokens, seconds, decode
+    tokens per second, time to the first token, tokens said so far, tokens of the prompt found in the cache).  An
+    error while answering drops the turn and starts the cache anew, as the reference does."""
+
+    def __init__(self, llm, options, stop_ids, write, interrupted=lambda: False):
+        self.llm, self.options, self.stop_ids = llm, options, stop_ids
+        self.write, self.interrupted = write, interrupted
+        self.chat = llm.conversation()
+        self.said: List[int] = []
+
+    def close(self) -> None:
+        self.chat.close()
+
+    def handle(self, line: str) -> bool:
+        """One line of input; False when the session is over."""
+        import time
+        text = line.strip()
+        if not text:
+            return True
+        command = text.lower()
+        if command == "/exit":
+            return False
+        if command == "/help":
+            self.write(CHAT_HELP + "\n")
+            return True
+        if command == "/memory":
+            self.write(json.dumps(self.llm.memory_status()) + "\n")
+            return True
+        if command == "/new":
+            self.chat.reset()
+            self.said = []
+            self.write("a new conversation\n")
+            return True
+        if text.startswith("/"):
+            self.write(f"unknown command {text.split()[0]}; " + CHAT_HELP + "\n")
+            return True
+        try:
+            turn = [int(x) for x in text.replace(",", " ").split()]
+        except ValueError:
+            self.write("a turn is a line of token ids, for instance: 5, 17, 3\n")
+            return True
+        start = time.perf_counter()
+        try:
+            r = self.chat.generate(self.said + turn, self.options, stop_ids=self.stop_ids,
+                                   on_token=lambda _, tok: self.write(f"{tok} "), should_cancel=self.interrupted)
+        except Exception as e:                       # the turn is dropped and the cache starts anew
+            self.write(f"\n{type(e).__name__}: {e}\n")
+            self.chat.reset()
+            self.said = []
+            return True
+        self.said = self.said + turn + list(r.tokens)
+        self.write(f"\n[{r.generated_tokens} tokens; {time.perf_counter() - start:.2f} s; decode: "
+                   f"{r.decode_tokens_per_second():.1f} tokens/s; first token: {r.time_to_first_token_seconds:.3f} s; "
+                   f"said so far: {len(self.said)}; reused: {r.reused_tokens}; {r.finish_reason}]\n")
+        return True
+
+
+def cmd_chat(args) -> int:
+    import signal
+    import torch
+    from .engine import LLM
+    from .sampling import GenerationOptions
+    if not torch.cuda.is_available():
+        print("chat: no CUDA device; quicknn_b200 has no CPU path", file=sys.stderr)
+        return 3
+    opts = GenerationOptions(max_new_tokens=args.max_new_tokens, hard_max_new_tokens=args.hard_max_new_tokens,
+                             top_k=args.top_k, auto_continue=args.auto_continue, temperature=args.temperature,
+                             top_p=args.top_p, repetition_penalty=args.repetition_penalty, seed=args.seed)
+    opts.validate()
+    llm = LLM(args.model, max_context=args.max_context, max_batch=1, dtype=args.dtype, device=args.device)
+    stops = None if args.stop_ids is None else [int(x) for x in args.stop_ids.replace(",", " ").split()]
+    state = {"interrupted": False}
+
+    def write(text: str) -> None:
+        sys.stdout.write(text)
+        sys.stdout.flush()
+
+    status = llm.memory_status()
+    write(f"model: {args.model}\ncache: {status['cache_bytes'] / 1048576.0:.1f} MiB; context: {args.max_context} tokens\n")
+    write(CHAT_HELP + "\n")
+    session = ChatSession(llm, opts, stops, write, lambda: state["interrupted"])
+    previous = signal.signal(signal.SIGINT, lambda *_: state.__setitem__("interrupted", True))
+    try:
+        while True:
+            state["interrupted"] = False
+            write("> ")
+            line = sys.stdin.readline()
+            if not line or not session.handle(line):
+                break
+    finally:
+        signal.signal(signal.SIGINT, previous)
+        session.close()
+    return 0
+
+
 def cmd_random(args) -> int:
     import torch
     from .config.base import find_architecture
@@ -153,6 +257,23 @@ def main(argv=None) -> int:
     g.add_argument("--profile", action="store_true",
                    help="time every step and every kind of part with CUDA events (steps then run eagerly) and print a table")
     g.set_defaults(fn=cmd_generate)
+
+    c = sub.add_parser("chat", help="a conversation over token ids, read line by line: /new /memory /help /exit",
+                       allow_abbrev=False)
+    c.add_argument("--model", required=True)
+    c.add_argument("--max-new-tokens", type=int, default=256)
+    c.add_argument("--hard-max-new-tokens", type=int, default=4096)
+    c.add_argument("--auto-continue", action="store_true")
+    c.add_argument("--top-k", type=int, default=20)
+    c.add_argument("--temperature", type=float, default=0.6)
+    c.add_argument("--top-p", type=float, default=0.95)
+    c.add_argument("--repetition-penalty", type=float, default=1.0)
+    c.add_argument("--seed", type=int, default=42)
+    c.add_argument("--stop-ids", default=None, help="override the configuration's eos_token_id")
+    c.add_argument("--max-context", type=int, default=2048)
+    c.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16")
+    c.add_argument("--device", default="cuda:0")
+    c.set_defaults(fn=cmd_chat)
 
     r = sub.add_parser("random", help="write a model folder with random weights", allow_abbrev=False)
     r.add_argument("--config", required=True)

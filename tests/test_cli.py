@@ -101,3 +101,101 @@ def test_generate_prints_what_the_plain_model_generates(folders, plain_models, t
         assert r["reused_tokens"] in (max(0, len(said) - 1), len(said))       # all that was said, but for a reply's last token
         said = said + turn + r["tokens"]
 
+
+
+class _FakeConversation:
+    def __init__(self, log):
+        self.log, self.held = log, []
+
+    def reset(self):
+        self.log.append("reset")
+        self.held = []
+
+    def close(self):
+        self.log.append("close")
+
+    def generate(self, prompt, options, on_token=None, stop_ids=None, should_cancel=None):
+        from quicknn_b200.engine.generate import GenerationResult
+        if prompt[-1] == 666:
+            raise RuntimeError("the device said no")
+        reused = 0
+        while reused < min(len(self.held), len(prompt) - 1) and self.held[reused] == prompt[reused]:
+            reused += 1
+        r = GenerationResult(index=0, prompt_tokens=len(prompt))
+        for t in (prompt[-1] + 1, prompt[-1] + 2):
+            if should_cancel is not None and should_cancel():
+                break
+            r.tokens.append(t)
+            on_token(0, t)
+        r.finish_reason = "max_tokens"
+        r.reused_tokens = reused
+        self.held = list(prompt) + r.tokens
+        self.log.append(("generate", list(prompt), stop_ids))
+        return r
+
+
+class _FakeLLM:
+    def __init__(self):
+        self.log = []
+
+    def conversation(self):
+        return _FakeConversation(self.log)
+
+    def memory_status(self):
+        return {"weight_bytes": 10, "cache_bytes": 20}
+
+
+def test_the_chat_loop_takes_commands_and_turns():
+    """``chat`` without a model: commands, turns that carry the history, an error that drops the turn and
+    starts anew, a reply that is interrupted, the figures after a reply."""
+    from quicknn_b200.cli import CHAT_HELP, ChatSession
+    out, stop = [], {"now": False}
+    llm = _FakeLLM()
+    s = ChatSession(llm, None, [1], out.append, lambda: stop["now"])
+    assert s.handle("\n") and s.handle("/help\n") and out[-1].startswith(CHAT_HELP)
+    assert s.handle("/memory") and json.loads(out[-1]) == {"weight_bytes": 10, "cache_bytes": 20}
+    assert s.handle("/nonsense") and out[-1].startswith("unknown command /nonsense")
+    assert s.handle("five six") and "token ids" in out[-1]
+    assert llm.log == []
+    out.clear()
+    assert s.handle("5, 17 3\n")
+    assert llm.log[-1] == ("generate", [5, 17, 3], [1])
+    assert out[:2] == ["4 ", "5 "] and "[2 tokens;" in out[-1] and "reused: 0; max_tokens]" in out[-1]
+    assert s.handle("9")                                                   # the next turn carries what was said
+    assert llm.log[-1] == ("generate", [5, 17, 3, 4, 5, 9], [1]) and "said so far: 8; reused: 5;" in out[-1]
+    assert s.handle("666") and "RuntimeError: the device said no" in out[-1] and llm.log[-1] == "reset"
+    assert s.handle("7") and llm.log[-1] == ("generate", [7], [1])         # the history went with the failed turn
+    assert s.handle("/NEW") and llm.log[-1] == "reset" and out[-1] == "a new conversation\n"
+    stop["now"] = True
+    out.clear()
+    assert s.handle("3") and "[0 tokens;" in out[-1]                         # interrupted before the first token
+    assert not s.handle(" /exit ")
+    s.close()
+    assert llm.log[-1] == "close"
+
+
+@pytest.mark.gpu
+def test_chat_answers_turns_as_the_plain_model_does(folders, plain_models):
+    """``chat`` on a tiny model, its lines from standard input: two turns of one conversation, /memory, /new, the
+    first turn again (the same reply), /exit; every reply is the plain model's for everything said so far."""
+    import re
+    import torch
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    folder = folders("A", "float32")
+    plain = plain_models("A", "float32")
+    first, second = prompts_for("A", [6, 3], seed=8)
+    lines = [", ".join(map(str, first)), " ".join(map(str, second)), "/memory", "/new", ",".join(map(str, first)), "/exit",
+             "5, 5"]
+    p = run("chat", "--model", folder, "--max-new-tokens", "5", "--temperature", "0", "--dtype", "float32",
+            "--max-context", "64", "--stop-ids", "", stdin="\n".join(lines) + "\n")
+    assert p.returncode == 0, p.stderr
+    replies = re.findall(r"> ((?:\d+ )+)\n\[(\d+) tokens; .*?reused: (\d+); (\w+)\]", p.stdout)
+    assert len(replies) == 3, p.stdout
+    a = plain.greedy(first, 5)
+    b = plain.greedy(first + a + second, 5)
+    assert [int(t) for t in replies[0][0].split()] == a and replies[0][1:] == ("5", "0", "max_tokens")
+    assert [int(t) for t in replies[1][0].split()] == b and int(replies[1][2]) >= len(first) + len(a) - 1
+    assert [int(t) for t in replies[2][0].split()] == a and replies[2][2] == "0"       # /new forgot the history
+    assert '"cache_bytes"' in p.stdout and "a new conversation" in p.stdout
+    assert p.stdout.count("> ") == 6                                                  # six lines are read, none after /exit
